@@ -1,0 +1,235 @@
+/*
+ * tqb200 — C ABI of the B200-native compressed-KV hot path (append/encode + decode-on-codes
+ * attention) that sits behind TurboQuant Pro's TurboQuantKVCache.
+ *
+ * The reference has no C ABI on this path: its boundary is the Python class
+ * TurboQuantKVCache (turboquant_pro/core.py:818-1307), the two stateless quantisers it
+ * wires together (turboquant_pro/per_channel_kv.py:146-539 for keys,
+ * turboquant_pro/core.py:139-654 for values) and the launch signature of its fused CuPy
+ * kernel (turboquant_pro/kv_kernel.py:255-381).  Every entry point below names the
+ * reference method(s) it replaces.
+ *
+ * Conventions
+ *  - Plain C.  Every function returns an int32 status: TQ_OK (0) or a negative TQ_ERR_*.
+ *    No exception crosses the boundary; tq_last_error() gives a message for the calling
+ *    thread's most recent failure.
+ *  - The library allocates NO device memory.  The caller asks tq_ctx_sizes() how many
+ *    bytes each region needs, allocates them (cudaMalloc, a torch tensor, an arena ...)
+ *    and hands the device pointers to tq_ctx_create().  The regions must stay alive until
+ *    tq_ctx_destroy() and must be zero-filled before tq_ctx_create().
+ *  - `stream` arguments are cudaStream_t passed as void*; NULL is the legacy default
+ *    stream.  All device work of a call is enqueued on that stream and the call returns
+ *    without synchronising unless it says otherwise.
+ *  - A context is not thread-safe; use one per thread or serialise calls.  Contexts on
+ *    different devices are independent.
+ *  - One context holds n_layers x n_seqs independent two-tier caches (one reference
+ *    TurboQuantKVCache each) that share geometry, rotation and codebooks.
+ */
+#ifndef TQB200_H
+#define TQB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_VERSION 100
+
+enum {
+  TQ_OK = 0,
+  TQ_ERR_INVALID = -1,      /* bad argument (shape, range, null pointer)            */
+  TQ_ERR_UNSUPPORTED = -2,  /* geometry the kernels do not implement                 */
+  TQ_ERR_CUDA = -3,         /* a CUDA runtime call failed; see tq_last_error()       */
+  TQ_ERR_CAPACITY = -4,     /* append beyond max_tokens_per_seq or a full outlier pool */
+  TQ_ERR_EMPTY = -5,        /* decode on a sequence with no tokens                   */
+  TQ_ERR_NO_DEVICE = -6     /* no CUDA device / wrong architecture                   */
+};
+
+/* element type of incoming K/V tokens, of the hot window that stores them, and of q */
+enum { TQ_F32 = 0, TQ_F16 = 1, TQ_BF16 = 2 };
+
+/* Geometry of a context.  Fill the first block, then call tq_geom_finish(), which
+ * validates it and derives the rest. */
+typedef struct tq_geom {
+  /* --- caller-provided --------------------------------------------------------- */
+  int32_t n_layers;
+  int32_t n_seqs;
+  int32_t n_kv_heads;
+  int32_t n_q_heads;          /* multiple of n_kv_heads; q head i reads KV head i / G  */
+  int32_t head_dim;           /* 128                                                   */
+  int32_t key_bits;           /* 4 (asymmetric NF4)                                    */
+  int32_t value_bits;         /* 3 or 4                                                */
+  int32_t hot_window;         /* tokens kept uncompressed, 2..512                      */
+  int32_t kv_dtype;           /* TQ_F32 / TQ_F16 / TQ_BF16: tokens in, hot window      */
+  int32_t max_tokens_per_seq;
+  int32_t reserved0_;
+  double outlier_frac;        /* per-channel fp16 outlier fraction, 0 disables         */
+  /* --- derived by tq_geom_finish ------------------------------------------------ */
+  int32_t group;              /* G = n_q_heads / n_kv_heads                            */
+  int32_t block_tokens;       /* tokens per cold block = (hot_window + 1) / 2          */
+  int32_t block_tokens_pad;   /* block_tokens rounded up to a multiple of 16           */
+  int32_t hot_cap;            /* ring capacity: multiple of block_tokens > hot_window  */
+  int32_t max_blocks;         /* cold blocks per sequence at max_tokens_per_seq        */
+  int32_t outlier_k;          /* outliers kept per channel and block (before ties)     */
+  int32_t k_bytes;            /* page section sizes in bytes ...                       */
+  int32_t v_bytes;
+  int32_t v_off, norm_off, scale_off, mean_off;
+  int32_t page_bytes;         /* ... and the page stride (multiple of 128)             */
+  int32_t pool_entries;       /* outlier-pool entries per (layer, seq, kv head)        */
+  int32_t max_splits;         /* partial slots per (seq, kv head) in the scratch area  */
+  int32_t reserved_;
+} tq_geom;
+
+/* Byte sizes of the device regions a context needs. */
+typedef struct tq_sizes {
+  size_t pages;      /* cold pages                                   */
+  size_t hot_k;      /* hot-window rings of keys                     */
+  size_t hot_v;      /* hot-window rings of values                   */
+  size_t pool_dec;   /* outlier entries read by decode (4 B each)    */
+  size_t pool_val;   /* outlier fp16 values kept for export (2 B)    */
+  size_t page_meta;  /* per-page outlier offset/count                */
+  size_t state;      /* sequence lengths, pool cursors, status word  */
+  size_t tables;     /* rotation matrices, codebooks                 */
+  size_t scratch;    /* decode partials                              */
+} tq_sizes;
+
+/* Device pointers to the regions, each at least the size tq_ctx_sizes() reported and
+ * 256-byte aligned. */
+typedef struct tq_buffers {
+  void* pages;
+  void* hot_k;
+  void* hot_v;
+  void* pool_dec;
+  void* pool_val;
+  void* page_meta;
+  void* state;
+  void* tables;
+  void* scratch;
+} tq_buffers;
+
+typedef struct tq_ctx tq_ctx;
+
+/* Library version (TQ_VERSION). */
+int32_t tq_version(void);
+
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char* tq_last_error(void);
+
+/* Validates the caller-provided half of `g` and fills the derived half.
+ * Mirrors the constructor checks of TurboQuantKVCache.__init__ (core.py:886-969) and
+ * PerChannelKV.__init__ (per_channel_kv.py:195-227) for the supported format. */
+int32_t tq_geom_finish(tq_geom* g);
+
+/* Bytes of every device region for geometry `g` (after tq_geom_finish). */
+int32_t tq_ctx_sizes(const tq_geom* g, tq_sizes* out);
+
+/* Creates a context over caller-allocated, zero-filled device regions and uploads the
+ * tables.  `pi` is the D x D rotation (row-major, host, float32; value decode computes
+ * y @ pi), `pi_t` its transpose (value encode computes x @ pi_t), `centroids` the
+ * 2^value_bits direction codebook and `boundaries` its 2^value_bits - 1 bin edges —
+ * what TurboQuantKV.__init__ builds (core.py:229-260).  Synchronises `stream`. */
+int32_t tq_ctx_create(const tq_geom* g, const tq_buffers* bufs, int32_t device,
+                      const float* pi, const float* pi_t, const float* centroids,
+                      const float* boundaries, void* stream, tq_ctx** out);
+
+int32_t tq_ctx_destroy(tq_ctx* ctx);
+
+/* Appends `n_tokens` tokens to each of the sequences [seq_begin, seq_begin + seq_count)
+ * of `layer`, performing exactly the flushes the reference would perform had the tokens
+ * been appended one at a time: TurboQuantKVCache.append + _flush_to_cold
+ * (core.py:986-1038), i.e. PerChannelKV.compress (per_channel_kv.py:285-401) for keys
+ * and TurboQuantKV.compress(kind="value") (core.py:542-607) for values.
+ * `k`/`v` are device pointers of element type geom.kv_dtype; element (seq i, token t,
+ * head h, channel d) is at  base + (i - seq_begin)*seq_stride + t*tok_stride +
+ * h*head_stride + d  (strides in elements). */
+int32_t tq_append(tq_ctx* ctx, int32_t layer, int32_t seq_begin, int32_t seq_count,
+                  const void* k, const void* v, int32_t n_tokens, int64_t seq_stride,
+                  int64_t tok_stride, int64_t head_stride, void* stream);
+
+/* One decode step of attention for every sequence of `layer`, computed on the codes:
+ * TurboQuantKVCache.fused_decode (core.py:1168-1265), whose result equals
+ * get_keys/get_values + softmax(qK^T/sqrt(D))V.  `q` is [n_seqs][n_q_heads][D] of
+ * `q_dtype`; `out` is [n_seqs][n_q_heads][D] float32.  Sequences with no tokens get
+ * zeros.  Uses the context's scratch region, so two decodes of one context must not
+ * overlap on the device. */
+int32_t tq_decode(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype, float* out,
+                  void* stream);
+
+/* Sequence-split form of tq_decode for one long sequence spread over several devices:
+ * attends only cold blocks [block_begin, block_end) and, if `with_hot` is non-zero, the
+ * hot window, and writes the un-normalised state (m, l, o[D]) per query head to
+ * `mlo` ([n_seqs][n_q_heads][2 + D] float32) instead of the final output.  The states
+ * of all ranks, gathered rank-major, go to tq_lse_combine.  Generalises the per-page
+ * partials of PreparedPCKBlock.partials (kv_fused_pck.py:211-236). */
+int32_t tq_decode_partial(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype,
+                          int32_t block_begin, int32_t block_end, int32_t with_hot, float* mlo,
+                          void* stream);
+
+/* Log-sum-exp merge of `n_parts` gathered states: merge_partials (kv_fused.py:139-153).
+ * `mlo` is [n_parts][n_rows][2 + D] float32 (device), `out` [n_rows][D] float32. */
+int32_t tq_lse_combine(const float* mlo, int32_t n_parts, int32_t n_rows, int32_t head_dim,
+                       float* out, void* stream);
+
+/* Dequantised keys and values of tokens [start, end) of one sequence, float32
+ * [n_kv_heads][end - start][D] each (device pointers, either may be NULL):
+ * TurboQuantKVCache.get_keys / get_values (core.py:1040-1117), bit-identical to
+ * PerChannelKV.decompress (per_channel_kv.py:497-539) and TurboQuantKV.decompress
+ * (core.py:619-654). */
+int32_t tq_dequant_range(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t start, int32_t end,
+                         float* k_out, float* v_out, void* stream);
+
+/* Copies cold block `block` of (layer, seq) to HOST arrays in the reference's container
+ * layout (CompressedPerChannelKV, per_channel_kv.py:103-143; CompressedKV,
+ * core.py:96-136) for all KV heads: key_indices [H*S*D/2] (bit-reversed nibbles of
+ * _pack_indices, per_channel_kv.py:87-93), nf4_scale/nf4_mean [H*D], outlier_idx
+ * (ascending flat index into (H,S,D)) and outlier_val (fp16 bits) with capacity
+ * `outlier_cap` (count returned in *n_outliers), value_indices (_pack_bits_cpu layout,
+ * core.py:350-398) and value_norms [H*S].  Synchronises `stream`. */
+int32_t tq_export_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
+                        uint8_t* key_indices, float* nf4_scale, float* nf4_mean,
+                        int32_t* outlier_idx, uint16_t* outlier_val, int32_t outlier_cap,
+                        int32_t* n_outliers, uint8_t* value_indices, float* value_norms,
+                        void* stream);
+
+/* Tokens currently held by (layer, seq): total, in cold blocks, in the hot window
+ * (TurboQuantKVCache.length / cold_length / hot_length, core.py:971-984). */
+int32_t tq_seq_lengths(const tq_ctx* ctx, int32_t layer, int32_t seq, int32_t* total,
+                       int32_t* cold, int32_t* hot);
+
+/* Bytes held by (layer, seq) counted like the reference's containers
+ * (TurboQuantKVCache.memory_stats, core.py:1267-1296); needs the outlier counts, so it
+ * synchronises `stream`. */
+int32_t tq_memory_stats(tq_ctx* ctx, int32_t layer, int32_t seq, double* cold_bytes,
+                        double* hot_bytes, void* stream);
+
+/* Empties (layer, seq) — TurboQuantKVCache.clear (core.py:1298-1307); seq = -1 clears
+ * every sequence of the layer. */
+int32_t tq_clear(tq_ctx* ctx, int32_t layer, int32_t seq, void* stream);
+
+/* Reads and clears the device status word (bit 0: an outlier pool overflowed and a block
+ * kept a truncated side-list).  Synchronises `stream`. */
+int32_t tq_status(tq_ctx* ctx, int32_t* flags, void* stream);
+
+/* Algorithmic bytes one tq_decode of `layer` reads (reference container sizes of every
+ * cold block + the hot windows + q and out), for roofline accounting. */
+int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes);
+
+/* Number of kernels the most recent tq_decode / tq_append of this context launched. */
+int32_t tq_last_launches(const tq_ctx* ctx);
+
+/* Per-kernel timing for benchmarks (no counterpart in the reference, whose harnesses time
+ * whole calls with time.perf_counter, benchmarks/p5_triton_bench.py:72-82).  While enabled,
+ * tq_decode brackets its attention kernel and its combine kernel with CUDA events on the
+ * launch stream (up to 4096 calls between reads). */
+int32_t tq_profile_enable(tq_ctx* ctx, int32_t on);
+
+/* Synchronises the recorded events and returns the summed attention-kernel and
+ * combine-kernel milliseconds and the number of tq_decode calls they cover; resets. */
+int32_t tq_profile_read(tq_ctx* ctx, double* attn_ms, double* combine_ms, int32_t* n_calls);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQB200_H */

@@ -1,0 +1,342 @@
+"""GPU parity tests: every call goes through the C ABI (via the ctypes binding) and is
+compared with the reference fixtures and with the CPU oracle on the same seeded inputs.
+
+Bars: emitted codes, scales, means, outlier lists, norms and the dequantised getters are
+bit-exact; attention outputs are within rtol 2e-2 / atol 2e-3 of dequantise-then-attend.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from conftest import load_golden
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 2e-2, 2e-3
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    return torch
+
+
+def _ctx(**kw):
+    from turboquant_pro_b200 import KVContext
+
+    return KVContext(**kw)
+
+
+def _np_dtype_name(a):
+    return "float16" if a.dtype == np.float16 else "float32"
+
+
+def _dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _oracle(h, vb, w, pi, k, v, frac=0.02):
+    from oracle import tq_oracle as orc
+
+    c = orc.OracleCache(128, h, 4, vb, w, frac, 0)
+    c.pi, c.pi_t = pi, np.ascontiguousarray(pi.T)
+    for t in range(k.shape[0]):
+        c.append(k[t], v[t])
+    return c
+
+
+def _check_block(blk, kb, vb_blk, vb):
+    from oracle import tq_oracle as orc
+
+    assert np.array_equal(blk["key_indices"], orc.pack_key_codes(kb["codes"]))
+    assert np.array_equal(blk["nf4_scale"][0], kb["scale"])
+    assert np.array_equal(blk["nf4_mean"][0], kb["mean"])
+    assert np.array_equal(blk["outlier_idx"], kb["out_idx"])
+    assert np.array_equal(blk["outlier_val"].view(np.uint16), kb["out_val"].view(np.uint16))
+    assert np.array_equal(blk["value_indices"], orc.pack_value_codes(vb_blk["codes"], vb))
+    assert np.array_equal(blk["value_norms"][0], vb_blk["norms"])
+
+
+# ------------------------------------------------------------------------------------ #
+# encoders against the reference fixtures                                               #
+# ------------------------------------------------------------------------------------ #
+
+@pytest.mark.parametrize("name", ["block_k4v3.npz", "block_k4v4_f16.npz", "block_ties.npz",
+                                  "block_short.npz"])
+def test_block_encoders_bit_exact_vs_reference(torch_cuda, name):
+    """One cold block flushed by the CUDA encoders == the reference's containers."""
+    torch = torch_cuda
+    g = load_golden(name)
+    k, v = g["k"], g["v"]                       # (S, H, D)
+    s, h, _ = k.shape
+    w = 2 * s                                   # block size (w+1)//2 == s
+    vb = int(g["value_bits"])
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, value_bits=vb, hot_window=w,
+               max_tokens_per_seq=4 * w, kv_dtype=_np_dtype_name(k), pi=g["pi"])
+    fill = np.zeros((w + 1 - s, h, 128), dtype=k.dtype)
+    kk = np.concatenate([k, fill + 1]) [None]
+    vv = np.concatenate([v, fill + 1])[None]
+    ctx.append(0, _dev(torch, kk), _dev(torch, vv))
+    assert ctx.lengths(0, 0) == (w + 1, s, w + 1 - s)
+    blk = ctx.export_block(0, 0, 0)
+    assert np.array_equal(blk["key_indices"], g["key_indices"])
+    assert np.array_equal(blk["nf4_scale"], g["nf4_scale"])
+    assert np.array_equal(blk["nf4_mean"], g["nf4_mean"])
+    assert np.array_equal(blk["outlier_idx"], g["outlier_idx"])
+    assert np.array_equal(blk["outlier_val"].view(np.uint16), g["outlier_val"].view(np.uint16))
+    assert np.array_equal(blk["value_norms"], g["value_norms"])
+    assert np.array_equal(blk["value_indices"], g["value_indices"])
+    kd, vd = ctx.dequant(0, 0, 0, s)
+    assert np.array_equal(kd.cpu().numpy(), g["key_dequant"])
+    assert np.array_equal(vd.cpu().numpy(), g["value_dequant"])
+    assert ctx.status() == 0
+
+
+@pytest.mark.parametrize("name,vb,bulk", [
+    ("cache_w16.npz", 4, False), ("cache_w16.npz", 4, True),
+    ("cache_w512_gqa.npz", 3, True), ("cache_w512_gqa.npz", 3, False),
+    ("cache_w7.npz", 3, False), ("cache_w7.npz", 3, True),
+])
+def test_cache_matches_reference(torch_cuda, name, vb, bulk):
+    """A cache filled token by token (or in one bulk call) reproduces the reference's cold
+    blocks, getters, statistics and dequantise-then-attend output."""
+    torch = torch_cuda
+    g = load_golden(name)
+    k, v, q = g["k"], g["v"], g["q"]
+    n, h, _ = k.shape
+    w = int(g["hot_window"])
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=q.shape[0], value_bits=vb,
+               hot_window=w, max_tokens_per_seq=n + 8, kv_dtype=_np_dtype_name(k), pi=g["pi"])
+    kd, vd = _dev(torch, k[None]), _dev(torch, v[None])
+    if bulk:
+        cut = n // 3  # two calls: exercises blocks that straddle ring and new tokens
+        ctx.append(0, kd[:, :cut], vd[:, :cut])
+        ctx.append(0, kd[:, cut:], vd[:, cut:])
+    else:
+        for t in range(n):
+            ctx.append(0, kd[:, t:t + 1], vd[:, t:t + 1])
+    total, cold, hot = ctx.lengths(0, 0)
+    assert (total, hot) == (int(g["length"]), int(g["hot_length"]))
+    nb = int(g["n_blocks"])
+    assert cold == int(g["cold_lengths"].sum())
+    for i in range(nb):
+        blk = ctx.export_block(0, 0, i)
+        assert np.array_equal(blk["key_indices"], g[f"b{i}_key_indices"])
+        assert np.array_equal(blk["nf4_scale"], g[f"b{i}_nf4_scale"])
+        assert np.array_equal(blk["nf4_mean"], g[f"b{i}_nf4_mean"])
+        assert np.array_equal(blk["outlier_idx"], g[f"b{i}_outlier_idx"])
+        assert np.array_equal(blk["outlier_val"].view(np.uint16),
+                              g[f"b{i}_outlier_val"].view(np.uint16))
+        assert np.array_equal(blk["value_indices"], g[f"b{i}_value_indices"])
+        assert np.array_equal(blk["value_norms"], g[f"b{i}_value_norms"])
+    keys, vals = ctx.dequant(0, 0, 0, total)
+    assert np.array_equal(keys[0].cpu().numpy(), g["keys_head0"])
+    assert np.array_equal(vals[0].cpu().numpy(), g["values_head0"])
+    cold_b, hot_b = ctx.memory_stats(0, 0)
+    assert [cold_b, hot_b] == g["memory_stats"][:2].tolist()
+    out = ctx.decode(0, _dev(torch, q[None]))[0].cpu().numpy()
+    err = np.abs(out - g["attn"]).max()
+    assert np.allclose(out, g["attn"], rtol=RTOL, atol=ATOL), f"max abs err {err}"
+    if "fused" in g.files:
+        assert np.allclose(out, g["fused"], rtol=RTOL, atol=ATOL)
+    assert ctx.status() == 0
+
+
+# ------------------------------------------------------------------------------------ #
+# decode against the oracle on seeded synthetic tensors                                 #
+# ------------------------------------------------------------------------------------ #
+
+@pytest.mark.parametrize("h,grp,n,w,vb,dt", [
+    (2, 1, 1500, 512, 4, "float32"),     # MHA, K4/V4, float32 hot window (config-0 shape)
+    (2, 4, 1500, 512, 3, "float16"),     # GQA 4, K4/V3 (Llama-3-8B shape)
+    (1, 8, 1100, 512, 4, "float16"),     # GQA 8 (Llama-3-70B shape)
+    (2, 4, 300, 512, 3, "bfloat16"),     # hot only
+    (2, 2, 770, 512, 3, "float16"),      # exactly at a flush boundary + 1
+    (1, 7, 200, 64, 3, "float32"),       # odd group (Qwen2.5-7B shape), small window
+    (1, 16, 150, 32, 4, "float16"),      # group 16
+])
+def test_decode_vs_oracle(torch_cuda, h, grp, n, w, vb, dt):
+    torch = torch_cuda
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    seed = 100 + n
+    k, v = make_kv(seed, h, n, dtype=np.float16)
+    if dt == "bfloat16":
+        kt = torch.from_numpy(k.astype(np.float32)).to(torch.bfloat16)
+        vt = torch.from_numpy(v.astype(np.float32)).to(torch.bfloat16)
+        k, v = kt.float().numpy(), vt.float().numpy()
+    else:
+        kt, vt = torch.from_numpy(k.astype(dt)), torch.from_numpy(v.astype(dt))
+        k, v = k.astype(np.float32), v.astype(np.float32)
+    q = make_q(seed, h * grp)
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h * grp, value_bits=vb,
+               hot_window=w, max_tokens_per_seq=n + 8, kv_dtype=dt, seed=seed)
+    ctx.append(0, kt[None].cuda(), vt[None].cuda())
+    ref = _oracle(h, vb, w, ctx.pi, k, v)
+    for i in range(len(ref.cold_k)):
+        _check_block(ctx.export_block(0, 0, i), ref.cold_k[i], ref.cold_v[i], vb)
+    want = ref.attend(q)
+    for qdt in (torch.float32, torch.bfloat16):
+        qq = torch.from_numpy(q).to(qdt)
+        got = ctx.decode(0, qq[None].cuda())[0].cpu().numpy()
+        want_q = ref.attend(qq.float().numpy())
+        err = np.abs(got - want_q).max()
+        assert np.allclose(got, want_q, rtol=RTOL, atol=ATOL), f"{qdt}: max abs err {err}"
+    assert want.shape == (h * grp, 128)
+
+
+def test_batched_layers_ragged(torch_cuda):
+    """Several layers and sequences with different lengths in one context; each cache is
+    independent and matches its own oracle."""
+    torch = torch_cuda
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, w, vb = 2, 4, 64, 3
+    lens = [0, 45, 200, 129]
+    ctx = _ctx(n_layers=2, n_seqs=len(lens), n_kv_heads=h, n_q_heads=h * grp, value_bits=vb,
+               hot_window=w, max_tokens_per_seq=256, kv_dtype="float16", seed=3)
+    refs = {}
+    for layer in range(2):
+        for s, n in enumerate(lens):
+            if n == 0:
+                continue
+            k, v = make_kv(1000 + 10 * layer + s, h, n, dtype=np.float16)
+            ctx.append(layer, _dev(torch, k[None]), _dev(torch, v[None]), seq_begin=s)
+            refs[(layer, s)] = _oracle(h, vb, w, ctx.pi, k.astype(np.float32),
+                                       v.astype(np.float32))
+    for layer in range(2):
+        q = np.stack([make_q(7 + s + 100 * layer, h * grp) for s in range(len(lens))])
+        out = ctx.decode(layer, _dev(torch, q)).cpu().numpy()
+        assert np.all(out[0] == 0.0)  # empty sequence -> zeros
+        for s, n in enumerate(lens):
+            if n == 0:
+                continue
+            want = refs[(layer, s)].attend(q[s])
+            assert np.allclose(out[s], want, rtol=RTOL, atol=ATOL), (layer, s)
+    # clearing one sequence leaves the others intact
+    ctx.clear(0, 2)
+    assert ctx.lengths(0, 2) == (0, 0, 0) and ctx.lengths(0, 3)[0] == 129
+    k, v = make_kv(55, h, 100, dtype=np.float16)
+    ctx.append(0, _dev(torch, k[None]), _dev(torch, v[None]), seq_begin=2)
+    ref = _oracle(h, vb, w, ctx.pi, k.astype(np.float32), v.astype(np.float32))
+    q = np.stack([make_q(70 + s, h * grp) for s in range(len(lens))])
+    out = ctx.decode(0, _dev(torch, q)).cpu().numpy()
+    assert np.allclose(out[2], ref.attend(q[2]), rtol=RTOL, atol=ATOL)
+    assert np.allclose(out[3], refs[(0, 3)].attend(q[3]), rtol=RTOL, atol=ATOL)
+
+
+def test_sequence_split_partials_merge(torch_cuda):
+    """Partial (m, l, o) states over disjoint block ranges + the hot window merge to the
+    full decode (the multi-device sequence split, emulated on one device)."""
+    torch = torch_cuda
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, n, w, vb = 2, 4, 1400, 128, 3
+    k, v = make_kv(9, h, n, dtype=np.float16)
+    q = _dev(torch, make_q(9, h * grp)[None])
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h * grp, value_bits=vb,
+               hot_window=w, max_tokens_per_seq=n, kv_dtype="float16", seed=9)
+    ctx.append(0, _dev(torch, k[None]), _dev(torch, v[None]))
+    full = ctx.decode(0, q).cpu().numpy()
+    nb = ctx.lengths(0, 0)[1] // ctx.block_tokens
+    world = 4
+    parts = []
+    for r in range(world):
+        lo, hi = nb * r // world, nb * (r + 1) // world
+        parts.append(ctx.decode_partial(0, q, lo, hi, with_hot=(r == world - 1)).clone())
+    mlo = torch.stack(parts).reshape(world, h * grp, 130)
+    merged = ctx.lse_combine(mlo).cpu().numpy()
+    assert np.allclose(merged, full[0], rtol=1e-4, atol=1e-5)
+    ref = _oracle(h, vb, w, ctx.pi, k.astype(np.float32), v.astype(np.float32))
+    assert np.allclose(merged, ref.attend(make_q(9, h * grp)), rtol=RTOL, atol=ATOL)
+
+
+def test_facade_matches_reference_api(torch_cuda):
+    """TurboQuantKVCache: the reference's constructor, append, getters, fused_decode,
+    memory_stats and clear, checked on the reference's own cache fixture."""
+    from turboquant_pro_b200 import AutoConfig, TurboQuantKVCache
+
+    g = load_golden("cache_w16.npz")
+    k, v, q = g["k"], g["v"], g["q"]
+    cache = TurboQuantKVCache.robust(head_dim=128, n_heads=2, key_bits=4, value_bits=4,
+                                     hot_window=16, seed=int(g["seed"]), max_tokens=256)
+    with pytest.raises(RuntimeError, match="cache is empty"):
+        cache.fused_decode(q)
+    for t in range(k.shape[0]):
+        if t % 2:
+            cache.append(k[t], v[t])                              # (H, D)
+        else:
+            cache.append(k[t][None, :, None, :], v[t][None, :, None, :])  # (1, H, 1, D)
+    assert cache.length == int(g["length"]) and cache.hot_length == int(g["hot_length"])
+    assert cache.cold_length == int(g["cold_lengths"].sum())
+    keys = cache.get_keys(0, cache.length)
+    assert keys.shape == (1, 2, cache.length, 128) and keys.dtype == np.float32
+    # the rotation comes from this host's LAPACK; keys do not depend on it
+    assert np.array_equal(keys[0, 0], g["keys_head0"])
+    assert cache.get_keys(5, 5).shape == (1, 2, 0, 128)
+    out = cache.fused_decode(q)
+    assert out.shape == (2, 128)
+    assert np.allclose(out, g["attn"], rtol=RTOL, atol=ATOL)
+    st = cache.memory_stats()
+    assert st["cold_bytes"] == g["memory_stats"][0] and st["hot_bytes"] == g["memory_stats"][1]
+    assert st["uncompressed_equivalent_bytes"] == g["memory_stats"][3]
+    cache.clear()
+    assert cache.length == 0
+    cfg = AutoConfig.from_pretrained("llama-3-8b")
+    c2 = cfg.build_cache(hot_window=32, use_gpu=True, seed=1, max_tokens=128)
+    assert (c2.key_bits, c2.value_bits, c2.n_heads, c2.hot_window) == (4, 3, 8, 32)
+    with pytest.raises(NotImplementedError):
+        TurboQuantKVCache(head_dim=128, n_heads=2, bits=4)  # bare uniform keys
+
+
+def test_abi_error_codes(torch_cuda):
+    """Invalid calls come back as status codes / the reference's exception types, and never
+    reach a kernel launch."""
+    torch = torch_cuda
+    ctx = _ctx(n_layers=1, n_seqs=2, n_kv_heads=2, value_bits=3, hot_window=16,
+               max_tokens_per_seq=32, kv_dtype="float16", seed=0)
+    k = torch.zeros((1, 40, 2, 128), dtype=torch.float16, device="cuda")
+    from turboquant_pro_b200._lib import TqError
+
+    with pytest.raises(TqError, match="CAPACITY"):
+        ctx.append(0, k, k)
+    with pytest.raises(ValueError):
+        ctx.append(3, k[:, :4], k[:, :4])          # bad layer
+    with pytest.raises(ValueError):
+        ctx.append(0, k[:, :4], k[:, :4], seq_begin=2)  # bad sequence
+    with pytest.raises(ValueError):
+        ctx.dequant(0, 0, 0, 5)                    # range beyond the stored tokens
+    with pytest.raises(ValueError):
+        ctx.decode(0, torch.zeros((2, 3, 128), device="cuda"))
+    assert ctx.lengths(0, 0) == (0, 0, 0)
+    with pytest.raises(NotImplementedError):
+        _ctx(n_kv_heads=2, head_dim=64)
+    with pytest.raises(NotImplementedError):
+        _ctx(n_kv_heads=2, value_bits=2)
+
+
+def test_degenerate_blocks(torch_cuda):
+    """All-equal and all-zero blocks: every entry ties with the k-th magnitude, so the whole
+    block lands in the outlier list, as in the reference; the pool absorbs it."""
+    torch = torch_cuda
+    h, w = 1, 16
+    k = np.zeros((20, h, 128), np.float32)
+    k[:8] = 0.5
+    v = np.ones((20, h, 128), np.float32)
+    v[3] = 0.0  # zero-norm value token
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, value_bits=3, hot_window=w,
+               max_tokens_per_seq=64, kv_dtype="float32", seed=2)
+    ctx.append(0, _dev(torch, k[None]), _dev(torch, v[None]))
+    ref = _oracle(h, 3, w, ctx.pi, k, v)
+    blk = ctx.export_block(0, 0, 0)
+    _check_block(blk, ref.cold_k[0], ref.cold_v[0], 3)
+    assert blk["outlier_idx"].size == 8 * 128
+    q = np.ones((1, 128), np.float32)
+    out = ctx.decode(0, _dev(torch, q[None]))[0].cpu().numpy()
+    assert np.allclose(out, ref.attend(q), rtol=RTOL, atol=ATOL)
+    assert ctx.status() == 0

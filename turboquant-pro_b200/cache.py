@@ -1,0 +1,193 @@
+"""TurboQuantKVCache — the reference's cache API on the B200-native kernels.
+
+Same constructor keywords, methods, properties, return shapes and exceptions as
+``turboquant_pro.core.TurboQuantKVCache`` (``core.py:818-1307``), so user code can switch
+imports.  Storage and arithmetic live on the GPU behind the C ABI; there is no numpy or
+CuPy path underneath and therefore no CPU fallback: constructing a cache without a CUDA
+device raises.
+
+Supported format: per-channel asymmetric-NF4 keys (``key_nf4_asym=True``, 4 bits,
+``key_zero_point="calibrated"``) with an optional fp16 outlier side-list, PolarQuant
+values at 3 or 4 bits.  Other key grids of the reference raise ``NotImplementedError``.
+"""
+
+from __future__ import annotations
+
+import logging
+
+import numpy as np
+
+from .context import KVContext
+
+logger = logging.getLogger(__name__)
+
+
+class TurboQuantKVCache:
+    """Two-tier (hot window + compressed cold blocks) KV cache of one layer and one sequence.
+
+    Keyword arguments follow ``core.py:886-904``.  Two additions, both keyword-only in
+    spirit: ``max_tokens`` (capacity the device buffers are sized for) and ``dtype``
+    (element type of the hot window; appended tokens are converted to it — float32 keeps
+    every input exactly, as the reference does).
+    """
+
+    @classmethod
+    def robust(cls, head_dim: int = 128, n_heads: int = 32, *, key_bits: int = 4,
+               value_bits: int = 4, hot_window: int = 512, outlier_frac: float = 0.02,
+               **kwargs) -> "TurboQuantKVCache":
+        """Asymmetric-NF4 keys + ``outlier_frac`` fp16 outliers (``core.py:856-884``)."""
+        return cls(head_dim=head_dim, n_heads=n_heads, key_bits=key_bits, value_bits=value_bits,
+                   hot_window=hot_window, key_nf4_asym=True, key_outlier_frac=outlier_frac,
+                   **kwargs)
+
+    def __init__(self, head_dim: int = 128, n_heads: int = 32, bits: int = 3,
+                 key_bits: int | None = None, value_bits: int | None = None,
+                 hot_window: int = 512, use_gpu: bool = True, device_id: int = 0,
+                 seed: int | None = None, per_channel_keys: bool = True, key_nuq: bool = False,
+                 key_nf4: bool = False, key_nf4_asym: bool = False,
+                 key_outlier_frac: float = 0.0, key_zero_point: str = "calibrated",
+                 key_rope_theta: float | None = None, key_k_bias=None, *,
+                 max_tokens: int = 32768, dtype="float32", n_q_heads: int | None = None) -> None:
+        for name, b in (("bits", bits), ("key_bits", key_bits), ("value_bits", value_bits)):
+            if b is not None and b not in (2, 3, 4):
+                raise ValueError(f"Unsupported {name}={b}; choose from [2, 3, 4]")
+        if not (0.0 <= key_outlier_frac < 1.0):
+            raise ValueError("outlier_frac must be in [0, 1)")
+        if key_zero_point not in ("calibrated", "sparse", "bias"):
+            raise ValueError("zero_point must be one of ('calibrated', 'sparse', 'bias')")
+        if not use_gpu:
+            raise RuntimeError("this build is GPU-only: use_gpu=False has no implementation "
+                               "(use the reference package for a numpy cache)")
+        self.head_dim = head_dim
+        self.n_heads = n_heads
+        self.bits = bits
+        self.key_bits = key_bits if key_bits is not None else bits
+        self.value_bits = value_bits if value_bits is not None else bits
+        self.hot_window = hot_window
+        self.per_channel_keys = per_channel_keys
+        if not per_channel_keys:
+            raise NotImplementedError("PolarQuant keys (per_channel_keys=False) are not "
+                                      "implemented on the CUDA path")
+        if not key_nf4_asym or key_nuq:
+            raise NotImplementedError(
+                "the CUDA path implements asymmetric-NF4 keys: build the cache with "
+                "TurboQuantKVCache.robust(...) or key_nf4_asym=True")
+        if key_zero_point != "calibrated":
+            raise NotImplementedError("key_zero_point 'sparse' and 'bias' are not implemented "
+                                      "on the CUDA path")
+        if self.key_bits != 4:
+            raise ValueError("nf4=True requires bits=4")
+        self._ctx = KVContext(
+            n_layers=1, n_seqs=1, n_kv_heads=n_heads, n_q_heads=n_q_heads or n_heads,
+            head_dim=head_dim, key_bits=self.key_bits, value_bits=self.value_bits,
+            hot_window=hot_window, outlier_frac=key_outlier_frac, max_tokens_per_seq=max_tokens,
+            kv_dtype=dtype, seed=seed, device=device_id)
+        self.key_outlier_frac = key_outlier_frac
+
+    # ------------------------------------------------------------------ properties --
+    @property
+    def length(self) -> int:
+        """Total number of tokens (cold + hot)."""
+        return self._ctx.lengths(0, 0)[0]
+
+    @property
+    def cold_length(self) -> int:
+        return self._ctx.lengths(0, 0)[1]
+
+    @property
+    def hot_length(self) -> int:
+        return self._ctx.lengths(0, 0)[2]
+
+    @property
+    def context(self) -> KVContext:
+        """The underlying device context."""
+        return self._ctx
+
+    # --------------------------------------------------------------------- append ----
+    def _to_device(self, x, what):
+        import torch
+
+        if isinstance(x, torch.Tensor):
+            t = x
+        else:
+            t = torch.from_numpy(np.ascontiguousarray(x))
+        if t.dim() == 4:  # (1, H, T, D) -> (T, H, D)
+            if t.shape[0] != 1:
+                raise ValueError(f"{what}: batch dimension must be 1")
+            t = t[0].permute(1, 0, 2)
+        elif t.dim() == 2:  # (H, D)
+            t = t[None]
+        elif t.dim() != 3:
+            raise ValueError(f"{what}: expected (1,H,1,D), (H,D) or (T,H,D), got {tuple(x.shape)}")
+        if t.shape[1] != self.n_heads or t.shape[2] != self.head_dim:
+            raise ValueError(f"{what}: expected {self.n_heads} heads of dim {self.head_dim}")
+        return t.to(device=self._ctx.device, dtype=self._ctx.kv_dtype)[None].contiguous()
+
+    def append(self, key, value) -> None:
+        """Add the K/V of one token: ``(1, n_heads, 1, head_dim)`` or ``(n_heads,
+        head_dim)`` (numpy or torch).  Flushes the oldest half of an over-full hot window
+        into one compressed block, as ``core.py:986-1038`` does."""
+        self._ctx.append(0, self._to_device(key, "key"), self._to_device(value, "value"))
+
+    def append_many(self, keys, values) -> None:
+        """Bulk form of :meth:`append`: ``(T, n_heads, head_dim)`` or ``(1, n_heads, T,
+        head_dim)``.  Produces exactly the blocks T single appends would."""
+        self._ctx.append(0, self._to_device(keys, "keys"), self._to_device(values, "values"))
+
+    # -------------------------------------------------------------------- getters ----
+    def _range(self, start, end, keys):
+        n = self.length
+        start, end = max(0, start), min(end, n)
+        if end <= start:
+            return np.zeros((1, self.n_heads, 0, self.head_dim), dtype=np.float32)
+        k, v = self._ctx.dequant(0, 0, start, end, keys=keys, values=not keys)
+        return (k if keys else v).cpu().numpy()[None]
+
+    def get_keys(self, start: int, end: int) -> np.ndarray:
+        """Dequantised keys of ``[start, end)``: ``(1, n_heads, n, head_dim)`` float32."""
+        return self._range(start, end, True)
+
+    def get_values(self, start: int, end: int) -> np.ndarray:
+        return self._range(start, end, False)
+
+    # --------------------------------------------------------------------- decode ----
+    def fused_decode(self, query, method: str = "warp"):
+        """One decode-step attention output over the whole cache, computed on the codes.
+
+        ``query``: ``(n_q_heads, head_dim)`` or ``(1, n_q_heads, 1, head_dim)``; returns
+        ``(n_q_heads, head_dim)`` float32 — a numpy array for numpy input, a CUDA tensor
+        for tensor input.  Unlike the reference (``core.py:1193``) it does not require
+        ``key_bits == value_bits``.
+        """
+        import torch
+
+        if self.length == 0:
+            raise RuntimeError("cache is empty")
+        is_np = not isinstance(query, torch.Tensor)
+        q = torch.from_numpy(np.ascontiguousarray(query, dtype=np.float32)) if is_np else query
+        hq = self._ctx.n_q_heads
+        q = q.reshape(1, hq, self.head_dim).to(self._ctx.device)
+        if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            q = q.float()
+        out = self._ctx.decode(0, q)[0]
+        return out.cpu().numpy() if is_np else out
+
+    # ---------------------------------------------------------------------- stats ----
+    def memory_stats(self) -> dict[str, float]:
+        """``cold_bytes``, ``hot_bytes``, ``total_bytes``, ``uncompressed_equivalent_bytes``
+        (float32 K+V, as the reference counts it) and ``effective_ratio``
+        (``core.py:1267-1296``)."""
+        cold, hot = self._ctx.memory_stats(0, 0)
+        total = cold + hot
+        unc = float(self.length * self.n_heads * self.head_dim * 4 * 2)
+        return {
+            "cold_bytes": float(cold),
+            "hot_bytes": float(hot),
+            "total_bytes": float(total),
+            "uncompressed_equivalent_bytes": unc,
+            "effective_ratio": unc / max(total, 1),
+        }
+
+    def clear(self) -> None:
+        """Reset the cache to empty."""
+        self._ctx.clear(0, 0)

@@ -1,0 +1,337 @@
+"""KVContext — a GPU-resident group of compressed two-tier KV caches.
+
+One context holds ``n_layers x n_seqs`` caches that share geometry, rotation and
+codebooks; each of them behaves exactly like one reference ``TurboQuantKVCache``
+(``turboquant_pro/core.py:818-1307``).  Batch, layers and GQA do not exist in the
+reference's cache API — they are what a serving engine adds around it — so this class is
+the extension point the benchmark configurations use, and the single-cache façade in
+:mod:`cache` is a thin view of a 1 x 1 context.
+
+PyTorch is used for device memory and streams only; all computation happens in the
+hand-written kernels behind the C ABI (``include/tqb200.h``).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+
+from . import _lib
+from ._lib import REGIONS, TqBuffers, TqGeom, TqSizes, check
+
+# Lloyd-Max centroids of N(0, 1) for 3 and 4 bits — the direction codebook of the value
+# quantiser (turboquant_pro/core.py:70-93).
+_LLOYD_MAX = {
+    3: (-1.748, -1.050, -0.500, -0.069, 0.069, 0.500, 1.050, 1.748),
+    4: (-2.401, -1.844, -1.437, -1.099, -0.800, -0.524, -0.262, -0.066,
+        0.066, 0.262, 0.524, 0.800, 1.099, 1.437, 1.844, 2.401),
+}
+
+
+def value_codebook(head_dim: int, bits: int):
+    """Centroids (scaled by 1/sqrt(d), rounded to float32) and the float32 mid-point
+    boundaries, as ``TurboQuantKV.__init__`` builds them (core.py:229-241)."""
+    if bits not in _LLOYD_MAX:
+        raise NotImplementedError(f"value_bits={bits}: the CUDA path implements 3 and 4")
+    c = (np.asarray(_LLOYD_MAX[bits], dtype=np.float64) * (1.0 / math.sqrt(head_dim))).astype(
+        np.float32)
+    bnd = ((c[:-1] + c[1:]) / np.float32(2.0)).astype(np.float32)
+    return c, bnd
+
+
+def rotation_matrix(head_dim: int, seed):
+    """Seeded random orthogonal matrix and its transpose (core.py:246-260): QR of a
+    float32 standard-normal matrix drawn from ``np.random.default_rng(seed)``."""
+    rng = np.random.default_rng(seed)
+    g = rng.standard_normal((head_dim, head_dim)).astype(np.float32)
+    q, _ = np.linalg.qr(g)
+    return np.ascontiguousarray(q), np.ascontiguousarray(q.T)
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _dtype_code(torch_dtype) -> int:
+    torch = _torch()
+    return {torch.float32: _lib.TQ_F32, torch.float16: _lib.TQ_F16,
+            torch.bfloat16: _lib.TQ_BF16}[torch_dtype]
+
+
+def _torch_dtype(name):
+    torch = _torch()
+    if isinstance(name, torch.dtype):
+        return name
+    key = np.dtype(name).name if not isinstance(name, str) else name
+    return {"float32": torch.float32, "float16": torch.float16,
+            "bfloat16": torch.bfloat16}[key]
+
+
+class KVContext:
+    """``n_layers x n_seqs`` compressed KV caches on one GPU.
+
+    Args:
+        n_layers, n_seqs, n_kv_heads, n_q_heads: cache-group geometry; query head ``i``
+            attends KV head ``i // (n_q_heads // n_kv_heads)``.
+        head_dim: 128.
+        key_bits: 4 (asymmetric NF4 keys).  value_bits: 3 or 4 (PolarQuant values).
+        hot_window: tokens kept uncompressed (2..512); a flush moves the oldest
+            ``(hot_window + 1) // 2`` tokens into one cold block.
+        outlier_frac: per-channel fraction of fp16 outliers kept beside the key codes.
+        max_tokens_per_seq: capacity each sequence is sized for.
+        kv_dtype: element type of appended tokens and of the hot window.
+        seed: seed of the rotation matrix; ``pi`` overrides it with an explicit matrix.
+        device: CUDA device ordinal.
+    """
+
+    def __init__(self, n_layers=1, n_seqs=1, n_kv_heads=8, n_q_heads=None, head_dim=128,
+                 key_bits=4, value_bits=3, hot_window=512, outlier_frac=0.02,
+                 max_tokens_per_seq=8192, kv_dtype="float32", seed=None, pi=None, device=0):
+        torch = _torch()
+        if not torch.cuda.is_available():
+            raise RuntimeError("KVContext needs a CUDA device: this package has no CPU fallback")
+        self._lib = _lib.load()
+        self.device = torch.device("cuda", device)
+        self.kv_dtype = _torch_dtype(kv_dtype)
+        g = TqGeom()
+        g.n_layers, g.n_seqs, g.n_kv_heads = n_layers, n_seqs, n_kv_heads
+        g.n_q_heads = n_q_heads if n_q_heads is not None else n_kv_heads
+        g.head_dim, g.key_bits, g.value_bits = head_dim, key_bits, value_bits
+        g.hot_window = hot_window
+        g.kv_dtype = _dtype_code(self.kv_dtype)
+        g.max_tokens_per_seq = max_tokens_per_seq
+        g.outlier_frac = float(outlier_frac)
+        check(self._lib.tq_geom_finish(C.byref(g)))
+        self.geom = g
+        sizes = TqSizes()
+        check(self._lib.tq_ctx_sizes(C.byref(g), C.byref(sizes)))
+        self.sizes = {n: int(getattr(sizes, n)) for n in REGIONS}
+        # device memory comes from torch's allocator; the library allocates nothing
+        self._regions = {n: torch.zeros(self.sizes[n], dtype=torch.uint8, device=self.device)
+                         for n in REGIONS}
+        bufs = TqBuffers()
+        for n in REGIONS:
+            setattr(bufs, n, self._regions[n].data_ptr())
+        if pi is None:
+            pi, pi_t = rotation_matrix(head_dim, seed)
+        else:
+            pi = np.ascontiguousarray(pi, dtype=np.float32)
+            pi_t = np.ascontiguousarray(pi.T)
+        self.pi, self.pi_t = pi, pi_t
+        self.centroids, self.boundaries = value_codebook(head_dim, value_bits)
+        handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_ctx_create(
+                C.byref(g), C.byref(bufs), device, pi.ctypes.data, pi_t.ctypes.data,
+                self.centroids.ctypes.data, self.boundaries.ctypes.data,
+                self._stream(), C.byref(handle)))
+        self._h = handle
+
+    # -- plumbing --------------------------------------------------------------------
+    def _stream(self):
+        return C.c_void_p(_torch().cuda.current_stream(self.device).cuda_stream)
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self._lib.tq_ctx_destroy(h)
+            self._h = None
+
+    @property
+    def n_layers(self):
+        return self.geom.n_layers
+
+    @property
+    def n_seqs(self):
+        return self.geom.n_seqs
+
+    @property
+    def n_kv_heads(self):
+        return self.geom.n_kv_heads
+
+    @property
+    def n_q_heads(self):
+        return self.geom.n_q_heads
+
+    @property
+    def block_tokens(self):
+        return self.geom.block_tokens
+
+    def device_bytes(self) -> int:
+        """Bytes of device memory held by this context."""
+        return sum(self.sizes.values())
+
+    # -- append ----------------------------------------------------------------------
+    def append(self, layer: int, k, v, seq_begin: int = 0) -> None:
+        """Append tokens to ``k.shape[0]`` consecutive sequences of ``layer``.
+
+        ``k``/``v``: CUDA tensors ``[n_seqs', T, n_kv_heads, D]`` (any strides with a
+        contiguous last dimension) of ``kv_dtype``.  Performs every flush the reference
+        would perform for token-by-token appends, with the same block boundaries.
+        """
+        torch = _torch()
+        if k.dim() != 4 or k.shape != v.shape:
+            raise ValueError(f"expected k, v of shape [n_seqs, T, H, D], got {tuple(k.shape)} "
+                             f"and {tuple(v.shape)}")
+        if k.shape[2] != self.n_kv_heads or k.shape[3] != self.geom.head_dim:
+            raise ValueError("head count / head_dim do not match the context")
+        if k.dtype != self.kv_dtype or v.dtype != self.kv_dtype:
+            k = k.to(self.kv_dtype)
+            v = v.to(self.kv_dtype)
+        if k.device != self.device:
+            k = k.to(self.device)
+            v = v.to(self.device)
+        if k.stride(3) != 1:
+            k = k.contiguous()
+        if v.stride() != k.stride():
+            v = v.contiguous()
+            k = k.contiguous()
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_append(self._h, layer, seq_begin, k.shape[0], k.data_ptr(),
+                                      v.data_ptr(), k.shape[1], k.stride(0), k.stride(1),
+                                      k.stride(2), self._stream()))
+
+    # -- decode ----------------------------------------------------------------------
+    def decode(self, layer: int, q, out=None):
+        """One decode step of attention on the codes for every sequence of ``layer``.
+
+        ``q``: CUDA tensor ``[n_seqs, n_q_heads, D]`` (float32 / float16 / bfloat16).
+        Returns float32 ``[n_seqs, n_q_heads, D]``.
+        """
+        torch = _torch()
+        g = self.geom
+        if tuple(q.shape) != (g.n_seqs, g.n_q_heads, g.head_dim):
+            raise ValueError(f"expected q of shape {(g.n_seqs, g.n_q_heads, g.head_dim)}, "
+                             f"got {tuple(q.shape)}")
+        q = q.contiguous()
+        if out is None:
+            out = torch.empty((g.n_seqs, g.n_q_heads, g.head_dim), dtype=torch.float32,
+                              device=self.device)
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_decode(self._h, layer, q.data_ptr(), _dtype_code(q.dtype),
+                                      out.data_ptr(), self._stream()))
+        return out
+
+    def decode_partial(self, layer: int, q, block_begin: int, block_end: int, with_hot: bool,
+                       mlo=None):
+        """Un-normalised ``(m, l, o)`` states over cold blocks ``[block_begin, block_end)``
+        (+ the hot window): float32 ``[n_seqs, n_q_heads, 2 + D]``."""
+        torch = _torch()
+        g = self.geom
+        q = q.contiguous()
+        if mlo is None:
+            mlo = torch.empty((g.n_seqs, g.n_q_heads, 2 + g.head_dim), dtype=torch.float32,
+                              device=self.device)
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_decode_partial(self._h, layer, q.data_ptr(), _dtype_code(q.dtype),
+                                              block_begin, block_end, int(bool(with_hot)),
+                                              mlo.data_ptr(), self._stream()))
+        return mlo
+
+    def lse_combine(self, mlo, out=None):
+        """Merge gathered states ``[n_parts, n_rows, 2 + D]`` into ``[n_rows, D]``."""
+        torch = _torch()
+        mlo = mlo.contiguous()
+        n_parts, n_rows, w = mlo.shape
+        if out is None:
+            out = torch.empty((n_rows, w - 2), dtype=torch.float32, device=mlo.device)
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_lse_combine(mlo.data_ptr(), n_parts, n_rows, w - 2,
+                                           out.data_ptr(), self._stream()))
+        return out
+
+    # -- read-back -------------------------------------------------------------------
+    def dequant(self, layer: int, seq: int, start: int, end: int, keys=True, values=True):
+        """Dequantised keys / values of tokens ``[start, end)``: float32 CUDA tensors
+        ``[n_kv_heads, end - start, D]`` (``None`` for the one not requested)."""
+        torch = _torch()
+        g = self.geom
+        n = max(end - start, 0)
+        k = torch.empty((g.n_kv_heads, n, g.head_dim), dtype=torch.float32,
+                        device=self.device) if keys else None
+        v = torch.empty((g.n_kv_heads, n, g.head_dim), dtype=torch.float32,
+                        device=self.device) if values else None
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_dequant_range(self._h, layer, seq, start, end,
+                                             k.data_ptr() if keys else None,
+                                             v.data_ptr() if values else None, self._stream()))
+        return k, v
+
+    def export_block(self, layer: int, seq: int, block: int) -> dict:
+        """Cold block ``block`` in the reference's container layout (host numpy arrays):
+        the fields of ``CompressedPerChannelKV`` and ``CompressedKV``."""
+        g = self.geom
+        h, s, d = g.n_kv_heads, g.block_tokens, g.head_dim
+        key_idx = np.empty(h * s * d // 2, np.uint8)
+        scale = np.empty((1, h, d), np.float32)
+        mean = np.empty((1, h, d), np.float32)
+        cap = h * s * d
+        oidx = np.empty(cap, np.int32)
+        oval = np.empty(cap, np.uint16)
+        n_out = C.c_int32(0)
+        val_idx = np.empty(h * s * d * g.value_bits // 8, np.uint8)
+        norms = np.empty((1, h, s), np.float32)
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_export_block(
+                self._h, layer, seq, block, key_idx.ctypes.data, scale.ctypes.data,
+                mean.ctypes.data, oidx.ctypes.data, oval.ctypes.data, cap, C.byref(n_out),
+                val_idx.ctypes.data, norms.ctypes.data, self._stream()))
+        n = n_out.value
+        has = g.outlier_k > 0
+        return {
+            "key_indices": key_idx, "nf4_scale": scale, "nf4_mean": mean,
+            "outlier_idx": oidx[:n].copy() if has else None,
+            "outlier_val": oval[:n].copy().view(np.float16) if has else None,
+            "value_indices": val_idx, "value_norms": norms,
+            "shape": (1, h, s, d), "key_bits": g.key_bits, "value_bits": g.value_bits,
+        }
+
+    # -- bookkeeping -----------------------------------------------------------------
+    def lengths(self, layer: int, seq: int):
+        """(total, cold, hot) token counts of one cache."""
+        t, c, h = C.c_int32(), C.c_int32(), C.c_int32()
+        check(self._lib.tq_seq_lengths(self._h, layer, seq, C.byref(t), C.byref(c), C.byref(h)))
+        return t.value, c.value, h.value
+
+    def memory_stats(self, layer: int, seq: int):
+        """(cold_bytes, hot_bytes) counted like the reference's containers."""
+        cold, hot = C.c_double(), C.c_double()
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_memory_stats(self._h, layer, seq, C.byref(cold), C.byref(hot),
+                                            self._stream()))
+        return cold.value, hot.value
+
+    def clear(self, layer: int, seq: int = -1) -> None:
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_clear(self._h, layer, seq, self._stream()))
+
+    def status(self) -> int:
+        """Device status flags (bit 0: an outlier pool overflowed); clears them."""
+        f = C.c_int32()
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_status(self._h, C.byref(f), self._stream()))
+        return f.value
+
+    def decode_bytes(self, layer: int) -> float:
+        """Algorithmic bytes one :meth:`decode` of ``layer`` reads."""
+        b = C.c_double()
+        check(self._lib.tq_decode_bytes(self._h, layer, C.byref(b)))
+        return b.value
+
+    def last_launches(self) -> int:
+        return int(self._lib.tq_last_launches(self._h))
+
+    def profile(self, on: bool) -> None:
+        """Bracket the attention and combine kernels of every decode with CUDA events."""
+        check(self._lib.tq_profile_enable(self._h, int(bool(on))))
+
+    def profile_read(self):
+        """(attention-kernel ms, combine-kernel ms, calls) summed since the last read."""
+        a, c, n = C.c_double(), C.c_double(), C.c_int32()
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_profile_read(self._h, C.byref(a), C.byref(c), C.byref(n)))
+        return a.value, c.value, n.value

@@ -1,0 +1,457 @@
+// Append path: key encoder (per-channel asymmetric NF4 + fp16 outlier side-list), value
+// encoder (PolarQuant: norm + rotated Lloyd-Max direction codes), hot-ring writer.
+//
+// Both encoders reproduce the reference's numpy arithmetic bit for bit, which pins the
+// evaluation order: sequential float32 sums over tokens, the 8-accumulator norm, a
+// multiply-then-add (never fused) rotation.  Every such operation uses the explicit
+// round-to-nearest intrinsics (__fadd_rn, __fmul_rn, __fdiv_rn, __fsqrt_rn), which the
+// compiler never contracts into FMAs.
+#include "common.cuh"
+
+namespace {
+
+struct EncodeArgs {
+  tq_geom g;
+  uint8_t* pages;
+  void* hot_k;
+  void* hot_v;
+  uint32_t* pool_dec;
+  uint16_t* pool_val;
+  PageMeta* page_meta;
+  int32_t* seq_len;      // [L][B]
+  uint32_t* pool_cursor; // [L][B][H]
+  int32_t* status;
+  const Tables* tables;
+  const void* k;
+  const void* v;
+  int layer, seq_begin, seq_count, n_tokens, max_new_blocks;
+  int64_t seq_stride, tok_stride, head_stride;
+};
+
+// Where token `pos` of (seq, head) currently lives: positions below n0 are already in the
+// hot ring, the rest are in the caller's tensor.
+template <int DT>
+struct TokenSource {
+  const void* ring;
+  const void* in;
+  int n0, cap;
+  int64_t tok_stride;
+  TQ_DEV float ld(int pos, int d) const {
+    if (pos < n0) return Elem<DT>::ld(ring, (size_t)(pos % cap) * TQ_D + d);
+    return Elem<DT>::ld(in, (size_t)(pos - n0) * tok_stride + d);
+  }
+};
+
+template <int DT>
+TQ_DEV TokenSource<DT> make_source(const EncodeArgs& a, const void* ring_base, const void* in_base,
+                                   int seq, int head, int n0) {
+  TokenSource<DT> s;
+  s.ring = (const uint8_t*)ring_base +
+           hot_offset_elems(a.g, a.layer, seq, head) * sizeof(typename Elem<DT>::type);
+  s.in = (const uint8_t*)in_base +
+         ((size_t)(seq - a.seq_begin) * a.seq_stride + (size_t)head * a.head_stride) *
+             sizeof(typename Elem<DT>::type);
+  s.n0 = n0;
+  s.cap = a.g.hot_cap;
+  s.tok_stride = a.tok_stride;
+  return s;
+}
+
+// ---------------------------------------------------------------------------------------
+// Key encoder.  One CTA per new cold block of one KV head, one thread per channel.
+//   mean   = (((x0 + x1) + x2) + ...) / S                      sequential float32 sum
+//   scale  = max(max_s |x - mean|, 1e-8)
+//   level  = fl(mean + fl(scale * NF4[l]));  code = first l minimising |fl(x - level_l)|
+//   outliers: every token whose |x| reaches the channel's k-th largest magnitude
+// ---------------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
+  const tq_geom& g = a.g;
+  const int seq = a.seq_begin + blockIdx.z;
+  const int head = blockIdx.y;
+  const int d = threadIdx.x;
+  const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
+  const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
+  const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
+  const int blk = nb0 + blockIdx.x;
+  if (blk >= nb1) return;
+  const int S = g.block_tokens;
+  const int pos0 = blk * S;
+  const TokenSource<DT> src = make_source<DT>(a, a.hot_k, a.k, seq, head, n0);
+  uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
+  const int kk = g.outlier_k;
+
+  __shared__ int s_count;
+  __shared__ uint32_t s_off;
+  __shared__ int s_alloc;
+  __shared__ int s_slot;
+  if (d == 0) {
+    s_count = 0;
+    s_slot = 0;
+  }
+
+  // pass 1: sequential sum and the k largest magnitudes (ascending; top[0] is the k-th)
+  float top[TQ_MAX_K_OUT];
+#pragma unroll
+  for (int i = 0; i < TQ_MAX_K_OUT; ++i) top[i] = -1.0f;
+  float acc = src.ld(pos0, d);
+  if (kk > 0) {
+    float a0 = fabsf(acc);
+    int i = 0;
+    while (i + 1 < kk && top[i + 1] < a0) { top[i] = top[i + 1]; ++i; }
+    top[i] = a0;
+  }
+  for (int t = 1; t < S; ++t) {
+    float x = src.ld(pos0 + t, d);
+    acc = __fadd_rn(acc, x);
+    if (kk > 0) {
+      float ax = fabsf(x);
+      if (ax > top[0]) {
+        int i = 0;
+        while (i + 1 < kk && top[i + 1] < ax) { top[i] = top[i + 1]; ++i; }
+        top[i] = ax;
+      }
+    }
+  }
+  const float mu = __fdiv_rn(acc, (float)S);
+  const float kth = (kk >= S) ? -1.0f : top[0];
+
+  // pass 2: scale, and how many outliers this channel keeps
+  float amax = 0.0f;
+  int my_out = 0;
+  for (int t = 0; t < S; ++t) {
+    float x = src.ld(pos0 + t, d);
+    amax = fmaxf(amax, fabsf(__fsub_rn(x, mu)));
+    if (kk > 0 && fabsf(x) >= kth) ++my_out;
+  }
+  amax = fmaxf(amax, 1e-8f);
+  float lev[16];
+#pragma unroll
+  for (int l = 0; l < 16; ++l) lev[l] = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[l]));
+
+  ((float*)(page + g.scale_off))[d] = amax;
+  ((float*)(page + g.mean_off))[d] = mu;
+
+  // allocate this page's slice of the (layer, seq, head) outlier slab
+  __syncthreads();
+  if (kk > 0) atomicAdd(&s_count, my_out);
+  __syncthreads();
+  if (d == 0) {
+    int n = s_count;
+    uint32_t off = 0;
+    int alloc = 0;
+    if (n > 0) {
+      int n4 = (n + 3) & ~3;
+      off = atomicAdd(&a.pool_cursor[unit_index(g, a.layer, seq, head)], (uint32_t)n4);
+      if (off >= (uint32_t)g.pool_entries) {
+        alloc = 0;
+        off = 0;
+      } else {
+        alloc = min(n4, g.pool_entries - (int)off);
+      }
+      if (alloc < n4) atomicOr(a.status, TQ_STATUS_POOL_OVERFLOW);
+    }
+    s_off = off;
+    s_alloc = alloc;
+    PageMeta pm;
+    pm.off = off;
+    pm.cnt = (uint32_t)min(n, alloc);
+    a.page_meta[unit_index(g, a.layer, seq, head) * g.max_blocks + blk] = pm;
+  }
+  __syncthreads();
+  const size_t slab = unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + s_off;
+  const int alloc = s_alloc;
+  {  // zero the padding entries so that a vector read of the list sees harmless deltas
+    int n = s_count;
+    int n4 = min((n + 3) & ~3, alloc);
+    if (d < 4 && n + d < n4) {
+      a.pool_dec[slab + n + d] = 0u;
+      a.pool_val[slab + n + d] = 0;
+    }
+  }
+
+  // pass 3: codes and outlier entries
+  for (int t = 0; t < S; ++t) {
+    float x = src.ld(pos0 + t, d);
+    int best = 0;
+    float bd = fabsf(__fsub_rn(x, lev[0]));
+#pragma unroll
+    for (int l = 1; l < 16; ++l) {
+      float dd = fabsf(__fsub_rn(x, lev[l]));
+      if (dd < bd) {
+        bd = dd;
+        best = l;
+      }
+    }
+    int other = __shfl_down_sync(0xffffffffu, best, 1);
+    if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
+    if (kk > 0 && fabsf(x) >= kth) {
+      int slot = atomicAdd(&s_slot, 1);
+      if (slot < alloc) {
+        __half hv = __float2half_rn(x);
+        float dense = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[best]));
+        __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
+        a.pool_dec[slab + slot] = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
+                                  ((uint32_t)t << 24);
+        a.pool_val[slab + slot] = __half_as_ushort(hv);
+      }
+    }
+  }
+  // padded token rows (block_tokens not a multiple of 16) keep code 0
+  for (int t = S; t < g.block_tokens_pad; ++t)
+    if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotation of 16 vectors held transposed in shared memory (us[d][t]) by the matrix column
+// this thread owns: acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every product and sum
+// rounded to float32 separately.
+// ---------------------------------------------------------------------------------------
+TQ_DEV void rotate16(const float (*us)[TQ_GROUP_TOK], const float* P, float* acc) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float4 u = *(const float4*)&us[0][4 * q];
+    acc[4 * q + 0] = __fmul_rn(u.x, P[0]);
+    acc[4 * q + 1] = __fmul_rn(u.y, P[0]);
+    acc[4 * q + 2] = __fmul_rn(u.z, P[0]);
+    acc[4 * q + 3] = __fmul_rn(u.w, P[0]);
+  }
+#pragma unroll
+  for (int dd = 1; dd < TQ_D; ++dd) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float4 u = *(const float4*)&us[dd][4 * q];
+      acc[4 * q + 0] = __fadd_rn(acc[4 * q + 0], __fmul_rn(u.x, P[dd]));
+      acc[4 * q + 1] = __fadd_rn(acc[4 * q + 1], __fmul_rn(u.y, P[dd]));
+      acc[4 * q + 2] = __fadd_rn(acc[4 * q + 2], __fmul_rn(u.z, P[dd]));
+      acc[4 * q + 3] = __fadd_rn(acc[4 * q + 3], __fmul_rn(u.w, P[dd]));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Value encoder.  Persistent CTAs of 128 threads; a work item is one 16-token group of a
+// new cold block.  Thread e owns output channel e and keeps column e of Pi^T in registers.
+//   norm = sqrt(pairwise sum of fl(x*x))      (numpy's 8-accumulator order for n = 128)
+//   u    = x / max(norm, 1e-30)
+//   y_e  = sequential, unfused sum over d of u_d * PiT[d][e]
+//   code = #{ j : boundary_j < y_e }
+// ---------------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
+  const tq_geom& g = a.g;
+  const int e = threadIdx.x;
+  const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
+  const int total = a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
+  const int vb = g.value_bits;
+  const int n_bnd = (1 << vb) - 1;
+
+  __shared__ __align__(16) float xs[TQ_GROUP_TOK][TQ_D];
+  __shared__ __align__(16) float us[TQ_D][TQ_GROUP_TOK];
+  __shared__ float s_norm[TQ_GROUP_TOK];
+  __shared__ float s_bnd[16];
+  __shared__ __align__(16) uint32_t img[256];
+
+  float P[TQ_D];
+#pragma unroll
+  for (int dd = 0; dd < TQ_D; ++dd) P[dd] = a.tables->pi_t[dd * TQ_D + e];
+  if (e < 16) s_bnd[e] = a.tables->boundaries[e];
+
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    int gq = w % groups;
+    int r = w / groups;
+    int jb = r % a.max_new_blocks;
+    r /= a.max_new_blocks;
+    int head = r % g.n_kv_heads;
+    int seq = a.seq_begin + r / g.n_kv_heads;
+    const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
+    const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
+    const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
+    const int blk = nb0 + jb;
+    if (blk >= nb1) continue;  // uniform over the CTA
+    const int S = g.block_tokens;
+    const TokenSource<DT> src = make_source<DT>(a, a.hot_v, a.v, seq, head, n0);
+    uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
+
+    __syncthreads();  // previous item fully consumed
+#pragma unroll 4
+    for (int t = 0; t < TQ_GROUP_TOK; ++t) {
+      int tt = gq * TQ_GROUP_TOK + t;
+      xs[t][e] = tt < S ? src.ld(blk * S + tt, e) : 0.0f;
+    }
+    img[e] = 0u;
+    img[e + 128] = 0u;
+    __syncthreads();
+    {  // norms: 8 threads per token, accumulator j sums elements j, j+8, j+16, ...
+      int t = e >> 3, j = e & 7;
+      float v0 = xs[t][j];
+      float rr = __fmul_rn(v0, v0);
+#pragma unroll
+      for (int i = 1; i < TQ_D / 8; ++i) {
+        float vv = xs[t][8 * i + j];
+        rr = __fadd_rn(rr, __fmul_rn(vv, vv));
+      }
+      rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 1));  // (r0+r1), (r2+r3), ...
+      rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 2));  // (r0+r1)+(r2+r3), ...
+      rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 4));
+      float nrm = __fsqrt_rn(rr);
+      if (j == 0) {
+        s_norm[t] = nrm;
+        ((float*)(page + g.norm_off))[gq * TQ_GROUP_TOK + t] = nrm;
+      }
+    }
+    __syncthreads();
+    {  // unit vectors, stored transposed for the broadcast reads of the rotation
+      int t = e >> 3, j = e & 7;
+      float safe = fmaxf(s_norm[t], 1e-30f);
+#pragma unroll
+      for (int i = 0; i < TQ_D / 8; ++i) us[8 * i + j][t] = __fdiv_rn(xs[t][8 * i + j], safe);
+    }
+    __syncthreads();
+    float acc[TQ_GROUP_TOK];
+    rotate16(us, P, acc);
+    int code[TQ_GROUP_TOK];
+#pragma unroll
+    for (int t = 0; t < TQ_GROUP_TOK; ++t) {
+      int c = 0;
+      for (int j = 0; j < n_bnd; ++j) c += (s_bnd[j] < acc[t]) ? 1 : 0;
+      code[t] = c;
+    }
+    // pack this channel's 8 token pairs into the group image
+    const int dq = e >> 4, i16 = e & 15;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        int ta = 2 * c + 8 * h;
+        int l = dq * 4 + c, p = 2 * i16 + h;
+        if (vb == 4) {
+          ((uint8_t*)img)[v_record_byte_off(4, l, p)] = (uint8_t)(code[ta] | (code[ta + 1] << 4));
+        } else {
+          uint32_t f = (uint32_t)(code[ta] | (code[ta + 1] << 3));
+          int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
+          atomicOr(&img[((wd >> 1) * 256 + l * 8 + (wd & 1) * 4) >> 2], f << sh);
+          if (sh > 26)
+            atomicOr(&img[((((wd + 1) >> 1)) * 256 + l * 8 + ((wd + 1) & 1) * 4) >> 2],
+                     f >> (32 - sh));
+        }
+      }
+    }
+    __syncthreads();
+    uint32_t* dst = (uint32_t*)(page + g.v_off + (size_t)gq * v_group_bytes(vb));
+    const int words = v_group_bytes(vb) / 4;
+    for (int i = e; i < words; i += TQ_D) dst[i] = img[i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Hot-ring writer: the new tokens that stay uncompressed go to slot (position % hot_cap).
+// grid = (tokens, heads, seqs); token index counts back from the newest.
+// ---------------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(TQ_D) ring_write_kernel(EncodeArgs a) {
+  using T = typename Elem<DT>::type;
+  const tq_geom& g = a.g;
+  const int seq = a.seq_begin + blockIdx.z;
+  const int head = blockIdx.y;
+  const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
+  const int n1 = n0 + a.n_tokens;
+  const int pos = n1 - 1 - (int)blockIdx.x;
+  const int hot_start = n_cold_blocks(n1, g.hot_window, g.block_tokens) * g.block_tokens;
+  if (pos < n0 || pos < hot_start) return;
+  const size_t in = (size_t)(seq - a.seq_begin) * a.seq_stride + (size_t)(pos - n0) * a.tok_stride +
+                    (size_t)head * a.head_stride + threadIdx.x;
+  const size_t out =
+      hot_offset_elems(g, a.layer, seq, head) + (size_t)(pos % g.hot_cap) * TQ_D + threadIdx.x;
+  ((T*)a.hot_k)[out] = ((const T*)a.k)[in];
+  ((T*)a.hot_v)[out] = ((const T*)a.v)[in];
+}
+
+__global__ void advance_len_kernel(int32_t* seq_len, int layer, int n_seqs, int seq_begin,
+                                   int seq_count, int n_tokens) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < seq_count) seq_len[layer * n_seqs + seq_begin + i] += n_tokens;
+}
+
+__global__ void clear_kernel(int32_t* seq_len, uint32_t* cursor, int layer, int n_seqs,
+                             int n_heads, int seq_begin, int seq_count) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < seq_count) seq_len[layer * n_seqs + seq_begin + i] = 0;
+  if (i < seq_count * n_heads)
+    cursor[((size_t)layer * n_seqs + seq_begin) * n_heads + i] = 0u;
+}
+
+template <int DT>
+int launch_encode_t(const EncodeArgs& a, int sm_count, cudaStream_t st, int* launches) {
+  const tq_geom& g = a.g;
+  if (a.max_new_blocks > 0) {
+    dim3 grid(a.max_new_blocks, g.n_kv_heads, a.seq_count);
+    encode_keys_kernel<DT><<<grid, TQ_D, 0, st>>>(a);
+    int groups = g.block_tokens_pad / TQ_GROUP_TOK;
+    long total = (long)a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
+    int ctas = (int)std::min<long>(total, (long)sm_count * 3);
+    encode_values_kernel<DT><<<ctas, TQ_D, 0, st>>>(a);
+    *launches += 2;
+  }
+  dim3 grid(std::min(a.n_tokens, g.hot_window), g.n_kv_heads, a.seq_count);
+  ring_write_kernel<DT><<<grid, TQ_D, 0, st>>>(a);
+  advance_len_kernel<<<(a.seq_count + 127) / 128, 128, 0, st>>>(a.seq_len, a.layer, g.n_seqs,
+                                                                a.seq_begin, a.seq_count,
+                                                                a.n_tokens);
+  *launches += 2;
+  return TQ_OK;
+}
+
+}  // namespace
+
+int tq_launch_encode(tq_ctx* ctx, int layer, int seq_begin, int seq_count, const void* k,
+                     const void* v, int n_tokens, int64_t seq_stride, int64_t tok_stride,
+                     int64_t head_stride, int max_new_blocks, cudaStream_t st) {
+  EncodeArgs a;
+  a.g = ctx->g;
+  a.pages = (uint8_t*)ctx->b.pages;
+  a.hot_k = ctx->b.hot_k;
+  a.hot_v = ctx->b.hot_v;
+  a.pool_dec = (uint32_t*)ctx->b.pool_dec;
+  a.pool_val = (uint16_t*)ctx->b.pool_val;
+  a.page_meta = (PageMeta*)ctx->b.page_meta;
+  a.seq_len = (int32_t*)((uint8_t*)ctx->b.state + state_len_off(ctx->g));
+  a.pool_cursor = (uint32_t*)((uint8_t*)ctx->b.state + state_cursor_off(ctx->g));
+  a.status = (int32_t*)((uint8_t*)ctx->b.state + state_status_off(ctx->g));
+  a.tables = (const Tables*)ctx->b.tables;
+  a.k = k;
+  a.v = v;
+  a.layer = layer;
+  a.seq_begin = seq_begin;
+  a.seq_count = seq_count;
+  a.n_tokens = n_tokens;
+  a.max_new_blocks = max_new_blocks;
+  a.seq_stride = seq_stride;
+  a.tok_stride = tok_stride;
+  a.head_stride = head_stride;
+  int sm_count = 148;
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
+  int launches = 0;
+  switch (ctx->g.kv_dtype) {
+    case TQ_F32: launch_encode_t<TQ_F32>(a, sm_count, st, &launches); break;
+    case TQ_F16: launch_encode_t<TQ_F16>(a, sm_count, st, &launches); break;
+    default: launch_encode_t<TQ_BF16>(a, sm_count, st, &launches); break;
+  }
+  ctx->last_launches = launches;
+  TQ_CUDA(cudaGetLastError());
+  return TQ_OK;
+}
+
+int tq_launch_clear(tq_ctx* ctx, int layer, int seq_begin, int seq_count, cudaStream_t st) {
+  const tq_geom& g = ctx->g;
+  int32_t* seq_len = (int32_t*)((uint8_t*)ctx->b.state + state_len_off(g));
+  uint32_t* cursor = (uint32_t*)((uint8_t*)ctx->b.state + state_cursor_off(g));
+  int n = seq_count * g.n_kv_heads;
+  clear_kernel<<<(n + 127) / 128, 128, 0, st>>>(seq_len, cursor, layer, g.n_seqs, g.n_kv_heads,
+                                                seq_begin, seq_count);
+  size_t first = unit_index(g, layer, seq_begin, 0) * g.max_blocks;
+  TQ_CUDA(cudaMemsetAsync((PageMeta*)ctx->b.page_meta + first, 0,
+                          (size_t)n * g.max_blocks * sizeof(PageMeta), st));
+  TQ_CUDA(cudaGetLastError());
+  return TQ_OK;
+}
