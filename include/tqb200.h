@@ -79,6 +79,8 @@ typedef struct tq_geom {
   int32_t page_bytes;         /* ... and the page stride (multiple of 128)             */
   int32_t pool_entries;       /* outlier-pool entries per (layer, seq, kv head)        */
   int32_t max_splits;         /* partial slots per (seq, kv head) in the scratch area  */
+  int32_t hdr_off;            /* page header: outlier count, pool offset, row starts   */
+  int32_t ent_off;            /* outlier entries kept inside the page (the first 768)  */
   int32_t reserved_;
 } tq_geom;
 
@@ -218,6 +220,12 @@ int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes);
 
 /* Number of kernels the most recent tq_decode / tq_append of this context launched. */
 int32_t tq_last_launches(const tq_ctx* ctx);
+
+/* Selects the decode kernel: 0 = automatic (the tensor-core kernel where the geometry
+ * allows: 256-token blocks, GQA group 1/2/4/8; else the general-shape kernel), 1 = always
+ * the general-shape float32 kernel.  Both compute the same function; tests compare them.
+ * No counterpart in the reference. */
+int32_t tq_set_kernel(tq_ctx* ctx, int32_t which);
 
 /* Per-kernel timing for benchmarks (no counterpart in the reference, whose harnesses time
  * whole calls with time.perf_counter, benchmarks/p5_triton_bench.py:72-82).  While enabled,

@@ -256,6 +256,82 @@ def test_sequence_split_partials_merge(torch_cuda):
     assert np.allclose(merged, ref.attend(make_q(9, h * grp)), rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("grp,vb,dt", [(4, 3, "float16"), (8, 4, "float16"), (1, 4, "float32"),
+                                        (2, 3, "bfloat16"), (4, 4, "bfloat16")])
+def test_tensor_core_and_general_kernels_agree(torch_cuda, grp, vb, dt):
+    """Ragged batch at the production geometry (256-token blocks): the tensor-core kernel
+    and the general-shape kernel compute the same attention, and both match the oracle."""
+    torch = torch_cuda
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, w = 2, 512
+    lens = [0, 300, 513, 1300, 2200, 769]
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}[dt]
+    ctx = _ctx(n_layers=1, n_seqs=len(lens), n_kv_heads=h, n_q_heads=h * grp, value_bits=vb,
+               hot_window=w, max_tokens_per_seq=2304, kv_dtype=dt, seed=17)
+    refs = {}
+    for s, n in enumerate(lens):
+        if n == 0:
+            continue
+        k, v = make_kv(300 + s, h, n, dtype=np.float16)
+        kt = torch.from_numpy(k.astype(np.float32)).to(tdt)
+        vt = torch.from_numpy(v.astype(np.float32)).to(tdt)
+        ctx.append(0, kt[None].cuda(), vt[None].cuda(), seq_begin=s)
+        refs[s] = _oracle(h, vb, w, ctx.pi, kt.float().numpy(), vt.float().numpy())
+    q = np.stack([make_q(40 + s, h * grp) for s in range(len(lens))])
+    qd = _dev(torch, q).to(torch.bfloat16)
+    qf = qd.float().cpu().numpy()
+    fast = ctx.decode(0, qd).cpu().numpy()
+    ctx.set_kernel("general")
+    slow = ctx.decode(0, qd).cpu().numpy()
+    ctx.set_kernel("auto")
+    assert ctx.status() == 0
+    assert np.all(fast[0] == 0.0)
+    for s, n in enumerate(lens):
+        if n == 0:
+            continue
+        want = refs[s].attend(qf[s])
+        assert np.allclose(slow[s], want, rtol=RTOL, atol=ATOL), f"general kernel, seq {s}"
+        err = np.abs(fast[s] - want).max()
+        assert np.allclose(fast[s], want, rtol=RTOL, atol=ATOL), f"seq {s}: max abs err {err}"
+        assert np.allclose(fast[s], slow[s], rtol=RTOL, atol=ATOL)
+
+
+def test_long_sequence_many_ctas_per_unit(torch_cuda):
+    """One long sequence of one KV head: its pages spread over every CTA of the persistent
+    kernel (one tile each), so the combine merges many partials; also the sequence-split
+    partial path of the same kernel."""
+    torch = torch_cuda
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, n, w, vb = 1, 4, 30000, 512, 3
+    k, v = make_kv(77, h, n, dtype=np.float16)
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=grp, value_bits=vb, hot_window=w,
+               max_tokens_per_seq=n, kv_dtype="float16", seed=77)
+    ctx.append(0, _dev(torch, k[None]), _dev(torch, v[None]))
+    q = make_q(77, grp)
+    qd = _dev(torch, q[None])
+    fast = ctx.decode(0, qd)[0].cpu().numpy()
+    ctx.set_kernel("general")
+    slow = ctx.decode(0, qd)[0].cpu().numpy()
+    ctx.set_kernel("auto")
+    assert np.allclose(fast, slow, rtol=RTOL, atol=ATOL), np.abs(fast - slow).max()
+    nb = ctx.lengths(0, 0)[1] // ctx.block_tokens
+    world = 3
+    parts = [ctx.decode_partial(0, qd, nb * r // world, nb * (r + 1) // world,
+                                with_hot=(r == world - 1)).clone() for r in range(world)]
+    merged = ctx.lse_combine(torch.stack(parts).reshape(world, grp, 130)).cpu().numpy()
+    assert np.allclose(merged, fast, rtol=1e-3, atol=1e-4), np.abs(merged - fast).max()
+    assert ctx.status() == 0
+    # dequantise-then-attend on the device getters, in float64 on the host
+    kd, vd = ctx.dequant(0, 0, 0, n)
+    kd, vd = kd.cpu().numpy().astype(np.float64), vd.cpu().numpy().astype(np.float64)
+    sc = np.einsum("gd,sd->gs", q.astype(np.float64), kd[0]) / np.sqrt(128.0)
+    p = np.exp(sc - sc.max(axis=1, keepdims=True))
+    want = (p / p.sum(axis=1, keepdims=True)) @ vd[0]
+    assert np.allclose(fast, want, rtol=RTOL, atol=ATOL), np.abs(fast - want).max()
+
+
 def test_facade_matches_reference_api(torch_cuda):
     """TurboQuantKVCache: the reference's constructor, append, getters, fused_decode,
     memory_stats and clear, checked on the reference's own cache fixture."""

@@ -37,7 +37,7 @@ class TqGeom(C.Structure):
         ("k_bytes", C.c_int32), ("v_bytes", C.c_int32), ("v_off", C.c_int32),
         ("norm_off", C.c_int32), ("scale_off", C.c_int32), ("mean_off", C.c_int32),
         ("page_bytes", C.c_int32), ("pool_entries", C.c_int32), ("max_splits", C.c_int32),
-        ("reserved_", C.c_int32),
+        ("hdr_off", C.c_int32), ("ent_off", C.c_int32), ("reserved_", C.c_int32),
     ]
 
 
@@ -85,6 +85,7 @@ SIGNATURES = {
     "tq_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
     "tq_decode_bytes": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_double)]),
     "tq_last_launches": (C.c_int32, [C.c_void_p]),
+    "tq_set_kernel": (C.c_int32, [C.c_void_p, C.c_int32]),
     "tq_profile_enable": (C.c_int32, [C.c_void_p, C.c_int32]),
     "tq_profile_read": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double),
                                     C.POINTER(C.c_int32)]),

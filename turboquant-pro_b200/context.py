@@ -325,6 +325,11 @@ class KVContext:
     def last_launches(self) -> int:
         return int(self._lib.tq_last_launches(self._h))
 
+    def set_kernel(self, which: str = "auto") -> None:
+        """``"auto"``: tensor-core kernel where the geometry allows; ``"general"``: always the
+        general-shape float32 kernel."""
+        check(self._lib.tq_set_kernel(self._h, {"auto": 0, "general": 1}[which]))
+
     def profile(self, on: bool) -> None:
         """Bracket the attention and combine kernels of every decode with CUDA events."""
         check(self._lib.tq_profile_enable(self._h, int(bool(on))))

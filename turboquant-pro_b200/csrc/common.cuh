@@ -22,6 +22,9 @@ constexpr int TQ_MAX_K_OUT = 32;   // most outliers per channel the key encoder 
 constexpr int TQ_MAX_G = 16;       // largest GQA group
 constexpr int TQ_PART_STRIDE = 2 + TQ_D;  // floats per partial state (m, l, acc[D])
 
+constexpr int TQ_INLINE_CAP = 768;  // outlier entries stored inside the page itself
+constexpr int TQ_HDR_BYTES = 640;   // page header: PageHeader + row starts (uint16 x 257)
+
 // bit 0 of the device status word: an outlier pool overflowed
 constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
 
@@ -35,6 +38,10 @@ constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
 //             +norm_off   value norms, float32 per token
 //             +scale_off  key scale per channel (max |x - mean|), float32
 //             +mean_off   key zero-point per channel, float32
+//             +hdr_off    PageHeader {outlier count, offset into the pool slab}, then
+//                         at +16 the start index of every token's outliers (uint16 x
+//                         (tokens + 1)): the side-list is grouped by token
+//             +ent_off    the first TQ_INLINE_CAP outlier entries (the rest only in the pool)
 // hot_k/v   [L][B][H][hot_cap][D] of kv_dtype; token at position p lives in slot p % hot_cap
 // pool_dec  [L][B][H][pool_entries] uint32: fp16 delta | channel << 16 | token << 24
 // pool_val  same shape, uint16: the outlier's fp16 value (kept for export / dequant)
@@ -65,6 +72,7 @@ struct tq_ctx {
   // one kernels read, both are advanced together by tq_append
   std::vector<int32_t> len;
   int last_launches;
+  bool force_generic = false;  // route every decode through the general-shape kernel
   // optional per-kernel timing: event triples (before attention, after it, after combine)
   bool prof_on = false;
   int prof_n = 0;
@@ -102,15 +110,17 @@ TQ_HD size_t state_status_off(const tq_geom& g) {
 TQ_HD size_t state_bytes(const tq_geom& g) { return state_status_off(g) + 256; }
 
 // Value codes of a 16-token group.  Element (token t of the group, channel d) belongs to
-// "lane" l = (d / 16) * 4 + (t % 8) / 2 and, inside that lane's record, to pair
-// p = 2 * (d % 16) + t / 8; the pair packs tokens (t & ~1, t | 1) of channel d, the even
+// "lane" l = (d % 8) * 4 + (t % 8) / 2 and, inside that lane's record, to pair
+// p = 2 * (d / 8) + t / 8; the pair packs tokens (t & ~1, t | 1) of channel d, the even
 // token in the low bits.  A lane record is 32 pairs: 32 bytes at 4 bits, 24 bytes at 3
 // bits.  Records are stored part-major ([part][lane]) in parts of 16 (4-bit) or 8 (3-bit)
 // bytes, so that one warp reads a part with one conflict-free vector load, and the pair
-// layout is exactly the B fragment of an m16n8k16 tensor-core tile (k = token, n = channel).
+// layout is exactly the A fragment of an m16n8k16 tensor-core tile whose rows are channels
+// and whose k index is the token: lane (r, c) of a warp owns channels r, r+8, r+16, ...
+// and tokens 2c, 2c+1, 2c+8, 2c+9.
 TQ_HD int v_group_bytes(int bits) { return TQ_GROUP_TOK * TQ_D * bits / 8; }
-TQ_HD int v_lane(int t, int d) { return (d >> 4) * 4 + ((t & 7) >> 1); }
-TQ_HD int v_pair(int t, int d) { return 2 * (d & 15) + (t >> 3); }
+TQ_HD int v_lane(int t, int d) { return (d & 7) * 4 + ((t & 7) >> 1); }
+TQ_HD int v_pair(int t, int d) { return 2 * (d >> 3) + (t >> 3); }
 
 // byte offset inside the group of byte `byte_in_record` of lane `l`'s record
 TQ_HD int v_record_byte_off(int bits, int l, int byte_in_record) {
@@ -191,4 +201,5 @@ int tq_launch_lse_combine(const float* mlo, int n_parts, int n_rows, int head_di
                           cudaStream_t st);
 int tq_launch_dequant(tq_ctx* ctx, int layer, int seq, int start, int end, float* k_out,
                       float* v_out, cudaStream_t st);
+size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units);
 int tq_launch_clear(tq_ctx* ctx, int layer, int seq_begin, int seq_count, cudaStream_t st);

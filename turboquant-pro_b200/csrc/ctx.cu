@@ -80,7 +80,9 @@ int32_t tq_geom_finish(tq_geom* g) {
   g->norm_off = g->v_off + g->v_bytes;
   g->scale_off = g->norm_off + g->block_tokens_pad * 4;
   g->mean_off = g->scale_off + TQ_D * 4;
-  g->page_bytes = (int)align_up(g->mean_off + TQ_D * 4, 128);
+  g->hdr_off = (int)align_up(g->mean_off + TQ_D * 4, 128);
+  g->ent_off = g->hdr_off + TQ_HDR_BYTES;
+  g->page_bytes = (int)align_up(g->ent_off + TQ_INLINE_CAP * 4, 128);
   if (g->outlier_k > 0) {
     int64_t nominal = (int64_t)g->max_blocks * g->outlier_k * TQ_D;
     int64_t cap = nominal + nominal / 4 + 4096;
@@ -108,8 +110,8 @@ int32_t tq_ctx_sizes(const tq_geom* g, tq_sizes* out) {
   out->state = align_up(state_bytes(*g), 256);
   out->tables = align_up(sizeof(Tables), 256);
   size_t layer_units = (size_t)g->n_seqs * g->n_kv_heads;
-  out->scratch =
-      align_up(layer_units * g->max_splits * g->group * TQ_PART_STRIDE * sizeof(float), 256);
+  size_t generic = layer_units * g->max_splits * g->group * TQ_PART_STRIDE * sizeof(float);
+  out->scratch = align_up(std::max(generic, tq_mma_scratch_bytes(*g, layer_units)), 256);
   return TQ_OK;
 }
 
@@ -186,6 +188,13 @@ int32_t tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx != nullptr)
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
   delete ctx;
+  return TQ_OK;
+}
+
+int32_t tq_set_kernel(tq_ctx* ctx, int32_t which) {
+  TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
+  TQ_REQUIRE(which == 0 || which == 1, TQ_ERR_INVALID, "which must be 0 (auto) or 1 (general)");
+  ctx->force_generic = which == 1;
   return TQ_OK;
 }
 

@@ -109,7 +109,10 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
   }
 
   const int tok = lane >> 1, half = lane & 1;  // key-score mapping: 2 lanes per token
-  const int dq = lane >> 2, c4 = lane & 3;     // value mapping: lane owns 16 channels, 4 tokens
+  // value mapping: a lane owns 4 tokens and 16 channels (cold codes: dq, dq+8, dq+16, ...;
+  // hot rows: 16dq .. 16dq+15)
+  const int dq = lane >> 2, c4 = lane & 3;
+  const bool cold_split = split < a.ns_cold;
 
   // online-softmax update of one 16-token group whose raw scores (already scaled, -inf
   // when masked) sit in sc[gg]; leaves p * weight in p_s for the value pass
@@ -332,7 +335,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
     }
     if (c4 == 0) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) mrg_acc[warp][gg][dq * 16 + i] = acc[gg][i];
+      for (int i = 0; i < 16; ++i)
+        mrg_acc[warp][gg][cold_split ? i * 8 + dq : dq * 16 + i] = acc[gg][i];
     }
   }
   __syncthreads();

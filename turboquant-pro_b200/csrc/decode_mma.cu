@@ -1,9 +1,821 @@
-// Tensor-core decode-on-codes kernel (placeholder until the kernel lands: reports that it
-// does not handle the launch, so the general-shape kernel runs).
+// Decode-on-codes attention for the common geometry (256-token cold blocks, head_dim 128,
+// GQA group <= 8): a persistent, warp-specialised kernel.
+//
+//   warp 8      streams tiles HBM -> shared memory with bulk asynchronous copies
+//               (cp.async.bulk + mbarrier transaction counts) through a ring of stages;
+//               a tile is one cold page (~30-34 KB of codes, norms, scales) or one slice
+//               of the hot window (32 KB of 16/32-bit K and V rows)
+//   warp 9      prepares the query-dependent, page-dependent operands of a landed tile:
+//               w = q * scale split into fp16 hi/lo tensor-core fragments, bias = q . mean,
+//               and the per-token outlier corrections
+//   warps 0-7   consume tiles: 4-bit key codes and 3/4-bit value code pairs are turned
+//               into fp16 pairs by one conflict-free shared-memory table lookup each and
+//               fed straight into m16n8k16 tensor-core tiles as register fragments
+//               (scores: M = query group padded to 16 with the lo parts in rows 8-15,
+//               N = 8 tokens, K = 16 channels; values: M = 16 channels, N = 8 query
+//               heads, K = 16 tokens); online softmax in fp32 registers.  K and V are
+//               never materialised.
+//
+// Work is a flat list of tiles over all (sequence, KV head) units of the layer, cut into
+// equal contiguous shares, one per CTA (one CTA per SM), so ragged contexts balance.
+// Every consumer warp keeps its own softmax state and writes its own partial
+// (m, l, acc[D]); the combine kernel merges them in a fixed order and applies the single
+// inverse rotation of the value accumulator.
+//
+// All waits are bounded: a wait that runs out sets bit 1 of the status word and an abort
+// flag that makes every later wait return at once, so the kernel always terminates.
 #include "common.cuh"
 
-int tq_launch_decode_mma(tq_ctx*, int, const void*, int, int, int, int, float*, float*,
-                         cudaStream_t, bool* handled) {
+namespace {
+
+constexpr int CW = 8;                       // consumer warps
+constexpr int THREADS = (CW + 2) * 32;      // + copy warp + prepare warp
+constexpr int MAX_UNITS = 512;
+constexpr int BLK = 256;                    // tokens per cold page
+constexpr float NEG_BIG = -1.0e30f;
+constexpr int SPIN_LIMIT = 1 << 21;
+constexpr int STATUS_TIMEOUT = 2;
+
+struct MmaArgs {
+  tq_geom g;
+  const uint8_t* pages;
+  const uint8_t* hot_k;
+  const uint8_t* hot_v;
+  const uint32_t* pool_dec;
+  const PageMeta* page_meta;
+  const int32_t* seq_len;
+  const Tables* tables;
+  const void* q;
+  float* partials;
+  float* out;
+  float* mlo;
+  int32_t* status;
+  int layer, q_dtype, n_units, n_cta;
+  int block_begin, block_end, with_hot;
+  float scale_log2;
+};
+
+// ---- PTX helpers --------------------------------------------------------------------------
+TQ_DEV uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+TQ_DEV void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+TQ_DEV void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+TQ_DEV void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+TQ_DEV uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// plain, non-multicast bulk copy from this GPU's global memory into this CTA's shared memory
+TQ_DEV void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+TQ_DEV uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+TQ_DEV uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+TQ_DEV uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+TQ_DEV void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+TQ_DEV uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *(uint32_t*)&h;
+}
+// two bf16 in one word -> two fp16 in one word (exact for magnitudes in fp16 range)
+TQ_DEV uint32_t bf16x2_to_h2(uint32_t w) {
+  return pack_h2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+// ---- shared-memory plan --------------------------------------------------------------------
+// Per stage: [data | fragments | corr | bias].  Sizes depend on the GQA group (corr rows)
+// and the value width (page size); the table sizes on the value width.
+template <int G, int VB>
+struct Smem {
+  // a tile is a whole page (codes, norms, scales, header, in-page outlier entries: 34432 B
+  // at V3, 38528 B at V4) or 32 KB of hot rows
+  static constexpr int DATA_BYTES = VB == 3 ? 34432 : 38528;
+  static constexpr int FRAG_OFF = DATA_BYTES;
+  static constexpr int CORR_OFF = FRAG_OFF + 8 * 32 * 16;
+  static constexpr int BIAS_OFF = CORR_OFF + G * BLK * 4;
+  static constexpr int STAGE_BYTES = BIAS_OFF + 64;
+  static constexpr int LUTK_BYTES = 256 * 128;
+  static constexpr int LUTV_BYTES = (VB == 3 ? 64 : 256) * 128;
+  static constexpr int FIXED = 8192 /* plan */ + 2 * 8 * 128 * 4 /* q copies */ + 256 /* bars */;
+  static constexpr int NSTAGE =
+      (232448 - 1024 - LUTK_BYTES - LUTV_BYTES - FIXED) / STAGE_BYTES >= 3 ? 3 : 2;
+  static constexpr int TOTAL = LUTK_BYTES + LUTV_BYTES + FIXED + NSTAGE * STAGE_BYTES;
+};
+
+struct Plan {  // lives in shared memory
+  int P[MAX_UNITS + 1];    // prefix sums of tiles per unit
+  int hot_start[MAX_UNITS];  // first hot token position of each unit's sequence
+  short nb[MAX_UNITS];     // cold tiles of each unit
+  short b0[MAX_UNITS];     // first cold block attended
+  short hot_len[MAX_UNITS];  // hot tokens attended
+};
+
+struct Tile {
+  int u, kind, idx;  // kind 0: cold page `idx` (absolute block), 1: hot tile `idx`
+};
+
+TQ_DEV int hot_tile_tokens(int dt) { return dt == TQ_F32 ? 32 : 64; }
+
+// cold / hot tile counts of a unit, identical in the attention and the combine kernel
+TQ_DEV void unit_tiles(const MmaArgs& a, int unit, int& nb, int& ht, int& b0, int& hot_start,
+                       int& hot_len) {
+  const tq_geom& g = a.g;
+  const int seq = unit / g.n_kv_heads;
+  const int N = a.seq_len[a.layer * g.n_seqs + seq];
+  const int nbt = n_cold_blocks(N, g.hot_window, BLK);
+  b0 = min(a.block_begin, nbt);
+  const int b1 = a.block_end < 0 ? nbt : min(a.block_end, nbt);
+  nb = max(b1 - b0, 0);
+  hot_start = nbt * BLK;
+  hot_len = a.with_hot ? N - nbt * BLK : 0;
+  const int htt = hot_tile_tokens(g.kv_dtype);
+  ht = (hot_len + htt - 1) / htt;
+}
+
+// Fills plan->P / plan->nb; every thread of the CTA must call it.
+TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int tid, int nthreads) {
+  for (int u = tid; u < a.n_units; u += nthreads) {
+    int nb, ht, b0, hs, hl;
+    unit_tiles(a, u, nb, ht, b0, hs, hl);
+    plan->nb[u] = (short)nb;
+    plan->b0[u] = (short)b0;
+    plan->hot_start[u] = hs;
+    plan->hot_len[u] = (short)hl;
+    plan->P[u + 1] = nb + ht;  // cost, scanned below
+  }
+  __syncthreads();
+  if (tid < 32) {
+    int carry = 0;
+    for (int base = 0; base < a.n_units; base += 32) {
+      int i = base + tid;
+      int v = i < a.n_units ? plan->P[i + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (tid >= o) v += n;
+      }
+      if (i < a.n_units) plan->P[i + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (tid == 0) plan->P[0] = 0;
+  }
+  __syncthreads();
+}
+
+TQ_DEV int find_unit(const Plan* plan, int n_units, int pos) {
+  int lo = 0, hi = n_units - 1;  // largest u with P[u] <= pos
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (plan->P[mid] <= pos) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+struct Waiter {
+  volatile int* abort_flag;
+  int32_t* status;
+  TQ_DEV void wait(uint32_t bar, uint32_t parity) const {
+    for (int i = 0; i < SPIN_LIMIT; ++i) {
+      if (mbar_test(bar, parity)) return;
+      if ((i & 63) == 63) {
+        if (*abort_flag) return;
+        __nanosleep(64);
+      }
+    }
+    *abort_flag = 1;
+    atomicOr(status, STATUS_TIMEOUT);
+  }
+};
+
+// fp16 hi / lo fragments of four consecutive weights of row r: {hi01, lo01, hi23, lo23}
+TQ_DEV uint4 frag_hilo(float w0, float w1, float w2, float w3) {
+  __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
+  float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+  uint4 o;
+  o.x = *(uint32_t*)&h01;
+  o.y = pack_h2(w0 - f01.x, w1 - f01.y);
+  o.z = *(uint32_t*)&h23;
+  o.w = pack_h2(w2 - f23.x, w3 - f23.y);
+  return o;
+}
+
+template <int G, int VB>
+__global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
+  using SM = Smem<G, VB>;
+  constexpr int NSTAGE = SM::NSTAGE;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const tq_geom& g = a.g;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, c = lane & 3;
+
+  uint8_t* lutk_p = smem;
+  uint8_t* lutv_p = lutk_p + SM::LUTK_BYTES;
+  Plan* plan = (Plan*)(lutv_p + SM::LUTV_BYTES);
+  static_assert(sizeof(Plan) <= 8192, "plan does not fit its shared-memory slot");
+  float* qg = (float*)((uint8_t*)plan + 8192);  // [G][128], prepare warp only
+  float* qc = qg + 8 * 128;                     // [128][G]
+  uint64_t* bars = (uint64_t*)(qc + 8 * 128);   // full[NSTAGE], ready[NSTAGE], empty[NSTAGE]
+  volatile int* abort_flag = (volatile int*)(bars + 12);
+  uint8_t* stages = (uint8_t*)bars + 256;
+
+  const uint32_t full0 = smem_addr(bars), ready0 = full0 + 8 * NSTAGE, empty0 = ready0 + 8 * NSTAGE;
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(ready0 + 8 * s, 32);
+      mbar_init(empty0 + 8 * s, CW);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // lookup tables: entry-major, one copy per lane so that a warp's 32 lookups never collide
+  {
+    float* small = qg;  // 32 floats of scratch until the prepare warp claims the area
+    if (tid < 16) small[tid] = a.tables->nf4[tid];
+    else if (tid < 32) small[tid] = a.tables->centroids[tid - 16];
+    __syncthreads();
+    for (int i = tid; i < 256 * 32; i += THREADS) {
+      int b = i >> 5;
+      ((uint32_t*)lutk_p)[i] = pack_h2(small[b & 15], small[b >> 4]);
+    }
+    constexpr int NV = VB == 3 ? 64 : 256;
+    for (int i = tid; i < NV * 32; i += THREADS) {
+      int b = i >> 5;
+      int ca = VB == 3 ? (b & 7) : (b & 15), cb = VB == 3 ? (b >> 3) : (b >> 4);
+      ((uint32_t*)lutv_p)[i] = pack_h2(small[16 + ca], small[16 + cb]);
+    }
+  }
+  build_plan(a, plan, tid, THREADS);  // contains the __syncthreads that publish all of the above
+
+  const int T = plan->P[a.n_units];
+  const int Q = (T + a.n_cta - 1) / a.n_cta;
+  const int lo = min((int)blockIdx.x * Q, T), hi = min(lo + Q, T);
+  if (lo >= hi) return;
+  const Waiter waiter{abort_flag, a.status};
+  const int htt = hot_tile_tokens(g.kv_dtype);
+  const int esz = elem_size(g.kv_dtype);
+
+  auto tile_at = [&](int pos, int& u_cursor) -> Tile {
+    while (pos >= plan->P[u_cursor + 1]) ++u_cursor;
+    Tile t;
+    t.u = u_cursor;
+    int j = pos - plan->P[u_cursor];
+    int nb = plan->nb[u_cursor];
+    t.kind = j >= nb;
+    t.idx = t.kind == 0 ? plan->b0[u_cursor] + j : j - nb;
+    return t;
+  };
+
+  // ============================== copy warp ==================================================
+  if (warp == CW) {
+    if (lane == 0) {
+      int u_cur = find_unit(plan, a.n_units, lo);
+      for (int pos = lo; pos < hi; ++pos) {
+        const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
+        Tile tl = tile_at(pos, u_cur);
+        const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
+        waiter.wait(empty0 + 8 * s, (k & 1) ^ 1);
+        if (*abort_flag) break;
+        const uint32_t dst = smem_addr(stages + (size_t)s * SM::STAGE_BYTES);
+        const uint32_t bar = full0 + 8 * s;
+        if (tl.kind == 0) {
+          const uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, tl.idx);
+          mbar_arrive_expect_tx(bar, (uint32_t)g.page_bytes);
+          bulk_g2s(dst, page, (uint32_t)g.page_bytes, bar);
+        } else {
+          const int slot = (plan->hot_start[tl.u] + tl.idx * htt) % g.hot_cap;
+          const size_t off = (hot_offset_elems(g, a.layer, seq, head) + (size_t)slot * TQ_D) * esz;
+          const uint32_t bytes = (uint32_t)(htt * TQ_D * esz);
+          mbar_arrive_expect_tx(bar, 2 * bytes);
+          bulk_g2s(dst, a.hot_k + off, bytes, bar);
+          bulk_g2s(dst + bytes, a.hot_v + off, bytes, bar);
+        }
+      }
+      // never leave with copies in flight: the last NSTAGE tiles are waited for here too
+      const int total = hi - lo;
+      for (int t = max(0, total - NSTAGE); t < total; ++t)
+        waiter.wait(full0 + 8 * (t % NSTAGE), (t / NSTAGE) & 1);
+    }
+    return;
+  }
+
+  // ============================== prepare warp ===============================================
+  if (warp == CW + 1) {
+    int u_cur = find_unit(plan, a.n_units, lo);
+    int q_unit = -1;
+    for (int pos = lo; pos < hi; ++pos) {
+      const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
+      Tile tl = tile_at(pos, u_cur);
+      const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
+      if (tl.u != q_unit) {  // this unit's query rows, both layouts, fp32
+        q_unit = tl.u;
+        __syncwarp();
+        for (int i = lane; i < G * TQ_D; i += 32) {
+          int gg = i / TQ_D, d = i % TQ_D;
+          size_t qi = ((size_t)seq * g.n_q_heads + head * G + gg) * TQ_D + d;
+          float v = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
+                    : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
+                                          : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
+          qg[gg * TQ_D + d] = v;
+          qc[d * G + gg] = v;
+        }
+        __syncwarp();
+      }
+      uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
+      waiter.wait(full0 + 8 * s, k & 1);
+      uint4* frag = (uint4*)(st + SM::FRAG_OFF);
+      const bool cold = tl.kind == 0;
+      const float* scale = (const float*)(st + g.scale_off);
+      const float* mean = (const float*)(st + g.mean_off);
+      float bias = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d0 = 32 * c + 4 * j;
+        float4 q4 = r < G ? *(const float4*)&qg[r * TQ_D + d0] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 s4 = cold ? *(const float4*)&scale[d0] : make_float4(1.f, 1.f, 1.f, 1.f);
+        if (cold) {
+          float4 m4 = *(const float4*)&mean[d0];
+          bias += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
+        }
+        frag[j * 32 + lane] = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
+      }
+      if (cold) {
+        bias += __shfl_xor_sync(0xffffffffu, bias, 1);
+        bias += __shfl_xor_sync(0xffffffffu, bias, 2);
+        float* bias_s = (float*)(st + SM::BIAS_OFF);
+        if (c == 0) bias_s[r] = r < G ? bias : 0.0f;
+        // outlier corrections: the side-list is grouped by token, so each lane sums the
+        // entries of its own tokens and no atomics are needed
+        float* corr = (float*)(st + SM::CORR_OFF);
+        const PageMeta pm = *(const PageMeta*)(st + g.hdr_off);
+        const uint16_t* rows = (const uint16_t*)(st + g.hdr_off + 16);
+        const uint32_t* ent_s = (const uint32_t*)(st + g.ent_off);
+        const uint32_t* ent_g =
+            a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
+#pragma unroll 1
+        for (int tk = lane; tk < BLK; tk += 32) {
+          float cacc[G];
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg) cacc[gg] = 0.0f;
+          const int e1 = rows[tk + 1];
+          for (int e = rows[tk]; e < e1; ++e) {
+            const uint32_t wv = e < TQ_INLINE_CAP ? ent_s[e] : ent_g[e];
+            const float delta = __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu)));
+            const int col = (wv >> 16) & 255;
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) cacc[gg] += qc[col * G + gg] * delta;
+          }
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg) corr[gg * BLK + tk] = cacc[gg];
+        }
+      }
+      mbar_arrive(ready0 + 8 * s);  // each lane releases its own writes
+    }
+    return;
+  }
+
+  // ============================== consumer warps =============================================
+  const uint32_t lutk = smem_addr(lutk_p) + lane * 4;
+  const uint32_t lutv = smem_addr(lutv_p) + lane * 4;
+  const int rg = r < G ? r : G - 1;
+  float m_run = NEG_BIG, l_run = 0.0f;
+  float acc[8][4];
+  auto reset_state = [&]() {
+    m_run = NEG_BIG;
+    l_run = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
+  };
+  reset_state();
+
+  auto flush = [&](int u, int kind) {
+    const int active = kind == 0 ? CW : htt / 16;
+    if (warp >= active) return;
+    float l = l_run;
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    float* pp = a.partials +
+                ((((size_t)u + blockIdx.x) * 2 + kind) * CW + warp) * (size_t)(G * TQ_PART_STRIDE);
+    if (c == 0 && r < G) {
+      pp[r * TQ_PART_STRIDE] = m_run;
+      pp[r * TQ_PART_STRIDE + 1] = l;
+    }
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int y = 0; y < 2; ++y) {
+          const int gg = 2 * c + y;
+          const int d = kind == 0 ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
+          if (gg < G) pp[gg * TQ_PART_STRIDE + 2 + d] = acc[mt][2 * x + y];
+        }
+  };
+
+  // online-softmax update with the four scores of this thread's row (two 8-token tiles,
+  // two tokens each); returns the probabilities in sv
+  auto softmax16 = [&](float (&sv)[2][2], const bool (&ok)[2][2]) {
+    float mx = NEG_BIG;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) mx = fmaxf(mx, ok[i][j] ? sv[i][j] : NEG_BIG);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float cf = exp2f(m_run - m_new);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        sv[i][j] = ok[i][j] ? exp2f(sv[i][j] - m_new) : 0.0f;
+        sum += sv[i][j];
+      }
+    l_run = l_run * cf + sum;
+    if (__any_sync(0xffffffffu, m_new > m_run)) {
+      // the accumulator columns of this thread belong to rows 2c and 2c+1
+      const float f0 = __shfl_sync(0xffffffffu, cf, 8 * c);
+      const float f1 = __shfl_sync(0xffffffffu, cf, 8 * c + 4);
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        acc[mt][0] *= f0;
+        acc[mt][1] *= f1;
+        acc[mt][2] *= f0;
+        acc[mt][3] *= f1;
+      }
+    }
+    m_run = m_new;
+  };
+
+  int u_cur = find_unit(plan, a.n_units, lo);
+  int cur_u = -1, cur_kind = -1;
+  for (int pos = lo; pos < hi; ++pos) {
+    const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
+    const Tile tl = tile_at(pos, u_cur);
+    if (tl.u != cur_u || tl.kind != cur_kind) {
+      if (cur_u >= 0) flush(cur_u, cur_kind);
+      reset_state();
+      cur_u = tl.u;
+      cur_kind = tl.kind;
+    }
+    const uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
+    const uint32_t st_a = smem_addr(st);
+    waiter.wait(ready0 + 8 * s, k & 1);
+    waiter.wait(full0 + 8 * s, k & 1);
+
+    uint32_t areg[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 f = lds128(st_a + SM::FRAG_OFF + (j * 32 + lane) * 16);
+      areg[j][0] = f.x; areg[j][1] = f.y; areg[j][2] = f.z; areg[j][3] = f.w;
+    }
+
+    if (tl.kind == 0) {
+      const float bias = ((const float*)(st + SM::BIAS_OFF))[rg];
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const int T0 = 32 * warp + 16 * half;
+        float sv[2][2];
+        const bool ok[2][2] = {{true, true}, {true, true}};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const uint4 kc = lds128(st_a + (T0 + 8 * nt + r) * 64 + c * 16);
+          const uint32_t kw[4] = {kc.x, kc.y, kc.z, kc.w};
+          float C[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t w = kw[j >> 1];
+            const uint32_t i0 = __byte_perm(w, 0, 0x4440 + 2 * (j & 1));
+            const uint32_t i1 = __byte_perm(w, 0, 0x4441 + 2 * (j & 1));
+            const uint32_t b0 = lds32(lutk + i0 * 128), b1 = lds32(lutk + i1 * 128);
+            mma16816(C, areg[j], b0, b1);
+          }
+          const uint2 cr = lds64(st_a + SM::CORR_OFF + (rg * BLK + T0 + 8 * nt + 2 * c) * 4);
+          sv[nt][0] = (C[0] + C[2] + bias + __uint_as_float(cr.x)) * a.scale_log2;
+          sv[nt][1] = (C[1] + C[3] + bias + __uint_as_float(cr.y)) * a.scale_log2;
+          if (r >= G) sv[nt][0] = sv[nt][1] = 0.0f;
+        }
+        softmax16(sv, ok);
+        const uint2 n0 = lds64(st_a + g.norm_off + (T0 + 2 * c) * 4);
+        const uint2 n1 = lds64(st_a + g.norm_off + (T0 + 8 + 2 * c) * 4);
+        const uint32_t pb0 = pack_h2(sv[0][0] * __uint_as_float(n0.x), sv[0][1] * __uint_as_float(n0.y));
+        const uint32_t pb1 = pack_h2(sv[1][0] * __uint_as_float(n1.x), sv[1][1] * __uint_as_float(n1.y));
+        const int gq = 2 * warp + half;
+        if (VB == 4) {
+          const uint32_t gb = st_a + g.v_off + gq * 1024 + lane * 16;
+          const uint4 r0 = lds128(gb), r1 = lds128(gb + 512);
+          const uint32_t rec[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            const uint32_t w = rec[mt];  // pairs 4mt .. 4mt+3
+            uint32_t af[4];
+            af[0] = lds32(lutv + __byte_perm(w, 0, 0x4440) * 128);
+            af[1] = lds32(lutv + __byte_perm(w, 0, 0x4442) * 128);
+            af[2] = lds32(lutv + __byte_perm(w, 0, 0x4441) * 128);
+            af[3] = lds32(lutv + __byte_perm(w, 0, 0x4443) * 128);
+            mma16816(acc[mt], af, pb0, pb1);
+          }
+        } else {
+          const uint32_t gb = st_a + g.v_off + gq * 768 + lane * 8;
+          const uint2 r0 = lds64(gb), r1 = lds64(gb + 256), r2 = lds64(gb + 512);
+          const uint32_t rec[7] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, 0u};
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            uint32_t af[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              // a0: pair 4mt, a1: pair 4mt+2, a2: pair 4mt+1, a3: pair 4mt+3
+              const int p = 4 * mt + ((e & 1) << 1) + (e >> 1);
+              const int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
+              const uint32_t f = sh > 26 ? __funnelshift_r(rec[wd], rec[wd + 1], sh) : rec[wd] >> sh;
+              af[e] = lds32(lutv + (f & 63u) * 128);
+            }
+            mma16816(acc[mt], af, pb0, pb1);
+          }
+        }
+      }
+    } else if (warp < htt / 16) {
+      // ---- hot tile: uncompressed rows, same tensor-core tiles, no tables ----------------
+      const int hot_len = plan->hot_len[tl.u];
+      const int T0 = 16 * warp;                 // first token of this warp inside the tile
+      const int base_tok = tl.idx * htt + T0;   // ... inside the hot window
+      const uint32_t kbase = st_a, vbase = st_a + htt * TQ_D * esz;
+      float sv[2][2];
+      bool ok[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const uint32_t row = kbase + ((T0 + 8 * nt + r) * TQ_D + 32 * c) * esz;
+        uint32_t kw[16];
+        if (esz == 2) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 v4 = lds128(row + 16 * i);
+            kw[4 * i] = v4.x; kw[4 * i + 1] = v4.y; kw[4 * i + 2] = v4.z; kw[4 * i + 3] = v4.w;
+          }
+          if (g.kv_dtype == TQ_BF16) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) kw[i] = bf16x2_to_h2(kw[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v4 = lds128(row + 16 * i);
+            kw[2 * i] = pack_h2(__uint_as_float(v4.x), __uint_as_float(v4.y));
+            kw[2 * i + 1] = pack_h2(__uint_as_float(v4.z), __uint_as_float(v4.w));
+          }
+        }
+        float C[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mma16816(C, areg[j], kw[2 * j], kw[2 * j + 1]);
+        sv[nt][0] = (C[0] + C[2]) * a.scale_log2;
+        sv[nt][1] = (C[1] + C[3]) * a.scale_log2;
+        ok[nt][0] = base_tok + 8 * nt + 2 * c < hot_len;
+        ok[nt][1] = base_tok + 8 * nt + 2 * c + 1 < hot_len;
+        if (r >= G) {
+          sv[nt][0] = sv[nt][1] = 0.0f;
+          ok[nt][0] = ok[nt][1] = true;
+        }
+      }
+      softmax16(sv, ok);
+      const uint32_t pb0 = pack_h2(sv[0][0], sv[0][1]);
+      const uint32_t pb1 = pack_h2(sv[1][0], sv[1][1]);
+      // value rows of tokens 2c, 2c+1, 2c+8, 2c+9, channels 16r .. 16r+15, as fp16 pairs
+      uint32_t vr[4][8];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int tloc = 2 * c + (q4 & 1) + 8 * (q4 >> 1);
+        const bool valid = base_tok + tloc < hot_len;
+        const uint32_t row = vbase + ((T0 + tloc) * TQ_D + 16 * r) * esz;
+        if (esz == 2) {
+          const uint4 x0 = lds128(row), x1 = lds128(row + 16);
+          vr[q4][0] = x0.x; vr[q4][1] = x0.y; vr[q4][2] = x0.z; vr[q4][3] = x0.w;
+          vr[q4][4] = x1.x; vr[q4][5] = x1.y; vr[q4][6] = x1.z; vr[q4][7] = x1.w;
+          if (g.kv_dtype == TQ_BF16) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vr[q4][i] = bf16x2_to_h2(vr[q4][i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 v4 = lds128(row + 16 * i);
+            vr[q4][2 * i] = pack_h2(__uint_as_float(v4.x), __uint_as_float(v4.y));
+            vr[q4][2 * i + 1] = pack_h2(__uint_as_float(v4.z), __uint_as_float(v4.w));
+          }
+        }
+        if (!valid) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) vr[q4][i] = 0u;
+        }
+      }
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        uint32_t af[4];
+        af[0] = __byte_perm(vr[0][mt], vr[1][mt], 0x5410);  // channel 16r+2mt,   tokens 2c, 2c+1
+        af[1] = __byte_perm(vr[0][mt], vr[1][mt], 0x7632);  // channel 16r+2mt+1
+        af[2] = __byte_perm(vr[2][mt], vr[3][mt], 0x5410);  // tokens 2c+8, 2c+9
+        af[3] = __byte_perm(vr[2][mt], vr[3][mt], 0x7632);
+        mma16816(acc[mt], af, pb0, pb1);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * s);
+  }
+  if (cur_u >= 0) flush(cur_u, cur_kind);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the per-warp
+// partials of every CTA that owned tiles of the unit (fixed order: CTA, cold before hot,
+// warp), un-rotates the cold part once and writes the output or the (m, l, o) state.
+// Partial maxima are in the log2 domain.
+// ---------------------------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
+  const tq_geom& g = a.g;
+  const int unit = blockIdx.x, e = threadIdx.x;
+  const int seq = unit / g.n_kv_heads, head = unit % g.n_kv_heads;
+  __shared__ Plan plan;
+  __shared__ float cs[G][TQ_D];
+  build_plan(a, &plan, e, TQ_D);
+  const int T = plan.P[a.n_units];
+  const int Q = max((T + a.n_cta - 1) / a.n_cta, 1);
+  const int p0 = plan.P[unit], p1 = plan.P[unit + 1], pc = p0 + plan.nb[unit];
+  const int hot_warps = hot_tile_tokens(g.kv_dtype) / 16;
+  float M[G], L[G], C[G], Hh[G];
+#pragma unroll
+  for (int gg = 0; gg < G; ++gg) {
+    M[gg] = NEG_BIG;
+    L[gg] = C[gg] = Hh[gg] = 0.0f;
+  }
+  if (p1 > p0) {
+    const int i0 = p0 / Q, i1 = (p1 - 1) / Q;
+    for (int pass = 0; pass < 2; ++pass)
+      for (int i = i0; i <= i1; ++i) {
+        const int lo = i * Q, hi = lo + Q;
+        for (int kind = 0; kind < 2; ++kind) {
+          const bool has = kind == 0 ? (max(lo, p0) < min(hi, pc)) : (max(lo, pc) < min(hi, p1));
+          if (!has) continue;
+          const int nw = kind == 0 ? CW : hot_warps;
+          for (int w = 0; w < nw; ++w) {
+            const float* pp = a.partials + ((((size_t)unit + i) * 2 + kind) * CW + w) *
+                                               (size_t)(G * TQ_PART_STRIDE);
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) {
+              const float m = pp[gg * TQ_PART_STRIDE], l = pp[gg * TQ_PART_STRIDE + 1];
+              if (l <= 0.0f) continue;
+              if (pass == 0) {
+                M[gg] = fmaxf(M[gg], m);
+              } else {
+                const float wgt = exp2f(m - M[gg]);
+                L[gg] += l * wgt;
+                const float v = pp[gg * TQ_PART_STRIDE + 2 + e] * wgt;
+                if (kind == 0) C[gg] += v; else Hh[gg] += v;
+              }
+            }
+          }
+        }
+      }
+  }
+#pragma unroll
+  for (int gg = 0; gg < G; ++gg) cs[gg][e] = C[gg];
+  __syncthreads();
+  float o[G];
+#pragma unroll
+  for (int gg = 0; gg < G; ++gg) o[gg] = 0.0f;
+  for (int d = 0; d < TQ_D; ++d) {
+    const float pv = a.tables->pi[d * TQ_D + e];
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg) o[gg] += cs[gg][d] * pv;
+  }
+#pragma unroll
+  for (int gg = 0; gg < G; ++gg) {
+    const size_t row = (size_t)seq * g.n_q_heads + head * G + gg;
+    const float val = o[gg] + Hh[gg];
+    if (a.mlo != nullptr) {
+      float* rr = a.mlo + row * TQ_PART_STRIDE;
+      if (e == 0) {
+        // natural-log domain, like the general kernel and tq_lse_combine
+        rr[0] = L[gg] > 0.0f ? M[gg] * 0.6931471805599453f : -INFINITY;
+        rr[1] = L[gg];
+      }
+      rr[2 + e] = val;
+    } else {
+      a.out[row * TQ_D + e] = L[gg] > 0.0f ? val / L[gg] : 0.0f;
+    }
+  }
+}
+
+template <int G, int VB>
+int launch_t(const MmaArgs& a, cudaStream_t st, tq_ctx* ctx) {
+  using SM = Smem<G, VB>;
+  static bool attr_set[16] = {};
+  int dev = ctx->device;
+  if (!attr_set[dev & 15]) {
+    TQ_CUDA(cudaFuncSetAttribute(decode_mma_kernel<G, VB>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL));
+    attr_set[dev & 15] = true;
+  }
+  cudaEvent_t e0 = tq_prof_event(ctx, 0), e1 = tq_prof_event(ctx, 1), e2 = tq_prof_event(ctx, 2);
+  if (e0) cudaEventRecord(e0, st);
+  decode_mma_kernel<G, VB><<<a.n_cta, THREADS, SM::TOTAL, st>>>(a);
+  if (e1) cudaEventRecord(e1, st);
+  combine_mma_kernel<G><<<a.n_units, TQ_D, 0, st>>>(a);
+  if (e2) {
+    cudaEventRecord(e2, st);
+    tq_prof_commit(ctx);
+  }
+  ctx->last_launches = 2;
+  TQ_CUDA(cudaGetLastError());
+  return TQ_OK;
+}
+
+}  // namespace
+
+// Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
+size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
+  return (units + 192) * 2 * CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
+}
+
+int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
+                         int block_end, int with_hot, float* out, float* mlo, cudaStream_t st,
+                         bool* handled) {
+  const tq_geom& g = ctx->g;
+  *handled = false;
+  const int n_units = g.n_seqs * g.n_kv_heads;
+  const int G = g.group;
+  if (ctx->force_generic) return TQ_OK;
+  if (g.block_tokens != BLK || (G != 1 && G != 2 && G != 4 && G != 8) || n_units > MAX_UNITS ||
+      g.hot_cap % 64 != 0)
+    return TQ_OK;
+  int sm_count = 148;
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
+  MmaArgs a;
+  a.g = g;
+  a.pages = (const uint8_t*)ctx->b.pages;
+  a.hot_k = (const uint8_t*)ctx->b.hot_k;
+  a.hot_v = (const uint8_t*)ctx->b.hot_v;
+  a.pool_dec = (const uint32_t*)ctx->b.pool_dec;
+  a.page_meta = (const PageMeta*)ctx->b.page_meta;
+  a.seq_len = (const int32_t*)((const uint8_t*)ctx->b.state + state_len_off(g));
+  a.tables = (const Tables*)ctx->b.tables;
+  a.q = q;
+  a.partials = (float*)ctx->b.scratch;
+  a.out = out;
+  a.mlo = mlo;
+  a.status = (int32_t*)((uint8_t*)ctx->b.state + state_status_off(g));
+  a.layer = layer;
+  a.q_dtype = q_dtype;
+  a.n_units = n_units;
+  a.n_cta = std::min(sm_count, 192);
+  a.block_begin = block_begin;
+  a.block_end = block_end;
+  a.with_hot = with_hot;
+  a.scale_log2 = 1.4426950408889634f / sqrtf((float)TQ_D);
+  *handled = true;
+#define TQ_CASE(GG, VV) \
+  if (G == GG && g.value_bits == VV) return launch_t<GG, VV>(a, st, ctx);
+  TQ_CASE(1, 3) TQ_CASE(2, 3) TQ_CASE(4, 3) TQ_CASE(8, 3)
+  TQ_CASE(1, 4) TQ_CASE(2, 4) TQ_CASE(4, 4) TQ_CASE(8, 4)
+#undef TQ_CASE
   *handled = false;
   return TQ_OK;
 }

@@ -84,11 +84,13 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   __shared__ int s_count;
   __shared__ uint32_t s_off;
   __shared__ int s_alloc;
-  __shared__ int s_slot;
-  if (d == 0) {
-    s_count = 0;
-    s_slot = 0;
-  }
+  __shared__ int s_tok_cnt[256];    // outliers per token, then the running fill position
+  __shared__ int s_row[257];        // start of every token's outliers in the side-list
+  __shared__ int s_warp_sum[TQ_D / 32];
+  if (d == 0) s_count = 0;
+  s_tok_cnt[d] = 0;
+  s_tok_cnt[d + TQ_D] = 0;
+  __syncthreads();
 
   // pass 1: sequential sum and the k largest magnitudes (ascending; top[0] is the k-th)
   float top[TQ_MAX_K_OUT];
@@ -122,7 +124,10 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   for (int t = 0; t < S; ++t) {
     float x = src.ld(pos0 + t, d);
     amax = fmaxf(amax, fabsf(__fsub_rn(x, mu)));
-    if (kk > 0 && fabsf(x) >= kth) ++my_out;
+    if (kk > 0 && fabsf(x) >= kth) {
+      ++my_out;
+      atomicAdd(&s_tok_cnt[t], 1);
+    }
   }
   amax = fmaxf(amax, 1e-8f);
   float lev[16];
@@ -157,18 +162,40 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     pm.off = off;
     pm.cnt = (uint32_t)min(n, alloc);
     a.page_meta[unit_index(g, a.layer, seq, head) * g.max_blocks + blk] = pm;
+    *(PageMeta*)(page + g.hdr_off) = pm;  // the page carries its own copy for the decode kernel
+  }
+  {  // exclusive prefix sum of the per-token counts: thread d owns tokens 2d and 2d+1
+    const int c0 = s_tok_cnt[2 * d], c1 = s_tok_cnt[2 * d + 1];
+    int v = c0 + c1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int nv = __shfl_up_sync(0xffffffffu, v, o);
+      if ((d & 31) >= o) v += nv;
+    }
+    if ((d & 31) == 31) s_warp_sum[d >> 5] = v;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < (d >> 5); ++w) base += s_warp_sum[w];
+    const int excl = base + v - (c0 + c1);
+    s_row[2 * d] = excl;
+    s_row[2 * d + 1] = excl + c0;
+    if (d == TQ_D - 1) s_row[256] = base + v;
+  }
+  __syncthreads();
+  {
+    uint16_t* rows = (uint16_t*)(page + g.hdr_off + 16);
+    // entries beyond the allocated slice do not exist: clamp the starts to the kept count
+    const int kept = min(s_count, s_alloc);
+    rows[2 * d] = (uint16_t)min(s_row[2 * d], kept);
+    rows[2 * d + 1] = (uint16_t)min(s_row[2 * d + 1], kept);
+    if (d == 0) rows[256] = (uint16_t)min(s_row[256], kept);
+    s_tok_cnt[2 * d] = s_row[2 * d];      // becomes the fill cursor of the token
+    s_tok_cnt[2 * d + 1] = s_row[2 * d + 1];
   }
   __syncthreads();
   const size_t slab = unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + s_off;
   const int alloc = s_alloc;
-  {  // zero the padding entries so that a vector read of the list sees harmless deltas
-    int n = s_count;
-    int n4 = min((n + 3) & ~3, alloc);
-    if (d < 4 && n + d < n4) {
-      a.pool_dec[slab + n + d] = 0u;
-      a.pool_val[slab + n + d] = 0;
-    }
-  }
+  uint32_t* inline_ent = (uint32_t*)(page + g.ent_off);
 
   // pass 3: codes and outlier entries
   for (int t = 0; t < S; ++t) {
@@ -186,14 +213,16 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     int other = __shfl_down_sync(0xffffffffu, best, 1);
     if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
     if (kk > 0 && fabsf(x) >= kth) {
-      int slot = atomicAdd(&s_slot, 1);
+      int slot = atomicAdd(&s_tok_cnt[t], 1);  // grouped by token, any order inside a token
       if (slot < alloc) {
         __half hv = __float2half_rn(x);
         float dense = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[best]));
         __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
-        a.pool_dec[slab + slot] = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
-                                  ((uint32_t)t << 24);
+        const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
+                             ((uint32_t)t << 24);
+        a.pool_dec[slab + slot] = ent;
         a.pool_val[slab + slot] = __half_as_ushort(hv);
+        if (slot < TQ_INLINE_CAP) inline_ent[slot] = ent;
       }
     }
   }
@@ -318,7 +347,7 @@ __global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
       code[t] = c;
     }
     // pack this channel's 8 token pairs into the group image
-    const int dq = e >> 4, i16 = e & 15;
+    const int dq = e & 7, i16 = e >> 3;  // record lane group and slot of channel e
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
 #pragma unroll
