@@ -1,20 +1,20 @@
 // Decode-on-codes attention for the common geometry (256-token cold blocks, head_dim 128,
-// GQA group <= 8): a persistent, warp-specialised kernel.
+// GQA group 1/2/4/8): a persistent, warp-specialised kernel.
 //
-//   warp 8      streams tiles HBM -> shared memory with bulk asynchronous copies
-//               (cp.async.bulk + mbarrier transaction counts) through a ring of stages;
-//               a tile is one cold page (~30-34 KB of codes, norms, scales) or one slice
-//               of the hot window (32 KB of 16/32-bit K and V rows)
-//   warp 9      prepares the query-dependent, page-dependent operands of a landed tile:
-//               w = q * scale split into fp16 hi/lo tensor-core fragments, bias = q . mean,
-//               and the per-token outlier corrections
-//   warps 0-7   consume tiles: 4-bit key codes and 3/4-bit value code pairs are turned
-//               into fp16 pairs by one conflict-free shared-memory table lookup each and
-//               fed straight into m16n8k16 tensor-core tiles as register fragments
-//               (scores: M = query group padded to 16 with the lo parts in rows 8-15,
-//               N = 8 tokens, K = 16 channels; values: M = 16 channels, N = 8 query
-//               heads, K = 16 tokens); online softmax in fp32 registers.  K and V are
-//               never materialised.
+//   warp 8        streams tiles HBM -> shared memory with bulk asynchronous copies
+//                 (cp.async.bulk + mbarrier transaction counts) through a ring of stages;
+//                 a tile is one cold page (codes, norms, scales and its outlier list:
+//                 34 KB at V3, 38 KB at V4) or one 32 KB slice of the hot window
+//   warps 9-11    prepare the query- and page-dependent operands of a landed tile, taking
+//                 turns tile by tile: w = q * scale split into fp16 hi/lo tensor-core
+//                 fragments, bias = q . mean, and the per-token outlier corrections
+//   warps 0-7     consume tiles: 4-bit key codes and 3/4-bit value code pairs become fp16
+//                 pairs through one conflict-free shared-memory table lookup each and go
+//                 straight into m16n8k16 tensor-core tiles as register fragments (scores:
+//                 M = query group padded to 16 with the lo parts in rows 8-15, N = 8 tokens,
+//                 K = 16 channels; values: M = 16 channels, N = 8 query heads, K = 16
+//                 tokens); online softmax in fp32 registers.  K and V are never
+//                 materialised.
 //
 // Work is a flat list of tiles over all (sequence, KV head) units of the layer, cut into
 // equal contiguous shares, one per CTA (one CTA per SM), so ragged contexts balance.
@@ -28,10 +28,11 @@
 
 namespace {
 
-constexpr int CW = 8;                       // consumer warps
-constexpr int THREADS = (CW + 2) * 32;      // + copy warp + prepare warp
+constexpr int CW = 8;                        // consumer warps
+constexpr int NP = 3;                        // prepare warps
+constexpr int THREADS = (CW + 1 + NP) * 32;  // + one copy warp
 constexpr int MAX_UNITS = 512;
-constexpr int BLK = 256;                    // tokens per cold page
+constexpr int BLK = 256;                     // tokens per cold page
 constexpr float NEG_BIG = -1.0e30f;
 constexpr int SPIN_LIMIT = 1 << 21;
 constexpr int STATUS_TIMEOUT = 2;
@@ -42,11 +43,11 @@ struct MmaArgs {
   const uint8_t* hot_k;
   const uint8_t* hot_v;
   const uint32_t* pool_dec;
-  const PageMeta* page_meta;
   const int32_t* seq_len;
   const Tables* tables;
   const void* q;
   float* partials;
+  int* plan_g;  // {T, Q, P[0..n_units], nb[0..n_units)} published by CTA 0 for the combine
   float* out;
   float* mlo;
   int32_t* status;
@@ -87,26 +88,15 @@ TQ_DEV void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
-TQ_DEV uint32_t lds32(uint32_t addr) {
+// Read of a constant lookup table: not volatile, so the scheduler may move and overlap it
+// freely (the tables never change after the prologue's barrier).
+TQ_DEV uint32_t lut_ld(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-TQ_DEV uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-TQ_DEV uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 TQ_DEV void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -121,12 +111,11 @@ TQ_DEV uint32_t bf16x2_to_h2(uint32_t w) {
 }
 
 // ---- shared-memory plan --------------------------------------------------------------------
-// Per stage: [data | fragments | corr | bias].  Sizes depend on the GQA group (corr rows)
-// and the value width (page size); the table sizes on the value width.
+// [value table (8 KB aligned) | key table | plan | q copies of the prepare warps | barriers |
+//  stages].  Per stage: [tile data | fragments | corr | bias].
 template <int G, int VB>
 struct Smem {
-  // a tile is a whole page (codes, norms, scales, header, in-page outlier entries: 34432 B
-  // at V3, 38528 B at V4) or 32 KB of hot rows
+  // a tile is a whole page (34432 B at V3, 38528 B at V4) or 32 KB of hot rows
   static constexpr int DATA_BYTES = VB == 3 ? 34432 : 38528;
   static constexpr int FRAG_OFF = DATA_BYTES;
   static constexpr int CORR_OFF = FRAG_OFF + 8 * 32 * 16;
@@ -134,17 +123,19 @@ struct Smem {
   static constexpr int STAGE_BYTES = BIAS_OFF + 64;
   static constexpr int LUTK_BYTES = 256 * 128;
   static constexpr int LUTV_BYTES = (VB == 3 ? 64 : 256) * 128;
-  static constexpr int FIXED = 8192 /* plan */ + 2 * 8 * 128 * 4 /* q copies */ + 256 /* bars */;
-  static constexpr int NSTAGE =
-      (232448 - 1024 - LUTK_BYTES - LUTV_BYTES - FIXED) / STAGE_BYTES >= 3 ? 3 : 2;
-  static constexpr int TOTAL = LUTK_BYTES + LUTV_BYTES + FIXED + NSTAGE * STAGE_BYTES;
+  static constexpr int ALIGN_SLACK = 8192;  // the value table starts on an 8 KB boundary
+  static constexpr int PLAN_BYTES = 8192;
+  static constexpr int Q_BYTES = NP * TQ_D * G * 4;
+  static constexpr int FIXED = ALIGN_SLACK + LUTK_BYTES + LUTV_BYTES + PLAN_BYTES + Q_BYTES + 256;
+  static constexpr int NSTAGE = (232448 - FIXED) / STAGE_BYTES >= 3 ? 3 : 2;
+  static constexpr int TOTAL = FIXED + NSTAGE * STAGE_BYTES;
 };
 
 struct Plan {  // lives in shared memory
-  int P[MAX_UNITS + 1];    // prefix sums of tiles per unit
+  int P[MAX_UNITS + 1];      // prefix sums of tiles per unit
   int hot_start[MAX_UNITS];  // first hot token position of each unit's sequence
-  short nb[MAX_UNITS];     // cold tiles of each unit
-  short b0[MAX_UNITS];     // first cold block attended
+  short nb[MAX_UNITS];       // cold tiles of each unit
+  short b0[MAX_UNITS];       // first cold block attended
   short hot_len[MAX_UNITS];  // hot tokens attended
 };
 
@@ -170,7 +161,7 @@ TQ_DEV void unit_tiles(const MmaArgs& a, int unit, int& nb, int& ht, int& b0, in
   ht = (hot_len + htt - 1) / htt;
 }
 
-// Fills plan->P / plan->nb; every thread of the CTA must call it.
+// Fills the plan; every thread of the CTA must call it.
 TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int tid, int nthreads) {
   for (int u = tid; u < a.n_units; u += nthreads) {
     int nb, ht, b0, hs, hl;
@@ -215,9 +206,9 @@ struct Waiter {
   TQ_DEV void wait(uint32_t bar, uint32_t parity) const {
     for (int i = 0; i < SPIN_LIMIT; ++i) {
       if (mbar_test(bar, parity)) return;
-      if ((i & 63) == 63) {
+      if ((i & 31) == 31) {
         if (*abort_flag) return;
-        __nanosleep(64);
+        __nanosleep(32);
       }
     }
     *abort_flag = 1;
@@ -225,7 +216,7 @@ struct Waiter {
   }
 };
 
-// fp16 hi / lo fragments of four consecutive weights of row r: {hi01, lo01, hi23, lo23}
+// fp16 hi / lo fragments of four consecutive weights of a row: {hi01, lo01, hi23, lo23}
 TQ_DEV uint4 frag_hilo(float w0, float w1, float w2, float w3) {
   __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
   float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
@@ -241,18 +232,20 @@ template <int G, int VB>
 __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   using SM = Smem<G, VB>;
   constexpr int NSTAGE = SM::NSTAGE;
-  extern __shared__ __align__(1024) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const tq_geom& g = a.g;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, c = lane & 3;
 
-  uint8_t* lutk_p = smem;
-  uint8_t* lutv_p = lutk_p + SM::LUTK_BYTES;
-  Plan* plan = (Plan*)(lutv_p + SM::LUTV_BYTES);
-  static_assert(sizeof(Plan) <= 8192, "plan does not fit its shared-memory slot");
-  float* qg = (float*)((uint8_t*)plan + 8192);  // [G][128], prepare warp only
-  float* qc = qg + 8 * 128;                     // [128][G]
-  uint64_t* bars = (uint64_t*)(qc + 8 * 128);   // full[NSTAGE], ready[NSTAGE], empty[NSTAGE]
+  // the value table sits on an 8 KB boundary of the shared address space so that a table
+  // address is (index bits) | (base + lane offset), one logic instruction
+  uint8_t* smem = smem_raw + ((8192u - (smem_addr(smem_raw) & 8191u)) & 8191u);
+  uint8_t* lutv_p = smem;
+  uint8_t* lutk_p = lutv_p + SM::LUTV_BYTES;
+  Plan* plan = (Plan*)(lutk_p + SM::LUTK_BYTES);
+  static_assert(sizeof(Plan) <= SM::PLAN_BYTES, "plan does not fit its shared-memory slot");
+  float* q_all = (float*)((uint8_t*)plan + SM::PLAN_BYTES);  // [NP][128][G]
+  uint64_t* bars = (uint64_t*)((uint8_t*)q_all + SM::Q_BYTES);  // full, ready, empty [NSTAGE]
   volatile int* abort_flag = (volatile int*)(bars + 12);
   uint8_t* stages = (uint8_t*)bars + 256;
 
@@ -268,7 +261,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   }
   // lookup tables: entry-major, one copy per lane so that a warp's 32 lookups never collide
   {
-    float* small = qg;  // 32 floats of scratch until the prepare warp claims the area
+    float* small = q_all;  // 32 floats of scratch until the prepare warps claim the area
     if (tid < 16) small[tid] = a.tables->nf4[tid];
     else if (tid < 32) small[tid] = a.tables->centroids[tid - 16];
     __syncthreads();
@@ -288,6 +281,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   const int T = plan->P[a.n_units];
   const int Q = (T + a.n_cta - 1) / a.n_cta;
   const int lo = min((int)blockIdx.x * Q, T), hi = min(lo + Q, T);
+  if (blockIdx.x == 0) {  // the combine kernel reads the plan instead of rebuilding it
+    if (tid == 0) {
+      a.plan_g[0] = T;
+      a.plan_g[1] = max(Q, 1);
+    }
+    for (int u = tid; u <= a.n_units; u += THREADS) a.plan_g[2 + u] = plan->P[u];
+    for (int u = tid; u < a.n_units; u += THREADS) a.plan_g[3 + a.n_units + u] = plan->nb[u];
+  }
   if (lo >= hi) return;
   const Waiter waiter{abort_flag, a.status};
   const int htt = hot_tile_tokens(g.kv_dtype);
@@ -337,15 +338,17 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
     return;
   }
 
-  // ============================== prepare warp ===============================================
-  if (warp == CW + 1) {
+  // ============================== prepare warps ==============================================
+  if (warp > CW) {
+    const int pw = warp - CW - 1;
+    float* qc = q_all + pw * TQ_D * G;  // this warp's copy of the unit's queries, [128][G]
     int u_cur = find_unit(plan, a.n_units, lo);
     int q_unit = -1;
-    for (int pos = lo; pos < hi; ++pos) {
+    for (int pos = lo + pw; pos < hi; pos += NP) {
       const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
       Tile tl = tile_at(pos, u_cur);
       const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
-      if (tl.u != q_unit) {  // this unit's query rows, both layouts, fp32
+      if (tl.u != q_unit) {
         q_unit = tl.u;
         __syncwarp();
         for (int i = lane; i < G * TQ_D; i += 32) {
@@ -354,7 +357,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
           float v = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
                     : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
                                           : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
-          qg[gg * TQ_D + d] = v;
           qc[d * G + gg] = v;
         }
         __syncwarp();
@@ -365,47 +367,65 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
       const bool cold = tl.kind == 0;
       const float* scale = (const float*)(st + g.scale_off);
       const float* mean = (const float*)(st + g.mean_off);
+      const int rq = r < G ? r : 0;
       float bias = 0.0f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int d0 = 32 * c + 4 * j;
-        float4 q4 = r < G ? *(const float4*)&qg[r * TQ_D + d0] : make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 s4 = cold ? *(const float4*)&scale[d0] : make_float4(1.f, 1.f, 1.f, 1.f);
+        float q0 = qc[(d0 + 0) * G + rq], q1 = qc[(d0 + 1) * G + rq];
+        float q2 = qc[(d0 + 2) * G + rq], q3 = qc[(d0 + 3) * G + rq];
+        if (r >= G) q0 = q1 = q2 = q3 = 0.0f;
+        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
         if (cold) {
-          float4 m4 = *(const float4*)&mean[d0];
-          bias += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
+          s4 = *(const float4*)&scale[d0];
+          const float4 m4 = *(const float4*)&mean[d0];
+          bias += q0 * m4.x + q1 * m4.y + q2 * m4.z + q3 * m4.w;
         }
-        frag[j * 32 + lane] = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
+        frag[j * 32 + lane] = frag_hilo(q0 * s4.x, q1 * s4.y, q2 * s4.z, q3 * s4.w);
       }
       if (cold) {
         bias += __shfl_xor_sync(0xffffffffu, bias, 1);
         bias += __shfl_xor_sync(0xffffffffu, bias, 2);
         float* bias_s = (float*)(st + SM::BIAS_OFF);
         if (c == 0) bias_s[r] = r < G ? bias : 0.0f;
-        // outlier corrections: the side-list is grouped by token, so each lane sums the
-        // entries of its own tokens and no atomics are needed
+        // outlier corrections: the side-list is grouped by token; a lane owns tokens
+        // lane, lane + 32, ... and walks their lists in step so the loads overlap
         float* corr = (float*)(st + SM::CORR_OFF);
         const PageMeta pm = *(const PageMeta*)(st + g.hdr_off);
         const uint16_t* rows = (const uint16_t*)(st + g.hdr_off + 16);
         const uint32_t* ent_s = (const uint32_t*)(st + g.ent_off);
         const uint32_t* ent_g =
             a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
-#pragma unroll 1
-        for (int tk = lane; tk < BLK; tk += 32) {
-          float cacc[G];
+        int e0[8], e1[8];
+        float cacc[8][G];
+        int kmax = 0;
 #pragma unroll
-          for (int gg = 0; gg < G; ++gg) cacc[gg] = 0.0f;
-          const int e1 = rows[tk + 1];
-          for (int e = rows[tk]; e < e1; ++e) {
-            const uint32_t wv = e < TQ_INLINE_CAP ? ent_s[e] : ent_g[e];
-            const float delta = __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu)));
-            const int col = (wv >> 16) & 255;
+        for (int i = 0; i < 8; ++i) {
+          e0[i] = rows[lane + 32 * i];
+          e1[i] = rows[lane + 32 * i + 1];
+          kmax = max(kmax, e1[i] - e0[i]);
 #pragma unroll
-            for (int gg = 0; gg < G; ++gg) cacc[gg] += qc[col * G + gg] * delta;
-          }
-#pragma unroll
-          for (int gg = 0; gg < G; ++gg) corr[gg * BLK + tk] = cacc[gg];
+          for (int gg = 0; gg < G; ++gg) cacc[i][gg] = 0.0f;
         }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+        for (int kk = 0; kk < kmax; ++kk) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int e = e0[i] + kk;
+            if (e < e1[i]) {
+              const uint32_t wv = e < TQ_INLINE_CAP ? ent_s[e] : ent_g[e];
+              const float delta = __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu)));
+              const float* qrow = qc + ((wv >> 16) & 255) * G;
+#pragma unroll
+              for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg) corr[gg * BLK + lane + 32 * i] = cacc[i][gg];
       }
       mbar_arrive(ready0 + 8 * s);  // each lane releases its own writes
     }
@@ -414,7 +434,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
 
   // ============================== consumer warps =============================================
   const uint32_t lutk = smem_addr(lutk_p) + lane * 4;
-  const uint32_t lutv = smem_addr(lutv_p) + lane * 4;
+  const uint32_t lutv = smem_addr(lutv_p) + lane * 4;  // 8 KB aligned base | lane offset
   const int rg = r < G ? r : G - 1;
   float m_run = NEG_BIG, l_run = 0.0f;
   float acc[8][4];
@@ -451,7 +471,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   };
 
   // online-softmax update with the four scores of this thread's row (two 8-token tiles,
-  // two tokens each); returns the probabilities in sv
+  // two tokens each); leaves the probabilities in sv
   auto softmax16 = [&](float (&sv)[2][2], const bool (&ok)[2][2]) {
     float mx = NEG_BIG;
 #pragma unroll
@@ -498,76 +518,91 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
       cur_kind = tl.kind;
     }
     const uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
-    const uint32_t st_a = smem_addr(st);
     waiter.wait(ready0 + 8 * s, k & 1);
     waiter.wait(full0 + 8 * s, k & 1);
 
     uint32_t areg[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const uint4 f = lds128(st_a + SM::FRAG_OFF + (j * 32 + lane) * 16);
+      const uint4 f = *(const uint4*)(st + SM::FRAG_OFF + (j * 32 + lane) * 16);
       areg[j][0] = f.x; areg[j][1] = f.y; areg[j][2] = f.z; areg[j][3] = f.w;
     }
 
     if (tl.kind == 0) {
       const float bias = ((const float*)(st + SM::BIAS_OFF))[rg];
+      const float* corr = (const float*)(st + SM::CORR_OFF) + rg * BLK;
+      const float* norms = (const float*)(st + g.norm_off);
+      const uint8_t* vcodes = st + g.v_off;
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         const int T0 = 32 * warp + 16 * half;
         float sv[2][2];
         const bool ok[2][2] = {{true, true}, {true, true}};
+        float C[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        uint32_t kw[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          const uint4 kc = lds128(st_a + (T0 + 8 * nt + r) * 64 + c * 16);
-          const uint32_t kw[4] = {kc.x, kc.y, kc.z, kc.w};
-          float C[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint4 kc = *(const uint4*)(st + (T0 + 8 * nt + r) * 64 + c * 16);
+          kw[nt][0] = kc.x; kw[nt][1] = kc.y; kw[nt][2] = kc.z; kw[nt][3] = kc.w;
+        }
+        // the two 8-token tiles advance together so their accumulation chains interleave
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t w = kw[j >> 1];
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const uint32_t w = kw[nt][j >> 1];
             const uint32_t i0 = __byte_perm(w, 0, 0x4440 + 2 * (j & 1));
             const uint32_t i1 = __byte_perm(w, 0, 0x4441 + 2 * (j & 1));
-            const uint32_t b0 = lds32(lutk + i0 * 128), b1 = lds32(lutk + i1 * 128);
-            mma16816(C, areg[j], b0, b1);
+            const uint32_t b0 = lut_ld(lutk + i0 * 128), b1 = lut_ld(lutk + i1 * 128);
+            mma16816(C[nt], areg[j], b0, b1);
           }
-          const uint2 cr = lds64(st_a + SM::CORR_OFF + (rg * BLK + T0 + 8 * nt + 2 * c) * 4);
-          sv[nt][0] = (C[0] + C[2] + bias + __uint_as_float(cr.x)) * a.scale_log2;
-          sv[nt][1] = (C[1] + C[3] + bias + __uint_as_float(cr.y)) * a.scale_log2;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float2 cr = *(const float2*)(corr + T0 + 8 * nt + 2 * c);
+          sv[nt][0] = (C[nt][0] + C[nt][2] + bias + cr.x) * a.scale_log2;
+          sv[nt][1] = (C[nt][1] + C[nt][3] + bias + cr.y) * a.scale_log2;
           if (r >= G) sv[nt][0] = sv[nt][1] = 0.0f;
         }
         softmax16(sv, ok);
-        const uint2 n0 = lds64(st_a + g.norm_off + (T0 + 2 * c) * 4);
-        const uint2 n1 = lds64(st_a + g.norm_off + (T0 + 8 + 2 * c) * 4);
-        const uint32_t pb0 = pack_h2(sv[0][0] * __uint_as_float(n0.x), sv[0][1] * __uint_as_float(n0.y));
-        const uint32_t pb1 = pack_h2(sv[1][0] * __uint_as_float(n1.x), sv[1][1] * __uint_as_float(n1.y));
+        const float2 n0 = *(const float2*)(norms + T0 + 2 * c);
+        const float2 n1 = *(const float2*)(norms + T0 + 8 + 2 * c);
+        const uint32_t pb0 = pack_h2(sv[0][0] * n0.x, sv[0][1] * n0.y);
+        const uint32_t pb1 = pack_h2(sv[1][0] * n1.x, sv[1][1] * n1.y);
         const int gq = 2 * warp + half;
         if (VB == 4) {
-          const uint32_t gb = st_a + g.v_off + gq * 1024 + lane * 16;
-          const uint4 r0 = lds128(gb), r1 = lds128(gb + 512);
+          const uint8_t* gb = vcodes + gq * 1024 + lane * 16;
+          const uint4 r0 = *(const uint4*)gb, r1 = *(const uint4*)(gb + 512);
           const uint32_t rec[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
           for (int mt = 0; mt < 8; ++mt) {
             const uint32_t w = rec[mt];  // pairs 4mt .. 4mt+3
             uint32_t af[4];
-            af[0] = lds32(lutv + __byte_perm(w, 0, 0x4440) * 128);
-            af[1] = lds32(lutv + __byte_perm(w, 0, 0x4442) * 128);
-            af[2] = lds32(lutv + __byte_perm(w, 0, 0x4441) * 128);
-            af[3] = lds32(lutv + __byte_perm(w, 0, 0x4443) * 128);
+            af[0] = lut_ld(lutv + __byte_perm(w, 0, 0x4440) * 128);
+            af[1] = lut_ld(lutv + __byte_perm(w, 0, 0x4442) * 128);
+            af[2] = lut_ld(lutv + __byte_perm(w, 0, 0x4441) * 128);
+            af[3] = lut_ld(lutv + __byte_perm(w, 0, 0x4443) * 128);
             mma16816(acc[mt], af, pb0, pb1);
           }
         } else {
-          const uint32_t gb = st_a + g.v_off + gq * 768 + lane * 8;
-          const uint2 r0 = lds64(gb), r1 = lds64(gb + 256), r2 = lds64(gb + 512);
+          const uint8_t* gb = vcodes + gq * 768 + lane * 8;
+          const uint2 r0 = *(const uint2*)gb, r1 = *(const uint2*)(gb + 256),
+                      r2 = *(const uint2*)(gb + 512);
           const uint32_t rec[7] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, 0u};
 #pragma unroll
           for (int mt = 0; mt < 8; ++mt) {
             uint32_t af[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              // a0: pair 4mt, a1: pair 4mt+2, a2: pair 4mt+1, a3: pair 4mt+3
+              // a0: pair 4mt, a1: pair 4mt+2, a2: pair 4mt+1, a3: pair 4mt+3; pair p is the
+              // 6-bit field at bit 6p of the 192-bit record and must land at bits 7..12
               const int p = 4 * mt + ((e & 1) << 1) + (e >> 1);
               const int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
-              const uint32_t f = sh > 26 ? __funnelshift_r(rec[wd], rec[wd + 1], sh) : rec[wd] >> sh;
-              af[e] = lds32(lutv + (f & 63u) * 128);
+              uint32_t f;
+              if (sh < 7) f = rec[wd] << (7 - sh);
+              else if (sh > 26) f = __funnelshift_r(rec[wd], rec[wd + 1], sh - 7);
+              else f = rec[wd] >> (sh - 7);
+              af[e] = lut_ld((f & 0x1f80u) | lutv);
             }
             mma16816(acc[mt], af, pb0, pb1);
           }
@@ -578,17 +613,18 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
       const int hot_len = plan->hot_len[tl.u];
       const int T0 = 16 * warp;                 // first token of this warp inside the tile
       const int base_tok = tl.idx * htt + T0;   // ... inside the hot window
-      const uint32_t kbase = st_a, vbase = st_a + htt * TQ_D * esz;
+      const uint8_t* kbase = st;
+      const uint8_t* vbase = st + htt * TQ_D * esz;
       float sv[2][2];
       bool ok[2][2];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const uint32_t row = kbase + ((T0 + 8 * nt + r) * TQ_D + 32 * c) * esz;
+        const uint8_t* row = kbase + ((T0 + 8 * nt + r) * TQ_D + 32 * c) * esz;
         uint32_t kw[16];
         if (esz == 2) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint4 v4 = lds128(row + 16 * i);
+            const uint4 v4 = *(const uint4*)(row + 16 * i);
             kw[4 * i] = v4.x; kw[4 * i + 1] = v4.y; kw[4 * i + 2] = v4.z; kw[4 * i + 3] = v4.w;
           }
           if (g.kv_dtype == TQ_BF16) {
@@ -598,9 +634,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const uint4 v4 = lds128(row + 16 * i);
-            kw[2 * i] = pack_h2(__uint_as_float(v4.x), __uint_as_float(v4.y));
-            kw[2 * i + 1] = pack_h2(__uint_as_float(v4.z), __uint_as_float(v4.w));
+            const float4 v4 = *(const float4*)(row + 16 * i);
+            kw[2 * i] = pack_h2(v4.x, v4.y);
+            kw[2 * i + 1] = pack_h2(v4.z, v4.w);
           }
         }
         float C[4] = {0.f, 0.f, 0.f, 0.f};
@@ -624,9 +660,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
       for (int q4 = 0; q4 < 4; ++q4) {
         const int tloc = 2 * c + (q4 & 1) + 8 * (q4 >> 1);
         const bool valid = base_tok + tloc < hot_len;
-        const uint32_t row = vbase + ((T0 + tloc) * TQ_D + 16 * r) * esz;
+        const uint8_t* row = vbase + ((T0 + tloc) * TQ_D + 16 * r) * esz;
         if (esz == 2) {
-          const uint4 x0 = lds128(row), x1 = lds128(row + 16);
+          const uint4 x0 = *(const uint4*)row, x1 = *(const uint4*)(row + 16);
           vr[q4][0] = x0.x; vr[q4][1] = x0.y; vr[q4][2] = x0.z; vr[q4][3] = x0.w;
           vr[q4][4] = x1.x; vr[q4][5] = x1.y; vr[q4][6] = x1.z; vr[q4][7] = x1.w;
           if (g.kv_dtype == TQ_BF16) {
@@ -636,9 +672,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         } else {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint4 v4 = lds128(row + 16 * i);
-            vr[q4][2 * i] = pack_h2(__uint_as_float(v4.x), __uint_as_float(v4.y));
-            vr[q4][2 * i + 1] = pack_h2(__uint_as_float(v4.z), __uint_as_float(v4.w));
+            const float4 v4 = *(const float4*)(row + 16 * i);
+            vr[q4][2 * i] = pack_h2(v4.x, v4.y);
+            vr[q4][2 * i + 1] = pack_h2(v4.z, v4.w);
           }
         }
         if (!valid) {
@@ -656,64 +692,123 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         mma16816(acc[mt], af, pb0, pb1);
       }
     }
+    // every read of the stage is complete before it is handed back to the copy warp
+    asm volatile("" ::: "memory");
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8 * s);
   }
   if (cur_u >= 0) flush(cur_u, cur_kind);
 }
 
-// ---------------------------------------------------------------------------------------------
+constexpr int MAX_PARTS = 96;  // partials merged per round
+
 // Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the per-warp
-// partials of every CTA that owned tiles of the unit (fixed order: CTA, cold before hot,
-// warp), un-rotates the cold part once and writes the output or the (m, l, o) state.
-// Partial maxima are in the log2 domain.
-// ---------------------------------------------------------------------------------------------
+// partials of every CTA that owned tiles of the unit, in the fixed order (CTA, cold before
+// hot, warp) and in rounds of MAX_PARTS with a running maximum, un-rotates the cold part
+// once (acc @ Pi) and writes the output or the (m, l, o) state.  Partial maxima are in the
+// log2 domain.
 template <int G>
 __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   const tq_geom& g = a.g;
   const int unit = blockIdx.x, e = threadIdx.x;
   const int seq = unit / g.n_kv_heads, head = unit % g.n_kv_heads;
-  __shared__ Plan plan;
   __shared__ float cs[G][TQ_D];
-  build_plan(a, &plan, e, TQ_D);
-  const int T = plan.P[a.n_units];
-  const int Q = max((T + a.n_cta - 1) / a.n_cta, 1);
-  const int p0 = plan.P[unit], p1 = plan.P[unit + 1], pc = p0 + plan.nb[unit];
+  __shared__ const float* s_ptr[MAX_PARTS];
+  __shared__ float s_w[MAX_PARTS][G];  // m, then the weight 2^(m - M) (0 for empty partials)
+  __shared__ float s_l[MAX_PARTS][G];
+  __shared__ int s_cold[MAX_PARTS];
+  __shared__ float s_M[G], s_L[G], s_scale[G];
+  __shared__ int s_n, s_it[3];  // round size; enumeration cursor (cta, kind, warp)
+  const int Q = a.plan_g[1];
+  const int p0 = a.plan_g[2 + unit], p1 = a.plan_g[3 + unit];
+  const int pc = p0 + a.plan_g[3 + a.n_units + unit];
   const int hot_warps = hot_tile_tokens(g.kv_dtype) / 16;
-  float M[G], L[G], C[G], Hh[G];
-#pragma unroll
-  for (int gg = 0; gg < G; ++gg) {
-    M[gg] = NEG_BIG;
-    L[gg] = C[gg] = Hh[gg] = 0.0f;
+  const int i0 = p1 > p0 ? p0 / Q : 0, i1 = p1 > p0 ? (p1 - 1) / Q : -1;
+  if (e < G) {
+    s_M[e] = NEG_BIG;
+    s_L[e] = 0.0f;
   }
-  if (p1 > p0) {
-    const int i0 = p0 / Q, i1 = (p1 - 1) / Q;
-    for (int pass = 0; pass < 2; ++pass)
-      for (int i = i0; i <= i1; ++i) {
-        const int lo = i * Q, hi = lo + Q;
-        for (int kind = 0; kind < 2; ++kind) {
-          const bool has = kind == 0 ? (max(lo, p0) < min(hi, pc)) : (max(lo, pc) < min(hi, p1));
-          if (!has) continue;
-          const int nw = kind == 0 ? CW : hot_warps;
-          for (int w = 0; w < nw; ++w) {
-            const float* pp = a.partials + ((((size_t)unit + i) * 2 + kind) * CW + w) *
-                                               (size_t)(G * TQ_PART_STRIDE);
+  if (e == 0) {
+    s_it[0] = i0;
+    s_it[1] = 0;
+    s_it[2] = 0;
+  }
+  float C[G], Hh[G];
 #pragma unroll
-            for (int gg = 0; gg < G; ++gg) {
-              const float m = pp[gg * TQ_PART_STRIDE], l = pp[gg * TQ_PART_STRIDE + 1];
-              if (l <= 0.0f) continue;
-              if (pass == 0) {
-                M[gg] = fmaxf(M[gg], m);
-              } else {
-                const float wgt = exp2f(m - M[gg]);
-                L[gg] += l * wgt;
-                const float v = pp[gg * TQ_PART_STRIDE + 2 + e] * wgt;
-                if (kind == 0) C[gg] += v; else Hh[gg] += v;
-              }
-            }
+  for (int gg = 0; gg < G; ++gg) C[gg] = Hh[gg] = 0.0f;
+  __syncthreads();
+  while (true) {
+    // 1. next round of partials, in the fixed merge order
+    if (e == 0) {
+      int n = 0, i = s_it[0], kind = s_it[1], w = s_it[2];
+      while (i <= i1 && n < MAX_PARTS) {
+        const int lo = i * Q, hi = lo + Q;
+        const bool has = kind == 0 ? (max(lo, p0) < min(hi, pc)) : (max(lo, pc) < min(hi, p1));
+        const int nw = kind == 0 ? CW : hot_warps;
+        if (has && w < nw) {
+          s_ptr[n] = a.partials + ((((size_t)unit + i) * 2 + kind) * CW + w) *
+                                      (size_t)(G * TQ_PART_STRIDE);
+          s_cold[n] = kind == 0;
+          ++n;
+          ++w;
+        } else {
+          w = 0;
+          if (++kind == 2) {
+            kind = 0;
+            ++i;
           }
         }
       }
+      s_it[0] = i;
+      s_it[1] = kind;
+      s_it[2] = w;
+      s_n = n;
+    }
+    __syncthreads();
+    const int n = s_n;
+    if (n == 0) break;
+    // 2. their (m, l), loaded in parallel
+    for (int i = e; i < n * G; i += TQ_D) {
+      const int j = i / G, gg = i % G;
+      const float* pp = s_ptr[j] + gg * TQ_PART_STRIDE;
+      s_w[j][gg] = pp[0];
+      s_l[j][gg] = pp[1];
+    }
+    __syncthreads();
+    if (e < G) {
+      float M = s_M[e];
+      for (int j = 0; j < n; ++j)
+        if (s_l[j][e] > 0.0f) M = fmaxf(M, s_w[j][e]);
+      const float sc = exp2f(s_M[e] - M);
+      float L = s_L[e] * sc;
+      for (int j = 0; j < n; ++j) {
+        const float wgt = s_l[j][e] > 0.0f ? exp2f(s_w[j][e] - M) : 0.0f;
+        L += s_l[j][e] * wgt;
+        s_w[j][e] = wgt;
+      }
+      s_scale[e] = sc;
+      s_M[e] = M;
+      s_L[e] = L;
+    }
+    __syncthreads();
+    // 3. weighted sums of the accumulators: independent loads
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg) {
+      C[gg] *= s_scale[gg];
+      Hh[gg] *= s_scale[gg];
+    }
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const float* pp = s_ptr[j] + 2 + e;
+      const bool cold = s_cold[j] != 0;
+#pragma unroll
+      for (int gg = 0; gg < G; ++gg) {
+        const float wgt = s_w[j][gg];
+        const float v = wgt > 0.0f ? pp[gg * TQ_PART_STRIDE] * wgt : 0.0f;
+        if (cold) C[gg] += v; else Hh[gg] += v;
+      }
+    }
+    __syncthreads();
   }
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) cs[gg][e] = C[gg];
@@ -721,6 +816,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   float o[G];
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) o[gg] = 0.0f;
+#pragma unroll 8
   for (int d = 0; d < TQ_D; ++d) {
     const float pv = a.tables->pi[d * TQ_D + e];
 #pragma unroll
@@ -730,16 +826,17 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   for (int gg = 0; gg < G; ++gg) {
     const size_t row = (size_t)seq * g.n_q_heads + head * G + gg;
     const float val = o[gg] + Hh[gg];
+    const float L = s_L[gg];
     if (a.mlo != nullptr) {
       float* rr = a.mlo + row * TQ_PART_STRIDE;
       if (e == 0) {
         // natural-log domain, like the general kernel and tq_lse_combine
-        rr[0] = L[gg] > 0.0f ? M[gg] * 0.6931471805599453f : -INFINITY;
-        rr[1] = L[gg];
+        rr[0] = L > 0.0f ? s_M[gg] * 0.6931471805599453f : -INFINITY;
+        rr[1] = L;
       }
       rr[2 + e] = val;
     } else {
-      a.out[row * TQ_D + e] = L[gg] > 0.0f ? val / L[gg] : 0.0f;
+      a.out[row * TQ_D + e] = L > 0.0f ? val / L : 0.0f;
     }
   }
 }
@@ -772,7 +869,7 @@ int launch_t(const MmaArgs& a, cudaStream_t st, tq_ctx* ctx) {
 
 // Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
 size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
-  return (units + 192) * 2 * CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
+  return 8192 + (units + 192) * 2 * CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
 }
 
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
@@ -794,11 +891,11 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   a.hot_k = (const uint8_t*)ctx->b.hot_k;
   a.hot_v = (const uint8_t*)ctx->b.hot_v;
   a.pool_dec = (const uint32_t*)ctx->b.pool_dec;
-  a.page_meta = (const PageMeta*)ctx->b.page_meta;
   a.seq_len = (const int32_t*)((const uint8_t*)ctx->b.state + state_len_off(g));
   a.tables = (const Tables*)ctx->b.tables;
   a.q = q;
-  a.partials = (float*)ctx->b.scratch;
+  a.plan_g = (int*)ctx->b.scratch;  // first 8 KB of the scratch region
+  a.partials = (float*)((uint8_t*)ctx->b.scratch + 8192);
   a.out = out;
   a.mlo = mlo;
   a.status = (int32_t*)((uint8_t*)ctx->b.state + state_status_off(g));
