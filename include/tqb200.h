@@ -227,6 +227,13 @@ int32_t tq_last_launches(const tq_ctx* ctx);
  * No counterpart in the reference. */
 int32_t tq_set_kernel(tq_ctx* ctx, int32_t which);
 
+/* Pipeline trace of the tensor-core decode kernel (debugging aid, no counterpart in the
+ * reference).  `on` switches stamping on or off for later tq_decode calls; if `stamps` is
+ * non-null the 512 SM-clock stamps of the most recent traced decode (first CTA, 64 tiles x
+ * 8 phases: copy wait/issue, prepare wait/start/done, consumer wait/start/done) are copied
+ * to that HOST array.  Synchronises `stream`. */
+int32_t tq_debug_trace(tq_ctx* ctx, int32_t on, uint64_t* stamps, void* stream);
+
 /* Per-kernel timing for benchmarks (no counterpart in the reference, whose harnesses time
  * whole calls with time.perf_counter, benchmarks/p5_triton_bench.py:72-82).  While enabled,
  * tq_decode brackets its attention kernel and its combine kernel with CUDA events on the

@@ -330,6 +330,15 @@ class KVContext:
         general-shape float32 kernel."""
         check(self._lib.tq_set_kernel(self._h, {"auto": 0, "general": 1}[which]))
 
+    def trace(self, on: bool, read: bool = False):
+        """Switch the decode kernel's pipeline stamping on/off; with ``read`` return the
+        stamps of the last traced decode as a (64, 8) uint64 array of SM clocks."""
+        buf = np.zeros((64, 8), np.uint64) if read else None
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_debug_trace(self._h, int(bool(on)),
+                                           buf.ctypes.data if read else None, self._stream()))
+        return buf
+
     def profile(self, on: bool) -> None:
         """Bracket the attention and combine kernels of every decode with CUDA events."""
         check(self._lib.tq_profile_enable(self._h, int(bool(on))))

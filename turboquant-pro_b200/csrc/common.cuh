@@ -72,7 +72,8 @@ struct tq_ctx {
   // one kernels read, both are advanced together by tq_append
   std::vector<int32_t> len;
   int last_launches;
-  bool force_generic = false;  // route every decode through the general-shape kernel
+  bool force_generic = false;
+  bool trace_on = false;       // the tensor-core decode kernel stamps its pipeline phases  // route every decode through the general-shape kernel
   // optional per-kernel timing: event triples (before attention, after it, after combine)
   bool prof_on = false;
   int prof_n = 0;

@@ -198,6 +198,19 @@ int32_t tq_set_kernel(tq_ctx* ctx, int32_t which) {
   return TQ_OK;
 }
 
+int32_t tq_debug_trace(tq_ctx* ctx, int32_t on, uint64_t* stamps, void* stream) {
+  TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
+  ctx->trace_on = on != 0;
+  if (stamps != nullptr) {
+    TQ_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    TQ_CUDA(cudaMemcpyAsync(stamps, (const uint8_t*)ctx->b.scratch + 8192, 4096,
+                            cudaMemcpyDeviceToHost, st));
+    TQ_CUDA(cudaStreamSynchronize(st));
+  }
+  return TQ_OK;
+}
+
 int32_t tq_profile_enable(tq_ctx* ctx, int32_t on) {
   TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
   ctx->prof_on = on != 0;

@@ -34,7 +34,7 @@ constexpr int THREADS = (CW + 1 + NP) * 32;  // + one copy warp
 constexpr int MAX_UNITS = 512;
 constexpr int BLK = 256;                     // tokens per cold page
 constexpr float NEG_BIG = -1.0e30f;
-constexpr int SPIN_LIMIT = 1 << 21;
+constexpr int SPIN_LIMIT = 1 << 18;  // probes per wait; each may suspend up to ~2 us
 constexpr int STATUS_TIMEOUT = 2;
 
 struct MmaArgs {
@@ -51,6 +51,7 @@ struct MmaArgs {
   float* out;
   float* mlo;
   int32_t* status;
+  unsigned long long* trace;  // optional: SM clock stamps of CTA 0's first 64 tiles
   int layer, q_dtype, n_units, n_cta;
   int block_begin, block_end, with_hot;
   float scale_log2;
@@ -69,14 +70,15 @@ TQ_DEV void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-TQ_DEV uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+// one bounded, possibly suspending probe of a barrier phase (the hint caps the suspension)
+TQ_DEV uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok;
 }
@@ -120,12 +122,12 @@ struct Smem {
   static constexpr int FRAG_OFF = DATA_BYTES;
   static constexpr int CORR_OFF = FRAG_OFF + 8 * 32 * 16;
   static constexpr int BIAS_OFF = CORR_OFF + G * BLK * 4;
-  static constexpr int STAGE_BYTES = BIAS_OFF + 64;
+  static constexpr int STAGE_BYTES = BIAS_OFF + 128;
   static constexpr int LUTK_BYTES = 256 * 128;
   static constexpr int LUTV_BYTES = (VB == 3 ? 64 : 256) * 128;
   static constexpr int ALIGN_SLACK = 8192;  // the value table starts on an 8 KB boundary
   static constexpr int PLAN_BYTES = 8192;
-  static constexpr int Q_BYTES = NP * TQ_D * G * 4;
+  static constexpr int Q_BYTES = 8 * 32 * 16 + TQ_D * G * 4;  // fragment-ordered + [128][G]
   static constexpr int FIXED = ALIGN_SLACK + LUTK_BYTES + LUTV_BYTES + PLAN_BYTES + Q_BYTES + 256;
   static constexpr int NSTAGE = (232448 - FIXED) / STAGE_BYTES >= 3 ? 3 : 2;
   static constexpr int TOTAL = FIXED + NSTAGE * STAGE_BYTES;
@@ -200,16 +202,20 @@ TQ_DEV int find_unit(const Plan* plan, int n_units, int pos) {
   return lo;
 }
 
+// debugging aid: slot k of tile t gets the SM clock (CTA 0, first 64 tiles, one lane)
+#define TQ_TRACE(k)                                                     \
+  do {                                                                  \
+    if (a.trace != nullptr && blockIdx.x == 0 && lane == 0 && t < 64)   \
+      a.trace[t * 8 + (k)] = (unsigned long long)clock64();             \
+  } while (0)
+
 struct Waiter {
   volatile int* abort_flag;
   int32_t* status;
   TQ_DEV void wait(uint32_t bar, uint32_t parity) const {
     for (int i = 0; i < SPIN_LIMIT; ++i) {
-      if (mbar_test(bar, parity)) return;
-      if ((i & 31) == 31) {
-        if (*abort_flag) return;
-        __nanosleep(32);
-      }
+      if (mbar_try(bar, parity)) return;
+      if ((i & 15) == 15 && *abort_flag) return;
     }
     *abort_flag = 1;
     atomicOr(status, STATUS_TIMEOUT);
@@ -253,7 +259,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   if (tid == 0) {
     for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(full0 + 8 * s, 1);
-      mbar_init(ready0 + 8 * s, 32);
+      mbar_init(ready0 + 8 * s, NP * 32);
       mbar_init(empty0 + 8 * s, CW);
     }
     *abort_flag = 0;
@@ -313,7 +319,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
         Tile tl = tile_at(pos, u_cur);
         const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
+        TQ_TRACE(0);
         waiter.wait(empty0 + 8 * s, (k & 1) ^ 1);
+        TQ_TRACE(1);
         if (*abort_flag) break;
         const uint32_t dst = smem_addr(stages + (size_t)s * SM::STAGE_BYTES);
         const uint32_t bar = full0 + 8 * s;
@@ -339,94 +347,133 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   }
 
   // ============================== prepare warps ==============================================
+  // The three warps work on the same tile: the fragment k-steps, the bias dot product and
+  // the tokens of the outlier list are split three ways, which keeps the latency from
+  // "tile landed" to "tile ready" short.
   if (warp > CW) {
-    const int pw = warp - CW - 1;
-    float* qc = q_all + pw * TQ_D * G;  // this warp's copy of the unit's queries, [128][G]
+    const int pw = warp - CW - 1, ptid = tid - (CW + 1) * 32;
+    float4* qf = (float4*)q_all;                 // [8][32] query values in fragment order
+    float* qc = q_all + 8 * 32 * 4;              // [128][G] for the outlier dot products
     int u_cur = find_unit(plan, a.n_units, lo);
     int q_unit = -1;
-    for (int pos = lo + pw; pos < hi; pos += NP) {
+    for (int pos = lo; pos < hi; ++pos) {
       const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
       Tile tl = tile_at(pos, u_cur);
       const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
-      if (tl.u != q_unit) {
+      if (tl.u != q_unit) {  // new unit: reload its query rows (all three warps in step)
         q_unit = tl.u;
-        __syncwarp();
-        for (int i = lane; i < G * TQ_D; i += 32) {
-          int gg = i / TQ_D, d = i % TQ_D;
-          size_t qi = ((size_t)seq * g.n_q_heads + head * G + gg) * TQ_D + d;
-          float v = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
-                    : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
-                                          : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
-          qc[d * G + gg] = v;
+        asm volatile("bar.sync 1, %0;" ::"n"(NP * 32) : "memory");
+        for (int i = ptid; i < 8 * 32 * 4; i += NP * 32) {
+          const int j = i >> 7, ln = (i >> 2) & 31, e = i & 3;
+          const int rr = ln >> 2, d = 32 * (ln & 3) + 4 * j + e;
+          float v = 0.0f;
+          if (rr < G) {
+            size_t qi = ((size_t)seq * g.n_q_heads + head * G + rr) * TQ_D + d;
+            v = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
+                : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
+                                      : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
+            qc[d * G + rr] = v;
+          }
+          ((float*)qf)[i] = v;
         }
-        __syncwarp();
+        asm volatile("bar.sync 1, %0;" ::"n"(NP * 32) : "memory");
       }
       uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
+      if (pw == 0) TQ_TRACE(2);
       waiter.wait(full0 + 8 * s, k & 1);
+      if (pw == 0) TQ_TRACE(3);
       uint4* frag = (uint4*)(st + SM::FRAG_OFF);
       const bool cold = tl.kind == 0;
       const float* scale = (const float*)(st + g.scale_off);
       const float* mean = (const float*)(st + g.mean_off);
-      const int rq = r < G ? r : 0;
       float bias = 0.0f;
+      // k-steps pw, pw+3, pw+6: a fixed trip count so that the three chains overlap
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int d0 = 32 * c + 4 * j;
-        float q0 = qc[(d0 + 0) * G + rq], q1 = qc[(d0 + 1) * G + rq];
-        float q2 = qc[(d0 + 2) * G + rq], q3 = qc[(d0 + 3) * G + rq];
-        if (r >= G) q0 = q1 = q2 = q3 = 0.0f;
-        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (cold) {
-          s4 = *(const float4*)&scale[d0];
-          const float4 m4 = *(const float4*)&mean[d0];
-          bias += q0 * m4.x + q1 * m4.y + q2 * m4.z + q3 * m4.w;
+      for (int i = 0; i < 3; ++i) {
+        const int j = pw + NP * i;
+        if (j < 8) {
+          const int d0 = 32 * c + 4 * j;
+          const float4 q4 = qf[j * 32 + lane];
+          float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (cold) {
+            s4 = *(const float4*)&scale[d0];
+            const float4 m4 = *(const float4*)&mean[d0];
+            bias += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
+          }
+          frag[j * 32 + lane] = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
         }
-        frag[j * 32 + lane] = frag_hilo(q0 * s4.x, q1 * s4.y, q2 * s4.z, q3 * s4.w);
       }
       if (cold) {
         bias += __shfl_xor_sync(0xffffffffu, bias, 1);
         bias += __shfl_xor_sync(0xffffffffu, bias, 2);
-        float* bias_s = (float*)(st + SM::BIAS_OFF);
-        if (c == 0) bias_s[r] = r < G ? bias : 0.0f;
-        // outlier corrections: the side-list is grouped by token; a lane owns tokens
-        // lane, lane + 32, ... and walks their lists in step so the loads overlap
+        float* bias_s = (float*)(st + SM::BIAS_OFF);  // [8 rows][4]: one partial per warp
+        if (c == 0) bias_s[r * 4 + pw] = bias;
+        // outlier corrections: the side-list is grouped by token; a lane owns up to three
+        // tokens (32-token groups pw, pw+3, pw+6) and walks their lists in step
         float* corr = (float*)(st + SM::CORR_OFF);
         const PageMeta pm = *(const PageMeta*)(st + g.hdr_off);
         const uint16_t* rows = (const uint16_t*)(st + g.hdr_off + 16);
         const uint32_t* ent_s = (const uint32_t*)(st + g.ent_off);
         const uint32_t* ent_g =
             a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
-        int e0[8], e1[8];
-        float cacc[8][G];
+        int e0[3], e1[3];
+        float cacc[3][G];
         int kmax = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          e0[i] = rows[lane + 32 * i];
-          e1[i] = rows[lane + 32 * i + 1];
+        for (int i = 0; i < 3; ++i) {
+          const int grp = pw + NP * i;
+          e0[i] = e1[i] = 0;
+          if (grp < BLK / 32) {
+            e0[i] = rows[32 * grp + lane];
+            e1[i] = rows[32 * grp + lane + 1];
+          }
           kmax = max(kmax, e1[i] - e0[i]);
 #pragma unroll
           for (int gg = 0; gg < G; ++gg) cacc[i][gg] = 0.0f;
         }
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+        // branch-free in the common case (every entry inside the page): a lane past the end
+        // of its list reads entry 0 and adds zero, so the three chains of a round and the
+        // rounds themselves overlap instead of serialising behind divergent branches
+        const bool spill = pm.cnt > (uint32_t)TQ_INLINE_CAP;
+#pragma unroll 2
         for (int kk = 0; kk < kmax; ++kk) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 3; ++i) {
             const int e = e0[i] + kk;
-            if (e < e1[i]) {
-              const uint32_t wv = e < TQ_INLINE_CAP ? ent_s[e] : ent_g[e];
-              const float delta = __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu)));
-              const float* qrow = qc + ((wv >> 16) & 255) * G;
+            const bool live = e < e1[i];
+            const int es = live ? min(e, TQ_INLINE_CAP - 1) : 0;
+            uint32_t wv = ent_s[es];
+            if (spill && live && e >= TQ_INLINE_CAP) wv = ent_g[e];
+            const float delta =
+                live ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
+            const float* qrow = qc + ((wv >> 16) & 255) * G;
+            if (G >= 4) {
+#pragma unroll
+              for (int g4 = 0; g4 < G / 4; ++g4) {
+                const float4 qv = *(const float4*)(qrow + 4 * g4);
+                cacc[i][4 * g4 + 0] += qv.x * delta;
+                cacc[i][4 * g4 + 1] += qv.y * delta;
+                cacc[i][4 * g4 + 2] += qv.z * delta;
+                cacc[i][4 * g4 + 3] += qv.w * delta;
+              }
+            } else {
 #pragma unroll
               for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
             }
           }
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 3; ++i) {
+          const int grp = pw + NP * i;
+          if (grp < BLK / 32) {
 #pragma unroll
-          for (int gg = 0; gg < G; ++gg) corr[gg * BLK + lane + 32 * i] = cacc[i][gg];
+            for (int gg = 0; gg < G; ++gg) corr[gg * BLK + 32 * grp + lane] = cacc[i][gg];
+          }
+        }
       }
+      if (pw == 0) TQ_TRACE(4);
       mbar_arrive(ready0 + 8 * s);  // each lane releases its own writes
     }
     return;
@@ -518,8 +565,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
       cur_kind = tl.kind;
     }
     const uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
+    if (warp == 0) TQ_TRACE(5);
     waiter.wait(ready0 + 8 * s, k & 1);
     waiter.wait(full0 + 8 * s, k & 1);
+    if (warp == 0) TQ_TRACE(6);
 
     uint32_t areg[8][4];
 #pragma unroll
@@ -529,7 +578,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
     }
 
     if (tl.kind == 0) {
-      const float bias = ((const float*)(st + SM::BIAS_OFF))[rg];
+      const float4 b4 = *(const float4*)(st + SM::BIAS_OFF + rg * 16);
+      const float bias = b4.x + b4.y + b4.z;
       const float* corr = (const float*)(st + SM::CORR_OFF) + rg * BLK;
       const float* norms = (const float*)(st + g.norm_off);
       const uint8_t* vcodes = st + g.v_off;
@@ -538,14 +588,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         const int T0 = 32 * warp + 16 * half;
         float sv[2][2];
         const bool ok[2][2] = {{true, true}, {true, true}};
-        float C[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // four independent accumulation chains: two 8-token tiles x even/odd k-steps
+        float C[2][2][4] = {};
         uint32_t kw[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           const uint4 kc = *(const uint4*)(st + (T0 + 8 * nt + r) * 64 + c * 16);
           kw[nt][0] = kc.x; kw[nt][1] = kc.y; kw[nt][2] = kc.z; kw[nt][3] = kc.w;
         }
-        // the two 8-token tiles advance together so their accumulation chains interleave
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
 #pragma unroll
@@ -554,14 +604,16 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
             const uint32_t i0 = __byte_perm(w, 0, 0x4440 + 2 * (j & 1));
             const uint32_t i1 = __byte_perm(w, 0, 0x4441 + 2 * (j & 1));
             const uint32_t b0 = lut_ld(lutk + i0 * 128), b1 = lut_ld(lutk + i1 * 128);
-            mma16816(C[nt], areg[j], b0, b1);
+            mma16816(C[nt][j & 1], areg[j], b0, b1);
           }
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           const float2 cr = *(const float2*)(corr + T0 + 8 * nt + 2 * c);
-          sv[nt][0] = (C[nt][0] + C[nt][2] + bias + cr.x) * a.scale_log2;
-          sv[nt][1] = (C[nt][1] + C[nt][3] + bias + cr.y) * a.scale_log2;
+          const float s0 = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
+          const float s1 = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
+          sv[nt][0] = (s0 + bias + cr.x) * a.scale_log2;
+          sv[nt][1] = (s1 + bias + cr.y) * a.scale_log2;
           if (r >= G) sv[nt][0] = sv[nt][1] = 0.0f;
         }
         softmax16(sv, ok);
@@ -695,6 +747,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
     // every read of the stage is complete before it is handed back to the copy warp
     asm volatile("" ::: "memory");
     __syncwarp();
+    if (warp == 0) TQ_TRACE(7);
     if (lane == 0) mbar_arrive(empty0 + 8 * s);
   }
   if (cur_u >= 0) flush(cur_u, cur_kind);
@@ -869,7 +922,7 @@ int launch_t(const MmaArgs& a, cudaStream_t st, tq_ctx* ctx) {
 
 // Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
 size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
-  return 8192 + (units + 192) * 2 * CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
+  return 8192 + 4096 + (units + 192) * 2 * CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
 }
 
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
@@ -894,8 +947,9 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   a.seq_len = (const int32_t*)((const uint8_t*)ctx->b.state + state_len_off(g));
   a.tables = (const Tables*)ctx->b.tables;
   a.q = q;
-  a.plan_g = (int*)ctx->b.scratch;  // first 8 KB of the scratch region
-  a.partials = (float*)((uint8_t*)ctx->b.scratch + 8192);
+  a.plan_g = (int*)ctx->b.scratch;  // first 8 KB of the scratch region, then 4 KB of trace
+  a.trace = ctx->trace_on ? (unsigned long long*)((uint8_t*)ctx->b.scratch + 8192) : nullptr;
+  a.partials = (float*)((uint8_t*)ctx->b.scratch + 8192 + 4096);
   a.out = out;
   a.mlo = mlo;
   a.status = (int32_t*)((uint8_t*)ctx->b.state + state_status_off(g));
