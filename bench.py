@@ -370,7 +370,7 @@ def run_native(args):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "tokens_per_s": world * B / (ms_per_step * 1e-3),
         "config": workload_config(args, cfg, world),
         "bytes_per_step_per_gpu": step_bytes,

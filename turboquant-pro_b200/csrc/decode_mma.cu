@@ -121,7 +121,8 @@ struct Smem {
   static constexpr int DATA_BYTES = VB == 3 ? 34432 : 38528;
   static constexpr int FRAG_OFF = DATA_BYTES;
   static constexpr int CORR_OFF = FRAG_OFF + 8 * 32 * 16;
-  static constexpr int BIAS_OFF = CORR_OFF + G * BLK * 4;
+  static constexpr int CORR_STRIDE = BLK + 8;  // floats per query row: rows land on different banks
+  static constexpr int BIAS_OFF = CORR_OFF + G * CORR_STRIDE * 4;
   static constexpr int STAGE_BYTES = BIAS_OFF + 128;
   static constexpr int LUTK_BYTES = 256 * 128;
   static constexpr int LUTV_BYTES = (VB == 3 ? 64 : 256) * 128;
@@ -469,7 +470,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
           const int grp = pw + NP * i;
           if (grp < BLK / 32) {
 #pragma unroll
-            for (int gg = 0; gg < G; ++gg) corr[gg * BLK + 32 * grp + lane] = cacc[i][gg];
+            for (int gg = 0; gg < G; ++gg) corr[gg * SM::CORR_STRIDE + 32 * grp + lane] = cacc[i][gg];
           }
         }
       }
@@ -580,7 +581,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
     if (tl.kind == 0) {
       const float4 b4 = *(const float4*)(st + SM::BIAS_OFF + rg * 16);
       const float bias = b4.x + b4.y + b4.z;
-      const float* corr = (const float*)(st + SM::CORR_OFF) + rg * BLK;
+      const float* corr = (const float*)(st + SM::CORR_OFF) + rg * SM::CORR_STRIDE;
       const float* norms = (const float*)(st + g.norm_off);
       const uint8_t* vcodes = st + g.v_off;
 #pragma unroll 1
