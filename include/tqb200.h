@@ -221,6 +221,18 @@ int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes);
 /* Number of kernels the most recent tq_decode / tq_append of this context launched. */
 int32_t tq_last_launches(const tq_ctx* ctx);
 
+/* tq_decode for callers that have no working memory to lend and may not allocate any (an
+ * engine plugin that only receives q and out, a process whose device allocations are frozen
+ * while it serves, a sandboxed extension).  It has no counterpart in the reference.  The
+ * split-K partials go to a fixed 4.1 MiB array inside the library image instead of the
+ * context's scratch region; nothing is allocated or freed.  Limit: n_seqs * n_q_heads <=
+ * 1024, otherwise TQ_ERR_CAPACITY.  The array is shared by all contexts and streams of the
+ * process on that GPU, so calls must not overlap on the device.  The first call on a device
+ * resolves the array's device address; make it before any stream capture.  Always runs the
+ * general-shape kernel; same result as tq_decode within rounding. */
+int32_t tq_decode_static_scratch(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype,
+                                 float* out, void* stream);
+
 /* Selects the decode kernel: 0 = automatic (the tensor-core kernel where the geometry
  * allows: 256-token blocks, GQA group 1/2/4/8; else the general-shape kernel), 1 = always
  * the general-shape float32 kernel.  Both compute the same function; tests compare them.

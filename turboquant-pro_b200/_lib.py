@@ -68,6 +68,8 @@ SIGNATURES = {
                               C.c_void_p]),
     "tq_decode": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
                               C.c_void_p]),
+    "tq_decode_static_scratch": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
+                                             C.c_void_p, C.c_void_p]),
     "tq_decode_partial": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "tq_lse_combine": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,

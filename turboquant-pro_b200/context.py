@@ -216,6 +216,26 @@ class KVContext:
                                       out.data_ptr(), self._stream()))
         return out
 
+    def decode_static_scratch(self, layer: int, q, out=None):
+        """:meth:`decode` for callers that may not allocate or lend working memory: the
+        split-K partials live in a fixed array inside the library (at most 1024
+        (sequence, query head) pairs; calls must not overlap on the device).  ``out`` should
+        be passed by such callers; it is created here only as a convenience."""
+        torch = _torch()
+        g = self.geom
+        if tuple(q.shape) != (g.n_seqs, g.n_q_heads, g.head_dim):
+            raise ValueError(f"expected q of shape {(g.n_seqs, g.n_q_heads, g.head_dim)}, "
+                             f"got {tuple(q.shape)}")
+        q = q.contiguous()
+        if out is None:
+            out = torch.empty((g.n_seqs, g.n_q_heads, g.head_dim), dtype=torch.float32,
+                              device=self.device)
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_decode_static_scratch(self._h, layer, q.data_ptr(),
+                                                     _dtype_code(q.dtype), out.data_ptr(),
+                                                     self._stream()))
+        return out
+
     def decode_partial(self, layer: int, q, block_begin: int, block_end: int, with_hot: bool,
                        mlo=None):
         """Un-normalised ``(m, l, o)`` states over cold blocks ``[block_begin, block_end)``

@@ -541,3 +541,101 @@ int tq_launch_lse_combine(const float* mlo, int n_parts, int n_rows, int head_di
   TQ_CUDA(cudaGetLastError());
   return TQ_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode without caller-provided scratch.
+//
+// Some embedders cannot give this library any working memory of their own: a plugin that is
+// handed only the query and the output tensor by its host engine, a component that runs
+// after its process has frozen device allocations for the serving phase, or a sandboxed
+// extension that is not allowed to touch the allocator at all.  For them the split-K
+// partials live in the fixed array below, which belongs to the library image itself: every
+// GPU that loads the library carries these 4.1 MiB until the process exits.
+//
+// Limits and rules:
+//  - at most TQ_STATIC_ROWS (sequence, query head) pairs per call, i.e.
+//    n_seqs * n_q_heads <= 1024; larger contexts are refused with TQ_ERR_CAPACITY;
+//  - the array is shared by every context and stream of the process on that GPU and keeps
+//    whatever the previous call left in it.  Nothing in it has to start at zero: each call
+//    overwrites every slot it later reads.  Two calls that run on the GPU at the same time
+//    would overwrite each other's partials, so calls must be ordered (same stream, or
+//    synchronised);
+//  - inside host code the array's name is only a handle; the kernels need its device address.
+//    The first call on a device looks that address up (cudaGetSymbolAddress, with that
+//    device current) and remembers it, so make the first call on each device before any
+//    stream capture begins.
+// No allocation happens on this path: no cudaMalloc / cudaFree, no allocating library call.
+// ---------------------------------------------------------------------------------------
+constexpr int TQ_STATIC_ROWS = 1024;   // most (sequence, query head) pairs per call
+constexpr int TQ_STATIC_SLOTS = 8;     // split-K slots per (sequence, KV head)
+static __device__ __align__(256) float g_static_partials[(size_t)TQ_STATIC_ROWS * TQ_STATIC_SLOTS *
+                                                         TQ_PART_STRIDE];
+static float* g_static_partials_addr[64] = {};  // device address of the array, per device
+
+extern "C" int32_t tq_decode_static_scratch(tq_ctx* ctx, int32_t layer, const void* q,
+                                            int32_t q_dtype, float* out, void* stream) {
+  TQ_REQUIRE(ctx != nullptr && layer >= 0 && layer < ctx->g.n_layers, TQ_ERR_INVALID,
+             "bad context or layer");
+  TQ_REQUIRE(q != nullptr && out != nullptr, TQ_ERR_INVALID, "q and out must be device pointers");
+  TQ_REQUIRE(q_dtype == TQ_F32 || q_dtype == TQ_F16 || q_dtype == TQ_BF16, TQ_ERR_INVALID,
+             "bad q_dtype");
+  const tq_geom& g = ctx->g;
+  TQ_REQUIRE((long)g.n_seqs * g.n_q_heads <= TQ_STATIC_ROWS, TQ_ERR_CAPACITY,
+             "tq_decode_static_scratch serves at most 1024 (sequence, query head) pairs "
+             "(n_seqs * n_q_heads); use tq_decode with a scratch region for larger contexts");
+  TQ_REQUIRE(ctx->device >= 0 && ctx->device < 64, TQ_ERR_INVALID, "device ordinal out of range");
+  TQ_CUDA(cudaSetDevice(ctx->device));
+  if (g_static_partials_addr[ctx->device] == nullptr) {
+    float* p = nullptr;
+    TQ_CUDA(cudaGetSymbolAddress((void**)&p, g_static_partials));
+    g_static_partials_addr[ctx->device] = p;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+
+  DecodeArgs a;
+  a.g = g;
+  a.g.max_splits = TQ_STATIC_SLOTS;  // slot stride of the partials inside the fixed array
+  a.pages = (const uint8_t*)ctx->b.pages;
+  a.hot_k = ctx->b.hot_k;
+  a.hot_v = ctx->b.hot_v;
+  a.pool_dec = (const uint32_t*)ctx->b.pool_dec;
+  a.page_meta = (const PageMeta*)ctx->b.page_meta;
+  a.seq_len = (const int32_t*)((const uint8_t*)ctx->b.state + state_len_off(g));
+  a.tables = (const Tables*)ctx->b.tables;
+  a.q = q;
+  a.partials = g_static_partials_addr[ctx->device];
+  a.out = out;
+  a.mlo = nullptr;
+  a.layer = layer;
+  a.q_dtype = q_dtype;
+  a.block_begin = 0;
+  a.block_end = -1;
+  a.with_hot = 1;
+  a.scale = 1.0f / sqrtf((float)TQ_D);
+
+  int max_nb = 0, max_hot = 0;
+  for (int s = 0; s < g.n_seqs; ++s) {
+    int n = ctx->len[(size_t)layer * g.n_seqs + s];
+    int nb = n_cold_blocks(n, g.hot_window, g.block_tokens);
+    max_nb = std::max(max_nb, nb);
+    max_hot = std::max(max_hot, n - nb * g.block_tokens);
+  }
+  const int n_units = g.n_seqs * g.n_kv_heads;
+  int ns_hot = max_hot > 0 ? std::min((max_hot + 127) / 128, 2) : 0;
+  int ns_cold = max_nb > 0 ? std::min(max_nb, TQ_STATIC_SLOTS - ns_hot) : 0;
+  if (ns_cold + ns_hot == 0) ns_hot = 1;  // empty layer: the kernels still write zeros
+  a.ns_cold = ns_cold;
+  a.ns_hot = ns_hot;
+
+  int gt = g.group >= 8 ? 8 : (g.group > 2 ? 4 : (g.group > 1 ? 2 : 1));
+  switch (gt) {
+    case 1: launch_generic<1>(a, n_units, st); break;
+    case 2: launch_generic<2>(a, n_units, st); break;
+    case 4: launch_generic<4>(a, n_units, st); break;
+    default: launch_generic<8>(a, n_units, st); break;
+  }
+  combine_kernel<<<n_units, TQ_D, 0, st>>>(a);
+  ctx->last_launches = 2;
+  TQ_CUDA(cudaGetLastError());
+  return TQ_OK;
+}
