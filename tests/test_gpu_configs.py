@@ -1,0 +1,260 @@
+"""Parity at the shapes of the benchmark configurations (through the C ABI).
+
+Config 0 runs at full size against the CPU oracle.  The larger configurations are checked
+at reduced batch / layer counts with the same per-sequence geometry, bit-exactly for the
+encoders on sampled blocks and, where the oracle would take too long, through
+size-independent properties: the tensor-core kernel against the general-shape kernel,
+sequence-split partials against the full decode, bulk appends against token-by-token appends.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 2e-2, 2e-3
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    return torch
+
+
+def _c_oracle_cache(k, v, h, vb, w, pi):
+    """Cold blocks + hot tokens of one sequence through the C restatement (fast)."""
+    from oracle import c_oracle as co
+    from oracle import tq_oracle as orc
+
+    f = orc.block_tokens(w)
+    n = k.shape[0]
+    nb = orc.n_cold_blocks(n, w)
+    cent, bnd = orc.value_tables(128, vb)
+    pi_t = np.ascontiguousarray(pi.T)
+    kout = orc.outlier_count(f, 0.02)
+    kb, vbk = [], []
+    for b in range(nb):
+        xs = np.ascontiguousarray(np.moveaxis(k[b * f:(b + 1) * f], 0, 1), dtype=np.float32)
+        vs = np.ascontiguousarray(np.moveaxis(v[b * f:(b + 1) * f], 0, 1), dtype=np.float32)
+        kb.append(co.encode_keys(xs, kout))
+        vbk.append(co.encode_values(vs, pi_t, bnd))
+    keys = [co.dequant_keys(b["codes"], b["scale"], b["mean"], b["out_idx"], b["out_val"])
+            for b in kb]
+    vals = [co.dequant_values(b["codes"], b["norms"], cent, pi) for b in vbk]
+    keys.append(np.moveaxis(k[nb * f:], 0, 1).astype(np.float32))
+    vals.append(np.moveaxis(v[nb * f:], 0, 1).astype(np.float32))
+    return kb, vbk, np.concatenate(keys, axis=1), np.concatenate(vals, axis=1)
+
+
+def _check_export(blk, kb, vb_blk, vb):
+    from oracle import tq_oracle as orc
+
+    assert np.array_equal(blk["key_indices"], orc.pack_key_codes(kb["codes"]))
+    assert np.array_equal(blk["nf4_scale"][0], kb["scale"])
+    assert np.array_equal(blk["nf4_mean"][0], kb["mean"])
+    assert np.array_equal(blk["outlier_idx"], kb["out_idx"])
+    assert np.array_equal(blk["outlier_val"].view(np.uint16), kb["out_val"].view(np.uint16))
+    assert np.array_equal(blk["value_indices"], orc.pack_value_codes(vb_blk["codes"], vb))
+    assert np.array_equal(blk["value_norms"][0], vb_blk["norms"])
+
+
+def test_config0_full_size(torch_cuda):
+    """MHA 32 heads x 128, batch 1, context 4096, robust() K4/V4, hot window 512, fp32 K/V:
+    every cold block bit-exact, decode within tolerance of dequantise-then-attend."""
+    torch = torch_cuda
+    from oracle import c_oracle as co
+    from turboquant_pro_b200 import TurboQuantKVCache
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, n, w, vb, seed = 32, 4096, 512, 4, 0
+    k, v = make_kv(seed, h, n)
+    q = make_q(seed, h)
+    cache = TurboQuantKVCache.robust(head_dim=128, n_heads=h, hot_window=w, seed=seed,
+                                     max_tokens=n + 8)
+    cache.append_many(k, v)
+    assert (cache.length, cache.cold_length, cache.hot_length) == (4096, 3584, 512)
+    ctx = cache.context
+    kb, vbk, keys, vals = _c_oracle_cache(k, v, h, vb, w, ctx.pi)
+    assert len(kb) == 14
+    for i in range(14):
+        _check_export(ctx.export_block(0, 0, i), kb[i], vbk[i], vb)
+    want = co.attention(q, keys, vals)
+    got = cache.fused_decode(q)
+    err = np.abs(got - want).max()
+    assert np.allclose(got, want, rtol=RTOL, atol=ATOL), f"max abs err {err}"
+    # the getters return the same dequantised tensors as the oracle, bit for bit
+    assert np.array_equal(cache.get_keys(0, n)[0], keys)
+    assert np.array_equal(cache.get_values(0, n)[0], vals)
+    st = cache.memory_stats()
+    assert st["hot_bytes"] == 2 * 512 * h * 128 * 4
+    assert 3.5 < st["effective_ratio"] < 4.5
+
+
+def test_config1_shape_reduced_batch(torch_cuda):
+    """Llama-3-8B shape (32 q / 8 KV heads, K4/V3, fp16 K/V, bf16 q, context 8192) with 2
+    layers and 3 sequences: encoders bit-exact on sampled blocks, decode within tolerance."""
+    torch = torch_cuda
+    from oracle import c_oracle as co
+    from turboquant_pro_b200 import AutoConfig
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    cfg = AutoConfig.from_pretrained("llama-3-8b")
+    L, B, n = 2, 3, 8192
+    ctx = cfg.build_context(n_seqs=B, max_tokens_per_seq=n, n_layers=L, seed=4)
+    data = {}
+    for layer in range(L):
+        ks, vs = [], []
+        for s in range(B):
+            k, v = make_kv(100 * layer + s, 8, n, dtype=np.float16)
+            data[(layer, s)] = (k, v)
+            ks.append(k)
+            vs.append(v)
+        ctx.append(layer, torch.from_numpy(np.stack(ks)).cuda(), torch.from_numpy(np.stack(vs)).cuda())
+    assert ctx.lengths(1, 2) == (8192, 7680, 512)
+    for layer, s in ((0, 0), (1, 2)):
+        k, v = data[(layer, s)]
+        kb, vbk, keys, vals = _c_oracle_cache(k.astype(np.float32), v.astype(np.float32), 8, 3,
+                                              512, ctx.pi)
+        for i in (0, 13, 29):
+            _check_export(ctx.export_block(layer, s, i), kb[i], vbk[i], 3)
+        q = np.stack([make_q(9 + j, 32) for j in range(B)])
+        qd = torch.from_numpy(q).cuda().to(torch.bfloat16)
+        out = ctx.decode(layer, qd).cpu().numpy()
+        want = co.attention(qd[s].float().cpu().numpy(), keys, vals)
+        err = np.abs(out[s] - want).max()
+        assert np.allclose(out[s], want, rtol=RTOL, atol=ATOL), f"max abs err {err}"
+    assert ctx.status() == 0
+
+
+def test_config2_long_context_split(torch_cuda):
+    """One sequence of 131072 tokens (510 blocks + 512 hot), Llama-3-8B shape: the decode
+    equals the general-shape kernel, and 1/2/4/8-way sequence splits merged by the LSE
+    combine equal the unsplit result."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import AutoConfig
+
+    cfg = AutoConfig.from_pretrained("llama-3-8b")
+    n = 131072
+    ctx = cfg.build_context(n_seqs=1, max_tokens_per_seq=n, n_layers=1, seed=2)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2)
+    scale = torch.exp(0.5 * torch.randn((8, 128), generator=gen, device="cuda"))
+    for t0 in range(0, n, 16384):
+        k = (torch.randn((1, 16384, 8, 128), generator=gen, device="cuda") * scale).half()
+        v = torch.randn((1, 16384, 8, 128), generator=gen, device="cuda").half()
+        ctx.append(0, k, v)
+    assert ctx.lengths(0, 0) == (n, 510 * 256, 512)
+    q = torch.randn((1, 32, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    full = ctx.decode(0, q).cpu().numpy()
+    ctx.set_kernel("general")
+    slow = ctx.decode(0, q).cpu().numpy()
+    ctx.set_kernel("auto")
+    assert np.allclose(full, slow, rtol=RTOL, atol=ATOL), np.abs(full - slow).max()
+    for world in (2, 4, 8):
+        parts = [ctx.decode_partial(0, q, 510 * r // world, 510 * (r + 1) // world,
+                                    with_hot=(r == world - 1)).clone() for r in range(world)]
+        merged = ctx.lse_combine(torch.stack(parts).reshape(world, 32, 130)).cpu().numpy()
+        assert np.allclose(merged, full[0], rtol=1e-3, atol=1e-4), (world,
+                                                                     np.abs(merged - full[0]).max())
+    assert ctx.status() == 0
+
+
+def test_config3_shape_ragged_group8(torch_cuda):
+    """Llama-3-70B shape sharded to one KV head per rank (8 q heads on 1 KV head, K4/V4),
+    ragged contexts in [1024, 32768]: tensor-core kernel == general kernel == oracle."""
+    torch = torch_cuda
+    from oracle import c_oracle as co
+    from turboquant_pro_b200 import AutoConfig
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    cfg = AutoConfig.from_pretrained("llama-3-70b", target="quality")
+    assert (cfg.key_bits, cfg.value_bits, cfg.n_q_heads, cfg.n_kv_heads) == (4, 4, 64, 8)
+    rng = np.random.default_rng(3)
+    lens = [1024, 32768] + rng.integers(1024, 32769, size=4).tolist()
+    ctx = cfg.build_context(n_seqs=len(lens), max_tokens_per_seq=32768, n_layers=1, seed=6,
+                            n_kv_heads=1)  # this rank's shard: 1 KV head, its 8 q heads
+    assert ctx.n_q_heads == 8
+    data = []
+    for s, n in enumerate(lens):
+        k, v = make_kv(700 + s, 1, n, dtype=np.float16)
+        data.append((k, v))
+        ctx.append(0, torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda(),
+                   seq_begin=s)
+    q = np.stack([make_q(80 + s, 8) for s in range(len(lens))])
+    qd = torch.from_numpy(q).cuda().to(torch.bfloat16)
+    fast = ctx.decode(0, qd).cpu().numpy()
+    ctx.set_kernel("general")
+    slow = ctx.decode(0, qd).cpu().numpy()
+    ctx.set_kernel("auto")
+    assert np.allclose(fast, slow, rtol=RTOL, atol=ATOL), np.abs(fast - slow).max()
+    for s in (0, 2):
+        k, v = data[s]
+        kb, vbk, keys, vals = _c_oracle_cache(k.astype(np.float32), v.astype(np.float32), 1, 4,
+                                              512, ctx.pi)
+        _check_export(ctx.export_block(0, s, len(kb) - 1), kb[-1], vbk[-1], 4)
+        want = co.attention(qd[s].float().cpu().numpy(), keys, vals)
+        assert np.allclose(fast[s], want, rtol=RTOL, atol=ATOL), np.abs(fast[s] - want).max()
+    assert ctx.status() == 0
+
+
+def test_config4_prefill_then_decode_appends(torch_cuda):
+    """Prefill-append of 16384 tokens followed by 256 single-token appends (one flush happens
+    on the way): identical blocks to a token-by-token oracle, bit for bit."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import AutoConfig
+    from turboquant_pro_b200.synth import make_kv
+
+    cfg = AutoConfig.from_pretrained("llama-3-8b")
+    B, n0, steps = 2, 16384, 256
+    ctx = cfg.build_context(n_seqs=B, max_tokens_per_seq=n0 + steps, n_layers=1, seed=8)
+    ks, vs = zip(*[make_kv(900 + s, 8, n0 + steps, dtype=np.float16) for s in range(B)])
+    k_all, v_all = torch.from_numpy(np.stack(ks)).cuda(), torch.from_numpy(np.stack(vs)).cuda()
+    ctx.append(0, k_all[:, :n0], v_all[:, :n0])
+    assert ctx.lengths(0, 0) == (n0, 62 * 256, 512)
+    for t in range(n0, n0 + steps):
+        ctx.append(0, k_all[:, t:t + 1], v_all[:, t:t + 1])
+    assert ctx.lengths(0, 1) == (n0 + steps, 63 * 256, 512)
+    kb, vbk, _, _ = _c_oracle_cache(ks[1].astype(np.float32), vs[1].astype(np.float32), 8, 3, 512,
+                                    ctx.pi)
+    assert len(kb) == 63
+    for i in (0, 31, 61, 62):  # 62 is the block flushed during the single-token appends
+        _check_export(ctx.export_block(0, 1, i), kb[i], vbk[i], 3)
+    assert ctx.status() == 0
+
+
+def test_page_wide_channel_side_codes(torch_cuda):
+    """The page header names the four channels with the largest scale (ties to the lower
+    channel) and repeats their codes token by token; both must agree with the oracle's
+    scales and codes, since the tensor-core kernel corrects its scores from them."""
+    torch = torch_cuda
+    from oracle import tq_oracle as orc
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200.synth import make_kv
+
+    h, n, w = 2, 1100, 512
+    k, v = make_kv(21, h, n, dtype=np.float16)
+    k[:600, 0, 7] = k[:600, 0, 3]  # equal scales on two channels of the first block
+    ctx = KVContext(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h, value_bits=3,
+                    hot_window=w, max_tokens_per_seq=n, kv_dtype="float16", seed=21)
+    ctx.append(0, torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda())
+    torch.cuda.synchronize()
+    g = ctx.geom
+    f = g.block_tokens
+    nb = orc.n_cold_blocks(n, w)
+    assert nb >= 2
+    pages = ctx._regions["pages"].cpu().numpy()
+    for head in range(h):
+        for b in range(nb):
+            enc = orc.encode_keys(np.moveaxis(k[b * f:(b + 1) * f, head:head + 1], 0, 1), 0.02)
+            scale, codes = enc["scale"][0], enc["codes"][0]
+            order = np.lexsort((np.arange(128), -scale.astype(np.float64)))[:4]
+            off = (head * g.max_blocks + b) * g.page_bytes + g.hdr_off
+            assert pages[off + 8:off + 12].tolist() == order.tolist()
+            side = pages[off + 640:off + 640 + 2 * f].view(np.uint16)
+            want = sum(codes[:, order[i]].astype(np.uint16) << (4 * i) for i in range(4))
+            assert np.array_equal(side, want)

@@ -22,8 +22,10 @@ constexpr int TQ_MAX_K_OUT = 32;   // most outliers per channel the key encoder 
 constexpr int TQ_MAX_G = 16;       // largest GQA group
 constexpr int TQ_PART_STRIDE = 2 + TQ_D;  // floats per partial state (m, l, acc[D])
 
-constexpr int TQ_INLINE_CAP = 768;  // outlier entries stored inside the page itself
-constexpr int TQ_HDR_BYTES = 640;   // page header: PageHeader + row starts (uint16 x 257)
+constexpr int TQ_INLINE_CAP = 672;  // outlier entries stored inside the page itself
+constexpr int TQ_SIDE_OFF = 640;    // within the header: wide-channel codes (uint16 x 256)
+constexpr int TQ_HDR_BYTES = 1152;  // page header: PageHeader, wide ids, row starts, side codes
+constexpr int TQ_WIDE = 4;          // channels per page whose codes are kept a second time
 
 // bit 0 of the device status word: an outlier pool overflowed
 constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
@@ -40,7 +42,10 @@ constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
 //             +mean_off   key zero-point per channel, float32
 //             +hdr_off    PageHeader {outlier count, offset into the pool slab}, then
 //                         at +16 the start index of every token's outliers (uint16 x
-//                         (tokens + 1)): the side-list is grouped by token
+//                         (tokens + 1)): the side-list is grouped by token; at +8 the
+//                         ids of the TQ_WIDE channels with the largest scale, and at
+//                         +TQ_SIDE_OFF one uint16 per token holding their four codes
+//                         (nibble i = code of wide channel i)
 //             +ent_off    the first TQ_INLINE_CAP outlier entries (the rest only in the pool)
 // hot_k/v   [L][B][H][hot_cap][D] of kv_dtype; token at position p lives in slot p % hot_cap
 // pool_dec  [L][B][H][pool_entries] uint32: fp16 delta | channel << 16 | token << 24

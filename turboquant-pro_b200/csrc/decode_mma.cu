@@ -117,8 +117,8 @@ TQ_DEV uint32_t bf16x2_to_h2(uint32_t w) {
 //  stages].  Per stage: [tile data | fragments | corr | bias].
 template <int G, int VB>
 struct Smem {
-  // a tile is a whole page (34432 B at V3, 38528 B at V4) or 32 KB of hot rows
-  static constexpr int DATA_BYTES = VB == 3 ? 34432 : 38528;
+  // a tile is a whole page (34560 B at V3, 38656 B at V4) or 32 KB of hot rows
+  static constexpr int DATA_BYTES = VB == 3 ? 34560 : 38656;
   static constexpr int FRAG_OFF = DATA_BYTES;
   static constexpr int CORR_OFF = FRAG_OFF + 8 * 32 * 16;
   static constexpr int CORR_STRIDE = BLK + 8;  // floats per query row: rows land on different banks
@@ -250,7 +250,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   uint8_t* lutv_p = smem;
   uint8_t* lutk_p = lutv_p + SM::LUTV_BYTES;
   Plan* plan = (Plan*)(lutk_p + SM::LUTK_BYTES);
-  static_assert(sizeof(Plan) <= SM::PLAN_BYTES, "plan does not fit its shared-memory slot");
+  static_assert(sizeof(Plan) <= SM::PLAN_BYTES - 64, "plan does not fit its shared-memory slot");
+  // NF4[c] - fp16(NF4[c]): what the half-precision key table loses, added back in float32
+  // for the widest channels of a page
+  float* dtab = (float*)((uint8_t*)plan + SM::PLAN_BYTES - 64);
   float* q_all = (float*)((uint8_t*)plan + SM::PLAN_BYTES);  // [NP][128][G]
   uint64_t* bars = (uint64_t*)((uint8_t*)q_all + SM::Q_BYTES);  // full, ready, empty [NSTAGE]
   volatile int* abort_flag = (volatile int*)(bars + 12);
@@ -272,6 +275,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
     if (tid < 16) small[tid] = a.tables->nf4[tid];
     else if (tid < 32) small[tid] = a.tables->centroids[tid - 16];
     __syncthreads();
+    if (tid < 16) dtab[tid] = small[tid] - __half2float(__float2half_rn(small[tid]));
     for (int i = tid; i < 256 * 32; i += THREADS) {
       int b = i >> 5;
       ((uint32_t*)lutk_p)[i] = pack_h2(small[b & 15], small[b >> 4]);
@@ -462,6 +466,33 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
             } else {
 #pragma unroll
               for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
+            }
+          }
+        }
+        // the widest channels of the page: their table rounding error, times a large
+        // weight, would show in the scores, so it is added back here token by token
+        {
+          const uchar4 wid = *(const uchar4*)(st + g.hdr_off + 8);
+          const uint16_t* side = (const uint16_t*)(st + g.hdr_off + TQ_SIDE_OFF);
+          const int wch[TQ_WIDE] = {wid.x, wid.y, wid.z, wid.w};
+          uint32_t sd[3];
+#pragma unroll
+          for (int i = 0; i < 3; ++i) {
+            const int grp = pw + NP * i;
+            sd[i] = grp < BLK / 32 ? side[32 * grp + lane] : 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < TQ_WIDE; ++j) {
+            const float sc = scale[wch[j]];
+            const float* qrow = qc + wch[j] * G;
+            float dl[3];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) {
+              const float qv = qrow[gg];
+#pragma unroll
+              for (int i = 0; i < 3; ++i) cacc[i][gg] += qv * dl[i];
             }
           }
         }

@@ -90,6 +90,10 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   if (d == 0) s_count = 0;
   s_tok_cnt[d] = 0;
   s_tok_cnt[d + TQ_D] = 0;
+  __shared__ float s_scale[TQ_D];       // channel scales, to rank the widest channels
+  __shared__ unsigned int s_side[256];  // per token: the codes of the four widest channels
+  s_side[d] = 0u;
+  s_side[d + TQ_D] = 0u;
   __syncthreads();
 
   // pass 1: sequential sum and the k largest magnitudes (ascending; top[0] is the k-th)
@@ -137,8 +141,19 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   ((float*)(page + g.scale_off))[d] = amax;
   ((float*)(page + g.mean_off))[d] = mu;
 
+  s_scale[d] = amax;
   // allocate this page's slice of the (layer, seq, head) outlier slab
   __syncthreads();
+  // Rank of this channel by scale (0 = widest; ties go to the lower channel).  The codes of
+  // the four widest channels are stored a second time, token by token, so that the decode
+  // kernel can add their contribution at full float32 table precision: w * NF4 of such a
+  // channel is large enough for the fp16 rounding of the table to show in the scores.
+  int rank = 0;
+  for (int o = 0; o < TQ_D; ++o) {
+    const float so = s_scale[o];
+    rank += (so > amax || (so == amax && o < d)) ? 1 : 0;
+  }
+  if (rank < 4) page[g.hdr_off + 8 + rank] = (uint8_t)d;
   if (kk > 0) atomicAdd(&s_count, my_out);
   __syncthreads();
   if (d == 0) {
@@ -210,6 +225,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
         best = l;
       }
     }
+    if (rank < 4) atomicOr(&s_side[t], (unsigned int)best << (4 * rank));
     int other = __shfl_down_sync(0xffffffffu, best, 1);
     if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
     if (kk > 0 && fabsf(x) >= kth) {
@@ -225,6 +241,12 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
         if (slot < TQ_INLINE_CAP) inline_ent[slot] = ent;
       }
     }
+  }
+  __syncthreads();
+  {
+    uint16_t* side = (uint16_t*)(page + g.hdr_off + TQ_SIDE_OFF);
+    side[2 * d] = (uint16_t)s_side[2 * d];
+    side[2 * d + 1] = (uint16_t)s_side[2 * d + 1];
   }
   // padded token rows (block_tokens not a multiple of 16) keep code 0
   for (int t = S; t < g.block_tokens_pad; ++t)
