@@ -1,20 +1,24 @@
 // Decode-on-codes attention for the common geometry (256-token cold blocks, head_dim 128,
 // GQA group 1/2/4/8): a persistent, warp-specialised kernel.
 //
-//   warp 8        streams tiles HBM -> shared memory with bulk asynchronous copies
-//                 (cp.async.bulk + mbarrier transaction counts) through a ring of stages;
-//                 a tile is one cold page (codes, norms, scales and its outlier list:
-//                 34 KB at V3, 38 KB at V4) or one 32 KB slice of the hot window
-//   warps 9-11    prepare the query- and page-dependent operands of a landed tile, taking
-//                 turns tile by tile: w = q * scale split into fp16 hi/lo tensor-core
-//                 fragments, bias = q . mean, and the per-token outlier corrections
-//   warps 0-7     consume tiles: 4-bit key codes and 3/4-bit value code pairs become fp16
-//                 pairs through one conflict-free shared-memory table lookup each and go
-//                 straight into m16n8k16 tensor-core tiles as register fragments (scores:
-//                 M = query group padded to 16 with the lo parts in rows 8-15, N = 8 tokens,
-//                 K = 16 channels; values: M = 16 channels, N = 8 query heads, K = 16
-//                 tokens); online softmax in fp32 registers.  K and V are never
-//                 materialised.
+//   tiles         stream HBM -> shared memory with bulk asynchronous copies (cp.async.bulk +
+//                 mbarrier transaction counts) through a ring of stages; a tile is one cold
+//                 page (codes, norms, scales and its outlier list: 34 KB at V3, 38 KB at V4)
+//                 or one 32 KB slice of the hot window.  There is no copy warp: the group
+//                 that has finished with a stage starts the copy of the tile that uses the
+//                 stage next.
+//   consumer      groups of four warps; group i owns tiles i, i + NG, i + 2 NG ... of the CTA's
+//   groups        share, so NG pages are being worked on at once while the next ones land.
+//                 Per page a group first builds the query- and page-dependent operands
+//                 (w = q * scale split into fp16 hi/lo tensor-core fragments, bias = q . mean,
+//                 the per-token outlier corrections: each warp for its own 64 tokens), then
+//                 each warp attends its 64 tokens: 4-bit key codes and 3/4-bit value code
+//                 pairs become fp16 pairs through one conflict-free shared-memory table
+//                 lookup each and go straight into m16n8k16 tensor-core tiles as register
+//                 fragments (scores: M = query group padded to 16 with the lo parts in rows
+//                 8-15, N = 8 tokens, K = 16 channels; values: M = 16 channels, N = 8 query
+//                 heads, K = 16 tokens); online softmax in fp32 registers.  K and V are
+//                 never materialised.
 //
 // Work is a flat list of tiles over all (sequence, KV head) units of the layer, cut into
 // equal contiguous shares, one per CTA (one CTA per SM), so ragged contexts balance.
@@ -28,11 +32,11 @@
 
 namespace {
 
-constexpr int CW = 8;                        // consumer warps
-constexpr int NP = 3;                        // prepare warps
-constexpr int THREADS = (CW + 1 + NP) * 32;  // + one copy warp
+constexpr int GW = 4;                // warps per consumer group
+constexpr int MAX_NG = 3;            // most consumer groups
+constexpr int MAX_CW = MAX_NG * GW;  // most consumer warps (partial slots per CTA and unit)
 constexpr int MAX_UNITS = 512;
-constexpr int BLK = 256;                     // tokens per cold page
+constexpr int BLK = 256;             // tokens per cold page
 constexpr float NEG_BIG = -1.0e30f;
 constexpr int SPIN_LIMIT = 1 << 18;  // probes per wait; each may suspend up to ~2 us
 constexpr int STATUS_TIMEOUT = 2;
@@ -53,6 +57,7 @@ struct MmaArgs {
   int32_t* status;
   unsigned long long* trace;  // optional: SM clock stamps of CTA 0's first 64 tiles
   int layer, q_dtype, n_units, n_cta;
+  int n_groups;  // consumer groups of the attention kernel (the combine enumerates their slots)
   int block_begin, block_end, with_hot;
   float scale_log2;
 };
@@ -113,25 +118,42 @@ TQ_DEV uint32_t bf16x2_to_h2(uint32_t w) {
 }
 
 // ---- shared-memory plan --------------------------------------------------------------------
-// [value table (8 KB aligned) | key table | plan | q copies of the prepare warps | barriers |
-//  stages].  Per stage: [tile data | fragments | corr | bias].
-template <int G, int VB>
-struct Smem {
+// [value table (8 KB aligned at V3) | key table | plan | group scratch x NG | barriers |
+//  stages].  A stage holds one tile; a group's scratch holds its query copy, the fragments
+// and bias of the page it works on and one outlier-correction strip per warp.
+template <int G, int VB, int NG>
+struct SmemT {
   // a tile is a whole page (34560 B at V3, 38656 B at V4) or 32 KB of hot rows
   static constexpr int DATA_BYTES = VB == 3 ? 34560 : 38656;
-  static constexpr int FRAG_OFF = DATA_BYTES;
-  static constexpr int CORR_OFF = FRAG_OFF + 8 * 32 * 16;
-  static constexpr int CORR_STRIDE = BLK + 8;  // floats per query row: rows land on different banks
-  static constexpr int BIAS_OFF = CORR_OFF + G * CORR_STRIDE * 4;
-  static constexpr int STAGE_BYTES = BIAS_OFF + 128;
   static constexpr int LUTK_BYTES = 256 * 128;
   static constexpr int LUTV_BYTES = (VB == 3 ? 64 : 256) * 128;
-  static constexpr int ALIGN_SLACK = 8192;  // the value table starts on an 8 KB boundary
+  // the 3-bit value table starts on an 8 KB boundary (its addresses are formed with OR)
+  static constexpr int ALIGN_SLACK = VB == 3 ? 8192 : 0;
   static constexpr int PLAN_BYTES = 8192;
-  static constexpr int Q_BYTES = 8 * 32 * 16 + TQ_D * G * 4;  // fragment-ordered + [128][G]
-  static constexpr int FIXED = ALIGN_SLACK + LUTK_BYTES + LUTV_BYTES + PLAN_BYTES + Q_BYTES + 256;
-  static constexpr int NSTAGE = (232448 - FIXED) / STAGE_BYTES >= 3 ? 3 : 2;
-  static constexpr int TOTAL = FIXED + NSTAGE * STAGE_BYTES;
+  static constexpr int QC_BYTES = TQ_D * G * 4;  // [128][G] query values
+  static constexpr int FRAG_BYTES = 8 * 32 * 16;
+  static constexpr int BIAS_BYTES = 128;         // [8 rows][GW]: one partial per warp
+  static constexpr int CORR_STRIDE = 64 + 8;     // floats per query row: rows on different banks
+  static constexpr int CORR_BYTES = G * CORR_STRIDE * 4;  // per warp
+  static constexpr int FRAG_OFF = QC_BYTES;
+  static constexpr int BIAS_OFF = FRAG_OFF + FRAG_BYTES;
+  static constexpr int CORR_OFF = BIAS_OFF + BIAS_BYTES;
+  static constexpr int GROUP_BYTES = CORR_OFF + GW * CORR_BYTES;
+  static constexpr int FIXED =
+      ALIGN_SLACK + LUTK_BYTES + LUTV_BYTES + PLAN_BYTES + NG * GROUP_BYTES + 256;
+  static constexpr int FIT = (232448 - FIXED) / DATA_BYTES;
+  static constexpr int NSTAGE = FIT >= 4 ? 4 : FIT;
+  static constexpr int TOTAL = FIXED + NSTAGE * DATA_BYTES;
+};
+
+// three groups when four stages still fit beside them (one page always in flight), else two
+template <int G, int VB>
+struct Cfg {
+  static constexpr int NG = SmemT<G, VB, 3>::NSTAGE >= 4 ? 3 : 2;
+  using SM = SmemT<G, VB, NG>;
+  static_assert(SM::NSTAGE > NG, "a group refills a stage for a later tile of another group");
+  static constexpr int CWT = NG * GW;  // consumer warps
+  static constexpr int THREADS = CWT * 32;
 };
 
 struct Plan {  // lives in shared memory
@@ -221,6 +243,11 @@ struct Waiter {
     *abort_flag = 1;
     atomicOr(status, STATUS_TIMEOUT);
   }
+  // bounded wait that ignores the abort flag
+  TQ_DEV void drain(uint32_t bar, uint32_t parity) const {
+    for (int i = 0; i < SPIN_LIMIT; ++i)
+      if (mbar_try(bar, parity)) return;
+  }
 };
 
 // fp16 hi / lo fragments of four consecutive weights of a row: {hi01, lo01, hi23, lo23}
@@ -236,17 +263,19 @@ TQ_DEV uint4 frag_hilo(float w0, float w1, float w2, float w3) {
 }
 
 template <int G, int VB>
-__global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
-  using SM = Smem<G, VB>;
-  constexpr int NSTAGE = SM::NSTAGE;
+__global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaArgs a) {
+  using CF = Cfg<G, VB>;
+  using SM = typename CF::SM;
+  constexpr int NG = CF::NG, NSTAGE = SM::NSTAGE, CWT = CF::CWT, THREADS = CF::THREADS;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const tq_geom& g = a.g;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, c = lane & 3;
 
-  // the value table sits on an 8 KB boundary of the shared address space so that a table
-  // address is (index bits) | (base + lane offset), one logic instruction
-  uint8_t* smem = smem_raw + ((8192u - (smem_addr(smem_raw) & 8191u)) & 8191u);
+  // the 3-bit value table sits on an 8 KB boundary of the shared address space so that a
+  // table address is (index bits) | (base + lane offset), one logic instruction
+  uint8_t* smem = smem_raw;
+  if (VB == 3) smem += (8192u - (smem_addr(smem_raw) & 8191u)) & 8191u;
   uint8_t* lutv_p = smem;
   uint8_t* lutk_p = lutv_p + SM::LUTV_BYTES;
   Plan* plan = (Plan*)(lutk_p + SM::LUTK_BYTES);
@@ -254,24 +283,25 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   // NF4[c] - fp16(NF4[c]): what the half-precision key table loses, added back in float32
   // for the widest channels of a page
   float* dtab = (float*)((uint8_t*)plan + SM::PLAN_BYTES - 64);
-  float* q_all = (float*)((uint8_t*)plan + SM::PLAN_BYTES);  // [NP][128][G]
-  uint64_t* bars = (uint64_t*)((uint8_t*)q_all + SM::Q_BYTES);  // full, ready, empty [NSTAGE]
-  volatile int* abort_flag = (volatile int*)(bars + 12);
+  uint8_t* groups = (uint8_t*)plan + SM::PLAN_BYTES;
+  // "tile landed" barriers.  Tile t lands in stage t % NSTAGE but signals barrier
+  // t % (2 NSTAGE): stages are refilled out of order (by whichever group frees them), so a
+  // group can come to wait for tile t + NSTAGE while tile t - NSTAGE still occupies the
+  // stage; with one barrier per stage that wait would see the parity of the older phase.
+  uint64_t* bars = (uint64_t*)(groups + NG * SM::GROUP_BYTES);
+  volatile int* abort_flag = (volatile int*)(bars + 16);
   uint8_t* stages = (uint8_t*)bars + 256;
+  static_assert(2 * NSTAGE <= 16, "barrier slots");
 
-  const uint32_t full0 = smem_addr(bars), ready0 = full0 + 8 * NSTAGE, empty0 = ready0 + 8 * NSTAGE;
+  const uint32_t full0 = smem_addr(bars);
   if (tid == 0) {
-    for (int s = 0; s < NSTAGE; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(ready0 + 8 * s, NP * 32);
-      mbar_init(empty0 + 8 * s, CW);
-    }
+    for (int s = 0; s < 2 * NSTAGE; ++s) mbar_init(full0 + 8 * s, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // lookup tables: entry-major, one copy per lane so that a warp's 32 lookups never collide
   {
-    float* small = q_all;  // 32 floats of scratch until the prepare warps claim the area
+    float* small = (float*)groups;  // 32 floats of scratch until the groups claim the area
     if (tid < 16) small[tid] = a.tables->nf4[tid];
     else if (tid < 32) small[tid] = a.tables->centroids[tid - 16];
     __syncthreads();
@@ -316,202 +346,43 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
     return t;
   };
 
-  // ============================== copy warp ==================================================
-  if (warp == CW) {
-    if (lane == 0) {
-      int u_cur = find_unit(plan, a.n_units, lo);
-      for (int pos = lo; pos < hi; ++pos) {
-        const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
-        Tile tl = tile_at(pos, u_cur);
-        const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
-        TQ_TRACE(0);
-        waiter.wait(empty0 + 8 * s, (k & 1) ^ 1);
-        TQ_TRACE(1);
-        if (*abort_flag) break;
-        const uint32_t dst = smem_addr(stages + (size_t)s * SM::STAGE_BYTES);
-        const uint32_t bar = full0 + 8 * s;
-        if (tl.kind == 0) {
-          const uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, tl.idx);
-          mbar_arrive_expect_tx(bar, (uint32_t)g.page_bytes);
-          bulk_g2s(dst, page, (uint32_t)g.page_bytes, bar);
-        } else {
-          const int slot = (plan->hot_start[tl.u] + tl.idx * htt) % g.hot_cap;
-          const size_t off = (hot_offset_elems(g, a.layer, seq, head) + (size_t)slot * TQ_D) * esz;
-          const uint32_t bytes = (uint32_t)(htt * TQ_D * esz);
-          mbar_arrive_expect_tx(bar, 2 * bytes);
-          bulk_g2s(dst, a.hot_k + off, bytes, bar);
-          bulk_g2s(dst + bytes, a.hot_v + off, bytes, bar);
-        }
-      }
-      // never leave with copies in flight: the last NSTAGE tiles are waited for here too
-      const int total = hi - lo;
-      for (int t = max(0, total - NSTAGE); t < total; ++t)
-        waiter.wait(full0 + 8 * (t % NSTAGE), (t / NSTAGE) & 1);
+  // Starts the copy of tile t of this CTA's share (one thread calls it).  The stage must be
+  // free: either it was never used or the caller's group has just finished with it.
+  const int total = hi - lo;
+  auto issue = [&](int t, int& u_cursor) {
+    const Tile tl = tile_at(lo + t, u_cursor);
+    const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
+    const uint32_t dst = smem_addr(stages + (size_t)(t % NSTAGE) * SM::DATA_BYTES);
+    const uint32_t bar = full0 + 8 * (t % (2 * NSTAGE));
+    if (tl.kind == 0) {
+      const uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, tl.idx);
+      mbar_arrive_expect_tx(bar, (uint32_t)g.page_bytes);
+      bulk_g2s(dst, page, (uint32_t)g.page_bytes, bar);
+    } else {
+      const int slot = (plan->hot_start[tl.u] + tl.idx * htt) % g.hot_cap;
+      const size_t off = (hot_offset_elems(g, a.layer, seq, head) + (size_t)slot * TQ_D) * esz;
+      const uint32_t bytes = (uint32_t)(htt * TQ_D * esz);
+      mbar_arrive_expect_tx(bar, 2 * bytes);
+      bulk_g2s(dst, a.hot_k + off, bytes, bar);
+      bulk_g2s(dst + bytes, a.hot_v + off, bytes, bar);
     }
-    return;
-  }
+  };
 
-  // ============================== prepare warps ==============================================
-  // The three warps work on the same tile: the fragment k-steps, the bias dot product and
-  // the tokens of the outlier list are split three ways, which keeps the latency from
-  // "tile landed" to "tile ready" short.
-  if (warp > CW) {
-    const int pw = warp - CW - 1, ptid = tid - (CW + 1) * 32;
-    float4* qf = (float4*)q_all;                 // [8][32] query values in fragment order
-    float* qc = q_all + 8 * 32 * 4;              // [128][G] for the outlier dot products
-    int u_cur = find_unit(plan, a.n_units, lo);
-    int q_unit = -1;
-    for (int pos = lo; pos < hi; ++pos) {
-      const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
-      Tile tl = tile_at(pos, u_cur);
-      const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
-      if (tl.u != q_unit) {  // new unit: reload its query rows (all three warps in step)
-        q_unit = tl.u;
-        asm volatile("bar.sync 1, %0;" ::"n"(NP * 32) : "memory");
-        for (int i = ptid; i < 8 * 32 * 4; i += NP * 32) {
-          const int j = i >> 7, ln = (i >> 2) & 31, e = i & 3;
-          const int rr = ln >> 2, d = 32 * (ln & 3) + 4 * j + e;
-          float v = 0.0f;
-          if (rr < G) {
-            size_t qi = ((size_t)seq * g.n_q_heads + head * G + rr) * TQ_D + d;
-            v = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
-                : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
-                                      : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
-            qc[d * G + rr] = v;
-          }
-          ((float*)qf)[i] = v;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(NP * 32) : "memory");
-      }
-      uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
-      if (pw == 0) TQ_TRACE(2);
-      waiter.wait(full0 + 8 * s, k & 1);
-      if (pw == 0) TQ_TRACE(3);
-      uint4* frag = (uint4*)(st + SM::FRAG_OFF);
-      const bool cold = tl.kind == 0;
-      const float* scale = (const float*)(st + g.scale_off);
-      const float* mean = (const float*)(st + g.mean_off);
-      float bias = 0.0f;
-      // k-steps pw, pw+3, pw+6: a fixed trip count so that the three chains overlap
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int j = pw + NP * i;
-        if (j < 8) {
-          const int d0 = 32 * c + 4 * j;
-          const float4 q4 = qf[j * 32 + lane];
-          float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
-          if (cold) {
-            s4 = *(const float4*)&scale[d0];
-            const float4 m4 = *(const float4*)&mean[d0];
-            bias += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
-          }
-          frag[j * 32 + lane] = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
-        }
-      }
-      if (cold) {
-        bias += __shfl_xor_sync(0xffffffffu, bias, 1);
-        bias += __shfl_xor_sync(0xffffffffu, bias, 2);
-        float* bias_s = (float*)(st + SM::BIAS_OFF);  // [8 rows][4]: one partial per warp
-        if (c == 0) bias_s[r * 4 + pw] = bias;
-        // outlier corrections: the side-list is grouped by token; a lane owns up to three
-        // tokens (32-token groups pw, pw+3, pw+6) and walks their lists in step
-        float* corr = (float*)(st + SM::CORR_OFF);
-        const PageMeta pm = *(const PageMeta*)(st + g.hdr_off);
-        const uint16_t* rows = (const uint16_t*)(st + g.hdr_off + 16);
-        const uint32_t* ent_s = (const uint32_t*)(st + g.ent_off);
-        const uint32_t* ent_g =
-            a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
-        int e0[3], e1[3];
-        float cacc[3][G];
-        int kmax = 0;
-#pragma unroll
-        for (int i = 0; i < 3; ++i) {
-          const int grp = pw + NP * i;
-          e0[i] = e1[i] = 0;
-          if (grp < BLK / 32) {
-            e0[i] = rows[32 * grp + lane];
-            e1[i] = rows[32 * grp + lane + 1];
-          }
-          kmax = max(kmax, e1[i] - e0[i]);
-#pragma unroll
-          for (int gg = 0; gg < G; ++gg) cacc[i][gg] = 0.0f;
-        }
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
-        // branch-free in the common case (every entry inside the page): a lane past the end
-        // of its list reads entry 0 and adds zero, so the three chains of a round and the
-        // rounds themselves overlap instead of serialising behind divergent branches
-        const bool spill = pm.cnt > (uint32_t)TQ_INLINE_CAP;
-#pragma unroll 2
-        for (int kk = 0; kk < kmax; ++kk) {
-#pragma unroll
-          for (int i = 0; i < 3; ++i) {
-            const int e = e0[i] + kk;
-            const bool live = e < e1[i];
-            const int es = live ? min(e, TQ_INLINE_CAP - 1) : 0;
-            uint32_t wv = ent_s[es];
-            if (spill && live && e >= TQ_INLINE_CAP) wv = ent_g[e];
-            const float delta =
-                live ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
-            const float* qrow = qc + ((wv >> 16) & 255) * G;
-            if (G >= 4) {
-#pragma unroll
-              for (int g4 = 0; g4 < G / 4; ++g4) {
-                const float4 qv = *(const float4*)(qrow + 4 * g4);
-                cacc[i][4 * g4 + 0] += qv.x * delta;
-                cacc[i][4 * g4 + 1] += qv.y * delta;
-                cacc[i][4 * g4 + 2] += qv.z * delta;
-                cacc[i][4 * g4 + 3] += qv.w * delta;
-              }
-            } else {
-#pragma unroll
-              for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
-            }
-          }
-        }
-        // the widest channels of the page: their table rounding error, times a large
-        // weight, would show in the scores, so it is added back here token by token
-        {
-          const uchar4 wid = *(const uchar4*)(st + g.hdr_off + 8);
-          const uint16_t* side = (const uint16_t*)(st + g.hdr_off + TQ_SIDE_OFF);
-          const int wch[TQ_WIDE] = {wid.x, wid.y, wid.z, wid.w};
-          uint32_t sd[3];
-#pragma unroll
-          for (int i = 0; i < 3; ++i) {
-            const int grp = pw + NP * i;
-            sd[i] = grp < BLK / 32 ? side[32 * grp + lane] : 0u;
-          }
-#pragma unroll
-          for (int j = 0; j < TQ_WIDE; ++j) {
-            const float sc = scale[wch[j]];
-            const float* qrow = qc + wch[j] * G;
-            float dl[3];
-#pragma unroll
-            for (int i = 0; i < 3; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
-#pragma unroll
-            for (int gg = 0; gg < G; ++gg) {
-              const float qv = qrow[gg];
-#pragma unroll
-              for (int i = 0; i < 3; ++i) cacc[i][gg] += qv * dl[i];
-            }
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 3; ++i) {
-          const int grp = pw + NP * i;
-          if (grp < BLK / 32) {
-#pragma unroll
-            for (int gg = 0; gg < G; ++gg) corr[gg * SM::CORR_STRIDE + 32 * grp + lane] = cacc[i][gg];
-          }
-        }
-      }
-      if (pw == 0) TQ_TRACE(4);
-      mbar_arrive(ready0 + 8 * s);  // each lane releases its own writes
-    }
-    return;
+  // ============================== consumer groups ============================================
+  const int gi = warp / GW, gw = warp % GW, gtid = tid - gi * (GW * 32);
+  int u_iss = find_unit(plan, a.n_units, lo);  // cursor of the copies this thread starts
+  if (tid == 0) {
+    for (int t = 0; t < min(NSTAGE, total); ++t) issue(t, u_iss);
   }
+  uint8_t* gs = groups + gi * SM::GROUP_BYTES;
+  float* qc = (float*)gs;                                   // [128][G]
+  uint4* frag = (uint4*)(gs + SM::FRAG_OFF);                // [8 k-steps][32 lanes]
+  float* bias_s = (float*)(gs + SM::BIAS_OFF);              // [8 rows][GW]
+  float* corr_w = (float*)(gs + SM::CORR_OFF) + gw * (G * SM::CORR_STRIDE);  // this warp's strip
+  auto group_sync = [&]() {
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "n"(GW * 32) : "memory");
+  };
 
-  // ============================== consumer warps =============================================
   const uint32_t lutk = smem_addr(lutk_p) + lane * 4;
   const uint32_t lutv = smem_addr(lutv_p) + lane * 4;  // 8 KB aligned base | lane offset
   const int rg = r < G ? r : G - 1;
@@ -526,13 +397,12 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   reset_state();
 
   auto flush = [&](int u, int kind) {
-    const int active = kind == 0 ? CW : htt / 16;
-    if (warp >= active) return;
+    if (kind != 0 && gw >= htt / 16) return;
     float l = l_run;
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     float* pp = a.partials +
-                ((((size_t)u + blockIdx.x) * 2 + kind) * CW + warp) * (size_t)(G * TQ_PART_STRIDE);
+                ((((size_t)u + blockIdx.x) * 2 + kind) * CWT + warp) * (size_t)(G * TQ_PART_STRIDE);
     if (c == 0 && r < G) {
       pp[r * TQ_PART_STRIDE] = m_run;
       pp[r * TQ_PART_STRIDE + 1] = l;
@@ -586,38 +456,168 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
   };
 
   int u_cur = find_unit(plan, a.n_units, lo);
-  int cur_u = -1, cur_kind = -1;
-  for (int pos = lo; pos < hi; ++pos) {
-    const int t = pos - lo, s = t % NSTAGE, k = t / NSTAGE;
+  int cur_u = -1, cur_kind = -1, q_unit = -1;
+  for (int pos = lo + gi; pos < hi; pos += NG) {
+    const int t = pos - lo, s = t % NSTAGE;
+    const uint32_t full_bar = full0 + 8 * (t % (2 * NSTAGE));
+    const uint32_t full_par = (t / (2 * NSTAGE)) & 1;
     const Tile tl = tile_at(pos, u_cur);
+    const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
     if (tl.u != cur_u || tl.kind != cur_kind) {
       if (cur_u >= 0) flush(cur_u, cur_kind);
       reset_state();
       cur_u = tl.u;
       cur_kind = tl.kind;
     }
-    const uint8_t* st = stages + (size_t)s * SM::STAGE_BYTES;
-    if (warp == 0) TQ_TRACE(5);
-    waiter.wait(ready0 + 8 * s, k & 1);
-    waiter.wait(full0 + 8 * s, k & 1);
-    if (warp == 0) TQ_TRACE(6);
+    // the group is done with the fragments, bias, query copy and stage of its previous tile
+    group_sync();
+    if (gtid == 0 && t >= NG && t - NG + NSTAGE < total && !*abort_flag) {
+      TQ_TRACE(1);
+      issue(t - NG + NSTAGE, u_iss);  // refill the stage that tile has just left
+    }
+    if (tl.u != q_unit) {  // new unit: reload its query rows
+      q_unit = tl.u;
+      for (int i = gtid; i < TQ_D * G; i += GW * 32) {
+        const int d = i / G, rr = i % G;
+        const size_t qi = ((size_t)seq * g.n_q_heads + head * G + rr) * TQ_D + d;
+        qc[i] = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
+                : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
+                                      : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
+      }
+      group_sync();
+    }
+    const uint8_t* st = stages + (size_t)s * SM::DATA_BYTES;
+    if (warp == 0) TQ_TRACE(2);
+    waiter.wait(full_bar, full_par);
+    if (warp == 0) TQ_TRACE(3);
+
+    // ---- operands that depend on the query and the page ------------------------------------
+    const bool cold = tl.kind == 0;
+    const float* scale = (const float*)(st + g.scale_off);
+    {
+      const float* mean = (const float*)(st + g.mean_off);
+      float bias = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8 / GW; ++i) {  // this warp's k-steps
+        const int j = gw + GW * i;
+        const int d0 = 32 * c + 4 * j;
+        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < G) {
+          q4.x = qc[(d0 + 0) * G + r];
+          q4.y = qc[(d0 + 1) * G + r];
+          q4.z = qc[(d0 + 2) * G + r];
+          q4.w = qc[(d0 + 3) * G + r];
+        }
+        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (cold) {
+          s4 = *(const float4*)&scale[d0];
+          const float4 m4 = *(const float4*)&mean[d0];
+          bias += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
+        }
+        frag[j * 32 + lane] = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
+      }
+      bias += __shfl_xor_sync(0xffffffffu, bias, 1);
+      bias += __shfl_xor_sync(0xffffffffu, bias, 2);
+      if (c == 0) bias_s[r * GW + gw] = bias;
+    }
+    if (cold) {
+      // outlier corrections of this warp's 64 tokens: the side-list is grouped by token; a
+      // lane owns two tokens (lane and lane + 32 of the strip) and walks their lists in step
+      const PageMeta pm = *(const PageMeta*)(st + g.hdr_off);
+      const uint16_t* rows = (const uint16_t*)(st + g.hdr_off + 16) + 64 * gw;
+      const uint32_t* ent_s = (const uint32_t*)(st + g.ent_off);
+      const uint32_t* ent_g =
+          a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
+      int e0[2], e1[2];
+      float cacc[2][G];
+      int kmax = 0;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        e0[i] = rows[32 * i + lane];
+        e1[i] = rows[32 * i + lane + 1];
+        kmax = max(kmax, e1[i] - e0[i]);
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg) cacc[i][gg] = 0.0f;
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+      // branch-free in the common case (every entry inside the page): a lane past the end
+      // of its list reads entry 0 and adds zero, so the chains of a round and the rounds
+      // themselves overlap instead of serialising behind divergent branches
+      const bool spill = pm.cnt > (uint32_t)TQ_INLINE_CAP;
+#pragma unroll 2
+      for (int kk = 0; kk < kmax; ++kk) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int e = e0[i] + kk;
+          const bool live = e < e1[i];
+          const int es = live ? min(e, TQ_INLINE_CAP - 1) : 0;
+          uint32_t wv = ent_s[es];
+          if (spill && live && e >= TQ_INLINE_CAP) wv = ent_g[e];
+          const float delta =
+              live ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
+          const float* qrow = qc + ((wv >> 16) & 255) * G;
+          if (G >= 4) {
+#pragma unroll
+            for (int g4 = 0; g4 < G / 4; ++g4) {
+              const float4 qv = *(const float4*)(qrow + 4 * g4);
+              cacc[i][4 * g4 + 0] += qv.x * delta;
+              cacc[i][4 * g4 + 1] += qv.y * delta;
+              cacc[i][4 * g4 + 2] += qv.z * delta;
+              cacc[i][4 * g4 + 3] += qv.w * delta;
+            }
+          } else {
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
+          }
+        }
+      }
+      // the widest channels of the page: their table rounding error, times a large
+      // weight, would show in the scores, so it is added back here token by token
+      {
+        const uchar4 wid = *(const uchar4*)(st + g.hdr_off + 8);
+        const uint16_t* side = (const uint16_t*)(st + g.hdr_off + TQ_SIDE_OFF) + 64 * gw;
+        const int wch[TQ_WIDE] = {wid.x, wid.y, wid.z, wid.w};
+        const uint32_t sd[2] = {side[lane], side[32 + lane]};
+#pragma unroll
+        for (int j = 0; j < TQ_WIDE; ++j) {
+          const float sc = scale[wch[j]];
+          const float* qrow = qc + wch[j] * G;
+          float dl[2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg) {
+            const float qv = qrow[gg];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) cacc[i][gg] += qv * dl[i];
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + 32 * i + lane] = cacc[i][gg];
+    }
+    group_sync();  // fragments and bias of all four warps are in place
+    if (warp == 0) TQ_TRACE(4);
 
     uint32_t areg[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const uint4 f = *(const uint4*)(st + SM::FRAG_OFF + (j * 32 + lane) * 16);
+      const uint4 f = frag[j * 32 + lane];
       areg[j][0] = f.x; areg[j][1] = f.y; areg[j][2] = f.z; areg[j][3] = f.w;
     }
 
-    if (tl.kind == 0) {
-      const float4 b4 = *(const float4*)(st + SM::BIAS_OFF + rg * 16);
-      const float bias = b4.x + b4.y + b4.z;
-      const float* corr = (const float*)(st + SM::CORR_OFF) + rg * SM::CORR_STRIDE;
+    if (cold) {
+      const float4 b4 = *(const float4*)(bias_s + rg * GW);
+      const float bias = (b4.x + b4.y) + (b4.z + b4.w);
+      const float* corr = corr_w + rg * SM::CORR_STRIDE;
       const float* norms = (const float*)(st + g.norm_off);
       const uint8_t* vcodes = st + g.v_off;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        const int T0 = 32 * warp + 16 * half;
+      for (int half = 0; half < 4; ++half) {
+        const int T0 = 64 * gw + 16 * half;
         float sv[2][2];
         const bool ok[2][2] = {{true, true}, {true, true}};
         // four independent accumulation chains: two 8-token tiles x even/odd k-steps
@@ -641,7 +641,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          const float2 cr = *(const float2*)(corr + T0 + 8 * nt + 2 * c);
+          const float2 cr = *(const float2*)(corr + 16 * half + 8 * nt + 2 * c);
           const float s0 = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
           const float s1 = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
           sv[nt][0] = (s0 + bias + cr.x) * a.scale_log2;
@@ -653,7 +653,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         const float2 n1 = *(const float2*)(norms + T0 + 8 + 2 * c);
         const uint32_t pb0 = pack_h2(sv[0][0] * n0.x, sv[0][1] * n0.y);
         const uint32_t pb1 = pack_h2(sv[1][0] * n1.x, sv[1][1] * n1.y);
-        const int gq = 2 * warp + half;
+        const int gq = 4 * gw + half;
         if (VB == 4) {
           const uint8_t* gb = vcodes + gq * 1024 + lane * 16;
           const uint4 r0 = *(const uint4*)gb, r1 = *(const uint4*)(gb + 512);
@@ -692,10 +692,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
           }
         }
       }
-    } else if (warp < htt / 16) {
+    } else if (gw < htt / 16) {
       // ---- hot tile: uncompressed rows, same tensor-core tiles, no tables ----------------
       const int hot_len = plan->hot_len[tl.u];
-      const int T0 = 16 * warp;                 // first token of this warp inside the tile
+      const int T0 = 16 * gw;                   // first token of this warp inside the tile
       const int base_tok = tl.idx * htt + T0;   // ... inside the hot window
       const uint8_t* kbase = st;
       const uint8_t* vbase = st + htt * TQ_D * esz;
@@ -776,20 +776,28 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(MmaArgs a) {
         mma16816(acc[mt], af, pb0, pb1);
       }
     }
-    // every read of the stage is complete before it is handed back to the copy warp
+    // every read of the stage is complete before the group's next barrier, after which the
+    // stage is refilled
     asm volatile("" ::: "memory");
     __syncwarp();
     if (warp == 0) TQ_TRACE(7);
-    if (lane == 0) mbar_arrive(empty0 + 8 * s);
   }
   if (cur_u >= 0) flush(cur_u, cur_kind);
+  // A group's last tile is among the last NG of the share, so no refill is owed here.  After
+  // a timed-out wait copies may still be in flight: they are waited for (bounded) before the
+  // CTA gives up its shared memory.
+  if (*abort_flag) {
+    if (gtid == 0)  // every copy this thread started signals one of these barriers
+      for (int t = max(0, total - 2 * NSTAGE); t < total; ++t)
+        waiter.drain(full0 + 8 * (t % (2 * NSTAGE)), (t / (2 * NSTAGE)) & 1);
+  }
 }
 
 constexpr int MAX_PARTS = 96;  // partials merged per round
 
 // Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the per-warp
-// partials of every CTA that owned tiles of the unit, in the fixed order (CTA, cold before
-// hot, warp) and in rounds of MAX_PARTS with a running maximum, un-rotates the cold part
+// partials of every CTA and consumer group that owned tiles of the unit, in the fixed order
+// (CTA, cold before hot, warp) and in rounds of MAX_PARTS with a running maximum, un-rotates the cold part
 // once (acc @ Pi) and writes the output or the (m, l, o) state.  Partial maxima are in the
 // log2 domain.
 template <int G>
@@ -808,6 +816,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   const int p0 = a.plan_g[2 + unit], p1 = a.plan_g[3 + unit];
   const int pc = p0 + a.plan_g[3 + a.n_units + unit];
   const int hot_warps = hot_tile_tokens(g.kv_dtype) / 16;
+  const int NG = a.n_groups, ncw = NG * GW;
   const int i0 = p1 > p0 ? p0 / Q : 0, i1 = p1 > p0 ? (p1 - 1) / Q : -1;
   if (e < G) {
     s_M[e] = NEG_BIG;
@@ -827,14 +836,21 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
     if (e == 0) {
       int n = 0, i = s_it[0], kind = s_it[1], w = s_it[2];
       while (i <= i1 && n < MAX_PARTS) {
+        // tiles of this kind that CTA i holds for the unit: positions [ra, rb); the tile at
+        // position p belongs to consumer group (p - lo) % NG
         const int lo = i * Q, hi = lo + Q;
-        const bool has = kind == 0 ? (max(lo, p0) < min(hi, pc)) : (max(lo, pc) < min(hi, p1));
-        const int nw = kind == 0 ? CW : hot_warps;
-        if (has && w < nw) {
-          s_ptr[n] = a.partials + ((((size_t)unit + i) * 2 + kind) * CW + w) *
-                                      (size_t)(G * TQ_PART_STRIDE);
-          s_cold[n] = kind == 0;
-          ++n;
+        const int ra = kind == 0 ? max(lo, p0) : max(lo, pc);
+        const int rb = kind == 0 ? min(hi, pc) : min(hi, p1);
+        if (ra < rb && w < ncw) {
+          const int gi = w / GW, gw = w % GW;
+          const int cnt = rb - ra, first = (ra - lo) % NG;
+          const bool owns = cnt >= NG || (gi - first + NG) % NG < cnt;
+          if (owns && (kind == 0 || gw < hot_warps)) {
+            s_ptr[n] = a.partials + ((((size_t)unit + i) * 2 + kind) * ncw + w) *
+                                        (size_t)(G * TQ_PART_STRIDE);
+            s_cold[n] = kind == 0;
+            ++n;
+          }
           ++w;
         } else {
           w = 0;
@@ -927,8 +943,9 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
 }
 
 template <int G, int VB>
-int launch_t(const MmaArgs& a, cudaStream_t st, tq_ctx* ctx) {
-  using SM = Smem<G, VB>;
+int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
+  using CF = Cfg<G, VB>;
+  using SM = typename CF::SM;
   static bool attr_set[16] = {};
   int dev = ctx->device;
   if (!attr_set[dev & 15]) {
@@ -938,7 +955,8 @@ int launch_t(const MmaArgs& a, cudaStream_t st, tq_ctx* ctx) {
   }
   cudaEvent_t e0 = tq_prof_event(ctx, 0), e1 = tq_prof_event(ctx, 1), e2 = tq_prof_event(ctx, 2);
   if (e0) cudaEventRecord(e0, st);
-  decode_mma_kernel<G, VB><<<a.n_cta, THREADS, SM::TOTAL, st>>>(a);
+  a.n_groups = CF::NG;
+  decode_mma_kernel<G, VB><<<a.n_cta, CF::THREADS, SM::TOTAL, st>>>(a);
   if (e1) cudaEventRecord(e1, st);
   combine_mma_kernel<G><<<a.n_units, TQ_D, 0, st>>>(a);
   if (e2) {
@@ -954,7 +972,7 @@ int launch_t(const MmaArgs& a, cudaStream_t st, tq_ctx* ctx) {
 
 // Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
 size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
-  return 8192 + 4096 + (units + 192) * 2 * CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
+  return 8192 + 4096 + (units + 192) * 2 * MAX_CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
 }
 
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
