@@ -22,9 +22,9 @@
 //
 // Work is a flat list of tiles over all (sequence, KV head) units of the layer, cut into
 // equal contiguous shares, one per CTA (one CTA per SM), so ragged contexts balance.
-// Every consumer warp keeps its own softmax state and writes its own partial
-// (m, l, acc[D]); the combine kernel merges them in a fixed order and applies the single
-// inverse rotation of the value accumulator.
+// Every consumer warp keeps its own softmax state; when a group leaves a unit its four warps
+// merge their states and write one partial (m, l, acc[D]); the combine kernel merges the
+// partials in a fixed order and applies the single inverse rotation of the value accumulator.
 //
 // All waits are bounded: a wait that runs out sets bit 1 of the status word and an abort
 // flag that makes every later wait return at once, so the kernel always terminates.
@@ -34,7 +34,6 @@ namespace {
 
 constexpr int GW = 4;                // warps per consumer group
 constexpr int MAX_NG = 3;            // most consumer groups
-constexpr int MAX_CW = MAX_NG * GW;  // most consumer warps (partial slots per CTA and unit)
 constexpr int MAX_UNITS = 512;
 constexpr int BLK = 256;             // tokens per cold page
 constexpr float NEG_BIG = -1.0e30f;
@@ -346,25 +345,42 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
     return t;
   };
 
-  // Starts the copy of tile t of this CTA's share (one thread calls it).  The stage must be
-  // free: either it was never used or the caller's group has just finished with it.
+  // The copy of tile t of this CTA's share: describe() works out addresses and sizes (it can
+  // run before the stage is free), fire() starts it (the stage must be free: never used, or
+  // the caller's group has just finished with it).
+  struct CopyDesc {
+    const uint8_t* src;
+    const uint8_t* src2;  // second source of a hot tile (the value rows), else null
+    uint32_t bytes, dst, bar;
+  };
   const int total = hi - lo;
-  auto issue = [&](int t, int& u_cursor) {
+  auto describe = [&](int t, int& u_cursor) -> CopyDesc {
     const Tile tl = tile_at(lo + t, u_cursor);
     const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
-    const uint32_t dst = smem_addr(stages + (size_t)(t % NSTAGE) * SM::DATA_BYTES);
-    const uint32_t bar = full0 + 8 * (t % (2 * NSTAGE));
+    CopyDesc d;
+    d.dst = smem_addr(stages + (size_t)(t % NSTAGE) * SM::DATA_BYTES);
+    d.bar = full0 + 8 * (t % (2 * NSTAGE));
     if (tl.kind == 0) {
-      const uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, tl.idx);
-      mbar_arrive_expect_tx(bar, (uint32_t)g.page_bytes);
-      bulk_g2s(dst, page, (uint32_t)g.page_bytes, bar);
+      d.src = a.pages + page_offset(g, a.layer, seq, head, tl.idx);
+      d.src2 = nullptr;
+      d.bytes = (uint32_t)g.page_bytes;
     } else {
       const int slot = (plan->hot_start[tl.u] + tl.idx * htt) % g.hot_cap;
       const size_t off = (hot_offset_elems(g, a.layer, seq, head) + (size_t)slot * TQ_D) * esz;
-      const uint32_t bytes = (uint32_t)(htt * TQ_D * esz);
-      mbar_arrive_expect_tx(bar, 2 * bytes);
-      bulk_g2s(dst, a.hot_k + off, bytes, bar);
-      bulk_g2s(dst + bytes, a.hot_v + off, bytes, bar);
+      d.src = a.hot_k + off;
+      d.src2 = a.hot_v + off;
+      d.bytes = (uint32_t)(htt * TQ_D * esz);
+    }
+    return d;
+  };
+  auto fire = [&](const CopyDesc& d) {
+    if (d.src2 == nullptr) {
+      mbar_arrive_expect_tx(d.bar, d.bytes);
+      bulk_g2s(d.dst, d.src, d.bytes, d.bar);
+    } else {
+      mbar_arrive_expect_tx(d.bar, 2 * d.bytes);
+      bulk_g2s(d.dst, d.src, d.bytes, d.bar);
+      bulk_g2s(d.dst + d.bytes, d.src2, d.bytes, d.bar);
     }
   };
 
@@ -372,7 +388,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
   const int gi = warp / GW, gw = warp % GW, gtid = tid - gi * (GW * 32);
   int u_iss = find_unit(plan, a.n_units, lo);  // cursor of the copies this thread starts
   if (tid == 0) {
-    for (int t = 0; t < min(NSTAGE, total); ++t) issue(t, u_iss);
+    for (int t = 0; t < min(NSTAGE, total); ++t) fire(describe(t, u_iss));
   }
   uint8_t* gs = groups + gi * SM::GROUP_BYTES;
   float* qc = (float*)gs;                                   // [128][G]
@@ -396,27 +412,73 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
   };
   reset_state();
 
+  // Writes the group's partial (m, l, acc[D]) of one (unit, kind): the four warps merge their
+  // states through shared memory (the fragment / bias / correction areas are idle between
+  // tiles) and the 128 threads store one coalesced record.  Called by all warps of the group.
   auto flush = [&](int u, int kind) {
-    if (kind != 0 && gw >= htt / 16) return;
+    // as many warps at a time as there is room for accumulator copies (row stride 132
+    // floats: the cold layout then stores without bank conflicts)
+    constexpr int MG_STRIDE = TQ_D + 4, MG_ONE = G * MG_STRIDE * 4;
+    constexpr int MG_ROOM = SM::GROUP_BYTES - SM::FRAG_OFF - 2 * GW * 8 * 4;
+    constexpr int MG_PAR = MG_ROOM >= 4 * MG_ONE ? 4 : (MG_ROOM >= 2 * MG_ONE ? 2 : 1);
+    static_assert(MG_ROOM >= MG_ONE, "merge scratch");
+    float* mg_m = (float*)(gs + SM::FRAG_OFF);  // [GW][8] maxima of the warps, per query row
+    float* mg_l = mg_m + GW * 8;                // [GW][8] their sums
+    float* mg_acc = mg_l + GW * 8;              // [MG_PAR][G][MG_STRIDE] scaled accumulators
+    group_sync();  // every warp has finished its last tile
     float l = l_run;
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    float* pp = a.partials +
-                ((((size_t)u + blockIdx.x) * 2 + kind) * CWT + warp) * (size_t)(G * TQ_PART_STRIDE);
-    if (c == 0 && r < G) {
-      pp[r * TQ_PART_STRIDE] = m_run;
-      pp[r * TQ_PART_STRIDE + 1] = l;
+    if (c == 0) {
+      mg_m[gw * 8 + r] = m_run;
+      mg_l[gw * 8 + r] = l;
     }
+    group_sync();
+    // the accumulator columns of this thread belong to query rows 2c and 2c+1
+    float M0 = NEG_BIG, M1 = NEG_BIG;
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt)
+    for (int w = 0; w < GW; ++w) {
+      M0 = fmaxf(M0, mg_m[w * 8 + 2 * c]);
+      M1 = fmaxf(M1, mg_m[w * 8 + 2 * c + 1]);
+    }
+    const float f0 = exp2f(mg_m[gw * 8 + 2 * c] - M0), f1 = exp2f(mg_m[gw * 8 + 2 * c + 1] - M1);
+    float* mine = mg_acc + (gw % MG_PAR) * (G * MG_STRIDE);
+    for (int step = 0; step < GW / MG_PAR; ++step) {
+      if (gw / MG_PAR == step) {
 #pragma unroll
-      for (int x = 0; x < 2; ++x)
+        for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
-        for (int y = 0; y < 2; ++y) {
-          const int gg = 2 * c + y;
-          const int d = kind == 0 ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
-          if (gg < G) pp[gg * TQ_PART_STRIDE + 2 + d] = acc[mt][2 * x + y];
-        }
+          for (int x = 0; x < 2; ++x)
+#pragma unroll
+            for (int y = 0; y < 2; ++y) {
+              const int gg = 2 * c + y;
+              const int d = kind == 0 ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
+              if (gg < G) {
+                const float v = acc[mt][2 * x + y] * (y ? f1 : f0);
+                if (step == 0) mine[gg * MG_STRIDE + d] = v; else mine[gg * MG_STRIDE + d] += v;
+              }
+            }
+      }
+      group_sync();
+    }
+    float* pp = a.partials +
+                ((((size_t)u + blockIdx.x) * 2 + kind) * NG + gi) * (size_t)(G * TQ_PART_STRIDE);
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg) {
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < MG_PAR; ++w) v += mg_acc[(w * G + gg) * MG_STRIDE + gtid];
+      pp[gg * TQ_PART_STRIDE + 2 + gtid] = v;
+    }
+    if (gtid < G) {
+      float M = NEG_BIG, L = 0.0f;
+#pragma unroll
+      for (int w = 0; w < GW; ++w) M = fmaxf(M, mg_m[w * 8 + gtid]);
+#pragma unroll
+      for (int w = 0; w < GW; ++w) L += mg_l[w * 8 + gtid] * exp2f(mg_m[w * 8 + gtid] - M);
+      pp[gtid * TQ_PART_STRIDE] = M;
+      pp[gtid * TQ_PART_STRIDE + 1] = L;
+    }
   };
 
   // online-softmax update with the four scores of this thread's row (two 8-token tiles,
@@ -469,11 +531,16 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
       cur_u = tl.u;
       cur_kind = tl.kind;
     }
+    // The stage of the group's previous tile is refilled once all four warps are done with
+    // it; the warps take turns at starting the copy and describe it before the barrier.
+    const bool refill = lane == 0 && gw == (t / NG) % GW && t >= NG && t - NG + NSTAGE < total;
+    CopyDesc cd;
+    if (refill) cd = describe(t - NG + NSTAGE, u_iss);
     // the group is done with the fragments, bias, query copy and stage of its previous tile
     group_sync();
-    if (gtid == 0 && t >= NG && t - NG + NSTAGE < total && !*abort_flag) {
+    if (refill && !*abort_flag) {
+      fire(cd);
       TQ_TRACE(1);
-      issue(t - NG + NSTAGE, u_iss);  // refill the stage that tile has just left
     }
     if (tl.u != q_unit) {  // new unit: reload its query rows
       q_unit = tl.u;
@@ -787,7 +854,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
   // a timed-out wait copies may still be in flight: they are waited for (bounded) before the
   // CTA gives up its shared memory.
   if (*abort_flag) {
-    if (gtid == 0)  // every copy this thread started signals one of these barriers
+    if (lane == 0)  // every copy this thread started signals one of these barriers
       for (int t = max(0, total - 2 * NSTAGE); t < total; ++t)
         waiter.drain(full0 + 8 * (t % (2 * NSTAGE)), (t / (2 * NSTAGE)) & 1);
   }
@@ -797,7 +864,7 @@ constexpr int MAX_PARTS = 96;  // partials merged per round
 
 // Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the per-warp
 // partials of every CTA and consumer group that owned tiles of the unit, in the fixed order
-// (CTA, cold before hot, warp) and in rounds of MAX_PARTS with a running maximum, un-rotates the cold part
+// (CTA, cold before hot, group) and in rounds of MAX_PARTS with a running maximum, un-rotates the cold part
 // once (acc @ Pi) and writes the output or the (m, l, o) state.  Partial maxima are in the
 // log2 domain.
 template <int G>
@@ -811,12 +878,11 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   __shared__ float s_l[MAX_PARTS][G];
   __shared__ int s_cold[MAX_PARTS];
   __shared__ float s_M[G], s_L[G], s_scale[G];
-  __shared__ int s_n, s_it[3];  // round size; enumeration cursor (cta, kind, warp)
+  __shared__ int s_n, s_it[3];  // round size; enumeration cursor (cta, kind, group)
   const int Q = a.plan_g[1];
   const int p0 = a.plan_g[2 + unit], p1 = a.plan_g[3 + unit];
   const int pc = p0 + a.plan_g[3 + a.n_units + unit];
-  const int hot_warps = hot_tile_tokens(g.kv_dtype) / 16;
-  const int NG = a.n_groups, ncw = NG * GW;
+  const int NG = a.n_groups;
   const int i0 = p1 > p0 ? p0 / Q : 0, i1 = p1 > p0 ? (p1 - 1) / Q : -1;
   if (e < G) {
     s_M[e] = NEG_BIG;
@@ -841,12 +907,11 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
         const int lo = i * Q, hi = lo + Q;
         const int ra = kind == 0 ? max(lo, p0) : max(lo, pc);
         const int rb = kind == 0 ? min(hi, pc) : min(hi, p1);
-        if (ra < rb && w < ncw) {
-          const int gi = w / GW, gw = w % GW;
+        if (ra < rb && w < NG) {
           const int cnt = rb - ra, first = (ra - lo) % NG;
-          const bool owns = cnt >= NG || (gi - first + NG) % NG < cnt;
-          if (owns && (kind == 0 || gw < hot_warps)) {
-            s_ptr[n] = a.partials + ((((size_t)unit + i) * 2 + kind) * ncw + w) *
+          const bool owns = cnt >= NG || (w - first + NG) % NG < cnt;
+          if (owns) {
+            s_ptr[n] = a.partials + ((((size_t)unit + i) * 2 + kind) * NG + w) *
                                         (size_t)(G * TQ_PART_STRIDE);
             s_cold[n] = kind == 0;
             ++n;
@@ -898,7 +963,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
       C[gg] *= s_scale[gg];
       Hh[gg] *= s_scale[gg];
     }
-#pragma unroll 4
+#pragma unroll 8
     for (int j = 0; j < n; ++j) {
       const float* pp = s_ptr[j] + 2 + e;
       const bool cold = s_cold[j] != 0;
@@ -917,7 +982,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   float o[G];
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) o[gg] = 0.0f;
-#pragma unroll 8
+#pragma unroll 64
   for (int d = 0; d < TQ_D; ++d) {
     const float pv = a.tables->pi[d * TQ_D + e];
 #pragma unroll
@@ -972,7 +1037,7 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
 
 // Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
 size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
-  return 8192 + 4096 + (units + 192) * 2 * MAX_CW * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
+  return 8192 + 4096 + (units + 192) * 2 * MAX_NG * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
 }
 
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
