@@ -80,7 +80,7 @@ typedef struct tq_geom {
   int32_t pool_entries;       /* outlier-pool entries per (layer, seq, kv head)        */
   int32_t max_splits;         /* partial slots per (seq, kv head) in the scratch area  */
   int32_t hdr_off;            /* page header: outlier count, pool offset, row starts   */
-  int32_t ent_off;            /* outlier entries kept inside the page (the first 672)   */
+  int32_t ent_off;            /* the page's own by-token copy of its outliers            */
   int32_t reserved_;
 } tq_geom;
 

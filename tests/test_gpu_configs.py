@@ -255,6 +255,62 @@ def test_page_wide_channel_side_codes(torch_cuda):
             order = np.lexsort((np.arange(128), -scale.astype(np.float64)))[:4]
             off = (head * g.max_blocks + b) * g.page_bytes + g.hdr_off
             assert pages[off + 8:off + 12].tolist() == order.tolist()
-            side = pages[off + 640:off + 640 + 2 * f].view(np.uint16)
+            side = pages[off + 64:off + 64 + 2 * f].view(np.uint16)
             want = sum(codes[:, order[i]].astype(np.uint16) << (4 * i) for i in range(4))
             assert np.array_equal(side, want)
+
+
+def test_heavy_tokens_overflow_and_spill(torch_cuda):
+    """Tokens that are outliers on many channels at once: more entries than a token's fixed
+    slots in the page (overflow list) and more than the page's overflow list holds (the kernel
+    then reads the pool's list).  Tensor-core kernel == general kernel == oracle, and two
+    calls give identical bits."""
+    torch = torch_cuda
+    from oracle import tq_oracle as orc
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, n, w, vb = 2, 4, 1100, 512, 3
+    k, v = make_kv(33, h, n, dtype=np.float16)
+    k = k.astype(np.float32)
+
+    def boost(tok, head, chans):
+        # the largest magnitude of its block on every given channel: certainly an outlier
+        b0 = tok // 256 * 256
+        k[tok, head, chans] = 1.5 * np.abs(k[b0:b0 + 256, head, chans]).max(axis=0)
+
+    boost(5, 0, slice(None))          # block 0, head 0: one token on all 128 channels -> spill
+    boost(300, 0, slice(0, 20))       # block 1, head 0: two tokens of one strip, 20 channels each
+    boost(301, 0, slice(10, 30))
+    boost(256 + 200, 0, slice(90, 102))  # and one token of the last strip
+    boost(100, 1, slice(0, 128, 3))   # head 1, block 0: 43 channels on one token
+    k = k.astype(np.float16)
+    q = make_q(33, h * grp)
+    ctx = KVContext(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h * grp, value_bits=vb,
+                    hot_window=w, max_tokens_per_seq=n, kv_dtype="float16", seed=33)
+    ctx.append(0, torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda())
+    torch.cuda.synchronize()
+    g = ctx.geom
+    pages = ctx._regions["pages"].cpu().numpy()
+    flags = {}
+    for head in range(h):
+        for b in range(2):
+            off = (head * g.max_blocks + b) * g.page_bytes + g.hdr_off
+            hdr = pages[off:off + 64]
+            flags[(head, b)] = (int(hdr[12:14].view(np.uint16)[0]), int(hdr[14:16].view(np.uint16)[0]))
+    assert flags[(0, 0)][1] == 1                      # spilled
+    assert flags[(0, 1)][1] == 0 and flags[(0, 1)][0] >= 40   # overflow list in use
+    assert flags[(1, 0)][1] == 0 and flags[(1, 0)][0] >= 30
+    kb, vbk, kk, vv = _c_oracle_cache(k, v, h, vb, w, ctx.pi)
+    want = orc.attention(q, kk, vv)
+    qq = torch.from_numpy(q)[None].cuda()
+    got = ctx.decode(0, qq)[0].cpu().numpy()
+    again = ctx.decode(0, qq)[0].cpu().numpy()
+    assert ctx.last_launches() == 2
+    assert np.array_equal(got, again)
+    ctx.set_kernel("general")
+    gen = ctx.decode(0, qq)[0].cpu().numpy()
+    ctx.set_kernel("auto")
+    assert np.allclose(got, want, rtol=RTOL, atol=ATOL), np.abs(got - want).max()
+    assert np.allclose(got, gen, rtol=RTOL, atol=ATOL), np.abs(got - gen).max()
+    assert ctx.status() == 0

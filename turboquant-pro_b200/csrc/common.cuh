@@ -22,10 +22,16 @@ constexpr int TQ_MAX_K_OUT = 32;   // most outliers per channel the key encoder 
 constexpr int TQ_MAX_G = 16;       // largest GQA group
 constexpr int TQ_PART_STRIDE = 2 + TQ_D;  // floats per partial state (m, l, acc[D])
 
-constexpr int TQ_INLINE_CAP = 672;  // outlier entries stored inside the page itself
-constexpr int TQ_SIDE_OFF = 640;    // within the header: wide-channel codes (uint16 x 256)
-constexpr int TQ_HDR_BYTES = 1152;  // page header: PageHeader, wide ids, row starts, side codes
+// Tail of a page, offsets from hdr_off: header | wide-channel codes | outliers by token
 constexpr int TQ_WIDE = 4;          // channels per page whose codes are kept a second time
+constexpr int TQ_SIDE_OFF = 64;     // uint16 x 256: the codes of the wide channels, per token
+constexpr int TQ_ELL_SLOTS = 4;     // outliers of a token kept in its fixed slots
+constexpr int TQ_ELL_OFF = TQ_SIDE_OFF + 512;            // fp16 delta [slots][256], then
+constexpr int TQ_ELL_COL_OFF = TQ_ELL_OFF + TQ_ELL_SLOTS * 512;  // uint8 channel [slots][256]
+constexpr int TQ_OVF_OFF = TQ_ELL_COL_OFF + TQ_ELL_SLOTS * 256;  // uint32 entries beyond the slots
+constexpr int TQ_OVF_CAP = 112;
+constexpr int TQ_TAIL_BYTES = TQ_OVF_OFF + TQ_OVF_CAP * 4;  // 4096
+constexpr int TQ_PAGE_SPILLED = 1;  // header flag: use the pool's list, not the in-page copy
 
 // bit 0 of the device status word: an outlier pool overflowed
 constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
@@ -40,13 +46,13 @@ constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
 //             +norm_off   value norms, float32 per token
 //             +scale_off  key scale per channel (max |x - mean|), float32
 //             +mean_off   key zero-point per channel, float32
-//             +hdr_off    PageHeader {outlier count, offset into the pool slab}, then
-//                         at +16 the start index of every token's outliers (uint16 x
-//                         (tokens + 1)): the side-list is grouped by token; at +8 the
-//                         ids of the TQ_WIDE channels with the largest scale, and at
-//                         +TQ_SIDE_OFF one uint16 per token holding their four codes
-//                         (nibble i = code of wide channel i)
-//             +ent_off    the first TQ_INLINE_CAP outlier entries (the rest only in the pool)
+//             +hdr_off    PageHeader (below), then at +TQ_SIDE_OFF one uint16 per token
+//                         holding the codes of the TQ_WIDE widest channels (nibble i = code
+//                         of wide channel i)
+//             +ent_off    the page's own copy of its outliers, by token: the first
+//                         TQ_ELL_SLOTS of every token as fp16 delta [slot][token] and uint8
+//                         channel [slot][token] (empty slots are zero), then up to
+//                         TQ_OVF_CAP further entries in pool format, ordered by token
 // hot_k/v   [L][B][H][hot_cap][D] of kv_dtype; token at position p lives in slot p % hot_cap
 // pool_dec  [L][B][H][pool_entries] uint32: fp16 delta | channel << 16 | token << 24
 // pool_val  same shape, uint16: the outlier's fp16 value (kept for export / dequant)
@@ -55,6 +61,17 @@ constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
 // tables    float pi[D*D], pi_t[D*D], centroids[16], boundaries[16], nf4[16]
 // scratch   decode partials
 // ---------------------------------------------------------------------------------------
+
+// First bytes of a page's tail.  The decode kernel reads the outliers from the page unless
+// TQ_PAGE_SPILLED is set (more overflow entries than fit, or the pool slab was full).
+struct PageHeader {
+  uint32_t off, cnt;       // the page's PageMeta
+  uint8_t wide[TQ_WIDE];   // channels with the largest scale, widest first
+  uint16_t ovf_n, flags;   // overflow entries stored in the page; TQ_PAGE_* bits
+  uint16_t ovf_start[5];   // first overflow entry of each 64-token strip, and the end
+  uint16_t pad_[19];
+};
+static_assert(sizeof(PageHeader) == TQ_SIDE_OFF, "page header size");
 
 struct PageMeta {
   uint32_t off;

@@ -81,8 +81,8 @@ int32_t tq_geom_finish(tq_geom* g) {
   g->scale_off = g->norm_off + g->block_tokens_pad * 4;
   g->mean_off = g->scale_off + TQ_D * 4;
   g->hdr_off = (int)align_up(g->mean_off + TQ_D * 4, 128);
-  g->ent_off = g->hdr_off + TQ_HDR_BYTES;
-  g->page_bytes = (int)align_up(g->ent_off + TQ_INLINE_CAP * 4, 128);
+  g->ent_off = g->hdr_off + TQ_ELL_OFF;
+  g->page_bytes = (int)align_up(g->hdr_off + TQ_TAIL_BYTES, 128);
   if (g->outlier_k > 0) {
     int64_t nominal = (int64_t)g->max_blocks * g->outlier_k * TQ_D;
     int64_t cap = nominal + nominal / 4 + 4096;

@@ -122,8 +122,8 @@ TQ_DEV uint32_t bf16x2_to_h2(uint32_t w) {
 // and bias of the page it works on and one outlier-correction strip per warp.
 template <int G, int VB, int NG>
 struct SmemT {
-  // a tile is a whole page (34560 B at V3, 38656 B at V4) or 32 KB of hot rows
-  static constexpr int DATA_BYTES = VB == 3 ? 34560 : 38656;
+  // a tile is a whole page (34816 B at V3, 38912 B at V4) or 32 KB of hot rows
+  static constexpr int DATA_BYTES = VB == 3 ? 34816 : 38912;
   static constexpr int LUTK_BYTES = 256 * 128;
   static constexpr int LUTV_BYTES = (VB == 3 ? 64 : 256) * 128;
   // the 3-bit value table starts on an 8 KB boundary (its addresses are formed with OR)
@@ -588,68 +588,51 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
       if (c == 0) bias_s[r * GW + gw] = bias;
     }
     if (cold) {
-      // outlier corrections of this warp's 64 tokens: the side-list is grouped by token; a
-      // lane owns two tokens (lane and lane + 32 of the strip) and walks their lists in step
-      const PageMeta pm = *(const PageMeta*)(st + g.hdr_off);
-      const uint16_t* rows = (const uint16_t*)(st + g.hdr_off + 16) + 64 * gw;
-      const uint32_t* ent_s = (const uint32_t*)(st + g.ent_off);
-      const uint32_t* ent_g =
-          a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
-      int e0[2], e1[2];
+      // Outlier corrections of this warp's 64 tokens (a lane owns tokens lane and lane + 32 of
+      // the strip).  The page keeps the first TQ_ELL_SLOTS outliers of every token in fixed
+      // slots, so the common case is a fixed number of independent, conflict-free rounds.
+      const PageHeader* hdr = (const PageHeader*)(st + g.hdr_off);
+      const bool spilled = (hdr->flags & TQ_PAGE_SPILLED) != 0;
       float cacc[2][G];
-      int kmax = 0;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        e0[i] = rows[32 * i + lane];
-        e1[i] = rows[32 * i + lane + 1];
-        kmax = max(kmax, e1[i] - e0[i]);
+      for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int gg = 0; gg < G; ++gg) cacc[i][gg] = 0.0f;
-      }
+      if (!spilled) {
+        const uint16_t* ell_d = (const uint16_t*)(st + g.hdr_off + TQ_ELL_OFF) + 64 * gw + lane;
+        const uint8_t* ell_c = st + g.hdr_off + TQ_ELL_COL_OFF + 64 * gw + lane;
 #pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
-      // branch-free in the common case (every entry inside the page): a lane past the end
-      // of its list reads entry 0 and adds zero, so the chains of a round and the rounds
-      // themselves overlap instead of serialising behind divergent branches
-      const bool spill = pm.cnt > (uint32_t)TQ_INLINE_CAP;
-#pragma unroll 2
-      for (int kk = 0; kk < kmax; ++kk) {
+        for (int j = 0; j < TQ_ELL_SLOTS; ++j) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int e = e0[i] + kk;
-          const bool live = e < e1[i];
-          const int es = live ? min(e, TQ_INLINE_CAP - 1) : 0;
-          uint32_t wv = ent_s[es];
-          if (spill && live && e >= TQ_INLINE_CAP) wv = ent_g[e];
-          const float delta =
-              live ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
-          const float* qrow = qc + ((wv >> 16) & 255) * G;
-          if (G >= 4) {
+          for (int i = 0; i < 2; ++i) {
+            const float delta = __half2float(__ushort_as_half(ell_d[j * 256 + 32 * i]));
+            const float* qrow = qc + (int)ell_c[j * 256 + 32 * i] * G;
+            if (G >= 4) {
 #pragma unroll
-            for (int g4 = 0; g4 < G / 4; ++g4) {
-              const float4 qv = *(const float4*)(qrow + 4 * g4);
-              cacc[i][4 * g4 + 0] += qv.x * delta;
-              cacc[i][4 * g4 + 1] += qv.y * delta;
-              cacc[i][4 * g4 + 2] += qv.z * delta;
-              cacc[i][4 * g4 + 3] += qv.w * delta;
+              for (int g4 = 0; g4 < G / 4; ++g4) {
+                const float4 qv = *(const float4*)(qrow + 4 * g4);
+                cacc[i][4 * g4 + 0] += qv.x * delta;
+                cacc[i][4 * g4 + 1] += qv.y * delta;
+                cacc[i][4 * g4 + 2] += qv.z * delta;
+                cacc[i][4 * g4 + 3] += qv.w * delta;
+              }
+            } else {
+#pragma unroll
+              for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
             }
-          } else {
-#pragma unroll
-            for (int gg = 0; gg < G; ++gg) cacc[i][gg] += qrow[gg] * delta;
           }
         }
       }
       // the widest channels of the page: their table rounding error, times a large
       // weight, would show in the scores, so it is added back here token by token
       {
-        const uchar4 wid = *(const uchar4*)(st + g.hdr_off + 8);
         const uint16_t* side = (const uint16_t*)(st + g.hdr_off + TQ_SIDE_OFF) + 64 * gw;
-        const int wch[TQ_WIDE] = {wid.x, wid.y, wid.z, wid.w};
         const uint32_t sd[2] = {side[lane], side[32 + lane]};
 #pragma unroll
         for (int j = 0; j < TQ_WIDE; ++j) {
-          const float sc = scale[wch[j]];
-          const float* qrow = qc + wch[j] * G;
+          const int wch = hdr->wide[j];
+          const float sc = scale[wch];
+          const float* qrow = qc + wch * G;
           float dl[2];
 #pragma unroll
           for (int i = 0; i < 2; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
@@ -665,6 +648,47 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + 32 * i + lane] = cacc[i][gg];
+      // Entries beyond the fixed slots (ordered by token), or, for a spilled page, the whole
+      // list from the pool: a lane per entry, equal tokens summed across lanes by a segmented
+      // reduction (fixed order, so the result does not depend on timing), and the first lane
+      // of each token adds the sum to the strip.
+      const int s0 = spilled ? 0 : (int)hdr->ovf_start[gw];
+      const int s1 = spilled ? (int)hdr->cnt : (int)hdr->ovf_start[gw + 1];
+      if (s1 > s0) {
+        const uint32_t* list =
+            spilled ? a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + hdr->off
+                    : (const uint32_t*)(st + g.hdr_off + TQ_OVF_OFF);
+        for (int eb = s0; eb < s1; eb += 32) {
+          __syncwarp();
+          const int e = eb + lane;
+          const bool valid = e < s1;
+          const uint32_t wv = valid ? list[e] : 0u;
+          const int tok = valid ? (int)(wv >> 24) : -1 - lane;
+          const bool mine = valid && (tok >> 6) == gw;
+          const float delta =
+              mine ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
+          const float* qrow = qc + ((wv >> 16) & 127) * G;
+          float pv[G];
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg) pv[gg] = qrow[gg] * delta;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int tk = __shfl_down_sync(0xffffffffu, tok, o);
+            const bool same = lane + o < 32 && tk == tok;
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) {
+              const float nv = __shfl_down_sync(0xffffffffu, pv[gg], o);
+              if (same) pv[gg] += nv;
+            }
+          }
+          const int prev = __shfl_up_sync(0xffffffffu, tok, 1);
+          if (mine && (lane == 0 || prev != tok)) {
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + (tok & 63)] += pv[gg];
+          }
+        }
+        __syncwarp();
+      }
     }
     group_sync();  // fragments and bias of all four warps are in place
     if (warp == 0) TQ_TRACE(4);

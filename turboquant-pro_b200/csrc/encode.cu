@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   __shared__ int s_alloc;
   __shared__ int s_tok_cnt[256];    // outliers per token, then the running fill position
   __shared__ int s_row[257];        // start of every token's outliers in the side-list
+  __shared__ int s_orow[257];       // start of every token's entries in the page's overflow list
   __shared__ int s_warp_sum[TQ_D / 32];
   if (d == 0) s_count = 0;
   s_tok_cnt[d] = 0;
@@ -153,7 +154,8 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     const float so = s_scale[o];
     rank += (so > amax || (so == amax && o < d)) ? 1 : 0;
   }
-  if (rank < 4) page[g.hdr_off + 8 + rank] = (uint8_t)d;
+  PageHeader* hdr = (PageHeader*)(page + g.hdr_off);
+  if (rank < TQ_WIDE) hdr->wide[rank] = (uint8_t)d;
   if (kk > 0) atomicAdd(&s_count, my_out);
   __syncthreads();
   if (d == 0) {
@@ -177,40 +179,61 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     pm.off = off;
     pm.cnt = (uint32_t)min(n, alloc);
     a.page_meta[unit_index(g, a.layer, seq, head) * g.max_blocks + blk] = pm;
-    *(PageMeta*)(page + g.hdr_off) = pm;  // the page carries its own copy for the decode kernel
+    hdr->off = pm.off;  // the page carries its own copy for the decode kernel
+    hdr->cnt = pm.cnt;
   }
-  {  // exclusive prefix sum of the per-token counts: thread d owns tokens 2d and 2d+1
+  uint16_t* ell_delta = (uint16_t*)(page + g.hdr_off + TQ_ELL_OFF);  // [slot][token]
+  uint8_t* ell_col = page + g.hdr_off + TQ_ELL_COL_OFF;               // [slot][token]
+  uint32_t* ovf = (uint32_t*)(page + g.hdr_off + TQ_OVF_OFF);
+  {  // exclusive prefix sums over tokens of the outlier counts and of the counts beyond the
+     // fixed slots (both in one word: each total stays below 65536); thread d owns tokens
+     // 2d and 2d+1
     const int c0 = s_tok_cnt[2 * d], c1 = s_tok_cnt[2 * d + 1];
-    int v = c0 + c1;
+    const int o0 = max(c0 - TQ_ELL_SLOTS, 0), o1 = max(c1 - TQ_ELL_SLOTS, 0);
+    const uint32_t mine = (uint32_t)(c0 + c1) | ((uint32_t)(o0 + o1) << 16);
+    uint32_t v = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      int nv = __shfl_up_sync(0xffffffffu, v, o);
+      uint32_t nv = __shfl_up_sync(0xffffffffu, v, o);
       if ((d & 31) >= o) v += nv;
     }
-    if ((d & 31) == 31) s_warp_sum[d >> 5] = v;
+    if ((d & 31) == 31) s_warp_sum[d >> 5] = (int)v;
     __syncthreads();
-    int base = 0;
-    for (int w = 0; w < (d >> 5); ++w) base += s_warp_sum[w];
-    const int excl = base + v - (c0 + c1);
-    s_row[2 * d] = excl;
-    s_row[2 * d + 1] = excl + c0;
-    if (d == TQ_D - 1) s_row[256] = base + v;
+    uint32_t base = 0;
+    for (int w = 0; w < (d >> 5); ++w) base += (uint32_t)s_warp_sum[w];
+    const uint32_t excl = base + v - mine;
+    s_row[2 * d] = (int)(excl & 0xffffu);
+    s_row[2 * d + 1] = (int)(excl & 0xffffu) + c0;
+    s_orow[2 * d] = (int)(excl >> 16);
+    s_orow[2 * d + 1] = (int)(excl >> 16) + o0;
+    if (d == TQ_D - 1) {
+      s_row[256] = (int)((base + v) & 0xffffu);
+      s_orow[256] = (int)((base + v) >> 16);
+    }
+    // slots the tokens do not use hold a zero delta on channel 0
+    for (int j = c0; j < TQ_ELL_SLOTS; ++j) {
+      ell_delta[j * 256 + 2 * d] = 0;
+      ell_col[j * 256 + 2 * d] = 0;
+    }
+    for (int j = c1; j < TQ_ELL_SLOTS; ++j) {
+      ell_delta[j * 256 + 2 * d + 1] = 0;
+      ell_col[j * 256 + 2 * d + 1] = 0;
+    }
   }
   __syncthreads();
-  {
-    uint16_t* rows = (uint16_t*)(page + g.hdr_off + 16);
-    // entries beyond the allocated slice do not exist: clamp the starts to the kept count
-    const int kept = min(s_count, s_alloc);
-    rows[2 * d] = (uint16_t)min(s_row[2 * d], kept);
-    rows[2 * d + 1] = (uint16_t)min(s_row[2 * d + 1], kept);
-    if (d == 0) rows[256] = (uint16_t)min(s_row[256], kept);
-    s_tok_cnt[2 * d] = s_row[2 * d];      // becomes the fill cursor of the token
-    s_tok_cnt[2 * d + 1] = s_row[2 * d + 1];
+  s_tok_cnt[2 * d] = s_row[2 * d];  // becomes the fill cursor of the token
+  s_tok_cnt[2 * d + 1] = s_row[2 * d + 1];
+  if (d < 5) hdr->ovf_start[d] = (uint16_t)min(s_orow[64 * d], TQ_OVF_CAP);
+  if (d == 5) {
+    // the in-page copy is complete unless the overflow list is too long or the pool slab
+    // could not take every entry (then the pool's shorter list is the cache's content)
+    const int n_ovf = s_orow[256];
+    hdr->ovf_n = (uint16_t)min(n_ovf, TQ_OVF_CAP);
+    hdr->flags = (n_ovf > TQ_OVF_CAP || s_alloc < s_count) ? TQ_PAGE_SPILLED : 0;
   }
   __syncthreads();
   const size_t slab = unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + s_off;
   const int alloc = s_alloc;
-  uint32_t* inline_ent = (uint32_t*)(page + g.ent_off);
 
   // pass 3: codes and outlier entries
   for (int t = 0; t < S; ++t) {
@@ -230,15 +253,22 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
     if (kk > 0 && fabsf(x) >= kth) {
       int slot = atomicAdd(&s_tok_cnt[t], 1);  // grouped by token, any order inside a token
+      __half hv = __float2half_rn(x);
+      float dense = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[best]));
+      __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
+      const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
+                           ((uint32_t)t << 24);
       if (slot < alloc) {
-        __half hv = __float2half_rn(x);
-        float dense = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[best]));
-        __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
-        const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
-                             ((uint32_t)t << 24);
         a.pool_dec[slab + slot] = ent;
         a.pool_val[slab + slot] = __half_as_ushort(hv);
-        if (slot < TQ_INLINE_CAP) inline_ent[slot] = ent;
+      }
+      const int j = slot - s_row[t];  // which of the token's outliers this is
+      if (j < TQ_ELL_SLOTS) {
+        ell_delta[j * 256 + t] = __half_as_ushort(delta);
+        ell_col[j * 256 + t] = (uint8_t)d;
+      } else {
+        const int oi = s_orow[t] + j - TQ_ELL_SLOTS;
+        if (oi < TQ_OVF_CAP) ovf[oi] = ent;
       }
     }
   }
