@@ -286,7 +286,6 @@ def run_native(args):
     for _ in range(max(args.warmup, 3)):
         step()
     launches_per_step = L * ctx.last_launches()
-    ctx.profile(True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
@@ -295,9 +294,17 @@ def run_native(args):
             step()
         e1.record()
         barrier()
+        # the same K steps once more with an event pair around every kernel launch (on the
+        # launching stream, inside the library): the per-kernel times of the roofline.  Kept
+        # out of the region above because the events stop the two kernels of a call from
+        # overlapping.
+        ctx.profile(True)
+        for _ in range(args.steps):
+            step()
+        barrier()
+        attn_ms, comb_ms, n_calls = ctx.profile_read()
+        ctx.profile(False)
     ms = e0.elapsed_time(e1)
-    attn_ms, comb_ms, n_calls = ctx.profile_read()
-    ctx.profile(False)
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

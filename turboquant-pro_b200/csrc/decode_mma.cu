@@ -316,7 +316,14 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
       ((uint32_t*)lutv_p)[i] = pack_h2(small[16 + ca], small[16 + cb]);
     }
   }
+  // Both kernels of a decode call are launched with programmatic stream serialization: this
+  // one may start while the kernel before it in the stream is still running.  Up to here it
+  // has read only the constant tables; everything else (lengths, query, pages, scratch) is
+  // touched after the wait, which returns once that kernel has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   build_plan(a, plan, tid, THREADS);  // contains the __syncthreads that publish all of the above
+  // the combine kernel that follows may be scheduled wherever an SM frees up
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int T = plan->P[a.n_units];
   const int Q = (T + a.n_cta - 1) / a.n_cta;
@@ -903,6 +910,14 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   __shared__ int s_cold[MAX_PARTS];
   __shared__ float s_M[G], s_L[G], s_scale[G];
   __shared__ int s_n, s_it[3];  // round size; enumeration cursor (cta, kind, group)
+  // This kernel is launched while the attention kernel may still be running (programmatic
+  // dependent launch): its column of the rotation matrix, which no kernel writes, is fetched
+  // first; everything the attention kernel produces is read after the wait.
+  float pcol[TQ_D];
+#pragma unroll
+  for (int d = 0; d < TQ_D; ++d) pcol[d] = a.tables->pi[d * TQ_D + e];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int Q = a.plan_g[1];
   const int p0 = a.plan_g[2 + unit], p1 = a.plan_g[3 + unit];
   const int pc = p0 + a.plan_g[3 + a.n_units + unit];
@@ -1006,11 +1021,10 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   float o[G];
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) o[gg] = 0.0f;
-#pragma unroll 64
-  for (int d = 0; d < TQ_D; ++d) {
-    const float pv = a.tables->pi[d * TQ_D + e];
 #pragma unroll
-    for (int gg = 0; gg < G; ++gg) o[gg] += cs[gg][d] * pv;
+  for (int d = 0; d < TQ_D; ++d) {
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg) o[gg] += cs[gg][d] * pcol[d];
   }
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) {
@@ -1045,9 +1059,24 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
   cudaEvent_t e0 = tq_prof_event(ctx, 0), e1 = tq_prof_event(ctx, 1), e2 = tq_prof_event(ctx, 2);
   if (e0) cudaEventRecord(e0, st);
   a.n_groups = CF::NG;
-  decode_mma_kernel<G, VB><<<a.n_cta, CF::THREADS, SM::TOTAL, st>>>(a);
+  // Either kernel may be scheduled before its predecessor in the stream has finished (where
+  // SMs are free) and waits for the predecessor's results itself (griddepcontrol.wait).
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3((unsigned)a.n_cta);
+  cfg.blockDim = dim3(CF::THREADS);
+  cfg.dynamicSmemBytes = SM::TOTAL;
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, decode_mma_kernel<G, VB>, a));
   if (e1) cudaEventRecord(e1, st);
-  combine_mma_kernel<G><<<a.n_units, TQ_D, 0, st>>>(a);
+  cfg.gridDim = dim3((unsigned)a.n_units);
+  cfg.blockDim = dim3(TQ_D);
+  cfg.dynamicSmemBytes = 0;
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, combine_mma_kernel<G>, a));
   if (e2) {
     cudaEventRecord(e2, st);
     tq_prof_commit(ctx);
