@@ -284,61 +284,79 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Rotation of 16 vectors held transposed in shared memory (us[d][t]) by the matrix column
-// this thread owns: acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every product and sum
-// rounded to float32 separately.
+// Rotation of 16 vectors held transposed in shared memory (us[d][t]) by column e of the
+// matrix in shared memory (pit[d][e]): acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every
+// product and sum rounded to float32 separately.  The loop is kept rolled (a fully unrolled
+// body does not fit the instruction cache) and each step issues its 16 independent products
+// before the 16 sums that depend on them.
 // ---------------------------------------------------------------------------------------
-TQ_DEV void rotate16(const float (*us)[TQ_GROUP_TOK], const float* P, float* acc) {
+TQ_DEV void rotate16(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, float* acc) {
+  {
+    const float p = pit[e];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float4 u = *(const float4*)&us[0][4 * q];
-    acc[4 * q + 0] = __fmul_rn(u.x, P[0]);
-    acc[4 * q + 1] = __fmul_rn(u.y, P[0]);
-    acc[4 * q + 2] = __fmul_rn(u.z, P[0]);
-    acc[4 * q + 3] = __fmul_rn(u.w, P[0]);
+    for (int q = 0; q < 4; ++q) {
+      float4 u = *(const float4*)&us[0][4 * q];
+      acc[4 * q + 0] = __fmul_rn(u.x, p);
+      acc[4 * q + 1] = __fmul_rn(u.y, p);
+      acc[4 * q + 2] = __fmul_rn(u.z, p);
+      acc[4 * q + 3] = __fmul_rn(u.w, p);
+    }
   }
-#pragma unroll
+#pragma unroll 4
   for (int dd = 1; dd < TQ_D; ++dd) {
+    const float p = pit[dd * TQ_D + e];
+    float m[TQ_GROUP_TOK];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float4 u = *(const float4*)&us[dd][4 * q];
-      acc[4 * q + 0] = __fadd_rn(acc[4 * q + 0], __fmul_rn(u.x, P[dd]));
-      acc[4 * q + 1] = __fadd_rn(acc[4 * q + 1], __fmul_rn(u.y, P[dd]));
-      acc[4 * q + 2] = __fadd_rn(acc[4 * q + 2], __fmul_rn(u.z, P[dd]));
-      acc[4 * q + 3] = __fadd_rn(acc[4 * q + 3], __fmul_rn(u.w, P[dd]));
+      m[4 * q + 0] = __fmul_rn(u.x, p);
+      m[4 * q + 1] = __fmul_rn(u.y, p);
+      m[4 * q + 2] = __fmul_rn(u.z, p);
+      m[4 * q + 3] = __fmul_rn(u.w, p);
     }
+#pragma unroll
+    for (int t = 0; t < TQ_GROUP_TOK; ++t) acc[t] = __fadd_rn(acc[t], m[t]);
   }
 }
 
 // ---------------------------------------------------------------------------------------
-// Value encoder.  Persistent CTAs of 128 threads; a work item is one 16-token group of a
-// new cold block.  Thread e owns output channel e and keeps column e of Pi^T in registers.
+// Value encoder.  Persistent CTAs of two 128-thread halves that share one copy of Pi^T in
+// shared memory; each half works on its own 16-token group of a new cold block, thread e of
+// the half owns output channel e.
 //   norm = sqrt(pairwise sum of fl(x*x))      (numpy's 8-accumulator order for n = 128)
 //   u    = x / max(norm, 1e-30)
 //   y_e  = sequential, unfused sum over d of u_d * PiT[d][e]
 //   code = #{ j : boundary_j < y_e }
 // ---------------------------------------------------------------------------------------
+constexpr int ENCV_HALVES = 2;
+struct EncvHalf {
+  float xs[TQ_GROUP_TOK][TQ_D];
+  float us[TQ_D][TQ_GROUP_TOK];
+  uint32_t img[256];
+  float norm[TQ_GROUP_TOK];
+};
+constexpr int ENCV_SMEM = TQ_D * TQ_D * 4 + ENCV_HALVES * (int)sizeof(EncvHalf) + 64;
+
 template <int DT>
-__global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
+__global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(EncodeArgs a) {
   const tq_geom& g = a.g;
-  const int e = threadIdx.x;
+  const int e = threadIdx.x & (TQ_D - 1), half = threadIdx.x >> 7;
   const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
   const int total = a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
   const int vb = g.value_bits;
   const int n_bnd = (1 << vb) - 1;
 
-  __shared__ __align__(16) float xs[TQ_GROUP_TOK][TQ_D];
-  __shared__ __align__(16) float us[TQ_D][TQ_GROUP_TOK];
-  __shared__ float s_norm[TQ_GROUP_TOK];
-  __shared__ float s_bnd[16];
-  __shared__ __align__(16) uint32_t img[256];
+  extern __shared__ __align__(16) uint8_t encv_smem[];
+  float* pit = (float*)encv_smem;                                   // [D][D]
+  EncvHalf* hs = (EncvHalf*)(encv_smem + TQ_D * TQ_D * 4) + half;
+  float* s_bnd = (float*)(encv_smem + TQ_D * TQ_D * 4 + ENCV_HALVES * sizeof(EncvHalf));
+  auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
 
-  float P[TQ_D];
-#pragma unroll
-  for (int dd = 0; dd < TQ_D; ++dd) P[dd] = a.tables->pi_t[dd * TQ_D + e];
-  if (e < 16) s_bnd[e] = a.tables->boundaries[e];
+  for (int i = threadIdx.x; i < TQ_D * TQ_D; i += ENCV_HALVES * TQ_D) pit[i] = a.tables->pi_t[i];
+  if (threadIdx.x < 16) s_bnd[threadIdx.x] = a.tables->boundaries[threadIdx.x];
+  __syncthreads();
 
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+  for (int w = blockIdx.x * ENCV_HALVES + half; w < total; w += gridDim.x * ENCV_HALVES) {
     int gq = w % groups;
     int r = w / groups;
     int jb = r % a.max_new_blocks;
@@ -349,27 +367,27 @@ __global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
     const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
     const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
     const int blk = nb0 + jb;
-    if (blk >= nb1) continue;  // uniform over the CTA
+    if (blk >= nb1) continue;  // uniform over the half
     const int S = g.block_tokens;
     const TokenSource<DT> src = make_source<DT>(a, a.hot_v, a.v, seq, head, n0);
     uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
 
-    __syncthreads();  // previous item fully consumed
+    half_sync();  // previous item fully consumed
 #pragma unroll 4
     for (int t = 0; t < TQ_GROUP_TOK; ++t) {
       int tt = gq * TQ_GROUP_TOK + t;
-      xs[t][e] = tt < S ? src.ld(blk * S + tt, e) : 0.0f;
+      hs->xs[t][e] = tt < S ? src.ld(blk * S + tt, e) : 0.0f;
     }
-    img[e] = 0u;
-    img[e + 128] = 0u;
-    __syncthreads();
+    hs->img[e] = 0u;
+    hs->img[e + 128] = 0u;
+    half_sync();
     {  // norms: 8 threads per token, accumulator j sums elements j, j+8, j+16, ...
       int t = e >> 3, j = e & 7;
-      float v0 = xs[t][j];
+      float v0 = hs->xs[t][j];
       float rr = __fmul_rn(v0, v0);
 #pragma unroll
       for (int i = 1; i < TQ_D / 8; ++i) {
-        float vv = xs[t][8 * i + j];
+        float vv = hs->xs[t][8 * i + j];
         rr = __fadd_rn(rr, __fmul_rn(vv, vv));
       }
       rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 1));  // (r0+r1), (r2+r3), ...
@@ -377,20 +395,21 @@ __global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
       rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 4));
       float nrm = __fsqrt_rn(rr);
       if (j == 0) {
-        s_norm[t] = nrm;
+        hs->norm[t] = nrm;
         ((float*)(page + g.norm_off))[gq * TQ_GROUP_TOK + t] = nrm;
       }
     }
-    __syncthreads();
+    half_sync();
     {  // unit vectors, stored transposed for the broadcast reads of the rotation
       int t = e >> 3, j = e & 7;
-      float safe = fmaxf(s_norm[t], 1e-30f);
+      float safe = fmaxf(hs->norm[t], 1e-30f);
 #pragma unroll
-      for (int i = 0; i < TQ_D / 8; ++i) us[8 * i + j][t] = __fdiv_rn(xs[t][8 * i + j], safe);
+      for (int i = 0; i < TQ_D / 8; ++i)
+        hs->us[8 * i + j][t] = __fdiv_rn(hs->xs[t][8 * i + j], safe);
     }
-    __syncthreads();
+    half_sync();
     float acc[TQ_GROUP_TOK];
-    rotate16(us, P, acc);
+    rotate16(hs->us, pit, e, acc);
     int code[TQ_GROUP_TOK];
 #pragma unroll
     for (int t = 0; t < TQ_GROUP_TOK; ++t) {
@@ -399,6 +418,7 @@ __global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
       code[t] = c;
     }
     // pack this channel's 8 token pairs into the group image
+    uint32_t* img = hs->img;
     const int dq = e & 7, i16 = e >> 3;  // record lane group and slot of channel e
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -418,7 +438,7 @@ __global__ void __launch_bounds__(TQ_D) encode_values_kernel(EncodeArgs a) {
         }
       }
     }
-    __syncthreads();
+    half_sync();
     uint32_t* dst = (uint32_t*)(page + g.v_off + (size_t)gq * v_group_bytes(vb));
     const int words = v_group_bytes(vb) / 4;
     for (int i = e; i < words; i += TQ_D) dst[i] = img[i];
@@ -463,15 +483,22 @@ __global__ void clear_kernel(int32_t* seq_len, uint32_t* cursor, int layer, int 
 }
 
 template <int DT>
-int launch_encode_t(const EncodeArgs& a, int sm_count, cudaStream_t st, int* launches) {
+int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t st, int* launches) {
   const tq_geom& g = a.g;
   if (a.max_new_blocks > 0) {
     dim3 grid(a.max_new_blocks, g.n_kv_heads, a.seq_count);
     encode_keys_kernel<DT><<<grid, TQ_D, 0, st>>>(a);
     int groups = g.block_tokens_pad / TQ_GROUP_TOK;
     long total = (long)a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
-    int ctas = (int)std::min<long>(total, (long)sm_count * 3);
-    encode_values_kernel<DT><<<ctas, TQ_D, 0, st>>>(a);
+    // one wave: two CTAs per SM, each working on two 16-token groups at a time
+    int ctas = (int)std::min<long>((total + ENCV_HALVES - 1) / ENCV_HALVES, (long)sm_count * 2);
+    static bool attr_set[16] = {};  // per device: the attribute belongs to the device's context
+    if (!attr_set[device & 15]) {
+      TQ_CUDA(cudaFuncSetAttribute(encode_values_kernel<DT>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, ENCV_SMEM));
+      attr_set[device & 15] = true;
+    }
+    encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(a);
     *launches += 2;
   }
   dim3 grid(std::min(a.n_tokens, g.hot_window), g.n_kv_heads, a.seq_count);
@@ -514,9 +541,9 @@ int tq_launch_encode(tq_ctx* ctx, int layer, int seq_begin, int seq_count, const
   cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
   int launches = 0;
   switch (ctx->g.kv_dtype) {
-    case TQ_F32: launch_encode_t<TQ_F32>(a, sm_count, st, &launches); break;
-    case TQ_F16: launch_encode_t<TQ_F16>(a, sm_count, st, &launches); break;
-    default: launch_encode_t<TQ_BF16>(a, sm_count, st, &launches); break;
+    case TQ_F32: launch_encode_t<TQ_F32>(a, sm_count, ctx->device, st, &launches); break;
+    case TQ_F16: launch_encode_t<TQ_F16>(a, sm_count, ctx->device, st, &launches); break;
+    default: launch_encode_t<TQ_BF16>(a, sm_count, ctx->device, st, &launches); break;
   }
   ctx->last_launches = launches;
   TQ_CUDA(cudaGetLastError());
