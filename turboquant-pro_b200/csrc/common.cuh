@@ -102,6 +102,11 @@ struct tq_ctx {
   std::vector<cudaEvent_t> prof_ev;
   float h_centroids[16];
   float h_boundaries[16];
+  // tensor maps (opaque 128-byte driver objects) of the two hot rings as 2-D arrays
+  // [ring rows][128] of 16-bit elements, for the decode kernel's swizzled tile copies;
+  // state 0: not built yet, 1: ready, -1: not available (float32 rings, or no driver entry)
+  alignas(64) unsigned char tmap_hot[2][128];
+  int tmap_state = 0;
 };
 
 TQ_HD size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }

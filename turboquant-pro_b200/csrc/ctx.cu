@@ -166,6 +166,13 @@ int32_t tq_ctx_create(const tq_geom* g, const tq_buffers* bufs, int32_t device, 
                                 1.0f};
   std::memcpy(t->nf4, nf4, sizeof(nf4));
   cudaError_t e = cudaMemcpyAsync(bufs->tables, t, sizeof(Tables), cudaMemcpyHostToDevice, st);
+  // The hot rings start zeroed: the decode kernel multiplies ring rows past the end of a
+  // window by probability 0, which needs them finite.
+  tq_sizes sz;
+  if (e == cudaSuccess && tq_ctx_sizes(g, &sz) == TQ_OK) {
+    e = cudaMemsetAsync(bufs->hot_k, 0, sz.hot_k, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(bufs->hot_v, 0, sz.hot_v, st);
+  }
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) {
     delete t;

@@ -28,6 +28,10 @@
 //
 // All waits are bounded: a wait that runs out sets bit 1 of the status word and an abort
 // flag that makes every later wait return at once, so the kernel always terminates.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 
 namespace {
@@ -56,6 +60,7 @@ struct MmaArgs {
   int32_t* status;
   unsigned long long* trace;  // optional: SM clock stamps of CTA 0's first 64 tiles
   int layer, q_dtype, n_units, n_cta;
+  int use_tmap;  // 16-bit hot tiles arrive through the tensor maps, 128-byte swizzled
   int n_groups;  // consumer groups of the attention kernel (the combine enumerates their slots)
   int block_begin, block_end, with_hot;
   float scale_log2;
@@ -107,6 +112,30 @@ TQ_DEV void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2-D tile of a tensor map into shared memory (no multicast); x counts elements of the inner
+// dimension (x * 2 bytes is a multiple of 16 at every call site), y rows
+TQ_DEV void tensor_g2s(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+// four 8x8 matrices of 16-bit elements, rows given by the lanes' addresses (lanes 8m..8m+7:
+// matrix m); thread (r, c) receives row r, columns 2c and 2c+1 of each, or with `trans`
+// rows 2c and 2c+1 of column r
+TQ_DEV void ldsm_x4(uint32_t* v, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "r"(addr)
+               : "memory");
+}
+TQ_DEV void ldsm_x4_trans(uint32_t* v, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "r"(addr)
+               : "memory");
+}
 TQ_DEV uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *(uint32_t*)&h;
@@ -138,8 +167,10 @@ struct SmemT {
   static constexpr int BIAS_OFF = FRAG_OFF + FRAG_BYTES;
   static constexpr int CORR_OFF = BIAS_OFF + BIAS_BYTES;
   static constexpr int GROUP_BYTES = CORR_OFF + GW * CORR_BYTES;
+  // the stages start on a 1 KB boundary (the swizzled hot tiles need it)
+  static constexpr int BARS_BYTES = 256 + (1024 - (NG * GROUP_BYTES + 256) % 1024) % 1024;
   static constexpr int FIXED =
-      ALIGN_SLACK + LUTK_BYTES + LUTV_BYTES + PLAN_BYTES + NG * GROUP_BYTES + 256;
+      ALIGN_SLACK + LUTK_BYTES + LUTV_BYTES + PLAN_BYTES + NG * GROUP_BYTES + BARS_BYTES;
   static constexpr int FIT = (232448 - FIXED) / DATA_BYTES;
   static constexpr int NSTAGE = FIT >= 4 ? 4 : FIT;
   static constexpr int TOTAL = FIXED + NSTAGE * DATA_BYTES;
@@ -262,7 +293,9 @@ TQ_DEV uint4 frag_hilo(float w0, float w1, float w2, float w3) {
 }
 
 template <int G, int VB>
-__global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaArgs a) {
+__global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
+    decode_mma_kernel(MmaArgs a, const __grid_constant__ CUtensorMap tm_hot_k,
+                      const __grid_constant__ CUtensorMap tm_hot_v) {
   using CF = Cfg<G, VB>;
   using SM = typename CF::SM;
   constexpr int NG = CF::NG, NSTAGE = SM::NSTAGE, CWT = CF::CWT, THREADS = CF::THREADS;
@@ -289,7 +322,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
   // stage; with one barrier per stage that wait would see the parity of the older phase.
   uint64_t* bars = (uint64_t*)(groups + NG * SM::GROUP_BYTES);
   volatile int* abort_flag = (volatile int*)(bars + 16);
-  uint8_t* stages = (uint8_t*)bars + 256;
+  uint8_t* stages = (uint8_t*)bars + SM::BARS_BYTES;
   static_assert(2 * NSTAGE <= 16, "barrier slots");
 
   const uint32_t full0 = smem_addr(bars);
@@ -359,6 +392,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
     const uint8_t* src;
     const uint8_t* src2;  // second source of a hot tile (the value rows), else null
     uint32_t bytes, dst, bar;
+    int row;  // hot tile: its first row in the ring seen as one 2-D array
   };
   const int total = hi - lo;
   auto describe = [&](int t, int& u_cursor) -> CopyDesc {
@@ -377,6 +411,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
       d.src = a.hot_k + off;
       d.src2 = a.hot_v + off;
       d.bytes = (uint32_t)(htt * TQ_D * esz);
+      d.row = (int)(unit_index(g, a.layer, seq, head) * (size_t)g.hot_cap) + slot;
     }
     return d;
   };
@@ -384,6 +419,14 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
     if (d.src2 == nullptr) {
       mbar_arrive_expect_tx(d.bar, d.bytes);
       bulk_g2s(d.dst, d.src, d.bytes, d.bar);
+    } else if (a.use_tmap) {
+      // 64 rows x 64 channels per copy, each landing as 8 KB of 128-byte rows whose 16-byte
+      // chunks are XOR-swizzled with the row number: [K left | K right | V left | V right]
+      mbar_arrive_expect_tx(d.bar, 2 * d.bytes);
+      tensor_g2s(d.dst, &tm_hot_k, 0, d.row, d.bar);
+      tensor_g2s(d.dst + 8192, &tm_hot_k, 64, d.row, d.bar);
+      tensor_g2s(d.dst + 16384, &tm_hot_v, 0, d.row, d.bar);
+      tensor_g2s(d.dst + 24576, &tm_hot_v, 64, d.row, d.bar);
     } else {
       mbar_arrive_expect_tx(d.bar, 2 * d.bytes);
       bulk_g2s(d.dst, d.src, d.bytes, d.bar);
@@ -459,7 +502,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
 #pragma unroll
             for (int y = 0; y < 2; ++y) {
               const int gg = 2 * c + y;
-              const int d = kind == 0 ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
+              const int d = (kind == 0 || a.use_tmap) ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
               if (gg < G) {
                 const float v = acc[mt][2 * x + y] * (y ? f1 : f0);
                 if (step == 0) mine[gg * MG_STRIDE + d] = v; else mine[gg * MG_STRIDE + d] += v;
@@ -574,13 +617,17 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
 #pragma unroll
       for (int i = 0; i < 8 / GW; ++i) {  // this warp's k-steps
         const int j = gw + GW * i;
-        const int d0 = 32 * c + 4 * j;
+        // channels of this lane's four fragment values: pages order them 32c + 4j + i (the
+        // order of their code bytes); swizzled hot tiles are read by 8x8 matrix loads and keep
+        // the tensor-core tile's own order 16j + {2c, 2c+1, 2c+8, 2c+9}
+        const int d0 = 32 * c + 4 * j, dn = 16 * j + 2 * c;
+        const bool natural = !cold && a.use_tmap;
         float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < G) {
-          q4.x = qc[(d0 + 0) * G + r];
-          q4.y = qc[(d0 + 1) * G + r];
-          q4.z = qc[(d0 + 2) * G + r];
-          q4.w = qc[(d0 + 3) * G + r];
+          q4.x = qc[(natural ? dn : d0 + 0) * G + r];
+          q4.y = qc[(natural ? dn + 1 : d0 + 1) * G + r];
+          q4.z = qc[(natural ? dn + 8 : d0 + 2) * G + r];
+          q4.w = qc[(natural ? dn + 9 : d0 + 3) * G + r];
         }
         float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
         if (cold) {
@@ -790,8 +837,63 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1) decode_mma_kernel(MmaA
           }
         }
       }
+    } else if (gw < htt / 16 && a.use_tmap) {
+      // ---- hot tile, swizzled 16-bit rows: 8x8 matrix loads straight into fragments --------
+      const int hot_len = plan->hot_len[tl.u];
+      const int T0 = 16 * gw;                   // first token of this warp inside the tile
+      const int base_tok = tl.idx * htt + T0;   // ... inside the hot window
+      // lanes 8m .. 8m+7 address the rows of matrix m: tokens T0 + 8 (m >> 1) + 0..7, 16-byte
+      // chunk (m & 1) of the current channel pair; chunk ch of row tr lives in the 8 KB half
+      // ch >> 3 at tr * 128 + ((ch & 7) ^ (tr & 7)) * 16
+      const int tr = T0 + 8 * (lane >> 4) + (lane & 7), m1 = (lane >> 3) & 1, sw = lane & 7;
+      const uint32_t ka = smem_addr(st) + tr * 128, va = ka + 16384;
+      const bool bf = g.kv_dtype == TQ_BF16;
+      float sv[2][2];
+      bool ok[2][2];
+      {
+        float C[2][2][4] = {};  // [token tile][k-step parity]: four accumulation chains
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t kb[4];  // key rows: {tile 0: k lo, k hi, tile 1: k lo, k hi}
+          ldsm_x4(kb, ka + (j >> 2) * 8192 + (((2 * (j & 3) + m1) ^ sw) << 4));
+          if (bf) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) kb[i] = bf16x2_to_h2(kb[i]);
+          }
+          mma16816(C[0][j & 1], areg[j], kb[0], kb[1]);
+          mma16816(C[1][j & 1], areg[j], kb[2], kb[3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          sv[nt][0] = ((C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2])) * a.scale_log2;
+          sv[nt][1] = ((C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3])) * a.scale_log2;
+          ok[nt][0] = base_tok + 8 * nt + 2 * c < hot_len;
+          ok[nt][1] = base_tok + 8 * nt + 2 * c + 1 < hot_len;
+          if (r >= G) {
+            sv[nt][0] = sv[nt][1] = 0.0f;
+            ok[nt][0] = ok[nt][1] = true;
+          }
+        }
+      }
+      softmax16(sv, ok);
+      // tokens past the end of the window have probability 0 (their rows hold finite values:
+      // the rings start zeroed and are only ever written with tokens)
+      const uint32_t pb0 = pack_h2(sv[0][0], sv[0][1]);
+      const uint32_t pb1 = pack_h2(sv[1][0], sv[1][1]);
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        // transposed loads: {tokens 0-7 | 8-15} x {channels 16mt + 0..7 | + 8..15} arrive as
+        // {rows r, rows r+8} x {k 0-7, k 8-15} of the A fragment, in matrix order
+        uint32_t af[4];
+        ldsm_x4_trans(af, va + (mt >> 2) * 8192 + (((2 * (mt & 3) + m1) ^ sw) << 4));
+        if (bf) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) af[i] = bf16x2_to_h2(af[i]);
+        }
+        mma16816(acc[mt], af, pb0, pb1);
+      }
     } else if (gw < htt / 16) {
-      // ---- hot tile: uncompressed rows, same tensor-core tiles, no tables ----------------
+      // ---- hot tile, plain rows (float32 rings, or no tensor maps): loads + conversion -----
       const int hot_len = plan->hot_len[tl.u];
       const int T0 = 16 * gw;                   // first token of this warp inside the tile
       const int base_tok = tl.idx * htt + T0;   // ... inside the hot window
@@ -1071,7 +1173,10 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
   cfg.gridDim = dim3((unsigned)a.n_cta);
   cfg.blockDim = dim3(CF::THREADS);
   cfg.dynamicSmemBytes = SM::TOTAL;
-  TQ_CUDA(cudaLaunchKernelEx(&cfg, decode_mma_kernel<G, VB>, a));
+  CUtensorMap tmk, tmv;
+  std::memcpy(&tmk, ctx->tmap_hot[0], sizeof(CUtensorMap));
+  std::memcpy(&tmv, ctx->tmap_hot[1], sizeof(CUtensorMap));
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, decode_mma_kernel<G, VB>, a, tmk, tmv));
   if (e1) cudaEventRecord(e1, st);
   cfg.gridDim = dim3((unsigned)a.n_units);
   cfg.blockDim = dim3(TQ_D);
@@ -1087,6 +1192,45 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
 }
 
 }  // namespace
+
+// Builds the tensor maps of the two hot rings (16-bit element types only).  The driver
+// function is looked up through the runtime, so the library does not link against libcuda.
+static void build_hot_tensor_maps(tq_ctx* ctx) {
+  static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+  ctx->tmap_state = -1;
+  const tq_geom& g = ctx->g;
+  if (g.kv_dtype == TQ_F32) return;
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) !=
+          cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+    cudaGetLastError();
+    return;
+  }
+  const cuuint64_t rows = (cuuint64_t)g.n_layers * g.n_seqs * g.n_kv_heads * g.hot_cap;
+  const cuuint64_t dims[2] = {(cuuint64_t)TQ_D, rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)TQ_D * 2};  // bytes between rows
+  const cuuint32_t box[2] = {64, 64};                     // 64 channels (128 B) x 64 tokens
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt =
+      g.kv_dtype == TQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  void* bases[2] = {ctx->b.hot_k, ctx->b.hot_v};
+  for (int i = 0; i < 2; ++i) {
+    CUtensorMap m;
+    if (((encode_fn)fn)(&m, dt, 2, bases[i], dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return;
+    std::memcpy(ctx->tmap_hot[i], &m, sizeof(m));
+  }
+  ctx->tmap_state = 1;
+}
 
 // Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
 size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
@@ -1129,6 +1273,8 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   a.block_end = block_end;
   a.with_hot = with_hot;
   a.scale_log2 = 1.4426950408889634f / sqrtf((float)TQ_D);
+  if (ctx->tmap_state == 0) build_hot_tensor_maps(ctx);
+  a.use_tmap = ctx->tmap_state == 1 ? 1 : 0;
   *handled = true;
 #define TQ_CASE(GG, VV) \
   if (G == GG && g.value_bits == VV) return launch_t<GG, VV>(a, st, ctx);
