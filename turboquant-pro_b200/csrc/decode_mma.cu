@@ -993,25 +993,24 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   }
 }
 
-constexpr int MAX_PARTS = 96;  // partials merged per round
-
-// Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the per-warp
-// partials of every CTA and consumer group that owned tiles of the unit, in the fixed order
-// (CTA, cold before hot, group) and in rounds of MAX_PARTS with a running maximum, un-rotates the cold part
-// once (acc @ Pi) and writes the output or the (m, l, o) state.  Partial maxima are in the
-// log2 domain.
+// Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the partials of
+// every CTA and consumer group that owned tiles of the unit, in the fixed order (CTA, cold
+// before hot, group) and in rounds with a running maximum, un-rotates the cold part once
+// (acc @ Pi) and writes the output or the (m, l, o) state.  Partial maxima are in the log2
+// domain.  Built for short dependency chains: the candidate slots are tested in parallel and
+// compacted in order, and a round's maxima, sums and accumulator rows are loaded together.
 template <int G>
 __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
+  constexpr int RP = G >= 8 ? 8 : (G >= 4 ? 16 : 32);  // partials per round
   const tq_geom& g = a.g;
-  const int unit = blockIdx.x, e = threadIdx.x;
+  const int unit = blockIdx.x, e = threadIdx.x, lane = e & 31, wid = e >> 5;
   const int seq = unit / g.n_kv_heads, head = unit % g.n_kv_heads;
   __shared__ float cs[G][TQ_D];
-  __shared__ const float* s_ptr[MAX_PARTS];
-  __shared__ float s_w[MAX_PARTS][G];  // m, then the weight 2^(m - M) (0 for empty partials)
-  __shared__ float s_l[MAX_PARTS][G];
-  __shared__ int s_cold[MAX_PARTS];
+  __shared__ const float* s_ptr[TQ_D];  // partials of the current chunk of candidates
+  __shared__ unsigned char s_cold[TQ_D];
+  __shared__ int s_wcount[TQ_D / 32];
+  __shared__ float s_m[RP][G], s_l[RP][G], s_wgt[RP][G];
   __shared__ float s_M[G], s_L[G], s_scale[G];
-  __shared__ int s_n, s_it[3];  // round size; enumeration cursor (cta, kind, group)
   // This kernel is launched while the attention kernel may still be running (programmatic
   // dependent launch): its column of the rotation matrix, which no kernel writes, is fetched
   // first; everything the attention kernel produces is read after the wait.
@@ -1029,93 +1028,100 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
     s_M[e] = NEG_BIG;
     s_L[e] = 0.0f;
   }
-  if (e == 0) {
-    s_it[0] = i0;
-    s_it[1] = 0;
-    s_it[2] = 0;
-  }
   float C[G], Hh[G];
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) C[gg] = Hh[gg] = 0.0f;
-  __syncthreads();
-  while (true) {
-    // 1. next round of partials, in the fixed merge order
-    if (e == 0) {
-      int n = 0, i = s_it[0], kind = s_it[1], w = s_it[2];
-      while (i <= i1 && n < MAX_PARTS) {
-        // tiles of this kind that CTA i holds for the unit: positions [ra, rb); the tile at
-        // position p belongs to consumer group (p - lo) % NG
-        const int lo = i * Q, hi = lo + Q;
-        const int ra = kind == 0 ? max(lo, p0) : max(lo, pc);
-        const int rb = kind == 0 ? min(hi, pc) : min(hi, p1);
-        if (ra < rb && w < NG) {
-          const int cnt = rb - ra, first = (ra - lo) % NG;
-          const bool owns = cnt >= NG || (w - first + NG) % NG < cnt;
-          if (owns) {
-            s_ptr[n] = a.partials + ((((size_t)unit + i) * 2 + kind) * NG + w) *
-                                        (size_t)(G * TQ_PART_STRIDE);
-            s_cold[n] = kind == 0;
-            ++n;
-          }
-          ++w;
-        } else {
-          w = 0;
-          if (++kind == 2) {
-            kind = 0;
-            ++i;
+  // candidate t = ((cta - i0) * 2 + kind) * NG + group, tested 128 at a time
+  const int n_cand = (i1 - i0 + 1) * 2 * NG;
+  for (int base = 0; base < n_cand; base += TQ_D) {
+    const int t = base + e;
+    bool valid = false;
+    const float* ptr = nullptr;
+    int kind = 0;
+    if (t < n_cand) {
+      const int w = t % NG, ck = t / NG;
+      kind = ck & 1;
+      const int i = i0 + (ck >> 1);
+      // tiles of this kind that CTA i holds for the unit: positions [ra, rb); the tile at
+      // position p belongs to consumer group (p - lo) % NG
+      const int lo = i * Q, hi = lo + Q;
+      const int ra = kind == 0 ? max(lo, p0) : max(lo, pc);
+      const int rb = kind == 0 ? min(hi, pc) : min(hi, p1);
+      const int cnt = rb - ra;
+      if (cnt > 0) {
+        const int first = (ra - lo) % NG;
+        valid = cnt >= NG || (w - first + NG) % NG < cnt;
+      }
+      ptr = a.partials +
+            ((((size_t)unit + i) * 2 + kind) * NG + w) * (size_t)(G * TQ_PART_STRIDE);
+    }
+    __syncthreads();  // the previous chunk's list is no longer in use
+    const unsigned ball = __ballot_sync(0xffffffffu, valid);
+    if (lane == 0) s_wcount[wid] = __popc(ball);
+    __syncthreads();
+    int off = __popc(ball & ((1u << lane) - 1u)), n_chunk = 0;
+    for (int w2 = 0; w2 < TQ_D / 32; ++w2) {
+      if (w2 < wid) off += s_wcount[w2];
+      n_chunk += s_wcount[w2];
+    }
+    if (valid) {
+      s_ptr[off] = ptr;
+      s_cold[off] = (unsigned char)(kind == 0);
+    }
+    __syncthreads();
+    for (int r0 = 0; r0 < n_chunk; r0 += RP) {
+      const int nr = min(RP, n_chunk - r0);
+      // this round's accumulator rows (all loads independent; rows past the end repeat the
+      // last one and are ignored), maxima and sums
+      float av[RP][G];
+#pragma unroll
+      for (int j = 0; j < RP; ++j) {
+        const float* pp = s_ptr[r0 + min(j, nr - 1)] + 2 + e;
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg) av[j][gg] = pp[gg * TQ_PART_STRIDE];
+      }
+      if (e < nr * G) {
+        const int j = e / G, gg = e % G;
+        const float* pp = s_ptr[r0 + j] + gg * TQ_PART_STRIDE;
+        s_m[j][gg] = pp[0];
+        s_l[j][gg] = pp[1];
+      }
+      __syncthreads();
+      if (e < G) {
+        float M = s_M[e];
+        for (int j = 0; j < nr; ++j)
+          if (s_l[j][e] > 0.0f) M = fmaxf(M, s_m[j][e]);
+        const float sc = exp2f(s_M[e] - M);
+        float L = s_L[e] * sc;
+        for (int j = 0; j < nr; ++j) {
+          const float wgt = s_l[j][e] > 0.0f ? exp2f(s_m[j][e] - M) : 0.0f;
+          L += s_l[j][e] * wgt;
+          s_wgt[j][e] = wgt;
+        }
+        s_scale[e] = sc;
+        s_M[e] = M;
+        s_L[e] = L;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int gg = 0; gg < G; ++gg) {
+        C[gg] *= s_scale[gg];
+        Hh[gg] *= s_scale[gg];
+      }
+#pragma unroll
+      for (int j = 0; j < RP; ++j) {
+        if (j < nr) {
+          const bool cold = s_cold[r0 + j] != 0;
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg) {
+            const float wgt = s_wgt[j][gg];
+            const float v = wgt > 0.0f ? av[j][gg] * wgt : 0.0f;
+            if (cold) C[gg] += v; else Hh[gg] += v;
           }
         }
       }
-      s_it[0] = i;
-      s_it[1] = kind;
-      s_it[2] = w;
-      s_n = n;
+      __syncthreads();  // s_m / s_l / s_wgt are rewritten by the next round
     }
-    __syncthreads();
-    const int n = s_n;
-    if (n == 0) break;
-    // 2. their (m, l), loaded in parallel
-    for (int i = e; i < n * G; i += TQ_D) {
-      const int j = i / G, gg = i % G;
-      const float* pp = s_ptr[j] + gg * TQ_PART_STRIDE;
-      s_w[j][gg] = pp[0];
-      s_l[j][gg] = pp[1];
-    }
-    __syncthreads();
-    if (e < G) {
-      float M = s_M[e];
-      for (int j = 0; j < n; ++j)
-        if (s_l[j][e] > 0.0f) M = fmaxf(M, s_w[j][e]);
-      const float sc = exp2f(s_M[e] - M);
-      float L = s_L[e] * sc;
-      for (int j = 0; j < n; ++j) {
-        const float wgt = s_l[j][e] > 0.0f ? exp2f(s_w[j][e] - M) : 0.0f;
-        L += s_l[j][e] * wgt;
-        s_w[j][e] = wgt;
-      }
-      s_scale[e] = sc;
-      s_M[e] = M;
-      s_L[e] = L;
-    }
-    __syncthreads();
-    // 3. weighted sums of the accumulators: independent loads
-#pragma unroll
-    for (int gg = 0; gg < G; ++gg) {
-      C[gg] *= s_scale[gg];
-      Hh[gg] *= s_scale[gg];
-    }
-#pragma unroll 8
-    for (int j = 0; j < n; ++j) {
-      const float* pp = s_ptr[j] + 2 + e;
-      const bool cold = s_cold[j] != 0;
-#pragma unroll
-      for (int gg = 0; gg < G; ++gg) {
-        const float wgt = s_w[j][gg];
-        const float v = wgt > 0.0f ? pp[gg * TQ_PART_STRIDE] * wgt : 0.0f;
-        if (cold) C[gg] += v; else Hh[gg] += v;
-      }
-    }
-    __syncthreads();
   }
 #pragma unroll
   for (int gg = 0; gg < G; ++gg) cs[gg][e] = C[gg];
