@@ -89,7 +89,7 @@ class ClockSampler:
                     self.samples.append([x.strip() for x in out.stdout.strip().split(",")])
             except Exception:  # noqa: BLE001 - sampling must never break the benchmark
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.02)
 
     def __enter__(self):
         self._t = threading.Thread(target=self._run, daemon=True)
