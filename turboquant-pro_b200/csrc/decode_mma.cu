@@ -136,6 +136,12 @@ TQ_DEV void ldsm_x4_trans(uint32_t* v, uint32_t addr) {
                : "r"(addr)
                : "memory");
 }
+// 2^x in one instruction (denormal results flush to zero; arguments here are <= 0 or tiny)
+TQ_DEV float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 TQ_DEV uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *(uint32_t*)&h;
@@ -542,13 +548,13 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m_run, mx);
-    const float cf = exp2f(m_run - m_new);
+    const float cf = ex2(m_run - m_new);
     float sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        sv[i][j] = ok[i][j] ? exp2f(sv[i][j] - m_new) : 0.0f;
+        sv[i][j] = ok[i][j] ? ex2(sv[i][j] - m_new) : 0.0f;
         sum += sv[i][j];
       }
     l_run = l_run * cf + sum;
@@ -597,9 +603,12 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       for (int i = gtid; i < TQ_D * G; i += GW * 32) {
         const int d = i / G, rr = i % G;
         const size_t qi = ((size_t)seq * g.n_q_heads + head * G + rr) * TQ_D + d;
-        qc[i] = a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
-                : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
-                                      : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]);
+        // the softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
+        // bias and corrections come out already scaled
+        qc[i] = a.scale_log2 *
+                (a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
+                 : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
+                                       : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]));
       }
       group_sync();
     }
@@ -690,12 +699,21 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           float dl[2];
 #pragma unroll
           for (int i = 0; i < 2; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
+          float qv[G];
+          if (G >= 4) {
 #pragma unroll
-          for (int gg = 0; gg < G; ++gg) {
-            const float qv = qrow[gg];
+            for (int g4 = 0; g4 < G / 4; ++g4) {
+              const float4 q4 = *(const float4*)(qrow + 4 * g4);
+              qv[4 * g4] = q4.x; qv[4 * g4 + 1] = q4.y; qv[4 * g4 + 2] = q4.z; qv[4 * g4 + 3] = q4.w;
+            }
+          } else {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) cacc[i][gg] += qv * dl[i];
+            for (int gg = 0; gg < G; ++gg) qv[gg] = qrow[gg];
           }
+#pragma unroll
+          for (int gg = 0; gg < G; ++gg)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) cacc[i][gg] += qv[gg] * dl[i];
         }
       }
 #pragma unroll
@@ -789,9 +807,9 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           const float2 cr = *(const float2*)(corr + 16 * half + 8 * nt + 2 * c);
           const float s0 = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
           const float s1 = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
-          sv[nt][0] = (s0 + bias + cr.x) * a.scale_log2;
-          sv[nt][1] = (s1 + bias + cr.y) * a.scale_log2;
-          if (r >= G) sv[nt][0] = sv[nt][1] = 0.0f;
+          // rows >= G carry zero weights: their scores are small finite numbers nobody reads
+          sv[nt][0] = s0 + (bias + cr.x);
+          sv[nt][1] = s1 + (bias + cr.y);
         }
         softmax16(sv, ok);
         const float2 n0 = *(const float2*)(norms + T0 + 2 * c);
@@ -865,8 +883,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          sv[nt][0] = ((C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2])) * a.scale_log2;
-          sv[nt][1] = ((C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3])) * a.scale_log2;
+          sv[nt][0] = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
+          sv[nt][1] = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
           ok[nt][0] = base_tok + 8 * nt + 2 * c < hot_len;
           ok[nt][1] = base_tok + 8 * nt + 2 * c + 1 < hot_len;
           if (r >= G) {
@@ -926,8 +944,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         float C[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 8; ++j) mma16816(C, areg[j], kw[2 * j], kw[2 * j + 1]);
-        sv[nt][0] = (C[0] + C[2]) * a.scale_log2;
-        sv[nt][1] = (C[1] + C[3]) * a.scale_log2;
+        sv[nt][0] = C[0] + C[2];
+        sv[nt][1] = C[1] + C[3];
         ok[nt][0] = base_tok + 8 * nt + 2 * c < hot_len;
         ok[nt][1] = base_tok + 8 * nt + 2 * c + 1 < hot_len;
         if (r >= G) {
