@@ -73,6 +73,11 @@ struct PageHeader {
 };
 static_assert(sizeof(PageHeader) == TQ_SIDE_OFF, "page header size");
 
+// Row of channel d in the decode kernel's [channel][query row] copy of the query.  The
+// fragment build reads channels 32c + 4j + i for c = 0..3 at once; the XOR spreads those
+// four rows over different banks.  The in-page outlier slots store channels in this form.
+TQ_HD int q_row(int d) { return d ^ ((d >> 5) << 1); }
+
 struct PageMeta {
   uint32_t off;
   uint32_t cnt;

@@ -605,7 +605,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         const size_t qi = ((size_t)seq * g.n_q_heads + head * G + rr) * TQ_D + d;
         // the softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
         // bias and corrections come out already scaled
-        qc[i] = a.scale_log2 *
+        qc[q_row(d) * G + rr] = a.scale_log2 *
                 (a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
                  : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
                                        : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]));
@@ -633,10 +633,10 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         const bool natural = !cold && a.use_tmap;
         float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < G) {
-          q4.x = qc[(natural ? dn : d0 + 0) * G + r];
-          q4.y = qc[(natural ? dn + 1 : d0 + 1) * G + r];
-          q4.z = qc[(natural ? dn + 8 : d0 + 2) * G + r];
-          q4.w = qc[(natural ? dn + 9 : d0 + 3) * G + r];
+          q4.x = qc[q_row(natural ? dn : d0 + 0) * G + r];
+          q4.y = qc[q_row(natural ? dn + 1 : d0 + 1) * G + r];
+          q4.z = qc[q_row(natural ? dn + 8 : d0 + 2) * G + r];
+          q4.w = qc[q_row(natural ? dn + 9 : d0 + 3) * G + r];
         }
         float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
         if (cold) {
@@ -695,7 +695,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         for (int j = 0; j < TQ_WIDE; ++j) {
           const int wch = hdr->wide[j];
           const float sc = scale[wch];
-          const float* qrow = qc + wch * G;
+          const float* qrow = qc + q_row(wch) * G;
           float dl[2];
 #pragma unroll
           for (int i = 0; i < 2; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
@@ -739,7 +739,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           const bool mine = valid && (tok >> 6) == gw;
           const float delta =
               mine ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
-          const float* qrow = qc + ((wv >> 16) & 127) * G;
+          const float* qrow = qc + q_row((wv >> 16) & 127) * G;
           float pv[G];
 #pragma unroll
           for (int gg = 0; gg < G; ++gg) pv[gg] = qrow[gg] * delta;

@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
       const int j = slot - s_row[t];  // which of the token's outliers this is
       if (j < TQ_ELL_SLOTS) {
         ell_delta[j * 256 + t] = __half_as_ushort(delta);
-        ell_col[j * 256 + t] = (uint8_t)d;
+        ell_col[j * 256 + t] = (uint8_t)q_row(d);
       } else {
         const int oi = s_orow[t] + j - TQ_ELL_SLOTS;
         if (oi < TQ_OVF_CAP) ovf[oi] = ent;
