@@ -778,18 +778,21 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       const float* corr = corr_w + rg * SM::CORR_STRIDE;
       const float* norms = (const float*)(st + g.norm_off);
       const uint8_t* vcodes = st + g.v_off;
-#pragma unroll 1
-      for (int half = 0; half < 4; ++half) {
+      // Score tiles of 16 tokens (two 8-token tiles x even/odd k-steps: four independent
+      // accumulation chains), and the value tiles of 16 tokens.  The loop below is unrolled
+      // with the score phase of strip h+1 placed before the value phase of strip h: the two
+      // are independent, so the scheduler can fill the lookup and tensor-core latencies of
+      // one with the other.
+      float C[2][2][4];
+      auto score_phase = [&](int half) {
         const int T0 = 64 * gw + 16 * half;
-        float sv[2][2];
-        const bool ok[2][2] = {{true, true}, {true, true}};
-        // four independent accumulation chains: two 8-token tiles x even/odd k-steps
-        float C[2][2][4] = {};
         uint32_t kw[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           const uint4 kc = *(const uint4*)(st + (T0 + 8 * nt + r) * 64 + c * 16);
           kw[nt][0] = kc.x; kw[nt][1] = kc.y; kw[nt][2] = kc.z; kw[nt][3] = kc.w;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) C[nt][x][0] = C[nt][x][1] = C[nt][x][2] = C[nt][x][3] = 0.0f;
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -802,20 +805,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
             mma16816(C[nt][j & 1], areg[j], b0, b1);
           }
         }
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const float2 cr = *(const float2*)(corr + 16 * half + 8 * nt + 2 * c);
-          const float s0 = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
-          const float s1 = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
-          // rows >= G carry zero weights: their scores are small finite numbers nobody reads
-          sv[nt][0] = s0 + (bias + cr.x);
-          sv[nt][1] = s1 + (bias + cr.y);
-        }
-        softmax16(sv, ok);
-        const float2 n0 = *(const float2*)(norms + T0 + 2 * c);
-        const float2 n1 = *(const float2*)(norms + T0 + 8 + 2 * c);
-        const uint32_t pb0 = pack_h2(sv[0][0] * n0.x, sv[0][1] * n0.y);
-        const uint32_t pb1 = pack_h2(sv[1][0] * n1.x, sv[1][1] * n1.y);
+      };
+      auto value_phase = [&](int half, uint32_t pb0, uint32_t pb1) {
         const int gq = 4 * gw + half;
         if (VB == 4) {
           const uint8_t* gb = vcodes + gq * 1024 + lane * 16;
@@ -854,6 +845,29 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
             mma16816(acc[mt], af, pb0, pb1);
           }
         }
+      };
+      score_phase(0);
+#pragma unroll
+      for (int half = 0; half < 4; ++half) {
+        const int T0 = 64 * gw + 16 * half;
+        float sv[2][2];
+        const bool ok[2][2] = {{true, true}, {true, true}};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float2 cr = *(const float2*)(corr + 16 * half + 8 * nt + 2 * c);
+          const float s0 = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
+          const float s1 = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
+          // rows >= G carry zero weights: their scores are small finite numbers nobody reads
+          sv[nt][0] = s0 + (bias + cr.x);
+          sv[nt][1] = s1 + (bias + cr.y);
+        }
+        softmax16(sv, ok);
+        const float2 n0 = *(const float2*)(norms + T0 + 2 * c);
+        const float2 n1 = *(const float2*)(norms + T0 + 8 + 2 * c);
+        const uint32_t pb0 = pack_h2(sv[0][0] * n0.x, sv[0][1] * n0.y);
+        const uint32_t pb1 = pack_h2(sv[1][0] * n1.x, sv[1][1] * n1.y);
+        if (half < 3) score_phase(half + 1);
+        value_phase(half, pb0, pb1);
       }
     } else if (gw < htt / 16 && a.use_tmap) {
       // ---- hot tile, swizzled 16-bit rows: 8x8 matrix loads straight into fragments --------
