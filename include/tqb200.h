@@ -50,6 +50,14 @@ enum {
 /* element type of incoming K/V tokens, of the hot window that stores them, and of q */
 enum { TQ_F32 = 0, TQ_F16 = 1, TQ_BF16 = 2 };
 
+/* Per-channel 4-bit key grids (per_channel_kv.py:285-401): dense value = mean + scale *
+ * grid[code].  The three that kv_fused_pck.py:54-94 gives an affine form for:
+ *   TQ_KEYS_NF4_ASYM  mean over the block's tokens, scale = max|x - mean|, NF4 grid (0 keeps
+ *                     the value of the field that used to be reserved)
+ *   TQ_KEYS_NF4       mean = 0, scale = max|x|, NF4 grid
+ *   TQ_KEYS_UNIFORM   mean = min, scale = (max - min) / 15, grid = 0..15, round-half-even */
+enum { TQ_KEYS_NF4_ASYM = 0, TQ_KEYS_NF4 = 1, TQ_KEYS_UNIFORM = 2 };
+
 /* Geometry of a context.  Fill the first block, then call tq_geom_finish(), which
  * validates it and derives the rest. */
 typedef struct tq_geom {
@@ -59,12 +67,12 @@ typedef struct tq_geom {
   int32_t n_kv_heads;
   int32_t n_q_heads;          /* multiple of n_kv_heads; q head i reads KV head i / G  */
   int32_t head_dim;           /* 128                                                   */
-  int32_t key_bits;           /* 4 (asymmetric NF4)                                    */
+  int32_t key_bits;           /* 4                                                     */
   int32_t value_bits;         /* 3 or 4                                                */
   int32_t hot_window;         /* tokens kept uncompressed, 2..512                      */
   int32_t kv_dtype;           /* TQ_F32 / TQ_F16 / TQ_BF16: tokens in, hot window      */
   int32_t max_tokens_per_seq;
-  int32_t reserved0_;
+  int32_t key_mode;           /* TQ_KEYS_*                                             */
   double outlier_frac;        /* per-channel fp16 outlier fraction, 0 disables         */
   /* --- derived by tq_geom_finish ------------------------------------------------ */
   int32_t group;              /* G = n_q_heads / n_kv_heads                            */

@@ -187,21 +187,52 @@ def key_outliers(x: np.ndarray, frac: float):
     return idx, val
 
 
-def encode_keys(x: np.ndarray, outlier_frac: float = 0.0):
-    """Asymmetric-NF4 key block encoder (per_channel_kv.py:324-353, 377-401).
+KEY_MODES = ("nf4_asym", "nf4", "uniform")  # the per-channel key grids with a fused form
+
+
+def key_grid(mode: str) -> np.ndarray:
+    """The 16-level grid of a key mode: dequant = mean + scale * grid[code]
+    (kv_fused_pck.py:54-94)."""
+    return np.arange(16, dtype=F32) if mode == "uniform" else NF4
+
+
+def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym"):
+    """Per-channel 4-bit key block encoder (per_channel_kv.py:285-401).
 
     ``x`` (H, S, D) any float dtype.  Returns a dict with unpacked ``codes`` (H,S,D)
-    uint8, ``scale`` (H,D) = max|x-mean| (floored at 1e-8), ``mean`` (H,D), and the
-    outlier side-list (``out_idx``, ``out_val``) or ``None``s.
+    uint8, per-channel ``scale`` and ``mean`` (H,D) such that the dense value is
+    ``mean + scale * grid[code]``, and the outlier side-list (``out_idx``, ``out_val``) or
+    ``None``s.  Modes:
+
+    * ``"nf4_asym"`` (:324-353, :377-401): mean over tokens, scale = max|x-mean| floored at
+      1e-8, level = fl(mean + fl(scale*NF4[l])), nearest level, first minimum wins;
+    * ``"nf4"`` (:354-357): mean = 0, scale = max|x| floored, level = fl(scale*NF4[l]);
+    * ``"uniform"`` (:303-318): mean = min, scale = fl(max(max-min, 1e-8) / 15),
+      code = clip(round_half_even(fl(fl(x-min)/scale)), 0, 15).
     """
+    if mode not in KEY_MODES:
+        raise ValueError(f"unknown key mode {mode!r}")
     x = np.asarray(x, dtype=F32)
     h, s, d = x.shape
     out_idx, out_val = key_outliers(x, outlier_frac)
-    mean = (_seq_sum_axis(x, 1) / F32(s)).astype(F32)
-    xc = (x - mean[:, None, :]).astype(F32)
-    amax = np.maximum(np.abs(xc).max(axis=1), F32(1e-8)).astype(F32)
-    # level l of channel (h, d): fl(mean + fl(amax * NF4[l]))
-    levels = (mean[..., None] + (amax[..., None] * NF4).astype(F32)).astype(F32)  # (H,D,16)
+    if mode == "uniform":
+        mn = x.min(axis=1)
+        mx = x.max(axis=1)
+        scale = (np.maximum((mx - mn).astype(F32), F32(1e-8)) / F32(15)).astype(F32)
+        q = ((x - mn[:, None, :]).astype(F32) / scale[:, None, :]).astype(F32)
+        codes = np.clip(np.round(q), 0, 15).astype(np.uint8)
+        return {"codes": codes, "scale": scale, "mean": mn.astype(F32), "out_idx": out_idx,
+                "out_val": out_val, "mode": mode}
+    if mode == "nf4_asym":
+        mean = (_seq_sum_axis(x, 1) / F32(s)).astype(F32)
+        xc = (x - mean[:, None, :]).astype(F32)
+        amax = np.maximum(np.abs(xc).max(axis=1), F32(1e-8)).astype(F32)
+        # level l of channel (h, d): fl(mean + fl(amax * NF4[l]))
+        levels = (mean[..., None] + (amax[..., None] * NF4).astype(F32)).astype(F32)  # (H,D,16)
+    else:
+        mean = np.zeros((h, d), dtype=F32)
+        amax = np.maximum(np.abs(x).max(axis=1), F32(1e-8)).astype(F32)
+        levels = (amax[..., None] * NF4).astype(F32)
     # nearest level, first minimum wins
     dist = np.abs((x[:, :, :, None] - levels[:, None, :, :]).astype(F32))  # (H,S,D,16)
     codes = dist.argmin(axis=-1).astype(np.uint8)
@@ -211,6 +242,7 @@ def encode_keys(x: np.ndarray, outlier_frac: float = 0.0):
         "mean": mean,
         "out_idx": out_idx,
         "out_val": out_val,
+        "mode": mode,
     }
 
 
@@ -235,10 +267,13 @@ def unpack_key_codes(packed: np.ndarray, n_values: int) -> np.ndarray:
     return out[:n_values]
 
 
-def dequant_keys(codes, scale, mean, out_idx=None, out_val=None) -> np.ndarray:
-    """Key block decoder (per_channel_kv.py:503-539): level = fl(fl(scale*NF4)+mean),
+def dequant_keys(codes, scale, mean, out_idx=None, out_val=None, mode="nf4_asym") -> np.ndarray:
+    """Key block decoder (per_channel_kv.py:497-539): level = fl(fl(scale*grid)+mean)
+    (symmetric NF4 adds no mean; uniform is fl(fl(code*scale)+zero), the same expression),
     then outlier positions are overwritten with their float16 values."""
-    levels = ((scale[..., None] * NF4).astype(F32) + mean[..., None]).astype(F32)  # (H,D,16)
+    levels = (scale[..., None] * key_grid(mode)).astype(F32)  # (H,D,16)
+    if mode != "nf4":
+        levels = (levels + mean[..., None]).astype(F32)
     h, s, d = codes.shape
     out = np.take_along_axis(
         levels[:, None, :, :], codes[..., None].astype(np.int64), axis=-1
@@ -382,8 +417,9 @@ def outlier_deltas(block):
     h_i = flat // (s * d)
     s_i = (flat // d) % s
     d_i = flat % d
+    grid = key_grid(block.get("mode", "nf4_asym"))
     dense = (block["mean"][h_i, d_i]
-             + block["scale"][h_i, d_i] * NF4[codes[h_i, s_i, d_i]]).astype(F32)
+             + block["scale"][h_i, d_i] * grid[codes[h_i, s_i, d_i]]).astype(F32)
     delta = (block["out_val"].astype(F32) - dense).astype(F32)
     return h_i, s_i, d_i, delta
 
@@ -395,7 +431,8 @@ def fused_key_scores(q, block):
     q = np.asarray(q, dtype=F32)
     w = q * block["scale"]
     bias = (q * block["mean"]).sum(axis=1)
-    sc = np.einsum("hd,hsd->hs", w, NF4[block["codes"].astype(np.int64)]) + bias[:, None]
+    grid = key_grid(block.get("mode", "nf4_asym"))
+    sc = np.einsum("hd,hsd->hs", w, grid[block["codes"].astype(np.int64)]) + bias[:, None]
     h_i, s_i, d_i, delta = outlier_deltas(block)
     if h_i.size:
         corr = np.zeros(sc.shape, dtype=np.float64)
@@ -417,9 +454,10 @@ class OracleCache:
     """
 
     def __init__(self, head_dim=128, n_heads=32, key_bits=4, value_bits=4, hot_window=512,
-                 outlier_frac=0.02, seed=None):
+                 outlier_frac=0.02, seed=None, key_mode="nf4_asym"):
         if key_bits != 4:
-            raise ValueError("the asymmetric NF4 key format is 4-bit")
+            raise ValueError("the per-channel key formats restated here are 4-bit")
+        self.key_mode = key_mode
         self.head_dim, self.n_heads = head_dim, n_heads
         self.key_bits, self.value_bits = key_bits, value_bits
         self.hot_window, self.outlier_frac = hot_window, outlier_frac
@@ -454,7 +492,7 @@ class OracleCache:
             return
         kb = np.stack(self.hot_k[:n], axis=1)  # (H, n, D)
         vb = np.stack(self.hot_v[:n], axis=1)
-        self.cold_k.append(encode_keys(kb, self.outlier_frac))
+        self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode))
         self.cold_v.append(encode_values(vb, self.pi_t, self.boundaries))
         self.cold_lengths.append(n)
         del self.hot_k[:n]
@@ -462,7 +500,8 @@ class OracleCache:
 
     def keys(self) -> np.ndarray:
         """All keys (H, N, D) float32: dequantised cold blocks then the hot tokens."""
-        parts = [dequant_keys(b["codes"], b["scale"], b["mean"], b["out_idx"], b["out_val"])
+        parts = [dequant_keys(b["codes"], b["scale"], b["mean"], b["out_idx"], b["out_val"],
+                              self.key_mode)
                  for b in self.cold_k]
         if self.hot_k:
             parts.append(np.stack(self.hot_k, axis=1).astype(F32))
@@ -488,7 +527,8 @@ class OracleCache:
         h, d = self.n_heads, self.head_dim
         cold = 0
         for kb, vb, n in zip(self.cold_k, self.cold_v, self.cold_lengths):
-            cold += h * n * d * self.key_bits // 8 + 2 * 4 * h * d
+            # per-channel float32 scalars: scale + mean (symmetric NF4 stores no mean)
+            cold += h * n * d * self.key_bits // 8 + (1 if self.key_mode == "nf4" else 2) * 4 * h * d
             if kb["out_idx"] is not None:
                 cold += kb["out_idx"].size * 6
             cold += (h * n * d * self.value_bits + 7) // 8 + 4 * h * n

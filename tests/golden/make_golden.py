@@ -79,8 +79,42 @@ def block_case(name, seed, h, s, value_bits, round_to=None, dtype=np.float32):
     )
 
 
+_KEY_MODE_FLAGS = {"nf4_asym": {"key_nf4_asym": True}, "nf4": {"key_nf4": True}, "uniform": {}}
+
+
+def _key_fields(ck):
+    """(scale, mean) of a key container as (1, H, D) arrays whatever its mode: the NF4
+    family keeps them in nf4_scale / nf4_mean (no mean when symmetric), the uniform grid in
+    scale / zero."""
+    if ck.nf4_scale is not None:
+        mean = ck.nf4_mean if ck.nf4_mean is not None else np.zeros_like(ck.nf4_scale)
+        return ck.nf4_scale, mean
+    return ck.scale[:, :, 0, :], ck.zero[:, :, 0, :]
+
+
+def key_block_case(name, seed, h, s, mode, frac, round_to=None, dtype=np.float32):
+    """One (1, H, S, D) key block through the per-channel encoder in another grid mode."""
+    rng = np.random.default_rng(seed)
+    k, _ = _scaled(rng, (h, D), s)
+    k = k + rng.standard_normal((1, h, D)).astype(np.float32)  # per-channel offsets
+    if round_to is not None:
+        k = (np.round(k / round_to) * round_to).astype(np.float32)
+    k = k.astype(dtype)
+    kb = np.ascontiguousarray(np.moveaxis(k, 0, 1))[None]
+    flags = {"nf4_asym": {"nf4_asym": True}, "nf4": {"nf4": True}, "uniform": {}}[mode]
+    kq = PerChannelKV(head_dim=D, n_heads=h, bits=4, outlier_frac=frac, **flags)
+    ck = kq.compress(kb, packed=True)
+    scale, mean = _key_fields(ck)
+    out = dict(k=k, seed=seed, mode=mode, frac=frac, key_indices=ck.indices, key_scale=scale,
+               key_mean=mean, key_dequant=kq.decompress(ck)[0])
+    if ck.outlier_idx is not None:
+        out["outlier_idx"] = ck.outlier_idx
+        out["outlier_val"] = ck.outlier_val
+    np.savez_compressed(os.path.join(HERE, name), **out)
+
+
 def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype=np.float32,
-               with_fused=False):
+               with_fused=False, key_mode="nf4_asym"):
     """A cache filled token by token; stores every cold container and the
     dequantise-then-attend output (plus ``fused_decode`` where the reference has it)."""
     rng = np.random.default_rng(seed)
@@ -90,8 +124,8 @@ def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype
     q = rng.standard_normal((n_q_heads, D)).astype(np.float32)
     cache = TurboQuantKVCache(
         head_dim=D, n_heads=h, bits=value_bits, key_bits=4, value_bits=value_bits,
-        hot_window=hot_window, use_gpu=False, seed=seed, key_nf4_asym=True,
-        key_outlier_frac=0.02, key_zero_point="calibrated",
+        hot_window=hot_window, use_gpu=False, seed=seed,
+        key_outlier_frac=0.02, key_zero_point="calibrated", **_KEY_MODE_FLAGS[key_mode],
     )
     for t in range(n_tokens):
         cache.append(k[t], v[t])
@@ -111,8 +145,7 @@ def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype
                                     st["uncompressed_equivalent_bytes"]], dtype=np.float64)
     for i, (ck, cv) in enumerate(zip(cache._cold_keys, cache._cold_values)):
         out[f"b{i}_key_indices"] = ck.indices
-        out[f"b{i}_nf4_scale"] = ck.nf4_scale
-        out[f"b{i}_nf4_mean"] = ck.nf4_mean
+        out[f"b{i}_nf4_scale"], out[f"b{i}_nf4_mean"] = _key_fields(ck)
         out[f"b{i}_outlier_idx"] = ck.outlier_idx
         out[f"b{i}_outlier_val"] = ck.outlier_val
         out[f"b{i}_value_indices"] = cv.indices
@@ -153,8 +186,24 @@ def main():
     cache_case("cache_w7.npz", seed=23, h=1, n_tokens=30, hot_window=7, value_bits=3,
                n_q_heads=4)
     pack_known_answer()
+    other_key_grids()
     print("golden fixtures written to", HERE)
 
 
+def other_key_grids():
+    """Blocks and caches in the other per-channel key grids that have a fused form."""
+    key_block_case("keys_uniform.npz", seed=31, h=2, s=256, mode="uniform", frac=0.02)
+    key_block_case("keys_uniform_ties.npz", seed=32, h=2, s=256, mode="uniform", frac=0.0,
+                   round_to=0.25, dtype=np.float16)
+    key_block_case("keys_nf4.npz", seed=33, h=2, s=256, mode="nf4", frac=0.02)
+    cache_case("cache_uniform.npz", seed=34, h=2, n_tokens=700, hot_window=512, value_bits=4,
+               n_q_heads=2, key_mode="uniform")
+    cache_case("cache_nf4_gqa.npz", seed=35, h=2, n_tokens=700, hot_window=512, value_bits=3,
+               n_q_heads=8, dtype=np.float16, key_mode="nf4")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "other_key_grids":
+        other_key_grids()
+    else:
+        main()

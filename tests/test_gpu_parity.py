@@ -367,7 +367,12 @@ def test_facade_matches_reference_api(torch_cuda):
     c2 = cfg.build_cache(hot_window=32, use_gpu=True, seed=1, max_tokens=128)
     assert (c2.key_bits, c2.value_bits, c2.n_heads, c2.hot_window) == (4, 3, 8, 32)
     with pytest.raises(NotImplementedError):
-        TurboQuantKVCache(head_dim=128, n_heads=2, bits=4)  # bare uniform keys
+        TurboQuantKVCache(head_dim=128, n_heads=2, bits=3)  # 3-bit uniform keys
+    with pytest.raises(NotImplementedError):
+        TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nuq=True)
+    with pytest.raises(NotImplementedError):
+        TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4_asym=True,
+                          key_zero_point="sparse", key_rope_theta=1e4)
 
 
 def test_abi_error_codes(torch_cuda):
@@ -416,3 +421,84 @@ def test_degenerate_blocks(torch_cuda):
     out = ctx.decode(0, _dev(torch, q[None]))[0].cpu().numpy()
     assert np.allclose(out, ref.attend(q), rtol=RTOL, atol=ATOL)
     assert ctx.status() == 0
+
+
+# ------------------------------------------------------------------------------------ #
+# the other per-channel key grids (uniform, symmetric NF4)                              #
+# ------------------------------------------------------------------------------------ #
+
+@pytest.mark.parametrize("name,mode,frac", [("keys_uniform.npz", "uniform", 0.02),
+                                            ("keys_uniform_ties.npz", "uniform", 0.0),
+                                            ("keys_nf4.npz", "nf4", 0.02)])
+def test_other_key_grids_encoder_bit_exact(torch_cuda, name, mode, frac):
+    """One 256-token block flushed through the CUDA key encoder in each mode: packed codes,
+    scale, mean / zero, outliers and the getter's dequantised keys equal the reference's."""
+    torch = torch_cuda
+    g = load_golden(name)
+    k = g["k"]  # (S, H, D)
+    s, h = k.shape[0], k.shape[1]
+    dt = _np_dtype_name(k)
+    # hot_window 511 -> blocks of 256 tokens; 512 + 1 tokens force exactly one flush... the
+    # fixture is a single block, so fill the window with copies and flush once
+    pad = np.zeros((257, h, 128), dtype=k.dtype)
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, value_bits=4, hot_window=512,
+               max_tokens_per_seq=1024, kv_dtype=dt, outlier_frac=frac, key_mode=mode, seed=0)
+    both = np.concatenate([k, pad], axis=0)
+    ctx.append(0, _dev(torch, both)[None], _dev(torch, both)[None])
+    assert ctx.lengths(0, 0) == (513, 256, 257)
+    blk = ctx.export_block(0, 0, 0)
+    assert np.array_equal(blk["key_indices"], g["key_indices"])
+    assert np.array_equal(blk["nf4_scale"], g["key_scale"])
+    assert np.array_equal(blk["nf4_mean"], g["key_mean"])
+    if frac > 0:
+        assert np.array_equal(blk["outlier_idx"], g["outlier_idx"])
+        assert np.array_equal(blk["outlier_val"].view(np.uint16), g["outlier_val"].view(np.uint16))
+    keys, _ = ctx.dequant(0, 0, 0, 256, values=False)
+    assert np.array_equal(keys.cpu().numpy(), g["key_dequant"])
+
+
+@pytest.mark.parametrize("name,mode,vb", [("cache_uniform.npz", "uniform", 4),
+                                          ("cache_nf4_gqa.npz", "nf4", 3)])
+def test_other_key_grids_cache_and_decode(torch_cuda, name, mode, vb):
+    """Caches in the other key grids: every cold container equals the reference's and the
+    decode on codes (both kernels) matches its dequantise-then-attend output."""
+    torch = torch_cuda
+    g = load_golden(name)
+    k, v, q = g["k"], g["v"], g["q"]
+    h, hq = k.shape[1], q.shape[0]
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=hq, value_bits=vb,
+               hot_window=int(g["hot_window"]), max_tokens_per_seq=1024,
+               kv_dtype=_np_dtype_name(k), key_mode=mode, seed=int(g["seed"]), pi=g["pi"])
+    ctx.append(0, _dev(torch, k)[None], _dev(torch, v)[None])
+    assert ctx.lengths(0, 0)[0] == int(g["length"])
+    for i in range(int(g["n_blocks"])):
+        blk = ctx.export_block(0, 0, i)
+        assert np.array_equal(blk["key_indices"], g[f"b{i}_key_indices"])
+        assert np.array_equal(blk["nf4_scale"], g[f"b{i}_nf4_scale"])
+        assert np.array_equal(blk["nf4_mean"], g[f"b{i}_nf4_mean"])
+        assert np.array_equal(blk["outlier_idx"], g[f"b{i}_outlier_idx"])
+        assert np.array_equal(blk["value_indices"], g[f"b{i}_value_indices"])
+    keys, vals = ctx.dequant(0, 0, 0, int(g["length"]))
+    assert np.array_equal(keys.cpu().numpy()[0], g["keys_head0"])
+    qq = _dev(torch, q)[None]
+    got = ctx.decode(0, qq)[0].cpu().numpy()
+    assert np.allclose(got, g["attn"], rtol=RTOL, atol=ATOL), np.abs(got - g["attn"]).max()
+    ctx.set_kernel("general")
+    gen = ctx.decode(0, qq)[0].cpu().numpy()
+    assert np.allclose(gen, g["attn"], rtol=RTOL, atol=ATOL), np.abs(gen - g["attn"]).max()
+    cold, hot = ctx.memory_stats(0, 0)
+    assert cold == g["memory_stats"][0] and hot == g["memory_stats"][1]
+
+
+def test_facade_key_grid_flags(torch_cuda):
+    """The reference's constructor flags select the grid: neither flag = uniform,
+    key_nf4 = symmetric NF4, key_nf4_asym = asymmetric NF4."""
+    from turboquant_pro_b200 import AutoConfig, TurboQuantKVCache
+
+    assert TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, max_tokens=64).key_mode == "uniform"
+    assert TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4=True,
+                             max_tokens=64).key_mode == "nf4"
+    assert TurboQuantKVCache.robust(128, 2, max_tokens=64).key_mode == "nf4_asym"
+    c = AutoConfig.from_pretrained("llama-3-8b").build_cache(robust=False, hot_window=32,
+                                                             max_tokens=64)
+    assert c.key_mode == "uniform" and c.key_outlier_frac == 0.0

@@ -75,15 +75,43 @@ def test_outlier_ties_are_kept():
     assert g["outlier_idx"].size > k * 2 * 128
 
 
-@pytest.mark.parametrize("name,vb", [("cache_w16.npz", 4), ("cache_w512_gqa.npz", 3),
-                                     ("cache_w7.npz", 3)])
-def test_cache_matches_reference(name, vb):
+@pytest.mark.parametrize("name,mode,frac", [("keys_uniform.npz", "uniform", 0.02),
+                                            ("keys_uniform_ties.npz", "uniform", 0.0),
+                                            ("keys_nf4.npz", "nf4", 0.02)])
+def test_other_key_grids_bit_exact(name, mode, frac):
+    """Uniform per-channel and symmetric NF4 keys (the other grids with a fused form)."""
+    g = load_golden(name)
+    enc = orc.encode_keys(_hsd(g["k"]), frac, mode)
+    assert np.array_equal(orc.pack_key_codes(enc["codes"]), g["key_indices"])
+    assert np.array_equal(enc["scale"], g["key_scale"][0])
+    assert np.array_equal(enc["mean"], g["key_mean"][0])
+    if frac > 0:
+        assert np.array_equal(enc["out_idx"], g["outlier_idx"])
+        assert np.array_equal(enc["out_val"].view(np.uint16), g["outlier_val"].view(np.uint16))
+    else:
+        assert enc["out_idx"] is None
+    deq = orc.dequant_keys(enc["codes"], enc["scale"], enc["mean"], enc["out_idx"],
+                           enc["out_val"], mode)
+    assert np.array_equal(deq, g["key_dequant"])
+    if mode == "uniform" and frac == 0.0:
+        # coarse-grid inputs put quotients exactly on .5: round-half-even decides the code
+        x = _hsd(g["k"]).astype(np.float32)
+        qv = (x - enc["mean"][:, None, :]) / enc["scale"][:, None, :]
+        assert np.any(np.abs(qv - np.floor(qv) - 0.5) < 1e-7)
+
+
+@pytest.mark.parametrize("name,vb,mode", [("cache_w16.npz", 4, "nf4_asym"),
+                                          ("cache_w512_gqa.npz", 3, "nf4_asym"),
+                                          ("cache_w7.npz", 3, "nf4_asym"),
+                                          ("cache_uniform.npz", 4, "uniform"),
+                                          ("cache_nf4_gqa.npz", 3, "nf4")])
+def test_cache_matches_reference(name, vb, mode):
     g = load_golden(name)
     k, v, q = g["k"], g["v"], g["q"]
     h = k.shape[1]
     cache = orc.OracleCache(head_dim=128, n_heads=h, key_bits=4, value_bits=vb,
                             hot_window=int(g["hot_window"]), outlier_frac=0.02,
-                            seed=int(g["seed"]))
+                            seed=int(g["seed"]), key_mode=mode)
     cache.pi, cache.pi_t = g["pi"], np.ascontiguousarray(g["pi"].T)
     for t in range(k.shape[0]):
         cache.append(k[t], v[t])

@@ -30,7 +30,7 @@ class TqGeom(C.Structure):
         ("n_layers", C.c_int32), ("n_seqs", C.c_int32), ("n_kv_heads", C.c_int32),
         ("n_q_heads", C.c_int32), ("head_dim", C.c_int32), ("key_bits", C.c_int32),
         ("value_bits", C.c_int32), ("hot_window", C.c_int32), ("kv_dtype", C.c_int32),
-        ("max_tokens_per_seq", C.c_int32), ("reserved0_", C.c_int32),
+        ("max_tokens_per_seq", C.c_int32), ("key_mode", C.c_int32),
         ("outlier_frac", C.c_double),
         ("group", C.c_int32), ("block_tokens", C.c_int32), ("block_tokens_pad", C.c_int32),
         ("hot_cap", C.c_int32), ("max_blocks", C.c_int32), ("outlier_k", C.c_int32),

@@ -143,9 +143,10 @@ class AutoConfig:
         """A configured :class:`TurboQuantKVCache` (``autoconfig.py:439-486``).
 
         This package is GPU-only, so the cache lives on the GPU whatever ``use_gpu`` says
-        (the keyword is kept so existing call sites work).  ``robust=False`` (the bare
-        uniform key grid) and the ``"bias"``/``"sparse"`` zero-points are not implemented
-        on the CUDA path and raise ``NotImplementedError``.
+        (the keyword is kept so existing call sites work).  ``robust=False`` gives the bare
+        uniform 4-bit key grid without outliers, as in the reference; the ``"bias"`` and
+        ``"sparse"`` zero-points are not implemented on the CUDA path and raise
+        ``NotImplementedError``.
         """
         from .cache import TurboQuantKVCache
 
@@ -161,7 +162,8 @@ class AutoConfig:
     def build_context(self, n_seqs: int, max_tokens_per_seq: int | None = None,
                       hot_window: int = 512, seed: int | None = None,
                       outlier_frac: float = 0.02, kv_dtype="float16", n_layers: int | None = None,
-                      n_kv_heads: int | None = None, n_q_heads: int | None = None, device: int = 0):
+                      n_kv_heads: int | None = None, n_q_heads: int | None = None, device: int = 0,
+                      key_mode: str = "nf4_asym"):
         """A batched, multi-layer :class:`KVContext` with this model's geometry — what a
         serving engine holds: ``n_layers x n_seqs`` caches, GQA-aware decode.
         ``n_kv_heads`` / ``n_q_heads`` override the model's counts for head-sharded
@@ -175,4 +177,4 @@ class AutoConfig:
             head_dim=self.head_dim, key_bits=self.key_bits, value_bits=self.value_bits,
             hot_window=hot_window, outlier_frac=outlier_frac,
             max_tokens_per_seq=max_tokens_per_seq or self.max_seq_len, kv_dtype=kv_dtype,
-            seed=seed, device=device)
+            seed=seed, device=device, key_mode=key_mode)

@@ -6,9 +6,11 @@ imports.  Storage and arithmetic live on the GPU behind the C ABI; there is no n
 CuPy path underneath and therefore no CPU fallback: constructing a cache without a CUDA
 device raises.
 
-Supported format: per-channel asymmetric-NF4 keys (``key_nf4_asym=True``, 4 bits,
-``key_zero_point="calibrated"``) with an optional fp16 outlier side-list, PolarQuant
-values at 3 or 4 bits.  Other key grids of the reference raise ``NotImplementedError``.
+Supported formats: per-channel 4-bit keys in the three grids the reference has an affine
+(fused) form for — asymmetric NF4 (``key_nf4_asym=True``, ``key_zero_point="calibrated"``),
+symmetric NF4 (``key_nf4=True``) and uniform (neither flag) — with an optional fp16 outlier
+side-list, PolarQuant values at 3 or 4 bits.  Data-fit tables (``key_nuq``), the ``sparse``
+and ``bias`` zero-points and other key widths raise ``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -68,20 +70,24 @@ class TurboQuantKVCache:
         if not per_channel_keys:
             raise NotImplementedError("PolarQuant keys (per_channel_keys=False) are not "
                                       "implemented on the CUDA path")
-        if not key_nf4_asym or key_nuq:
-            raise NotImplementedError(
-                "the CUDA path implements asymmetric-NF4 keys: build the cache with "
-                "TurboQuantKVCache.robust(...) or key_nf4_asym=True")
+        if key_nuq:
+            raise NotImplementedError("data-fit key tables (key_nuq=True) have no fused form; "
+                                      "they are not implemented on the CUDA path")
         if key_zero_point != "calibrated":
+            if not key_nf4_asym:
+                raise ValueError(f"zero_point={key_zero_point!r} requires nf4_asym=True")
             raise NotImplementedError("key_zero_point 'sparse' and 'bias' are not implemented "
                                       "on the CUDA path")
-        if self.key_bits != 4:
+        if (key_nf4 or key_nf4_asym) and self.key_bits != 4:
             raise ValueError("nf4=True requires bits=4")
+        if self.key_bits != 4:
+            raise NotImplementedError("the CUDA path implements 4-bit per-channel keys")
+        self.key_mode = "nf4_asym" if key_nf4_asym else ("nf4" if key_nf4 else "uniform")
         self._ctx = KVContext(
             n_layers=1, n_seqs=1, n_kv_heads=n_heads, n_q_heads=n_q_heads or n_heads,
             head_dim=head_dim, key_bits=self.key_bits, value_bits=self.value_bits,
             hot_window=hot_window, outlier_frac=key_outlier_frac, max_tokens_per_seq=max_tokens,
-            kv_dtype=dtype, seed=seed, device=device_id)
+            kv_dtype=dtype, seed=seed, device=device_id, key_mode=self.key_mode)
         self.key_outlier_frac = key_outlier_frac
 
     # ------------------------------------------------------------------ properties --

@@ -71,6 +71,9 @@ def _torch_dtype(name):
             "bfloat16": torch.bfloat16}[key]
 
 
+KEY_MODES = ("nf4_asym", "nf4", "uniform")  # TQ_KEYS_* of the C ABI, in order
+
+
 class KVContext:
     """``n_layers x n_seqs`` compressed KV caches on one GPU.
 
@@ -78,7 +81,9 @@ class KVContext:
         n_layers, n_seqs, n_kv_heads, n_q_heads: cache-group geometry; query head ``i``
             attends KV head ``i // (n_q_heads // n_kv_heads)``.
         head_dim: 128.
-        key_bits: 4 (asymmetric NF4 keys).  value_bits: 3 or 4 (PolarQuant values).
+        key_bits: 4.  value_bits: 3 or 4 (PolarQuant values).
+        key_mode: per-channel key grid, ``"nf4_asym"`` (default), ``"nf4"`` (symmetric) or
+            ``"uniform"`` (``per_channel_kv.py:285-401``).
         hot_window: tokens kept uncompressed (2..512); a flush moves the oldest
             ``(hot_window + 1) // 2`` tokens into one cold block.
         outlier_frac: per-channel fraction of fp16 outliers kept beside the key codes.
@@ -90,7 +95,8 @@ class KVContext:
 
     def __init__(self, n_layers=1, n_seqs=1, n_kv_heads=8, n_q_heads=None, head_dim=128,
                  key_bits=4, value_bits=3, hot_window=512, outlier_frac=0.02,
-                 max_tokens_per_seq=8192, kv_dtype="float32", seed=None, pi=None, device=0):
+                 max_tokens_per_seq=8192, kv_dtype="float32", seed=None, pi=None, device=0,
+                 key_mode="nf4_asym"):
         torch = _torch()
         if not torch.cuda.is_available():
             raise RuntimeError("KVContext needs a CUDA device: this package has no CPU fallback")
@@ -101,6 +107,10 @@ class KVContext:
         g.n_layers, g.n_seqs, g.n_kv_heads = n_layers, n_seqs, n_kv_heads
         g.n_q_heads = n_q_heads if n_q_heads is not None else n_kv_heads
         g.head_dim, g.key_bits, g.value_bits = head_dim, key_bits, value_bits
+        if key_mode not in KEY_MODES:
+            raise ValueError(f"key_mode must be one of {KEY_MODES}, got {key_mode!r}")
+        self.key_mode = key_mode
+        g.key_mode = KEY_MODES.index(key_mode)
         g.hot_window = hot_window
         g.kv_dtype = _dtype_code(self.kv_dtype)
         g.max_tokens_per_seq = max_tokens_per_seq

@@ -88,7 +88,7 @@ struct Tables {
   float pi_t[TQ_D * TQ_D];
   float centroids[16];
   float boundaries[16];
-  float nf4[16];
+  float grid[16];  // key levels: NF4, or 0..15 for uniform keys
 };
 
 struct tq_ctx {

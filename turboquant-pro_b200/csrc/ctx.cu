@@ -47,8 +47,9 @@ int32_t tq_geom_finish(tq_geom* g) {
   TQ_REQUIRE(g->n_q_heads >= g->n_kv_heads && g->n_q_heads % g->n_kv_heads == 0, TQ_ERR_INVALID,
              "n_q_heads must be a positive multiple of n_kv_heads");
   TQ_REQUIRE(g->head_dim == TQ_D, TQ_ERR_UNSUPPORTED, "only head_dim == 128 is implemented");
-  TQ_REQUIRE(g->key_bits == 4, TQ_ERR_UNSUPPORTED,
-             "keys are asymmetric NF4: key_bits must be 4");
+  TQ_REQUIRE(g->key_bits == 4, TQ_ERR_UNSUPPORTED, "per-channel keys: key_bits must be 4");
+  TQ_REQUIRE(g->key_mode >= TQ_KEYS_NF4_ASYM && g->key_mode <= TQ_KEYS_UNIFORM, TQ_ERR_INVALID,
+             "key_mode must be one of TQ_KEYS_*");
   TQ_REQUIRE(g->value_bits == 3 || g->value_bits == 4, TQ_ERR_UNSUPPORTED,
              "value_bits must be 3 or 4");
   TQ_REQUIRE(g->hot_window >= 2 && g->hot_window <= 512, TQ_ERR_UNSUPPORTED,
@@ -164,7 +165,7 @@ int32_t tq_ctx_create(const tq_geom* g, const tq_buffers* bufs, int32_t device, 
                                 0.5626170039176941f,
                                 0.7229568362236023f,
                                 1.0f};
-  std::memcpy(t->nf4, nf4, sizeof(nf4));
+  for (int i = 0; i < 16; ++i) t->grid[i] = g->key_mode == TQ_KEYS_UNIFORM ? (float)i : nf4[i];
   cudaError_t e = cudaMemcpyAsync(bufs->tables, t, sizeof(Tables), cudaMemcpyHostToDevice, st);
   // The hot rings start zeroed: the decode kernel multiplies ring rows past the end of a
   // window by probability 0, which needs them finite.
@@ -446,7 +447,9 @@ int32_t tq_memory_stats(tq_ctx* ctx, int32_t layer, int32_t seq, double* cold_by
     for (int b = 0; b < nb; ++b) {
       double n_out = 0;
       for (int h = 0; h < H; ++h) n_out += meta[(size_t)h * g.max_blocks + b].cnt;
-      cold += (double)H * S * D * g.key_bits / 8 + 2.0 * 4 * H * D + 6.0 * n_out;
+      // symmetric NF4 containers hold no mean
+      cold += (double)H * S * D * g.key_bits / 8 +
+              (g.key_mode == TQ_KEYS_NF4 ? 1.0 : 2.0) * 4 * H * D + 6.0 * n_out;
       cold += (double)H * S * D * g.value_bits / 8 + 4.0 * H * S;
     }
   }
@@ -486,7 +489,7 @@ int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes) {
   // reference container bytes of one cold block of one KV head, with the nominal
   // outlier count (ties add a few entries that are not counted)
   double blk = (double)S * D * g.key_bits / 8 + (double)S * D * g.value_bits / 8 + 4.0 * S +
-               8.0 * D + 6.0 * g.outlier_k * D;
+               (g.key_mode == TQ_KEYS_NF4 ? 4.0 : 8.0) * D + 6.0 * g.outlier_k * D;
   double total = 0.0;
   for (int s = 0; s < g.n_seqs; ++s) {
     int n = ctx->len[(size_t)layer * g.n_seqs + s];

@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
   __shared__ float mrg_acc[WARPS][GT][TQ_D];
 
   if (tid < 16) {
-    nf4_s[tid] = a.tables->nf4[tid];
+    nf4_s[tid] = a.tables->grid[tid];
     cent_s[tid] = a.tables->centroids[tid];
   }
   for (int i = tid; i < GT * TQ_D; i += WARPS * 32) {

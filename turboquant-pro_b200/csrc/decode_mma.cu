@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   // lookup tables: entry-major, one copy per lane so that a warp's 32 lookups never collide
   {
     float* small = (float*)groups;  // 32 floats of scratch until the groups claim the area
-    if (tid < 16) small[tid] = a.tables->nf4[tid];
+    if (tid < 16) small[tid] = a.tables->grid[tid];
     else if (tid < 32) small[tid] = a.tables->centroids[tid - 16];
     __syncthreads();
     if (tid < 16) dtab[tid] = small[tid] - __half2float(__float2half_rn(small[tid]));

@@ -41,7 +41,8 @@ __global__ void __launch_bounds__(TQ_D) dequant_dense_kernel(DequantArgs a) {
     const int code = (d & 1) ? (b >> 4) : (b & 15);
     const float sc = ((const float*)(page + g.scale_off))[d];
     const float mu = ((const float*)(page + g.mean_off))[d];
-    a.k_out[o] = __fadd_rn(__fmul_rn(sc, a.tables->nf4[code]), mu);
+    // symmetric NF4 stores mean 0, uniform keys are fl(fl(code * scale) + zero): one form
+    a.k_out[o] = __fadd_rn(__fmul_rn(sc, a.tables->grid[code]), mu);
   } else {
     const size_t i = hot_offset_elems(g, a.layer, a.seq, head) + (size_t)(pos % g.hot_cap) * TQ_D + d;
     if (a.k_out) a.k_out[o] = ld_any(a.hot_k, i, g.kv_dtype);

@@ -59,10 +59,14 @@ TQ_DEV TokenSource<DT> make_source(const EncodeArgs& a, const void* ring_base, c
 
 // ---------------------------------------------------------------------------------------
 // Key encoder.  One CTA per new cold block of one KV head, one thread per channel.
+// Asymmetric NF4 (TQ_KEYS_NF4_ASYM):
 //   mean   = (((x0 + x1) + x2) + ...) / S                      sequential float32 sum
 //   scale  = max(max_s |x - mean|, 1e-8)
 //   level  = fl(mean + fl(scale * NF4[l]));  code = first l minimising |fl(x - level_l)|
-//   outliers: every token whose |x| reaches the channel's k-th largest magnitude
+// Symmetric NF4 (TQ_KEYS_NF4): mean = 0, scale = max(max_s |x|, 1e-8), level = fl(scale * NF4[l]).
+// Uniform (TQ_KEYS_UNIFORM): mean = min_s x, scale = fl(max(fl(max - min), 1e-8) / 15),
+//   code = clip(round-half-even(fl(fl(x - min) / scale)), 0, 15).
+// All modes: outliers are every token whose |x| reaches the channel's k-th largest magnitude.
 // ---------------------------------------------------------------------------------------
 template <int DT>
 __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
@@ -101,7 +105,9 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   float top[TQ_MAX_K_OUT];
 #pragma unroll
   for (int i = 0; i < TQ_MAX_K_OUT; ++i) top[i] = -1.0f;
+  const int mode = g.key_mode;
   float acc = src.ld(pos0, d);
+  float xmin = acc, xmax = acc;
   if (kk > 0) {
     float a0 = fabsf(acc);
     int i = 0;
@@ -111,6 +117,8 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   for (int t = 1; t < S; ++t) {
     float x = src.ld(pos0 + t, d);
     acc = __fadd_rn(acc, x);
+    xmin = fminf(xmin, x);
+    xmax = fmaxf(xmax, x);
     if (kk > 0) {
       float ax = fabsf(x);
       if (ax > top[0]) {
@@ -120,7 +128,9 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
       }
     }
   }
-  const float mu = __fdiv_rn(acc, (float)S);
+  const float mu = mode == TQ_KEYS_NF4_ASYM ? __fdiv_rn(acc, (float)S)
+                   : mode == TQ_KEYS_NF4    ? 0.0f
+                                            : xmin;
   const float kth = (kk >= S) ? -1.0f : top[0];
 
   // pass 2: scale, and how many outliers this channel keeps
@@ -128,16 +138,21 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   int my_out = 0;
   for (int t = 0; t < S; ++t) {
     float x = src.ld(pos0 + t, d);
-    amax = fmaxf(amax, fabsf(__fsub_rn(x, mu)));
+    amax = fmaxf(amax, fabsf(mode == TQ_KEYS_NF4_ASYM ? __fsub_rn(x, mu) : x));
     if (kk > 0 && fabsf(x) >= kth) {
       ++my_out;
       atomicAdd(&s_tok_cnt[t], 1);
     }
   }
   amax = fmaxf(amax, 1e-8f);
+  if (mode == TQ_KEYS_UNIFORM) amax = __fdiv_rn(fmaxf(__fsub_rn(xmax, xmin), 1e-8f), 15.0f);
+  // from here on `amax` is the channel's scale in every mode: dense = mean + scale * grid[code]
   float lev[16];
 #pragma unroll
-  for (int l = 0; l < 16; ++l) lev[l] = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[l]));
+  for (int l = 0; l < 16; ++l) {
+    const float sl = __fmul_rn(amax, a.tables->grid[l]);
+    lev[l] = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
+  }
 
   ((float*)(page + g.scale_off))[d] = amax;
   ((float*)(page + g.mean_off))[d] = mu;
@@ -239,13 +254,18 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   for (int t = 0; t < S; ++t) {
     float x = src.ld(pos0 + t, d);
     int best = 0;
-    float bd = fabsf(__fsub_rn(x, lev[0]));
+    if (mode == TQ_KEYS_UNIFORM) {
+      const float qv = rintf(__fdiv_rn(__fsub_rn(x, mu), amax));  // ties to even, like np.round
+      best = (int)fminf(fmaxf(qv, 0.0f), 15.0f);
+    } else {
+      float bd = fabsf(__fsub_rn(x, lev[0]));
 #pragma unroll
-    for (int l = 1; l < 16; ++l) {
-      float dd = fabsf(__fsub_rn(x, lev[l]));
-      if (dd < bd) {
-        bd = dd;
-        best = l;
+      for (int l = 1; l < 16; ++l) {
+        float dd = fabsf(__fsub_rn(x, lev[l]));
+        if (dd < bd) {
+          bd = dd;
+          best = l;
+        }
       }
     }
     if (rank < 4) atomicOr(&s_side[t], (unsigned int)best << (4 * rank));
@@ -254,7 +274,10 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     if (kk > 0 && fabsf(x) >= kth) {
       int slot = atomicAdd(&s_tok_cnt[t], 1);  // grouped by token, any order inside a token
       __half hv = __float2half_rn(x);
-      float dense = __fadd_rn(mu, __fmul_rn(amax, a.tables->nf4[best]));
+      // the decoder's value of this position (the level, recomputed: indexing lev[] with a
+      // runtime index would move the whole array out of registers)
+      const float sl = __fmul_rn(amax, a.tables->grid[best]);
+      float dense = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
       __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
       const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
                            ((uint32_t)t << 24);
