@@ -222,8 +222,9 @@ TQ_DEV void unit_tiles(const MmaArgs& a, int unit, int& nb, int& ht, int& b0, in
   ht = (hot_len + htt - 1) / htt;
 }
 
-// Fills the plan; every thread of the CTA must call it.
-TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int tid, int nthreads) {
+// Fills the plan; every thread of the CTA must call it.  `tot` is scratch for one int per
+// 32-unit chunk.
+TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int* tot, int tid, int nthreads) {
   for (int u = tid; u < a.n_units; u += nthreads) {
     int nb, ht, b0, hs, hl;
     unit_tiles(a, u, nb, ht, b0, hs, hl);
@@ -231,23 +232,28 @@ TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int tid, int nthreads) {
     plan->b0[u] = (short)b0;
     plan->hot_start[u] = hs;
     plan->hot_len[u] = (short)hl;
-    plan->P[u + 1] = nb + ht;  // cost, scanned below
+    plan->P[u + 1] = nb + ht;  // tiles of the unit, scanned below
   }
   __syncthreads();
-  if (tid < 32) {
-    int carry = 0;
-    for (int base = 0; base < a.n_units; base += 32) {
-      int i = base + tid;
-      int v = i < a.n_units ? plan->P[i + 1] : 0;
+  // inclusive scan: every warp scans chunks of 32 units, then the chunk totals are added
+  const int lane = tid & 31, n_chunks = (a.n_units + 31) / 32;
+  for (int ch = tid >> 5; ch < n_chunks; ch += nthreads >> 5) {
+    const int i = 32 * ch + lane;
+    int v = i < a.n_units ? plan->P[i + 1] : 0;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int n = __shfl_up_sync(0xffffffffu, v, o);
-        if (tid >= o) v += n;
-      }
-      if (i < a.n_units) plan->P[i + 1] = carry + v;
-      carry += __shfl_sync(0xffffffffu, v, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += n;
     }
-    if (tid == 0) plan->P[0] = 0;
+    if (i < a.n_units) plan->P[i + 1] = v;
+    if (lane == 31) tot[ch] = v;
+  }
+  if (tid == 0) plan->P[0] = 0;
+  __syncthreads();
+  for (int i = tid; i < a.n_units; i += nthreads) {
+    int base = 0;
+    for (int ch = 0; ch < (i >> 5); ++ch) base += tot[ch];
+    plan->P[i + 1] += base;
   }
   __syncthreads();
 }
@@ -264,8 +270,15 @@ TQ_DEV int find_unit(const Plan* plan, int n_units, int pos) {
 // debugging aid: slot k of tile t gets the SM clock (CTA 0, first 64 tiles, one lane)
 #define TQ_TRACE(k)                                                     \
   do {                                                                  \
-    if (a.trace != nullptr && blockIdx.x == 0 && lane == 0 && t < 64)   \
+    if (a.trace != nullptr && blockIdx.x == 0 && lane == 0 && t < 63)   \
       a.trace[t * 8 + (k)] = (unsigned long long)clock64();             \
+  } while (0)
+// row 63 of the trace: the kernel's own phases (entry, tables built, predecessor done, plan
+// built, first copies started), stamped by thread 0 of CTA 0
+#define TQ_TRACE_PHASE(k)                                               \
+  do {                                                                  \
+    if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0)      \
+      a.trace[63 * 8 + (k)] = (unsigned long long)clock64();            \
   } while (0)
 
 struct Waiter {
@@ -331,6 +344,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   uint8_t* stages = (uint8_t*)bars + SM::BARS_BYTES;
   static_assert(2 * NSTAGE <= 16, "barrier slots");
 
+  TQ_TRACE_PHASE(0);
   const uint32_t full0 = smem_addr(bars);
   if (tid == 0) {
     for (int s = 0; s < 2 * NSTAGE; ++s) mbar_init(full0 + 8 * s, 1);
@@ -359,8 +373,11 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   // one may start while the kernel before it in the stream is still running.  Up to here it
   // has read only the constant tables; everything else (lengths, query, pages, scratch) is
   // touched after the wait, which returns once that kernel has completed.
+  TQ_TRACE_PHASE(1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  build_plan(a, plan, tid, THREADS);  // contains the __syncthreads that publish all of the above
+  TQ_TRACE_PHASE(2);
+  // (contains the __syncthreads that publish all of the above; the groups' area is free)
+  build_plan(a, plan, (int*)groups, tid, THREADS);
   // the combine kernel that follows may be scheduled wherever an SM frees up
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -376,6 +393,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     for (int u = tid; u < a.n_units; u += THREADS) a.plan_g[3 + a.n_units + u] = plan->nb[u];
   }
   if (lo >= hi) return;
+  TQ_TRACE_PHASE(3);
   const Waiter waiter{abort_flag, a.status};
   const int htt = hot_tile_tokens(g.kv_dtype);
   const int esz = elem_size(g.kv_dtype);
@@ -443,9 +461,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   // ============================== consumer groups ============================================
   const int gi = warp / GW, gw = warp % GW, gtid = tid - gi * (GW * 32);
   int u_iss = find_unit(plan, a.n_units, lo);  // cursor of the copies this thread starts
-  if (tid == 0) {
-    for (int t = 0; t < min(NSTAGE, total); ++t) fire(describe(t, u_iss));
-  }
+  if (warp == 0 && lane < min(NSTAGE, total)) fire(describe(lane, u_iss));  // a lane per tile
+  TQ_TRACE_PHASE(4);
   uint8_t* gs = groups + gi * SM::GROUP_BYTES;
   float* qc = (float*)gs;                                   // [128][G]
   uint4* frag = (uint4*)(gs + SM::FRAG_OFF);                // [8 k-steps][32 lanes]
@@ -600,15 +617,26 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     }
     if (tl.u != q_unit) {  // new unit: reload its query rows
       q_unit = tl.u;
-      for (int i = gtid; i < TQ_D * G; i += GW * 32) {
-        const int d = i / G, rr = i % G;
-        const size_t qi = ((size_t)seq * g.n_q_heads + head * G + rr) * TQ_D + d;
-        // the softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
-        // bias and corrections come out already scaled
-        qc[q_row(d) * G + rr] = a.scale_log2 *
-                (a.q_dtype == TQ_F32   ? ((const float*)a.q)[qi]
-                 : a.q_dtype == TQ_F16 ? __half2float(((const __half*)a.q)[qi])
-                                       : __bfloat162float(((const __nv_bfloat16*)a.q)[qi]));
+      {
+        // thread d of the group loads channel d of the G rows: coalesced, independent loads.
+        // The softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
+        // bias and corrections come out already scaled.
+        const size_t q0 = ((size_t)seq * g.n_q_heads + head * G) * TQ_D + gtid;
+        float qv[G];
+        if (a.q_dtype == TQ_F32) {
+#pragma unroll
+          for (int rr = 0; rr < G; ++rr) qv[rr] = ((const float*)a.q)[q0 + rr * TQ_D];
+        } else if (a.q_dtype == TQ_F16) {
+#pragma unroll
+          for (int rr = 0; rr < G; ++rr)
+            qv[rr] = __half2float(((const __half*)a.q)[q0 + rr * TQ_D]);
+        } else {
+#pragma unroll
+          for (int rr = 0; rr < G; ++rr)
+            qv[rr] = __bfloat162float(((const __nv_bfloat16*)a.q)[q0 + rr * TQ_D]);
+        }
+#pragma unroll
+        for (int rr = 0; rr < G; ++rr) qc[q_row(gtid) * G + rr] = a.scale_log2 * qv[rr];
       }
       group_sync();
     }
