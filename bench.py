@@ -405,8 +405,8 @@ def run_native(args):
         "avg_launch_ms": attn_ms_avg, "combine_avg_launch_ms": comb_ms / max(n_calls, 1),
         "launches_timed": n_calls,
         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at the
-        # default workload (335.0 MB + 6.1 MB per launch), scaled by the bytes a launch covers
-        "traffic": 341.1e6 * layer_bytes / 333578240.0,
+        # default workload (335.0 MB + 6.8 MB per launch), scaled by the bytes a launch covers
+        "traffic": 341.8e6 * layer_bytes / 333578240.0,
         "traffic_source": "ncu capture of the default workload (profiles/), scaled by "
                           "algorithmic bytes",
         "timing": "CUDA events around every launch on the launching stream, in a second pass "
