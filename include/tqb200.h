@@ -241,6 +241,14 @@ int32_t tq_last_launches(const tq_ctx* ctx);
 int32_t tq_decode_static_scratch(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype,
                                  float* out, void* stream);
 
+/* The "sparse" zero-point of asymmetric NF4 keys (per_channel_kv.py:337-342, :517-522): the
+ * per-channel mean is kept only on the channels whose mask byte is non-zero (the reference
+ * derives the mask from the rotary wavelengths, dc_channel_mask at :233-241; the caller
+ * computes it) and is 0 elsewhere.  `mask` is head_dim bytes of host memory; a null mask
+ * restores the default (every channel).  Set it before the first append; blocks already
+ * encoded keep the zero-points they were encoded with.  TQ_KEYS_NF4_ASYM only. */
+int32_t tq_set_key_mean_mask(tq_ctx* ctx, const uint8_t* mask, void* stream);
+
 /* Selects the decode kernel: 0 = automatic (the tensor-core kernel where the geometry
  * allows: 256-token blocks, GQA group 1/2/4/8; else the general-shape kernel), 1 = always
  * the general-shape float32 kernel.  Both compute the same function; tests compare them.

@@ -196,7 +196,18 @@ def key_grid(mode: str) -> np.ndarray:
     return np.arange(16, dtype=F32) if mode == "uniform" else NF4
 
 
-def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym"):
+def dc_channel_mask(rope_theta: float, head_dim: int, window: int) -> np.ndarray:
+    """Channels whose rotary wavelength exceeds ``window`` tokens (per_channel_kv.py:233-241):
+    pair i of the rotate-half layout turns with angular frequency theta^(-2i/D), so its
+    wavelength is 2*pi*theta^(2i/D); channels i and i + D/2 share it."""
+    half = head_dim // 2
+    inv_freq = rope_theta ** (-2.0 * np.arange(half) / head_dim)
+    wavelength = 2.0 * np.pi / inv_freq
+    return np.tile(wavelength, 2)[:head_dim] > float(window)
+
+
+def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym",
+                dc_mask: np.ndarray | None = None):
     """Per-channel 4-bit key block encoder (per_channel_kv.py:285-401).
 
     ``x`` (H, S, D) any float dtype.  Returns a dict with unpacked ``codes`` (H,S,D)
@@ -209,6 +220,9 @@ def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym"
     * ``"nf4"`` (:354-357): mean = 0, scale = max|x| floored, level = fl(scale*NF4[l]);
     * ``"uniform"`` (:303-318): mean = min, scale = fl(max(max-min, 1e-8) / 15),
       code = clip(round_half_even(fl(fl(x-min)/scale)), 0, 15).
+
+    ``dc_mask`` (D,) bool, asymmetric NF4 only: the "sparse" zero-point (:337-342) keeps the
+    mean on the masked channels and uses 0 elsewhere.
     """
     if mode not in KEY_MODES:
         raise ValueError(f"unknown key mode {mode!r}")
@@ -225,6 +239,8 @@ def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym"
                 "out_val": out_val, "mode": mode}
     if mode == "nf4_asym":
         mean = (_seq_sum_axis(x, 1) / F32(s)).astype(F32)
+        if dc_mask is not None:
+            mean = (mean * np.asarray(dc_mask, dtype=bool)[None, :]).astype(F32)
         xc = (x - mean[:, None, :]).astype(F32)
         amax = np.maximum(np.abs(xc).max(axis=1), F32(1e-8)).astype(F32)
         # level l of channel (h, d): fl(mean + fl(amax * NF4[l]))
@@ -454,10 +470,12 @@ class OracleCache:
     """
 
     def __init__(self, head_dim=128, n_heads=32, key_bits=4, value_bits=4, hot_window=512,
-                 outlier_frac=0.02, seed=None, key_mode="nf4_asym"):
+                 outlier_frac=0.02, seed=None, key_mode="nf4_asym", rope_theta=None):
         if key_bits != 4:
             raise ValueError("the per-channel key formats restated here are 4-bit")
         self.key_mode = key_mode
+        # rope_theta selects the "sparse" zero-point: means only on long-wavelength channels
+        self.rope_theta = rope_theta
         self.head_dim, self.n_heads = head_dim, n_heads
         self.key_bits, self.value_bits = key_bits, value_bits
         self.hot_window, self.outlier_frac = hot_window, outlier_frac
@@ -469,6 +487,13 @@ class OracleCache:
         self.cold_v: list[dict] = []
         self.cold_lengths: list[int] = []
         self.length = 0
+
+    def _dc_mask(self, n_tokens: int):
+        """The sparse zero-point's channel mask for a block of ``n_tokens`` (the window the
+        wavelengths are compared with is the block itself), or None."""
+        if self.rope_theta is None:
+            return None
+        return dc_channel_mask(self.rope_theta, self.head_dim, n_tokens)
 
     @property
     def cold_length(self):
@@ -492,7 +517,7 @@ class OracleCache:
             return
         kb = np.stack(self.hot_k[:n], axis=1)  # (H, n, D)
         vb = np.stack(self.hot_v[:n], axis=1)
-        self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode))
+        self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode, self._dc_mask(n)))
         self.cold_v.append(encode_values(vb, self.pi_t, self.boundaries))
         self.cold_lengths.append(n)
         del self.hot_k[:n]
@@ -528,7 +553,9 @@ class OracleCache:
         cold = 0
         for kb, vb, n in zip(self.cold_k, self.cold_v, self.cold_lengths):
             # per-channel float32 scalars: scale + mean (symmetric NF4 stores no mean)
-            cold += h * n * d * self.key_bits // 8 + (1 if self.key_mode == "nf4" else 2) * 4 * h * d
+            n_mean = d if self.rope_theta is None else int(self._dc_mask(n).sum())
+            cold += (h * n * d * self.key_bits // 8 + 4 * h * d
+                     + (0 if self.key_mode == "nf4" else 4 * h * n_mean))
             if kb["out_idx"] is not None:
                 cold += kb["out_idx"].size * 6
             cold += (h * n * d * self.value_bits + 7) // 8 + 4 * h * n

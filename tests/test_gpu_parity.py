@@ -372,7 +372,10 @@ def test_facade_matches_reference_api(torch_cuda):
         TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nuq=True)
     with pytest.raises(NotImplementedError):
         TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4_asym=True,
-                          key_zero_point="sparse", key_rope_theta=1e4)
+                          key_zero_point="bias", key_rope_theta=1e4, key_k_bias=np.zeros(256))
+    sp = TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4_asym=True, max_tokens=64,
+                           key_zero_point="sparse", key_rope_theta=1e4)
+    assert int(sp.context.key_mean_mask.sum()) == 76  # wavelengths beyond a 256-token block
 
 
 def test_abi_error_codes(torch_cuda):
@@ -458,7 +461,8 @@ def test_other_key_grids_encoder_bit_exact(torch_cuda, name, mode, frac):
 
 
 @pytest.mark.parametrize("name,mode,vb", [("cache_uniform.npz", "uniform", 4),
-                                          ("cache_nf4_gqa.npz", "nf4", 3)])
+                                          ("cache_nf4_gqa.npz", "nf4", 3),
+                                          ("cache_sparse_zp.npz", "nf4_asym", 3)])
 def test_other_key_grids_cache_and_decode(torch_cuda, name, mode, vb):
     """Caches in the other key grids: every cold container equals the reference's and the
     decode on codes (both kernels) matches its dequantise-then-attend output."""
@@ -468,7 +472,8 @@ def test_other_key_grids_cache_and_decode(torch_cuda, name, mode, vb):
     h, hq = k.shape[1], q.shape[0]
     ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=hq, value_bits=vb,
                hot_window=int(g["hot_window"]), max_tokens_per_seq=1024,
-               kv_dtype=_np_dtype_name(k), key_mode=mode, seed=int(g["seed"]), pi=g["pi"])
+               kv_dtype=_np_dtype_name(k), key_mode=mode, seed=int(g["seed"]), pi=g["pi"],
+               key_mean_mask=g["dc_mask"] if "dc_mask" in g else None)
     ctx.append(0, _dev(torch, k)[None], _dev(torch, v)[None])
     assert ctx.lengths(0, 0)[0] == int(g["length"])
     for i in range(int(g["n_blocks"])):

@@ -12,6 +12,8 @@ from __future__ import annotations
 import logging
 from dataclasses import dataclass
 
+import numpy as np
+
 logger = logging.getLogger(__name__)
 
 # (head_dim, query heads, KV heads, layers, rope theta, max positions) of the models the
@@ -54,6 +56,17 @@ def _registry_dict(name: str) -> dict:
     hd, nq, nkv, nl, theta, maxpos = _MODELS[name]
     return dict(head_dim=hd, num_attention_heads=nq, num_key_value_heads=nkv,
                 num_hidden_layers=nl, rope_theta=theta, max_position_embeddings=maxpos)
+
+
+def rope_long_wavelength_mask(rope_theta: float, head_dim: int, window: int) -> np.ndarray:
+    """``(head_dim,)`` booleans: the channels whose rotary wavelength is longer than ``window``
+    tokens, i.e. those that carry the keys' DC offset over a block of that length
+    (``per_channel_kv.py:233-241``).  In the rotate-half layout channel ``d`` turns with
+    angular frequency ``theta ** (-2 (d mod D/2) / D)``."""
+    half = head_dim // 2
+    inv_freq = rope_theta ** (-2.0 * np.arange(half) / head_dim)
+    wavelength = 2.0 * np.pi / inv_freq
+    return np.tile(wavelength, 2)[:head_dim] > float(window)
 
 
 @dataclass

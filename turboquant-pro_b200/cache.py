@@ -9,8 +9,9 @@ device raises.
 Supported formats: per-channel 4-bit keys in the three grids the reference has an affine
 (fused) form for — asymmetric NF4 (``key_nf4_asym=True``, ``key_zero_point="calibrated"``),
 symmetric NF4 (``key_nf4=True``) and uniform (neither flag) — with an optional fp16 outlier
-side-list, PolarQuant values at 3 or 4 bits.  Data-fit tables (``key_nuq``), the ``sparse``
-and ``bias`` zero-points and other key widths raise ``NotImplementedError``.
+side-list, PolarQuant values at 3 or 4 bits; asymmetric NF4 also with the ``sparse``
+zero-point.  Data-fit tables (``key_nuq``), the ``bias`` zero-point and other key widths
+raise ``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -76,8 +77,11 @@ class TurboQuantKVCache:
         if key_zero_point != "calibrated":
             if not key_nf4_asym:
                 raise ValueError(f"zero_point={key_zero_point!r} requires nf4_asym=True")
-            raise NotImplementedError("key_zero_point 'sparse' and 'bias' are not implemented "
-                                      "on the CUDA path")
+            if key_rope_theta is None:
+                raise ValueError(f"zero_point={key_zero_point!r} requires rope_theta")
+            if key_zero_point == "bias":
+                raise NotImplementedError("key_zero_point='bias' is not implemented on the "
+                                          "CUDA path")
         if (key_nf4 or key_nf4_asym) and self.key_bits != 4:
             raise ValueError("nf4=True requires bits=4")
         if self.key_bits != 4:
@@ -88,6 +92,13 @@ class TurboQuantKVCache:
             head_dim=head_dim, key_bits=self.key_bits, value_bits=self.value_bits,
             hot_window=hot_window, outlier_frac=key_outlier_frac, max_tokens_per_seq=max_tokens,
             kv_dtype=dtype, seed=seed, device=device_id, key_mode=self.key_mode)
+        self.key_zero_point = key_zero_point
+        if key_zero_point == "sparse":
+            # means only on the channels that stay put over a block (per_channel_kv.py:337-342)
+            from .autoconfig import rope_long_wavelength_mask
+
+            self._ctx.set_key_mean_mask(rope_long_wavelength_mask(
+                key_rope_theta, head_dim, self._ctx.block_tokens))
         self.key_outlier_frac = key_outlier_frac
 
     # ------------------------------------------------------------------ properties --

@@ -84,6 +84,8 @@ class KVContext:
         key_bits: 4.  value_bits: 3 or 4 (PolarQuant values).
         key_mode: per-channel key grid, ``"nf4_asym"`` (default), ``"nf4"`` (symmetric) or
             ``"uniform"`` (``per_channel_kv.py:285-401``).
+        key_mean_mask: ``(head_dim,)`` booleans, asymmetric NF4 only: the channels that keep
+            their mean as zero-point (the reference's ``zero_point="sparse"``); default all.
         hot_window: tokens kept uncompressed (2..512); a flush moves the oldest
             ``(hot_window + 1) // 2`` tokens into one cold block.
         outlier_frac: per-channel fraction of fp16 outliers kept beside the key codes.
@@ -96,7 +98,7 @@ class KVContext:
     def __init__(self, n_layers=1, n_seqs=1, n_kv_heads=8, n_q_heads=None, head_dim=128,
                  key_bits=4, value_bits=3, hot_window=512, outlier_frac=0.02,
                  max_tokens_per_seq=8192, kv_dtype="float32", seed=None, pi=None, device=0,
-                 key_mode="nf4_asym"):
+                 key_mode="nf4_asym", key_mean_mask=None):
         torch = _torch()
         if not torch.cuda.is_available():
             raise RuntimeError("KVContext needs a CUDA device: this package has no CPU fallback")
@@ -140,6 +142,9 @@ class KVContext:
                 self.centroids.ctypes.data, self.boundaries.ctypes.data,
                 self._stream(), C.byref(handle)))
         self._h = handle
+        self.key_mean_mask = None
+        if key_mean_mask is not None:
+            self.set_key_mean_mask(key_mean_mask)
 
     # -- plumbing --------------------------------------------------------------------
     def _stream(self):
@@ -354,6 +359,19 @@ class KVContext:
 
     def last_launches(self) -> int:
         return int(self._lib.tq_last_launches(self._h))
+
+    def set_key_mean_mask(self, mask) -> None:
+        """Channels whose mean is kept as the key zero-point (``None``: all).  Applies to the
+        blocks encoded from now on."""
+        m = None
+        if mask is not None:
+            m = np.ascontiguousarray(np.asarray(mask).astype(bool).astype(np.uint8))
+            if m.shape != (self.geom.head_dim,):
+                raise ValueError(f"expected a mask of {self.geom.head_dim} channels")
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_set_key_mean_mask(self._h, m.ctypes.data if m is not None else None,
+                                                 self._stream()))
+        self.key_mean_mask = None if m is None else m.astype(bool)
 
     def set_kernel(self, which: str = "auto") -> None:
         """``"auto"``: tensor-core kernel where the geometry allows; ``"general"``: always the

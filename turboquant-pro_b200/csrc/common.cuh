@@ -89,6 +89,7 @@ struct Tables {
   float centroids[16];
   float boundaries[16];
   float grid[16];  // key levels: NF4, or 0..15 for uniform keys
+  uint8_t mean_mask[TQ_D];  // asymmetric NF4: channels that keep their mean (default all)
 };
 
 struct tq_ctx {
@@ -110,6 +111,7 @@ struct tq_ctx {
   // tensor maps (opaque 128-byte driver objects) of the two hot rings as 2-D arrays
   // [ring rows][128] of 16-bit elements, for the decode kernel's swizzled tile copies;
   // state 0: not built yet, 1: ready, -1: not available (float32 rings, or no driver entry)
+  int mean_channels = TQ_D;  // channels with a stored mean, for the byte accounting
   alignas(64) unsigned char tmap_hot[2][128];
   int tmap_state = 0;
 };

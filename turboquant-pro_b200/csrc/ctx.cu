@@ -166,6 +166,7 @@ int32_t tq_ctx_create(const tq_geom* g, const tq_buffers* bufs, int32_t device, 
                                 0.7229568362236023f,
                                 1.0f};
   for (int i = 0; i < 16; ++i) t->grid[i] = g->key_mode == TQ_KEYS_UNIFORM ? (float)i : nf4[i];
+  std::memset(t->mean_mask, 1, sizeof(t->mean_mask));
   cudaError_t e = cudaMemcpyAsync(bufs->tables, t, sizeof(Tables), cudaMemcpyHostToDevice, st);
   // The hot rings start zeroed: the decode kernel multiplies ring rows past the end of a
   // window by probability 0, which needs them finite.
@@ -196,6 +197,25 @@ int32_t tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx != nullptr)
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
   delete ctx;
+  return TQ_OK;
+}
+
+int32_t tq_set_key_mean_mask(tq_ctx* ctx, const uint8_t* mask, void* stream) {
+  TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
+  TQ_REQUIRE(ctx->g.key_mode == TQ_KEYS_NF4_ASYM, TQ_ERR_INVALID,
+             "a mean mask applies to asymmetric NF4 keys only");
+  uint8_t m[TQ_D];
+  int n = 0;
+  for (int d = 0; d < TQ_D; ++d) {
+    m[d] = (mask == nullptr || mask[d] != 0) ? 1 : 0;
+    n += m[d];
+  }
+  TQ_CUDA(cudaSetDevice(ctx->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  TQ_CUDA(cudaMemcpyAsync((uint8_t*)ctx->b.tables + offsetof(Tables, mean_mask), m, TQ_D,
+                          cudaMemcpyHostToDevice, st));
+  TQ_CUDA(cudaStreamSynchronize(st));  // `m` lives on this stack frame
+  ctx->mean_channels = n;
   return TQ_OK;
 }
 
@@ -449,7 +469,8 @@ int32_t tq_memory_stats(tq_ctx* ctx, int32_t layer, int32_t seq, double* cold_by
       for (int h = 0; h < H; ++h) n_out += meta[(size_t)h * g.max_blocks + b].cnt;
       // symmetric NF4 containers hold no mean
       cold += (double)H * S * D * g.key_bits / 8 +
-              (g.key_mode == TQ_KEYS_NF4 ? 1.0 : 2.0) * 4 * H * D + 6.0 * n_out;
+              4.0 * H * D + (g.key_mode == TQ_KEYS_NF4 ? 0.0 : 4.0 * H * ctx->mean_channels) +
+              6.0 * n_out;
       cold += (double)H * S * D * g.value_bits / 8 + 4.0 * H * S;
     }
   }
@@ -489,7 +510,8 @@ int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes) {
   // reference container bytes of one cold block of one KV head, with the nominal
   // outlier count (ties add a few entries that are not counted)
   double blk = (double)S * D * g.key_bits / 8 + (double)S * D * g.value_bits / 8 + 4.0 * S +
-               (g.key_mode == TQ_KEYS_NF4 ? 4.0 : 8.0) * D + 6.0 * g.outlier_k * D;
+               4.0 * D + (g.key_mode == TQ_KEYS_NF4 ? 0.0 : 4.0 * ctx->mean_channels) +
+               6.0 * g.outlier_k * D;
   double total = 0.0;
   for (int s = 0; s < g.n_seqs; ++s) {
     int n = ctx->len[(size_t)layer * g.n_seqs + s];

@@ -128,9 +128,11 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
       }
     }
   }
-  const float mu = mode == TQ_KEYS_NF4_ASYM ? __fdiv_rn(acc, (float)S)
-                   : mode == TQ_KEYS_NF4    ? 0.0f
-                                            : xmin;
+  // (the "sparse" zero-point keeps the mean on the masked channels only)
+  const float mu = mode == TQ_KEYS_NF4_ASYM
+                       ? (a.tables->mean_mask[d] ? __fdiv_rn(acc, (float)S) : 0.0f)
+                   : mode == TQ_KEYS_NF4 ? 0.0f
+                                         : xmin;
   const float kth = (kk >= S) ? -1.0f : top[0];
 
   // pass 2: scale, and how many outliers this channel keeps
