@@ -249,6 +249,16 @@ int32_t tq_decode_static_scratch(tq_ctx* ctx, int32_t layer, const void* q, int3
  * encoded keep the zero-points they were encoded with.  TQ_KEYS_NF4_ASYM only. */
 int32_t tq_set_key_mean_mask(tq_ctx* ctx, const uint8_t* mask, void* stream);
 
+/* The "bias" zero-point of asymmetric NF4 keys (per_channel_kv.py:327-336, :506-516): the
+ * zero-point of a block is not measured but given — the reference derives it from the
+ * model's key-projection bias rotated and averaged over the block's positions
+ * (rope_averaged_bias at :243-267), so it depends only on the KV head and on where the block
+ * starts.  `means` is host memory [max_blocks][n_kv_heads][head_dim] float32, entry b for the
+ * block that starts at token b * block_tokens; it is copied into the tables region.  A null
+ * pointer goes back to measured means.  Set it before the first append.  TQ_KEYS_NF4_ASYM
+ * only; the byte accounting then counts no stored mean, like the reference. */
+int32_t tq_set_key_bias_means(tq_ctx* ctx, const float* means, void* stream);
+
 /* Selects the decode kernel: 0 = automatic (the tensor-core kernel where the geometry
  * allows: 256-token blocks, GQA group 1/2/4/8; else the general-shape kernel), 1 = always
  * the general-shape float32 kernel.  Both compute the same function; tests compare them.

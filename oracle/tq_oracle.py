@@ -206,8 +206,25 @@ def dc_channel_mask(rope_theta: float, head_dim: int, window: int) -> np.ndarray
     return np.tile(wavelength, 2)[:head_dim] > float(window)
 
 
+def rope_averaged_bias(k_bias, rope_theta: float, head_dim: int, start: int, n: int):
+    """The "bias" zero-point (per_channel_kv.py:243-267): the key-projection bias ``(H, D)``
+    rotated by RoPE and averaged over positions ``[start, start + n)``.  The means of cos and
+    sin are taken in float64 and rounded to float32; the rotation itself
+    (b*cos + rotate_half(b)*sin) is float32."""
+    half = head_dim // 2
+    inv_freq = rope_theta ** (-2.0 * np.arange(half, dtype=np.float64) / head_dim)
+    angle = np.arange(start, start + n, dtype=np.float64)[:, None] * inv_freq[None, :]
+    mean_cos = np.cos(angle).mean(axis=0)
+    mean_sin = np.sin(angle).mean(axis=0)
+    cos_full = np.concatenate([mean_cos, mean_cos]).astype(F32)
+    sin_full = np.concatenate([mean_sin, mean_sin]).astype(F32)
+    b = np.asarray(k_bias, dtype=F32).reshape(-1, head_dim)
+    rotated_half = np.concatenate([-b[:, half:], b[:, :half]], axis=1)
+    return b * cos_full[None, :] + rotated_half * sin_full[None, :]
+
+
 def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym",
-                dc_mask: np.ndarray | None = None):
+                dc_mask: np.ndarray | None = None, given_mean: np.ndarray | None = None):
     """Per-channel 4-bit key block encoder (per_channel_kv.py:285-401).
 
     ``x`` (H, S, D) any float dtype.  Returns a dict with unpacked ``codes`` (H,S,D)
@@ -222,7 +239,8 @@ def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym"
       code = clip(round_half_even(fl(fl(x-min)/scale)), 0, 15).
 
     ``dc_mask`` (D,) bool, asymmetric NF4 only: the "sparse" zero-point (:337-342) keeps the
-    mean on the masked channels and uses 0 elsewhere.
+    mean on the masked channels and uses 0 elsewhere.  ``given_mean`` (H, D), asymmetric NF4
+    only: the "bias" zero-point (:327-336) uses it instead of the measured mean.
     """
     if mode not in KEY_MODES:
         raise ValueError(f"unknown key mode {mode!r}")
@@ -239,6 +257,8 @@ def encode_keys(x: np.ndarray, outlier_frac: float = 0.0, mode: str = "nf4_asym"
                 "out_val": out_val, "mode": mode}
     if mode == "nf4_asym":
         mean = (_seq_sum_axis(x, 1) / F32(s)).astype(F32)
+        if given_mean is not None:
+            mean = np.asarray(given_mean, dtype=F32)
         if dc_mask is not None:
             mean = (mean * np.asarray(dc_mask, dtype=bool)[None, :]).astype(F32)
         xc = (x - mean[:, None, :]).astype(F32)
@@ -470,12 +490,15 @@ class OracleCache:
     """
 
     def __init__(self, head_dim=128, n_heads=32, key_bits=4, value_bits=4, hot_window=512,
-                 outlier_frac=0.02, seed=None, key_mode="nf4_asym", rope_theta=None):
+                 outlier_frac=0.02, seed=None, key_mode="nf4_asym", rope_theta=None,
+                 k_bias=None):
         if key_bits != 4:
             raise ValueError("the per-channel key formats restated here are 4-bit")
         self.key_mode = key_mode
-        # rope_theta selects the "sparse" zero-point: means only on long-wavelength channels
+        # rope_theta alone selects the "sparse" zero-point (means only on long-wavelength
+        # channels); with k_bias it selects the "bias" zero-point (no measured mean at all)
         self.rope_theta = rope_theta
+        self.k_bias = None if k_bias is None else np.asarray(k_bias, F32).reshape(n_heads, head_dim)
         self.head_dim, self.n_heads = head_dim, n_heads
         self.key_bits, self.value_bits = key_bits, value_bits
         self.hot_window, self.outlier_frac = hot_window, outlier_frac
@@ -491,7 +514,7 @@ class OracleCache:
     def _dc_mask(self, n_tokens: int):
         """The sparse zero-point's channel mask for a block of ``n_tokens`` (the window the
         wavelengths are compared with is the block itself), or None."""
-        if self.rope_theta is None:
+        if self.rope_theta is None or self.k_bias is not None:
             return None
         return dc_channel_mask(self.rope_theta, self.head_dim, n_tokens)
 
@@ -517,7 +540,12 @@ class OracleCache:
             return
         kb = np.stack(self.hot_k[:n], axis=1)  # (H, n, D)
         vb = np.stack(self.hot_v[:n], axis=1)
-        self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode, self._dc_mask(n)))
+        given = None
+        if self.k_bias is not None:
+            given = rope_averaged_bias(self.k_bias, self.rope_theta, self.head_dim,
+                                       sum(self.cold_lengths), n)
+        self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode, self._dc_mask(n),
+                                       given))
         self.cold_v.append(encode_values(vb, self.pi_t, self.boundaries))
         self.cold_lengths.append(n)
         del self.hot_k[:n]
@@ -553,7 +581,8 @@ class OracleCache:
         cold = 0
         for kb, vb, n in zip(self.cold_k, self.cold_v, self.cold_lengths):
             # per-channel float32 scalars: scale + mean (symmetric NF4 stores no mean)
-            n_mean = d if self.rope_theta is None else int(self._dc_mask(n).sum())
+            n_mean = (0 if self.k_bias is not None else
+                      d if self.rope_theta is None else int(self._dc_mask(n).sum()))
             cold += (h * n * d * self.key_bits // 8 + 4 * h * d
                      + (0 if self.key_mode == "nf4" else 4 * h * n_mean))
             if kb["out_idx"] is not None:

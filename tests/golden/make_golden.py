@@ -114,7 +114,7 @@ def key_block_case(name, seed, h, s, mode, frac, round_to=None, dtype=np.float32
 
 
 def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype=np.float32,
-               with_fused=False, key_mode="nf4_asym", sparse_theta=None):
+               with_fused=False, key_mode="nf4_asym", sparse_theta=None, bias_theta=None):
     """A cache filled token by token; stores every cold container and the
     dequantise-then-attend output (plus ``fused_decode`` where the reference has it)."""
     rng = np.random.default_rng(seed)
@@ -122,11 +122,16 @@ def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype
     k = k.astype(dtype)
     v = v.astype(dtype)
     q = rng.standard_normal((n_q_heads, D)).astype(np.float32)
+    k_bias = None
+    if bias_theta is not None:  # a key-projection bias, and keys that carry it
+        k_bias = (3.0 * rng.standard_normal((h, D))).astype(np.float32)
+        k = (k.astype(np.float32) + k_bias[None]).astype(dtype)
     cache = TurboQuantKVCache(
         head_dim=D, n_heads=h, bits=value_bits, key_bits=4, value_bits=value_bits,
         hot_window=hot_window, use_gpu=False, seed=seed, key_outlier_frac=0.02,
-        key_zero_point="calibrated" if sparse_theta is None else "sparse",
-        key_rope_theta=sparse_theta, **_KEY_MODE_FLAGS[key_mode],
+        key_zero_point="bias" if bias_theta else ("sparse" if sparse_theta else "calibrated"),
+        key_rope_theta=bias_theta or sparse_theta, key_k_bias=k_bias,
+        **_KEY_MODE_FLAGS[key_mode],
     )
     for t in range(n_tokens):
         cache.append(k[t], v[t])
@@ -146,7 +151,13 @@ def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype
                                     st["uncompressed_equivalent_bytes"]], dtype=np.float64)
     for i, (ck, cv) in enumerate(zip(cache._cold_keys, cache._cold_values)):
         out[f"b{i}_key_indices"] = ck.indices
-        out[f"b{i}_nf4_scale"], out[f"b{i}_nf4_mean"] = _key_fields(ck)
+        if bias_theta is not None:  # nothing stored: the zero-point is recomputed from k_bias
+            out[f"b{i}_nf4_scale"] = ck.nf4_scale
+            out[f"b{i}_nf4_mean"] = cache._kq.rope_averaged_bias(
+                k_bias, bias_theta, D, ck.position_start, cache._cold_lengths[i])[None]
+            out["k_bias"] = k_bias
+        else:
+            out[f"b{i}_nf4_scale"], out[f"b{i}_nf4_mean"] = _key_fields(ck)
         if sparse_theta is not None:  # compact (1, H, n_dc) means -> full width, zeros elsewhere
             dc = PerChannelKV.dc_channel_mask(sparse_theta, D, cache._cold_lengths[i])
             full = np.zeros_like(ck.nf4_scale)
@@ -209,6 +220,8 @@ def other_key_grids():
                n_q_heads=8, dtype=np.float16, key_mode="nf4")
     cache_case("cache_sparse_zp.npz", seed=36, h=2, n_tokens=700, hot_window=512, value_bits=3,
                n_q_heads=4, dtype=np.float16, sparse_theta=10000.0)
+    cache_case("cache_bias_zp.npz", seed=37, h=2, n_tokens=1100, hot_window=512, value_bits=3,
+               n_q_heads=4, dtype=np.float16, bias_theta=10000.0)
 
 
 if __name__ == "__main__":

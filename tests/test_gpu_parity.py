@@ -370,9 +370,11 @@ def test_facade_matches_reference_api(torch_cuda):
         TurboQuantKVCache(head_dim=128, n_heads=2, bits=3)  # 3-bit uniform keys
     with pytest.raises(NotImplementedError):
         TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nuq=True)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):
         TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4_asym=True,
-                          key_zero_point="bias", key_rope_theta=1e4, key_k_bias=np.zeros(256))
+                          key_zero_point="bias", key_rope_theta=1e4)  # no k_bias
+    TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4_asym=True, max_tokens=64,
+                      key_zero_point="bias", key_rope_theta=1e4, key_k_bias=np.ones(256))
     sp = TurboQuantKVCache(head_dim=128, n_heads=2, bits=4, key_nf4_asym=True, max_tokens=64,
                            key_zero_point="sparse", key_rope_theta=1e4)
     assert int(sp.context.key_mean_mask.sum()) == 76  # wavelengths beyond a 256-token block
@@ -462,7 +464,8 @@ def test_other_key_grids_encoder_bit_exact(torch_cuda, name, mode, frac):
 
 @pytest.mark.parametrize("name,mode,vb", [("cache_uniform.npz", "uniform", 4),
                                           ("cache_nf4_gqa.npz", "nf4", 3),
-                                          ("cache_sparse_zp.npz", "nf4_asym", 3)])
+                                          ("cache_sparse_zp.npz", "nf4_asym", 3),
+                                          ("cache_bias_zp.npz", "nf4_asym", 3)])
 def test_other_key_grids_cache_and_decode(torch_cuda, name, mode, vb):
     """Caches in the other key grids: every cold container equals the reference's and the
     decode on codes (both kernels) matches its dequantise-then-attend output."""
@@ -471,9 +474,15 @@ def test_other_key_grids_cache_and_decode(torch_cuda, name, mode, vb):
     k, v, q = g["k"], g["v"], g["q"]
     h, hq = k.shape[1], q.shape[0]
     ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=hq, value_bits=vb,
-               hot_window=int(g["hot_window"]), max_tokens_per_seq=1024,
+               hot_window=int(g["hot_window"]), max_tokens_per_seq=1280,
                kv_dtype=_np_dtype_name(k), key_mode=mode, seed=int(g["seed"]), pi=g["pi"],
                key_mean_mask=g["dc_mask"] if "dc_mask" in g else None)
+    if "k_bias" in g:  # the "bias" zero-point: one given mean per block index
+        from turboquant_pro_b200.autoconfig import rope_averaged_bias
+
+        f = ctx.block_tokens
+        ctx.set_key_bias_means(np.stack([rope_averaged_bias(g["k_bias"], 10000.0, 128, b * f, f)
+                                         for b in range(ctx.geom.max_blocks)]))
     ctx.append(0, _dev(torch, k)[None], _dev(torch, v)[None])
     assert ctx.lengths(0, 0)[0] == int(g["length"])
     for i in range(int(g["n_blocks"])):

@@ -105,7 +105,8 @@ def test_other_key_grids_bit_exact(name, mode, frac):
                                           ("cache_w7.npz", 3, "nf4_asym"),
                                           ("cache_uniform.npz", 4, "uniform"),
                                           ("cache_nf4_gqa.npz", 3, "nf4"),
-                                          ("cache_sparse_zp.npz", 3, "nf4_asym")])
+                                          ("cache_sparse_zp.npz", 3, "nf4_asym"),
+                                          ("cache_bias_zp.npz", 3, "nf4_asym")])
 def test_cache_matches_reference(name, vb, mode):
     g = load_golden(name)
     k, v, q = g["k"], g["v"], g["q"]
@@ -113,7 +114,8 @@ def test_cache_matches_reference(name, vb, mode):
     cache = orc.OracleCache(head_dim=128, n_heads=h, key_bits=4, value_bits=vb,
                             hot_window=int(g["hot_window"]), outlier_frac=0.02,
                             seed=int(g["seed"]), key_mode=mode,
-                            rope_theta=10000.0 if "sparse" in name else None)
+                            rope_theta=10000.0 if "_zp" in name else None,
+                            k_bias=g["k_bias"] if "k_bias" in g else None)
     cache.pi, cache.pi_t = g["pi"], np.ascontiguousarray(g["pi"].T)
     for t in range(k.shape[0]):
         cache.append(k[t], v[t])

@@ -89,6 +89,7 @@ SIGNATURES = {
     "tq_last_launches": (C.c_int32, [C.c_void_p]),
     "tq_set_kernel": (C.c_int32, [C.c_void_p, C.c_int32]),
     "tq_set_key_mean_mask": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tq_set_key_bias_means": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "tq_debug_trace": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "tq_profile_enable": (C.c_int32, [C.c_void_p, C.c_int32]),
     "tq_profile_read": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double),

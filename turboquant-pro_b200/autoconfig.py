@@ -69,6 +69,22 @@ def rope_long_wavelength_mask(rope_theta: float, head_dim: int, window: int) -> 
     return np.tile(wavelength, 2)[:head_dim] > float(window)
 
 
+def rope_averaged_bias(k_bias, rope_theta: float, head_dim: int, start: int, n: int) -> np.ndarray:
+    """``(n_heads, head_dim)`` float32: the key-projection bias seen through RoPE, averaged
+    over the positions ``[start, start + n)`` of a block — the zero-point of the reference's
+    ``zero_point="bias"`` mode (``per_channel_kv.py:243-267``).  cos and sin are averaged in
+    float64 and rounded to float32; rotate-half layout."""
+    half = head_dim // 2
+    inv_freq = rope_theta ** (-2.0 * np.arange(half, dtype=np.float64) / head_dim)
+    angle = np.arange(start, start + n, dtype=np.float64)[:, None] * inv_freq[None, :]
+    cos_mean, sin_mean = np.cos(angle).mean(axis=0), np.sin(angle).mean(axis=0)
+    cos_full = np.concatenate([cos_mean, cos_mean]).astype(np.float32)
+    sin_full = np.concatenate([sin_mean, sin_mean]).astype(np.float32)
+    b = np.asarray(k_bias, dtype=np.float32).reshape(-1, head_dim)
+    turned = np.concatenate([-b[:, half:], b[:, :half]], axis=1)
+    return b * cos_full[None, :] + turned * sin_full[None, :]
+
+
 @dataclass
 class AutoConfig:
     """Model geometry + compression target; ``build_*`` produce configured caches."""
@@ -157,9 +173,7 @@ class AutoConfig:
 
         This package is GPU-only, so the cache lives on the GPU whatever ``use_gpu`` says
         (the keyword is kept so existing call sites work).  ``robust=False`` gives the bare
-        uniform 4-bit key grid without outliers, as in the reference; the ``"bias"`` and
-        ``"sparse"`` zero-points are not implemented on the CUDA path and raise
-        ``NotImplementedError``.
+        uniform 4-bit key grid without outliers, as in the reference.
         """
         from .cache import TurboQuantKVCache
 

@@ -9,9 +9,9 @@ device raises.
 Supported formats: per-channel 4-bit keys in the three grids the reference has an affine
 (fused) form for — asymmetric NF4 (``key_nf4_asym=True``, ``key_zero_point="calibrated"``),
 symmetric NF4 (``key_nf4=True``) and uniform (neither flag) — with an optional fp16 outlier
-side-list, PolarQuant values at 3 or 4 bits; asymmetric NF4 also with the ``sparse``
-zero-point.  Data-fit tables (``key_nuq``), the ``bias`` zero-point and other key widths
-raise ``NotImplementedError``.
+side-list, PolarQuant values at 3 or 4 bits; asymmetric NF4 also with the ``sparse`` and
+``bias`` zero-points.  Data-fit tables (``key_nuq``) and other key widths raise
+``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -79,9 +79,8 @@ class TurboQuantKVCache:
                 raise ValueError(f"zero_point={key_zero_point!r} requires nf4_asym=True")
             if key_rope_theta is None:
                 raise ValueError(f"zero_point={key_zero_point!r} requires rope_theta")
-            if key_zero_point == "bias":
-                raise NotImplementedError("key_zero_point='bias' is not implemented on the "
-                                          "CUDA path")
+            if key_zero_point == "bias" and key_k_bias is None:
+                raise ValueError('zero_point="bias" requires k_bias')
         if (key_nf4 or key_nf4_asym) and self.key_bits != 4:
             raise ValueError("nf4=True requires bits=4")
         if self.key_bits != 4:
@@ -99,6 +98,15 @@ class TurboQuantKVCache:
 
             self._ctx.set_key_mean_mask(rope_long_wavelength_mask(
                 key_rope_theta, head_dim, self._ctx.block_tokens))
+        elif key_zero_point == "bias":
+            # zero-point of block b = the k-projection bias under RoPE, averaged over the
+            # block's positions (per_channel_kv.py:327-336): known in advance for every block
+            from .autoconfig import rope_averaged_bias
+
+            f, nb = self._ctx.block_tokens, self._ctx.geom.max_blocks
+            kb = np.asarray(key_k_bias, dtype=np.float32).reshape(n_heads, head_dim)
+            self._ctx.set_key_bias_means(np.stack(
+                [rope_averaged_bias(kb, key_rope_theta, head_dim, b * f, f) for b in range(nb)]))
         self.key_outlier_frac = key_outlier_frac
 
     # ------------------------------------------------------------------ properties --

@@ -373,6 +373,22 @@ class KVContext:
                                                  self._stream()))
         self.key_mean_mask = None if m is None else m.astype(bool)
 
+    def set_key_bias_means(self, means) -> None:
+        """Given key zero-points, one ``(n_kv_heads, head_dim)`` row per cold block index
+        (``[max_blocks, n_kv_heads, head_dim]`` float32; ``None`` goes back to measured
+        means): the reference's ``zero_point="bias"``.  Applies to blocks encoded from now
+        on."""
+        g = self.geom
+        m = None
+        if means is not None:
+            m = np.ascontiguousarray(means, dtype=np.float32)
+            if m.shape != (g.max_blocks, g.n_kv_heads, g.head_dim):
+                raise ValueError(f"expected means of shape "
+                                 f"{(g.max_blocks, g.n_kv_heads, g.head_dim)}, got {m.shape}")
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_set_key_bias_means(
+                self._h, m.ctypes.data if m is not None else None, self._stream()))
+
     def set_kernel(self, which: str = "auto") -> None:
         """``"auto"``: tensor-core kernel where the geometry allows; ``"general"``: always the
         general-shape float32 kernel."""

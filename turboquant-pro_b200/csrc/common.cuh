@@ -112,6 +112,7 @@ struct tq_ctx {
   // [ring rows][128] of 16-bit elements, for the decode kernel's swizzled tile copies;
   // state 0: not built yet, 1: ready, -1: not available (float32 rings, or no driver entry)
   int mean_channels = TQ_D;  // channels with a stored mean, for the byte accounting
+  bool bias_means = false;   // key zero-points come from the table behind the Tables struct
   alignas(64) unsigned char tmap_hot[2][128];
   int tmap_state = 0;
 };

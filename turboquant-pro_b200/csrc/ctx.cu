@@ -109,7 +109,9 @@ int32_t tq_ctx_sizes(const tq_geom* g, tq_sizes* out) {
   out->pool_val = align_up(std::max<size_t>(units * (size_t)g->pool_entries * 2, 256), 256);
   out->page_meta = align_up(units * g->max_blocks * sizeof(PageMeta), 256);
   out->state = align_up(state_bytes(*g), 256);
-  out->tables = align_up(sizeof(Tables), 256);
+  // the Tables struct, then room for given key zero-points [max_blocks][H][D] (float32)
+  out->tables = align_up(sizeof(Tables), 256) +
+                align_up((size_t)g->max_blocks * g->n_kv_heads * TQ_D * sizeof(float), 256);
   size_t layer_units = (size_t)g->n_seqs * g->n_kv_heads;
   size_t generic = layer_units * g->max_splits * g->group * TQ_PART_STRIDE * sizeof(float);
   out->scratch = align_up(std::max(generic, tq_mma_scratch_bytes(*g, layer_units)), 256);
@@ -216,6 +218,25 @@ int32_t tq_set_key_mean_mask(tq_ctx* ctx, const uint8_t* mask, void* stream) {
                           cudaMemcpyHostToDevice, st));
   TQ_CUDA(cudaStreamSynchronize(st));  // `m` lives on this stack frame
   ctx->mean_channels = n;
+  return TQ_OK;
+}
+
+int32_t tq_set_key_bias_means(tq_ctx* ctx, const float* means, void* stream) {
+  TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
+  TQ_REQUIRE(ctx->g.key_mode == TQ_KEYS_NF4_ASYM, TQ_ERR_INVALID,
+             "given zero-points apply to asymmetric NF4 keys only");
+  if (means == nullptr) {
+    ctx->bias_means = false;
+    return TQ_OK;
+  }
+  const tq_geom& g = ctx->g;
+  const size_t bytes = (size_t)g.max_blocks * g.n_kv_heads * TQ_D * sizeof(float);
+  TQ_CUDA(cudaSetDevice(ctx->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  TQ_CUDA(cudaMemcpyAsync((uint8_t*)ctx->b.tables + align_up(sizeof(Tables), 256), means, bytes,
+                          cudaMemcpyHostToDevice, st));
+  TQ_CUDA(cudaStreamSynchronize(st));  // the caller's buffer may go away after the call
+  ctx->bias_means = true;
   return TQ_OK;
 }
 
@@ -469,7 +490,8 @@ int32_t tq_memory_stats(tq_ctx* ctx, int32_t layer, int32_t seq, double* cold_by
       for (int h = 0; h < H; ++h) n_out += meta[(size_t)h * g.max_blocks + b].cnt;
       // symmetric NF4 containers hold no mean
       cold += (double)H * S * D * g.key_bits / 8 +
-              4.0 * H * D + (g.key_mode == TQ_KEYS_NF4 ? 0.0 : 4.0 * H * ctx->mean_channels) +
+              4.0 * H * D +
+              (g.key_mode == TQ_KEYS_NF4 || ctx->bias_means ? 0.0 : 4.0 * H * ctx->mean_channels) +
               6.0 * n_out;
       cold += (double)H * S * D * g.value_bits / 8 + 4.0 * H * S;
     }
@@ -510,7 +532,8 @@ int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes) {
   // reference container bytes of one cold block of one KV head, with the nominal
   // outlier count (ties add a few entries that are not counted)
   double blk = (double)S * D * g.key_bits / 8 + (double)S * D * g.value_bits / 8 + 4.0 * S +
-               4.0 * D + (g.key_mode == TQ_KEYS_NF4 ? 0.0 : 4.0 * ctx->mean_channels) +
+               4.0 * D +
+               (g.key_mode == TQ_KEYS_NF4 || ctx->bias_means ? 0.0 : 4.0 * ctx->mean_channels) +
                6.0 * g.outlier_k * D;
   double total = 0.0;
   for (int s = 0; s < g.n_seqs; ++s) {

@@ -22,6 +22,7 @@ struct EncodeArgs {
   uint32_t* pool_cursor; // [L][B][H]
   int32_t* status;
   const Tables* tables;
+  const float* bias_means;  // given key zero-points [max_blocks][H][D], or null
   const void* k;
   const void* v;
   int layer, seq_begin, seq_count, n_tokens, max_new_blocks;
@@ -130,7 +131,10 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   }
   // (the "sparse" zero-point keeps the mean on the masked channels only)
   const float mu = mode == TQ_KEYS_NF4_ASYM
-                       ? (a.tables->mean_mask[d] ? __fdiv_rn(acc, (float)S) : 0.0f)
+                       ? (a.bias_means != nullptr
+                              ? a.bias_means[((size_t)blk * g.n_kv_heads + head) * TQ_D + d]
+                          : a.tables->mean_mask[d] ? __fdiv_rn(acc, (float)S)
+                                                   : 0.0f)
                    : mode == TQ_KEYS_NF4 ? 0.0f
                                          : xmin;
   const float kth = (kk >= S) ? -1.0f : top[0];
@@ -552,6 +556,9 @@ int tq_launch_encode(tq_ctx* ctx, int layer, int seq_begin, int seq_count, const
   a.pool_cursor = (uint32_t*)((uint8_t*)ctx->b.state + state_cursor_off(ctx->g));
   a.status = (int32_t*)((uint8_t*)ctx->b.state + state_status_off(ctx->g));
   a.tables = (const Tables*)ctx->b.tables;
+  a.bias_means = ctx->bias_means
+                     ? (const float*)((const uint8_t*)ctx->b.tables + align_up(sizeof(Tables), 256))
+                     : nullptr;
   a.k = k;
   a.v = v;
   a.layer = layer;
