@@ -314,3 +314,58 @@ def test_heavy_tokens_overflow_and_spill(torch_cuda):
     assert np.allclose(got, want, rtol=RTOL, atol=ATOL), np.abs(got - want).max()
     assert np.allclose(got, gen, rtol=RTOL, atol=ATOL), np.abs(got - gen).max()
     assert ctx.status() == 0
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_geometries_kernels_agree(torch_cuda, seed):
+    """Randomised geometry (sequences, heads, GQA group, value bits, element type, ragged
+    lengths incl. empty and hot-only sequences, appended in random chunks): the tensor-core
+    kernel, the general kernel and sequence-split partials give the same attention."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    rng = np.random.default_rng(1000 + seed)
+    n_seqs, h = int(rng.integers(1, 5)), int(rng.integers(1, 4))
+    grp = int(rng.choice([1, 2, 4, 8]))
+    vb = int(rng.choice([3, 4]))
+    dt = str(rng.choice(["float16", "bfloat16", "float32"]))
+    mode = str(rng.choice(["nf4_asym", "nf4", "uniform"]))
+    lens = [int(rng.choice([0, int(rng.integers(1, 513)), int(rng.integers(513, 2600))]))
+            for _ in range(n_seqs)]
+    if max(lens) == 0:
+        lens[0] = 700
+    ctx = KVContext(n_layers=1, n_seqs=n_seqs, n_kv_heads=h, n_q_heads=h * grp, value_bits=vb,
+                    hot_window=512, max_tokens_per_seq=2600, kv_dtype=dt, key_mode=mode,
+                    seed=seed)
+    tdt = getattr(torch, dt)
+    for s, n in enumerate(lens):
+        if n == 0:
+            continue
+        k, v = make_kv(2000 + 10 * seed + s, h, n, dtype=np.float32)
+        pos = 0
+        while pos < n:  # random chunks, some of them single tokens
+            step = int(rng.choice([1, int(rng.integers(1, 700))]))
+            kt = torch.from_numpy(k[pos:pos + step]).to(tdt)[None].cuda()
+            vt = torch.from_numpy(v[pos:pos + step]).to(tdt)[None].cuda()
+            ctx.append(0, kt, vt, seq_begin=s)
+            pos += step
+    assert [ctx.lengths(0, s)[0] for s in range(n_seqs)] == lens
+    q = torch.from_numpy(np.stack([make_q(3000 + seed + s, h * grp) for s in range(n_seqs)])).cuda()
+    fast = ctx.decode(0, q).cpu().numpy()
+    ctx.set_kernel("general")
+    slow = ctx.decode(0, q).cpu().numpy()
+    ctx.set_kernel("auto")
+    assert ctx.status() == 0
+    assert np.allclose(fast, slow, rtol=RTOL, atol=ATOL), np.abs(fast - slow).max()
+    for s, n in enumerate(lens):
+        if n == 0:
+            assert not fast[s].any()
+    # two ranges of cold blocks + the hot window, merged, equal the full decode
+    nb = max(ctx.lengths(0, s)[1] for s in range(n_seqs)) // 256
+    cut = nb // 2
+    parts = torch.stack([ctx.decode_partial(0, q, 0, cut, False),
+                         ctx.decode_partial(0, q, cut, -1, True)])
+    merged = ctx.lse_combine(parts.reshape(2, n_seqs * h * grp, 130)).cpu().numpy()
+    live = np.repeat(np.asarray(lens) > 0, h * grp)
+    assert np.allclose(merged[live], fast.reshape(-1, 128)[live], rtol=1e-3, atol=1e-4)
