@@ -205,7 +205,28 @@ def main():
                n_q_heads=4)
     pack_known_answer()
     other_key_grids()
+    blob_case()
     print("golden fixtures written to", HERE)
+
+
+def blob_case():
+    """A cold block of a small cache written by the reference's own blob writer
+    (connectors/vllm_v1.py:113-137), with the tokens that produced it."""
+    from turboquant_pro.connectors import vllm_v1 as conn
+
+    rng = np.random.default_rng(41)
+    k, v = _scaled(rng, (2, D), 20)
+    cache = TurboQuantKVCache(head_dim=D, n_heads=2, bits=3, key_bits=4, value_bits=3,
+                              hot_window=16, use_gpu=False, seed=41, key_nf4_asym=True,
+                              key_outlier_frac=0.02)
+    for t in range(20):
+        cache.append(k[t], v[t])
+    ck, cv = cache._cold_keys[0], cache._cold_values[0]
+    rec = conn._BlockRecord(key_payload=ck, value_payload=cv, shape=tuple(ck.shape),
+                            dtype="float32", num_tokens=ck.shape[2], head_dim=D, n_heads=2)
+    blob = conn._rec_to_blob(rec)
+    np.savez_compressed(os.path.join(HERE, "blob_ref.npz"), k=k, v=v, pi=cache._tq._Pi,
+                        blob=np.frombuffer(blob, dtype=np.uint8), hot_window=16, seed=41)
 
 
 def other_key_grids():
@@ -225,7 +246,7 @@ def other_key_grids():
 
 
 if __name__ == "__main__":
-    if len(sys.argv) > 1 and sys.argv[1] == "other_key_grids":
-        other_key_grids()
+    if len(sys.argv) > 1 and sys.argv[1] in ("other_key_grids", "blob_case"):
+        globals()[sys.argv[1]]()
     else:
         main()

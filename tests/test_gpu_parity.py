@@ -516,3 +516,27 @@ def test_facade_key_grid_flags(torch_cuda):
     c = AutoConfig.from_pretrained("llama-3-8b").build_cache(robust=False, hot_window=32,
                                                              max_tokens=64)
     assert c.key_mode == "uniform" and c.key_outlier_frac == 0.0
+
+
+def test_export_blob_equals_reference_blob(torch_cuda):
+    """A block exported from the device in the wire format of the reference's vLLM connector
+    carries the same arrays and scalars as the blob the reference wrote for the same tokens."""
+    torch = torch_cuda
+    from turboquant_pro_b200.kv_blob import blob_to_block
+
+    g = load_golden("blob_ref.npz")
+    k, v = g["k"], g["v"]
+    ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=2, value_bits=3, hot_window=int(g["hot_window"]),
+               max_tokens_per_seq=64, kv_dtype="float32", seed=int(g["seed"]), pi=g["pi"])
+    ctx.append(0, _dev(torch, k)[None], _dev(torch, v)[None])
+    ref = blob_to_block(g["blob"].tobytes())
+    got = blob_to_block(ctx.export_blob(0, 0, 0))
+    assert got["header"] == ref["header"]
+    for part in ("key", "value"):
+        assert sorted(got[part]) == sorted(ref[part])
+        for name, want in ref[part].items():
+            if isinstance(want, np.ndarray):
+                assert got[part][name].dtype == want.dtype, name
+                assert np.array_equal(got[part][name], want), name
+            else:
+                assert got[part][name] == want, name

@@ -325,6 +325,21 @@ class KVContext:
             "shape": (1, h, s, d), "key_bits": g.key_bits, "value_bits": g.value_bits,
         }
 
+    def export_blob(self, layer: int, seq: int, block: int, rope_theta: float | None = None,
+                    zero_point: str = "calibrated") -> bytes:
+        """Cold block ``block`` as one ``tqp-kv-npz/1`` byte string, the layout of the
+        reference's vLLM connector (``connectors/vllm_v1.py:113-137``); see
+        :mod:`turboquant_pro_b200.kv_blob`.  ``zero_point`` / ``rope_theta`` name the key
+        zero-point mode the context was set up with (``"sparse"`` after
+        :meth:`set_key_mean_mask`, ``"bias"`` after :meth:`set_key_bias_means`)."""
+        from .kv_blob import block_to_blob
+
+        dt = {0: "float32", 1: "float16", 2: "bfloat16"}[self.geom.kv_dtype]
+        return block_to_blob(self.export_block(layer, seq, block), key_mode=self.key_mode,
+                             zero_point=zero_point, mean_mask=self.key_mean_mask,
+                             rope_theta=rope_theta,
+                             position_start=block * self.geom.block_tokens, dtype=dt)
+
     # -- bookkeeping -----------------------------------------------------------------
     def lengths(self, layer: int, seq: int):
         """(total, cold, hot) token counts of one cache."""
