@@ -15,10 +15,11 @@
 //                 each warp attends its 64 tokens: 4-bit key codes and 3/4-bit value code
 //                 pairs become fp16 pairs through one conflict-free shared-memory table
 //                 lookup each and go straight into m16n8k16 tensor-core tiles as register
-//                 fragments (scores: M = query group padded to 16 with the lo parts in rows
-//                 8-15, N = 8 tokens, K = 16 channels; values: M = 16 channels, N = 8 query
-//                 heads, K = 16 tokens); online softmax in fp32 registers.  K and V are
-//                 never materialised.
+//                 fragments (scores: M = 16 tokens, N = four query heads x {hi, lo} weight
+//                 parts, K = 16 channels; values: M = 16 channels, N = the same eight columns,
+//                 K = 16 tokens; the probabilities change from the score tile's layout to the
+//                 value tile's with one 8x8 register transpose); online softmax in fp32
+//                 registers.  K and V are never materialised.
 //
 // Work is a flat list of tiles over all (sequence, KV head) units of the layer, cut into
 // equal contiguous shares, one per CTA (one CTA per SM), so ragged contexts balance.
@@ -136,6 +137,13 @@ TQ_DEV void ldsm_x4_trans(uint32_t* v, uint32_t addr) {
                : "r"(addr)
                : "memory");
 }
+// transpose of an 8x8 matrix of 16-bit elements held one row per four lanes (lane 4i + c:
+// row i, columns 2c and 2c+1)
+TQ_DEV uint32_t transpose8x8(uint32_t v) {
+  uint32_t o;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(o) : "r"(v));
+  return o;
+}
 // 2^x in one instruction (denormal results flush to zero; arguments here are <= 0 or tiny)
 TQ_DEV float ex2(float x) {
   float y;
@@ -165,8 +173,8 @@ struct SmemT {
   static constexpr int ALIGN_SLACK = VB == 3 ? 8192 : 0;
   static constexpr int PLAN_BYTES = 8192;
   static constexpr int QC_BYTES = TQ_D * G * 4;  // [128][G] query values
-  static constexpr int FRAG_BYTES = 8 * 32 * 16;
-  static constexpr int BIAS_BYTES = 128;         // [8 rows][GW]: one partial per warp
+  static constexpr int FRAG_BYTES = 8 * 32 * 16;  // [G/4 column groups][8 k-steps][32 lanes] x 8 B
+  static constexpr int BIAS_BYTES = 256;         // [8 heads][GW]: one partial per warp (+ spare)
   static constexpr int CORR_STRIDE = 64 + 8;     // floats per query row: rows on different banks
   static constexpr int CORR_BYTES = G * CORR_STRIDE * 4;  // per warp
   static constexpr int FRAG_OFF = QC_BYTES;
@@ -465,8 +473,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   TQ_TRACE_PHASE(4);
   uint8_t* gs = groups + gi * SM::GROUP_BYTES;
   float* qc = (float*)gs;                                   // [128][G]
-  uint4* frag = (uint4*)(gs + SM::FRAG_OFF);                // [8 k-steps][32 lanes]
-  float* bias_s = (float*)(gs + SM::BIAS_OFF);              // [8 rows][GW]
+  uint2* frag = (uint2*)(gs + SM::FRAG_OFF);                // [G/4][8 k-steps][32 lanes]
+  float* bias_s = (float*)(gs + SM::BIAS_OFF);              // [8 heads][GW]
   float* corr_w = (float*)(gs + SM::CORR_OFF) + gw * (G * SM::CORR_STRIDE);  // this warp's strip
   auto group_sync = [&]() {
     asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "n"(GW * 32) : "memory");
@@ -474,12 +482,22 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 
   const uint32_t lutk = smem_addr(lutk_p) + lane * 4;
   const uint32_t lutv = smem_addr(lutv_p) + lane * 4;  // 8 KB aligned base | lane offset
-  const int rg = r < G ? r : G - 1;
-  float m_run = NEG_BIG, l_run = 0.0f;
+  // Column n of a score or value tile: query head n / 2, and n & 1 selects the hi or lo fp16
+  // part of its weights.  A group of eight heads takes two such score tiles (heads 0-3, 4-7);
+  // its value tile then has head n / 2 + 4 (n & 1) in column n.  A lane's two columns (2c,
+  // 2c+1) therefore always belong to head c (and c + 4): its softmax state is its own.
+  constexpr int NH = G == 8 ? 2 : 1;
+  int hc[NH];  // the lane's heads, clamped to the group
+#pragma unroll
+  for (int nh = 0; nh < NH; ++nh) hc[nh] = min(c + 4 * nh, G - 1);
+  float m_run[NH], l_run[NH];  // l_run: the sum over this lane's own tokens
   float acc[8][4];
   auto reset_state = [&]() {
-    m_run = NEG_BIG;
-    l_run = 0.0f;
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      m_run[nh] = NEG_BIG;
+      l_run[nh] = 0.0f;
+    }
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
   };
@@ -489,9 +507,9 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   // states through shared memory (the fragment / bias / correction areas are idle between
   // tiles) and the 128 threads store one coalesced record.  Called by all warps of the group.
   auto flush = [&](int u, int kind) {
-    // as many warps at a time as there is room for accumulator copies (row stride 132
+    // as many warps at a time as there is room for accumulator copies (row stride 136
     // floats: the cold layout then stores without bank conflicts)
-    constexpr int MG_STRIDE = TQ_D + 4, MG_ONE = G * MG_STRIDE * 4;
+    constexpr int MG_STRIDE = TQ_D + 8, MG_ONE = G * MG_STRIDE * 4;
     constexpr int MG_ROOM = SM::GROUP_BYTES - SM::FRAG_OFF - 2 * GW * 8 * 4;
     constexpr int MG_PAR = MG_ROOM >= 4 * MG_ONE ? 4 : (MG_ROOM >= 2 * MG_ONE ? 2 : 1);
     static_assert(MG_ROOM >= MG_ONE, "merge scratch");
@@ -499,38 +517,47 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     float* mg_l = mg_m + GW * 8;                // [GW][8] their sums
     float* mg_acc = mg_l + GW * 8;              // [MG_PAR][G][MG_STRIDE] scaled accumulators
     group_sync();  // every warp has finished its last tile
-    float l = l_run;
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (c == 0) {
-      mg_m[gw * 8 + r] = m_run;
-      mg_l[gw * 8 + r] = l;
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      float l = l_run[nh];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      if (r == 0) {
+        mg_m[gw * 8 + c + 4 * nh] = m_run[nh];
+        mg_l[gw * 8 + c + 4 * nh] = l;
+      }
     }
     group_sync();
-    // the accumulator columns of this thread belong to query rows 2c and 2c+1
-    float M0 = NEG_BIG, M1 = NEG_BIG;
+    float f[NH];  // this warp's state relative to the group's maximum, per head of the lane
 #pragma unroll
-    for (int w = 0; w < GW; ++w) {
-      M0 = fmaxf(M0, mg_m[w * 8 + 2 * c]);
-      M1 = fmaxf(M1, mg_m[w * 8 + 2 * c + 1]);
+    for (int nh = 0; nh < NH; ++nh) {
+      float M = NEG_BIG;
+#pragma unroll
+      for (int w = 0; w < GW; ++w) M = fmaxf(M, mg_m[w * 8 + c + 4 * nh]);
+      f[nh] = exp2f(mg_m[gw * 8 + c + 4 * nh] - M);
     }
-    const float f0 = exp2f(mg_m[gw * 8 + 2 * c] - M0), f1 = exp2f(mg_m[gw * 8 + 2 * c + 1] - M1);
     float* mine = mg_acc + (gw % MG_PAR) * (G * MG_STRIDE);
     for (int step = 0; step < GW / MG_PAR; ++step) {
       if (gw / MG_PAR == step) {
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
-          for (int x = 0; x < 2; ++x)
+          for (int x = 0; x < 2; ++x) {
+            const int d = (kind == 0 || a.use_tmap) ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
+            if (G == 8) {  // the two columns are two heads
 #pragma unroll
-            for (int y = 0; y < 2; ++y) {
-              const int gg = 2 * c + y;
-              const int d = (kind == 0 || a.use_tmap) ? 16 * mt + r + 8 * x : 16 * r + 2 * mt + x;
-              if (gg < G) {
-                const float v = acc[mt][2 * x + y] * (y ? f1 : f0);
-                if (step == 0) mine[gg * MG_STRIDE + d] = v; else mine[gg * MG_STRIDE + d] += v;
+              for (int y = 0; y < 2; ++y) {
+                const float v = acc[mt][2 * x + y] * f[NH - 1 < y ? NH - 1 : y];
+                float* dst = mine + (c + 4 * y) * MG_STRIDE + d;
+                if (step == 0) *dst = v; else *dst += v;
               }
+            } else if (c < G) {  // ... or the hi and lo parts of one head's probabilities
+              const float v = (acc[mt][2 * x] + acc[mt][2 * x + 1]) * f[0];
+              float* dst = mine + c * MG_STRIDE + d;
+              if (step == 0) *dst = v; else *dst += v;
             }
+          }
       }
       group_sync();
     }
@@ -554,31 +581,27 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     }
   };
 
-  // online-softmax update with the four scores of this thread's row (two 8-token tiles,
-  // two tokens each); leaves the probabilities in sv
-  auto softmax16 = [&](float (&sv)[2][2], const bool (&ok)[2][2]) {
-    float mx = NEG_BIG;
+  // online-softmax update with the scores of this lane's two tokens (rows r and r + 8 of a
+  // 16-token tile) for each of its heads; leaves the probabilities in sv
+  auto softmax16 = [&](float (&sv)[NH][2], const bool (&ok)[2]) {
+    float cf[NH];
+    bool grew = false;
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) mx = fmaxf(mx, ok[i][j] ? sv[i][j] : NEG_BIG);
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m_run, mx);
-    const float cf = ex2(m_run - m_new);
-    float sum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        sv[i][j] = ok[i][j] ? ex2(sv[i][j] - m_new) : 0.0f;
-        sum += sv[i][j];
-      }
-    l_run = l_run * cf + sum;
-    if (__any_sync(0xffffffffu, m_new > m_run)) {
-      // the accumulator columns of this thread belong to rows 2c and 2c+1
-      const float f0 = __shfl_sync(0xffffffffu, cf, 8 * c);
-      const float f1 = __shfl_sync(0xffffffffu, cf, 8 * c + 4);
+    for (int nh = 0; nh < NH; ++nh) {
+      float mx = fmaxf(ok[0] ? sv[nh][0] : NEG_BIG, ok[1] ? sv[nh][1] : NEG_BIG);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[nh], mx);
+      cf[nh] = ex2(m_run[nh] - m_new);
+      sv[nh][0] = ok[0] ? ex2(sv[nh][0] - m_new) : 0.0f;
+      sv[nh][1] = ok[1] ? ex2(sv[nh][1] - m_new) : 0.0f;
+      l_run[nh] = l_run[nh] * cf[nh] + (sv[nh][0] + sv[nh][1]);
+      grew |= m_new > m_run[nh];
+      m_run[nh] = m_new;
+    }
+    if (__any_sync(0xffffffffu, grew)) {
+      const float f0 = cf[0], f1 = cf[NH - 1];
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt) {
         acc[mt][0] *= f0;
@@ -587,7 +610,25 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         acc[mt][3] *= f1;
       }
     }
-    m_run = m_new;
+  };
+  // The value tile's B fragments (tokens down the K dimension, the eight columns across) from
+  // the probabilities of this lane's tokens, already times the token's value norm: column 2c
+  // gets head c and column 2c+1 the rounding residual of the same number (so the product is
+  // accurate beyond fp16), or head c + 4 for a group of eight.
+  auto prob_frags = [&](const float (&sv)[NH][2], float n0, float n1, uint32_t& pb0,
+                        uint32_t& pb1) {
+    uint32_t w0, w1;
+    if (G == 8) {
+      w0 = pack_h2(sv[0][0] * n0, sv[NH - 1][0] * n0);
+      w1 = pack_h2(sv[0][1] * n1, sv[NH - 1][1] * n1);
+    } else {
+      const float v0 = sv[0][0] * n0, v1 = sv[0][1] * n1;
+      const float h0 = __half2float(__float2half_rn(v0)), h1 = __half2float(__float2half_rn(v1));
+      w0 = pack_h2(h0, v0 - h0);
+      w1 = pack_h2(h1, v1 - h1);
+    }
+    pb0 = transpose8x8(w0);  // tokens 0-7 of the tile: lane (r, c) gets tokens 2c, 2c+1, column r
+    pb1 = transpose8x8(w1);  // tokens 8-15
   };
 
   int u_cur = find_unit(plan, a.n_units, lo);
@@ -649,8 +690,12 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     const bool cold = tl.kind == 0;
     const float* scale = (const float*)(st + g.scale_off);
     {
+      // B fragments of the weights: lane (r, c) holds column r (head r / 2, part r & 1) at the
+      // channels of rows 2c, 2c+1 and 2c+8, 2c+9 of the k-step
       const float* mean = (const float*)(st + g.mean_off);
-      float bias = 0.0f;
+      float bias[NH];
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) bias[nh] = 0.0f;
 #pragma unroll
       for (int i = 0; i < 8 / GW; ++i) {  // this warp's k-steps
         const int j = gw + GW * i;
@@ -659,24 +704,32 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         // the tensor-core tile's own order 16j + {2c, 2c+1, 2c+8, 2c+9}
         const int d0 = 32 * c + 4 * j, dn = 16 * j + 2 * c;
         const bool natural = !cold && a.use_tmap;
-        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < G) {
-          q4.x = qc[q_row(natural ? dn : d0 + 0) * G + r];
-          q4.y = qc[q_row(natural ? dn + 1 : d0 + 1) * G + r];
-          q4.z = qc[q_row(natural ? dn + 8 : d0 + 2) * G + r];
-          q4.w = qc[q_row(natural ? dn + 9 : d0 + 3) * G + r];
-        }
-        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), m4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (cold) {
           s4 = *(const float4*)&scale[d0];
-          const float4 m4 = *(const float4*)&mean[d0];
-          bias += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
+          m4 = *(const float4*)&mean[d0];
         }
-        frag[j * 32 + lane] = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+          const int hb = 4 * nh + (r >> 1);
+          float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (hb < G) {
+            q4.x = qc[q_row(natural ? dn : d0 + 0) * G + hb];
+            q4.y = qc[q_row(natural ? dn + 1 : d0 + 1) * G + hb];
+            q4.z = qc[q_row(natural ? dn + 8 : d0 + 2) * G + hb];
+            q4.w = qc[q_row(natural ? dn + 9 : d0 + 3) * G + hb];
+          }
+          bias[nh] += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
+          const uint4 f = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
+          frag[(nh * 8 + j) * 32 + lane] = (r & 1) ? make_uint2(f.y, f.w) : make_uint2(f.x, f.z);
+        }
       }
-      bias += __shfl_xor_sync(0xffffffffu, bias, 1);
-      bias += __shfl_xor_sync(0xffffffffu, bias, 2);
-      if (c == 0) bias_s[r * GW + gw] = bias;
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) {
+        bias[nh] += __shfl_xor_sync(0xffffffffu, bias[nh], 1);
+        bias[nh] += __shfl_xor_sync(0xffffffffu, bias[nh], 2);
+        if (c == 0 && (r & 1) == 0) bias_s[(4 * nh + (r >> 1)) * GW + gw] = bias[nh];
+      }
     }
     if (cold) {
       // Outlier corrections of this warp's 64 tokens (a lane owns tokens lane and lane + 32 of
@@ -793,25 +846,33 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     group_sync();  // fragments and bias of all four warps are in place
     if (warp == 0) TQ_TRACE(4);
 
-    uint32_t areg[8][4];
+    uint32_t breg[NH][8][2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint4 f = frag[j * 32 + lane];
-      areg[j][0] = f.x; areg[j][1] = f.y; areg[j][2] = f.z; areg[j][3] = f.w;
-    }
+    for (int nh = 0; nh < NH; ++nh)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint2 f = frag[(nh * 8 + j) * 32 + lane];
+        breg[nh][j][0] = f.x;
+        breg[nh][j][1] = f.y;
+      }
 
     if (cold) {
-      const float4 b4 = *(const float4*)(bias_s + rg * GW);
-      const float bias = (b4.x + b4.y) + (b4.z + b4.w);
-      const float* corr = corr_w + rg * SM::CORR_STRIDE;
+      float bias[NH];
+      const float* corr[NH];
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) {
+        const float4 b4 = *(const float4*)(bias_s + hc[nh] * GW);
+        bias[nh] = (b4.x + b4.y) + (b4.z + b4.w);
+        corr[nh] = corr_w + hc[nh] * SM::CORR_STRIDE + r;
+      }
       const float* norms = (const float*)(st + g.norm_off);
       const uint8_t* vcodes = st + g.v_off;
-      // Score tiles of 16 tokens (two 8-token tiles x even/odd k-steps: four independent
-      // accumulation chains), and the value tiles of 16 tokens.  The loop below is unrolled
-      // with the score phase of strip h+1 placed before the value phase of strip h: the two
-      // are independent, so the scheduler can fill the lookup and tensor-core latencies of
-      // one with the other.
-      float C[2][2][4];
+      // Score tiles of 16 tokens (the lane looks up the codes of tokens r and r + 8; even and
+      // odd k-steps accumulate separately: two independent chains per column group), and the
+      // value tiles of 16 tokens.  The loop below is unrolled with the score phase of strip
+      // h+1 placed before the value phase of strip h: the two are independent, so the
+      // scheduler can fill the lookup and tensor-core latencies of one with the other.
+      float C[NH][2][4];
       auto score_phase = [&](int half) {
         const int T0 = 64 * gw + 16 * half;
         uint32_t kw[2][4];
@@ -819,19 +880,24 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         for (int nt = 0; nt < 2; ++nt) {
           const uint4 kc = *(const uint4*)(st + (T0 + 8 * nt + r) * 64 + c * 16);
           kw[nt][0] = kc.x; kw[nt][1] = kc.y; kw[nt][2] = kc.z; kw[nt][3] = kc.w;
-#pragma unroll
-          for (int x = 0; x < 2; ++x) C[nt][x][0] = C[nt][x][1] = C[nt][x][2] = C[nt][x][3] = 0.0f;
         }
 #pragma unroll
+        for (int nh = 0; nh < NH; ++nh)
+#pragma unroll
+          for (int x = 0; x < 2; ++x) C[nh][x][0] = C[nh][x][1] = C[nh][x][2] = C[nh][x][3] = 0.0f;
+#pragma unroll
         for (int j = 0; j < 8; ++j) {
+          uint32_t af[4];  // {token r | r+8} x {channels of rows 2c.. | 2c+8..}
 #pragma unroll
           for (int nt = 0; nt < 2; ++nt) {
             const uint32_t w = kw[nt][j >> 1];
             const uint32_t i0 = __byte_perm(w, 0, 0x4440 + 2 * (j & 1));
             const uint32_t i1 = __byte_perm(w, 0, 0x4441 + 2 * (j & 1));
-            const uint32_t b0 = lut_ld(lutk + i0 * 128), b1 = lut_ld(lutk + i1 * 128);
-            mma16816(C[nt][j & 1], areg[j], b0, b1);
+            af[nt] = lut_ld(lutk + i0 * 128);
+            af[2 + nt] = lut_ld(lutk + i1 * 128);
           }
+#pragma unroll
+          for (int nh = 0; nh < NH; ++nh) mma16816(C[nh][j & 1], af, breg[nh][j][0], breg[nh][j][1]);
         }
       };
       auto value_phase = [&](int half, uint32_t pb0, uint32_t pb1) {
@@ -878,22 +944,20 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 #pragma unroll
       for (int half = 0; half < 4; ++half) {
         const int T0 = 64 * gw + 16 * half;
-        float sv[2][2];
-        const bool ok[2][2] = {{true, true}, {true, true}};
+        float sv[NH][2];
+        const bool ok[2] = {true, true};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const float2 cr = *(const float2*)(corr + 16 * half + 8 * nt + 2 * c);
-          const float s0 = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
-          const float s1 = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
-          // rows >= G carry zero weights: their scores are small finite numbers nobody reads
-          sv[nt][0] = s0 + (bias + cr.x);
-          sv[nt][1] = s1 + (bias + cr.y);
+        for (int nh = 0; nh < NH; ++nh) {
+          // columns 2c, 2c+1 of the tile: the hi and lo weight parts of the lane's head (heads
+          // beyond the group carry zero weights: finite scores nobody reads)
+          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
+          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
+          sv[nh][0] = s0 + (bias[nh] + corr[nh][16 * half]);
+          sv[nh][1] = s1 + (bias[nh] + corr[nh][16 * half + 8]);
         }
         softmax16(sv, ok);
-        const float2 n0 = *(const float2*)(norms + T0 + 2 * c);
-        const float2 n1 = *(const float2*)(norms + T0 + 8 + 2 * c);
-        const uint32_t pb0 = pack_h2(sv[0][0] * n0.x, sv[0][1] * n0.y);
-        const uint32_t pb1 = pack_h2(sv[1][0] * n1.x, sv[1][1] * n1.y);
+        uint32_t pb0, pb1;
+        prob_frags(sv, norms[T0 + r], norms[T0 + r + 8], pb0, pb1);
         if (half < 3) score_phase(half + 1);
         value_phase(half, pb0, pb1);
       }
@@ -908,38 +972,33 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       const int tr = T0 + 8 * (lane >> 4) + (lane & 7), m1 = (lane >> 3) & 1, sw = lane & 7;
       const uint32_t ka = smem_addr(st) + tr * 128, va = ka + 16384;
       const bool bf = g.kv_dtype == TQ_BF16;
-      float sv[2][2];
-      bool ok[2][2];
+      float sv[NH][2];
+      const bool ok[2] = {base_tok + r < hot_len, base_tok + r + 8 < hot_len};
       {
-        float C[2][2][4] = {};  // [token tile][k-step parity]: four accumulation chains
+        float C[NH][2][4] = {};  // [column group][k-step parity]: independent chains
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          uint32_t kb[4];  // key rows: {tile 0: k lo, k hi, tile 1: k lo, k hi}
+          uint32_t kb[4];  // key rows: {tokens 0-7: k lo, k hi, tokens 8-15: k lo, k hi}
           ldsm_x4(kb, ka + (j >> 2) * 8192 + (((2 * (j & 3) + m1) ^ sw) << 4));
           if (bf) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) kb[i] = bf16x2_to_h2(kb[i]);
           }
-          mma16816(C[0][j & 1], areg[j], kb[0], kb[1]);
-          mma16816(C[1][j & 1], areg[j], kb[2], kb[3]);
+          const uint32_t af[4] = {kb[0], kb[2], kb[1], kb[3]};
+#pragma unroll
+          for (int nh = 0; nh < NH; ++nh) mma16816(C[nh][j & 1], af, breg[nh][j][0], breg[nh][j][1]);
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          sv[nt][0] = (C[nt][0][0] + C[nt][1][0]) + (C[nt][0][2] + C[nt][1][2]);
-          sv[nt][1] = (C[nt][0][1] + C[nt][1][1]) + (C[nt][0][3] + C[nt][1][3]);
-          ok[nt][0] = base_tok + 8 * nt + 2 * c < hot_len;
-          ok[nt][1] = base_tok + 8 * nt + 2 * c + 1 < hot_len;
-          if (r >= G) {
-            sv[nt][0] = sv[nt][1] = 0.0f;
-            ok[nt][0] = ok[nt][1] = true;
-          }
+        for (int nh = 0; nh < NH; ++nh) {
+          sv[nh][0] = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
+          sv[nh][1] = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
         }
       }
       softmax16(sv, ok);
       // tokens past the end of the window have probability 0 (their rows hold finite values:
       // the rings start zeroed and are only ever written with tokens)
-      const uint32_t pb0 = pack_h2(sv[0][0], sv[0][1]);
-      const uint32_t pb1 = pack_h2(sv[1][0], sv[1][1]);
+      uint32_t pb0, pb1;
+      prob_frags(sv, 1.0f, 1.0f, pb0, pb1);
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt) {
         // transposed loads: {tokens 0-7 | 8-15} x {channels 16mt + 0..7 | + 8..15} arrive as
@@ -959,45 +1018,48 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       const int base_tok = tl.idx * htt + T0;   // ... inside the hot window
       const uint8_t* kbase = st;
       const uint8_t* vbase = st + htt * TQ_D * esz;
-      float sv[2][2];
-      bool ok[2][2];
+      float sv[NH][2];
+      const bool ok[2] = {base_tok + r < hot_len, base_tok + r + 8 < hot_len};
+      {
+        uint32_t kw[2][16];  // tokens r and r + 8, channels 32c .. 32c+31 as fp16 pairs
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const uint8_t* row = kbase + ((T0 + 8 * nt + r) * TQ_D + 32 * c) * esz;
-        uint32_t kw[16];
-        if (esz == 2) {
+        for (int nt = 0; nt < 2; ++nt) {
+          const uint8_t* row = kbase + ((T0 + 8 * nt + r) * TQ_D + 32 * c) * esz;
+          if (esz == 2) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint4 v4 = *(const uint4*)(row + 16 * i);
-            kw[4 * i] = v4.x; kw[4 * i + 1] = v4.y; kw[4 * i + 2] = v4.z; kw[4 * i + 3] = v4.w;
-          }
-          if (g.kv_dtype == TQ_BF16) {
+            for (int i = 0; i < 4; ++i) {
+              const uint4 v4 = *(const uint4*)(row + 16 * i);
+              kw[nt][4 * i] = v4.x; kw[nt][4 * i + 1] = v4.y;
+              kw[nt][4 * i + 2] = v4.z; kw[nt][4 * i + 3] = v4.w;
+            }
+            if (g.kv_dtype == TQ_BF16) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) kw[i] = bf16x2_to_h2(kw[i]);
-          }
-        } else {
+              for (int i = 0; i < 16; ++i) kw[nt][i] = bf16x2_to_h2(kw[nt][i]);
+            }
+          } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 v4 = *(const float4*)(row + 16 * i);
-            kw[2 * i] = pack_h2(v4.x, v4.y);
-            kw[2 * i + 1] = pack_h2(v4.z, v4.w);
+            for (int i = 0; i < 8; ++i) {
+              const float4 v4 = *(const float4*)(row + 16 * i);
+              kw[nt][2 * i] = pack_h2(v4.x, v4.y);
+              kw[nt][2 * i + 1] = pack_h2(v4.z, v4.w);
+            }
           }
         }
-        float C[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mma16816(C, areg[j], kw[2 * j], kw[2 * j + 1]);
-        sv[nt][0] = C[0] + C[2];
-        sv[nt][1] = C[1] + C[3];
-        ok[nt][0] = base_tok + 8 * nt + 2 * c < hot_len;
-        ok[nt][1] = base_tok + 8 * nt + 2 * c + 1 < hot_len;
-        if (r >= G) {
-          sv[nt][0] = sv[nt][1] = 0.0f;
-          ok[nt][0] = ok[nt][1] = true;
+        for (int nh = 0; nh < NH; ++nh) {
+          float C[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t af[4] = {kw[0][2 * j], kw[1][2 * j], kw[0][2 * j + 1], kw[1][2 * j + 1]};
+            mma16816(C, af, breg[nh][j][0], breg[nh][j][1]);
+          }
+          sv[nh][0] = C[0] + C[1];
+          sv[nh][1] = C[2] + C[3];
         }
       }
       softmax16(sv, ok);
-      const uint32_t pb0 = pack_h2(sv[0][0], sv[0][1]);
-      const uint32_t pb1 = pack_h2(sv[1][0], sv[1][1]);
+      uint32_t pb0, pb1;
+      prob_frags(sv, 1.0f, 1.0f, pb0, pb1);
       // value rows of tokens 2c, 2c+1, 2c+8, 2c+9, channels 16r .. 16r+15, as fp16 pairs
       uint32_t vr[4][8];
 #pragma unroll
