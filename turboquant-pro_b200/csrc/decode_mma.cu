@@ -406,16 +406,31 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   const int htt = hot_tile_tokens(g.kv_dtype);
   const int esz = elem_size(g.kv_dtype);
 
-  auto tile_at = [&](int pos, int& u_cursor) -> Tile {
-    while (pos >= plan->P[u_cursor + 1]) ++u_cursor;
+  // A cursor into the tile list: the unit that holds a position, kept in registers and looked
+  // up again only when the positions (which only grow) leave the unit.
+  struct Cursor {
+    int u, P0, P1, nb, b0;
+  };
+  auto tile_at = [&](int pos, Cursor& cu) -> Tile {
+    if (pos >= cu.P1) {
+      int u = cu.u;
+      while (pos >= plan->P[u + 1]) ++u;
+      cu.u = u;
+      cu.P0 = plan->P[u];
+      cu.P1 = plan->P[u + 1];
+      cu.nb = plan->nb[u];
+      cu.b0 = plan->b0[u];
+    }
     Tile t;
-    t.u = u_cursor;
-    int j = pos - plan->P[u_cursor];
-    int nb = plan->nb[u_cursor];
-    t.kind = j >= nb;
-    t.idx = t.kind == 0 ? plan->b0[u_cursor] + j : j - nb;
+    t.u = cu.u;
+    const int j = pos - cu.P0;
+    t.kind = j >= cu.nb;
+    t.idx = t.kind == 0 ? cu.b0 + j : j - cu.nb;
     return t;
   };
+  // units of this layer are numbered (sequence, KV head) row-major, and so are their pages,
+  // hot rings, pool lists and query rows: no division by the head count is ever needed
+  const size_t unit0 = (size_t)a.layer * g.n_seqs * g.n_kv_heads;
 
   // The copy of tile t of this CTA's share: describe() works out addresses and sizes (it can
   // run before the stage is free), fire() starts it (the stage must be free: never used, or
@@ -427,23 +442,23 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     int row;  // hot tile: its first row in the ring seen as one 2-D array
   };
   const int total = hi - lo;
-  auto describe = [&](int t, int& u_cursor) -> CopyDesc {
-    const Tile tl = tile_at(lo + t, u_cursor);
-    const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
+  auto describe = [&](int t, Cursor& cu) -> CopyDesc {
+    const Tile tl = tile_at(lo + t, cu);
+    const size_t unit = unit0 + tl.u;
     CopyDesc d;
     d.dst = smem_addr(stages + (size_t)(t % NSTAGE) * SM::DATA_BYTES);
     d.bar = full0 + 8 * (t % (2 * NSTAGE));
     if (tl.kind == 0) {
-      d.src = a.pages + page_offset(g, a.layer, seq, head, tl.idx);
+      d.src = a.pages + (unit * g.max_blocks + tl.idx) * (size_t)g.page_bytes;
       d.src2 = nullptr;
       d.bytes = (uint32_t)g.page_bytes;
     } else {
       const int slot = (plan->hot_start[tl.u] + tl.idx * htt) % g.hot_cap;
-      const size_t off = (hot_offset_elems(g, a.layer, seq, head) + (size_t)slot * TQ_D) * esz;
+      const size_t off = (unit * g.hot_cap + slot) * (size_t)(TQ_D * esz);
       d.src = a.hot_k + off;
       d.src2 = a.hot_v + off;
       d.bytes = (uint32_t)(htt * TQ_D * esz);
-      d.row = (int)(unit_index(g, a.layer, seq, head) * (size_t)g.hot_cap) + slot;
+      d.row = (int)(unit * g.hot_cap) + slot;
     }
     return d;
   };
@@ -468,7 +483,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 
   // ============================== consumer groups ============================================
   const int gi = warp / GW, gw = warp % GW, gtid = tid - gi * (GW * 32);
-  int u_iss = find_unit(plan, a.n_units, lo);  // cursor of the copies this thread starts
+  const int u_first = find_unit(plan, a.n_units, lo);
+  Cursor u_iss = {u_first, 0, 0, 0, 0};  // cursor of the copies this thread starts
   if (warp == 0 && lane < min(NSTAGE, total)) fire(describe(lane, u_iss));  // a lane per tile
   TQ_TRACE_PHASE(4);
   uint8_t* gs = groups + gi * SM::GROUP_BYTES;
@@ -631,14 +647,13 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     pb1 = transpose8x8(w1);  // tokens 8-15
   };
 
-  int u_cur = find_unit(plan, a.n_units, lo);
+  Cursor u_cur = {u_first, 0, 0, 0, 0};
   int cur_u = -1, cur_kind = -1, q_unit = -1;
   for (int pos = lo + gi; pos < hi; pos += NG) {
     const int t = pos - lo, s = t % NSTAGE;
     const uint32_t full_bar = full0 + 8 * (t % (2 * NSTAGE));
     const uint32_t full_par = (t / (2 * NSTAGE)) & 1;
     const Tile tl = tile_at(pos, u_cur);
-    const int seq = tl.u / g.n_kv_heads, head = tl.u % g.n_kv_heads;
     if (tl.u != cur_u || tl.kind != cur_kind) {
       if (cur_u >= 0) flush(cur_u, cur_kind);
       reset_state();
@@ -662,7 +677,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         // thread d of the group loads channel d of the G rows: coalesced, independent loads.
         // The softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
         // bias and corrections come out already scaled.
-        const size_t q0 = ((size_t)seq * g.n_q_heads + head * G) * TQ_D + gtid;
+        const size_t q0 = (size_t)tl.u * (G * TQ_D) + gtid;  // query heads follow their KV head
         float qv[G];
         if (a.q_dtype == TQ_F32) {
 #pragma unroll
@@ -731,12 +746,14 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         if (c == 0 && (r & 1) == 0) bias_s[(4 * nh + (r >> 1)) * GW + gw] = bias[nh];
       }
     }
-    if (cold) {
+    // Outlier corrections of this warp's 64 tokens, in two parts: the fixed slots and the
+    // page's widest channels, then the entries beyond the slots.
+    const PageHeader* hdr = (const PageHeader*)(st + g.hdr_off);
+    const bool spilled = cold && (hdr->flags & TQ_PAGE_SPILLED) != 0;
+    auto fixed_corrections = [&]() {
       // Outlier corrections of this warp's 64 tokens (a lane owns tokens lane and lane + 32 of
       // the strip).  The page keeps the first TQ_ELL_SLOTS outliers of every token in fixed
       // slots, so the common case is a fixed number of independent, conflict-free rounds.
-      const PageHeader* hdr = (const PageHeader*)(st + g.hdr_off);
-      const bool spilled = (hdr->flags & TQ_PAGE_SPILLED) != 0;
       float cacc[2][G];
 #pragma unroll
       for (int i = 0; i < 2; ++i)
@@ -801,6 +818,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + 32 * i + lane] = cacc[i][gg];
+    };
+    auto overflow_corrections = [&]() {
       // Entries beyond the fixed slots (ordered by token), or, for a spilled page, the whole
       // list from the pool: a lane per entry, equal tokens summed across lanes by a segmented
       // reduction (fixed order, so the result does not depend on timing), and the first lane
@@ -809,7 +828,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       const int s1 = spilled ? (int)hdr->cnt : (int)hdr->ovf_start[gw + 1];
       if (s1 > s0) {
         const uint32_t* list =
-            spilled ? a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + hdr->off
+            spilled ? a.pool_dec + (unit0 + tl.u) * (size_t)g.pool_entries + hdr->off
                     : (const uint32_t*)(st + g.hdr_off + TQ_OVF_OFF);
         for (int eb = s0; eb < s1; eb += 32) {
           __syncwarp();
@@ -842,6 +861,10 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         }
         __syncwarp();
       }
+    };
+    if (cold) {
+      fixed_corrections();
+      overflow_corrections();
     }
     group_sync();  // fragments and bias of all four warps are in place
     if (warp == 0) TQ_TRACE(4);
