@@ -627,6 +627,44 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       }
     }
   };
+  // the same over NT consecutive 16-token tiles at once (all tokens valid): one reduction
+  // and at most one rescaling of the accumulator for all of them
+  auto softmax_many = [&](auto& sv) {
+    constexpr int NT = sizeof(sv) / sizeof(sv[0]);
+    float cf[NH];
+    bool grew = false;
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      float mx = NEG_BIG;
+#pragma unroll
+      for (int h = 0; h < NT; ++h) mx = fmaxf(mx, fmaxf(sv[h][nh][0], sv[h][nh][1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[nh], mx);
+      cf[nh] = ex2(m_run[nh] - m_new);
+      float sum = 0.0f;
+#pragma unroll
+      for (int h = 0; h < NT; ++h) {
+        sv[h][nh][0] = ex2(sv[h][nh][0] - m_new);
+        sv[h][nh][1] = ex2(sv[h][nh][1] - m_new);
+        sum += sv[h][nh][0] + sv[h][nh][1];
+      }
+      l_run[nh] = l_run[nh] * cf[nh] + sum;
+      grew |= m_new > m_run[nh];
+      m_run[nh] = m_new;
+    }
+    if (__any_sync(0xffffffffu, grew)) {
+      const float f0 = cf[0], f1 = cf[NH - 1];
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        acc[mt][0] *= f0;
+        acc[mt][1] *= f1;
+        acc[mt][2] *= f0;
+        acc[mt][3] *= f1;
+      }
+    }
+  };
   // The value tile's B fragments (tokens down the K dimension, the eight columns across) from
   // the probabilities of this lane's tokens, already times the token's value norm: column 2c
   // gets head c and column 2c+1 the rounding residual of the same number (so the product is
@@ -963,26 +1001,48 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           }
         }
       };
-      score_phase(0);
-#pragma unroll
-      for (int half = 0; half < 4; ++half) {
-        const int T0 = 64 * gw + 16 * half;
-        float sv[NH][2];
-        const bool ok[2] = {true, true};
+      {
+        float sv[4][NH][2];
+        score_phase(0);
 #pragma unroll
         for (int nh = 0; nh < NH; ++nh) {
-          // columns 2c, 2c+1 of the tile: the hi and lo weight parts of the lane's head (heads
-          // beyond the group carry zero weights: finite scores nobody reads)
           const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
           const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
-          sv[nh][0] = s0 + (bias[nh] + corr[nh][16 * half]);
-          sv[nh][1] = s1 + (bias[nh] + corr[nh][16 * half + 8]);
+          sv[0][nh][0] = s0 + (bias[nh] + corr[nh][16 * 0]);
+          sv[0][nh][1] = s1 + (bias[nh] + corr[nh][16 * 0 + 8]);
         }
-        softmax16(sv, ok);
-        uint32_t pb0, pb1;
-        prob_frags(sv, norms[T0 + r], norms[T0 + r + 8], pb0, pb1);
-        if (half < 3) score_phase(half + 1);
-        value_phase(half, pb0, pb1);
+        score_phase(1);
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
+          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
+          sv[1][nh][0] = s0 + (bias[nh] + corr[nh][16 * 1]);
+          sv[1][nh][1] = s1 + (bias[nh] + corr[nh][16 * 1 + 8]);
+        }
+        score_phase(2);
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
+          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
+          sv[2][nh][0] = s0 + (bias[nh] + corr[nh][16 * 2]);
+          sv[2][nh][1] = s1 + (bias[nh] + corr[nh][16 * 2 + 8]);
+        }
+        score_phase(3);
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
+          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
+          sv[3][nh][0] = s0 + (bias[nh] + corr[nh][16 * 3]);
+          sv[3][nh][1] = s1 + (bias[nh] + corr[nh][16 * 3 + 8]);
+        }
+        softmax_many(sv);
+#pragma unroll
+        for (int half = 0; half < 4; ++half) {
+          const int T0 = 64 * gw + 16 * half;
+          uint32_t pb0, pb1;
+          prob_frags(sv[half], norms[T0 + r], norms[T0 + r + 8], pb0, pb1);
+          value_phase(half, pb0, pb1);
+        }
       }
     } else if (gw < htt / 16 && a.use_tmap) {
       // ---- hot tile, swizzled 16-bit rows: 8x8 matrix loads straight into fragments --------
