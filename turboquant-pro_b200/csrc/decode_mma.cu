@@ -37,7 +37,15 @@
 
 namespace {
 
-constexpr int GW = 4;                // warps per consumer group
+#ifndef TQ_GW
+#define TQ_GW 4
+#endif
+// warps per consumer group: 4 (three groups, 168 registers per thread); 8 (two groups, 128
+// registers) builds and runs but measured 30 % slower on the common geometry
+constexpr int GW = TQ_GW;
+constexpr int TPW = 256 / GW;        // tokens of a cold page per warp
+constexpr int HALVES = TPW / 16;     // 16-token tiles per warp and page
+static_assert(GW == 4 || GW == 8, "a warp owns 64 or 32 tokens of a page");
 constexpr int MAX_NG = 3;            // most consumer groups
 constexpr int MAX_UNITS = 512;
 constexpr int BLK = 256;             // tokens per cold page
@@ -174,8 +182,8 @@ struct SmemT {
   static constexpr int PLAN_BYTES = 8192;
   static constexpr int QC_BYTES = TQ_D * G * 4;  // [128][G] query values
   static constexpr int FRAG_BYTES = 8 * 32 * 16;  // [G/4 column groups][8 k-steps][32 lanes] x 8 B
-  static constexpr int BIAS_BYTES = 256;         // [8 heads][GW]: one partial per warp (+ spare)
-  static constexpr int CORR_STRIDE = 64 + 8;     // floats per query row: rows on different banks
+  static constexpr int BIAS_BYTES = 8 * GW * 4 + 128;  // [8 heads][GW]: a partial per warp (+ spare)
+  static constexpr int CORR_STRIDE = TPW + 8;    // floats per query row: rows on different banks
   static constexpr int CORR_BYTES = G * CORR_STRIDE * 4;  // per warp
   static constexpr int FRAG_OFF = QC_BYTES;
   static constexpr int BIAS_OFF = FRAG_OFF + FRAG_BYTES;
@@ -193,7 +201,7 @@ struct SmemT {
 // three groups when four stages still fit beside them (one page always in flight), else two
 template <int G, int VB>
 struct Cfg {
-  static constexpr int NG = SmemT<G, VB, 3>::NSTAGE >= 4 ? 3 : 2;
+  static constexpr int NG = GW == 8 ? 2 : (SmemT<G, VB, 3>::NSTAGE >= 4 ? 3 : 2);
   using SM = SmemT<G, VB, NG>;
   static_assert(SM::NSTAGE > NG, "a group refills a stage for a later tile of another group");
   static constexpr int CWT = NG * GW;  // consumer warps
@@ -579,12 +587,14 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     }
     float* pp = a.partials +
                 ((((size_t)u + blockIdx.x) * 2 + kind) * NG + gi) * (size_t)(G * TQ_PART_STRIDE);
+    if (gtid < TQ_D) {
 #pragma unroll
-    for (int gg = 0; gg < G; ++gg) {
-      float v = 0.0f;
+      for (int gg = 0; gg < G; ++gg) {
+        float v = 0.0f;
 #pragma unroll
-      for (int w = 0; w < MG_PAR; ++w) v += mg_acc[(w * G + gg) * MG_STRIDE + gtid];
-      pp[gg * TQ_PART_STRIDE + 2 + gtid] = v;
+        for (int w = 0; w < MG_PAR; ++w) v += mg_acc[(w * G + gg) * MG_STRIDE + gtid];
+        pp[gg * TQ_PART_STRIDE + 2 + gtid] = v;
+      }
     }
     if (gtid < G) {
       float M = NEG_BIG, L = 0.0f;
@@ -711,7 +721,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     }
     if (tl.u != q_unit) {  // new unit: reload its query rows
       q_unit = tl.u;
-      {
+      if (gtid < TQ_D) {
         // thread d of the group loads channel d of the G rows: coalesced, independent loads.
         // The softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
         // bias and corrections come out already scaled.
@@ -792,18 +802,19 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       // Outlier corrections of this warp's 64 tokens (a lane owns tokens lane and lane + 32 of
       // the strip).  The page keeps the first TQ_ELL_SLOTS outliers of every token in fixed
       // slots, so the common case is a fixed number of independent, conflict-free rounds.
-      float cacc[2][G];
+      constexpr int NI = TPW / 32;  // tokens of the strip per lane
+      float cacc[NI][G];
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < NI; ++i)
 #pragma unroll
         for (int gg = 0; gg < G; ++gg) cacc[i][gg] = 0.0f;
       if (!spilled) {
-        const uint16_t* ell_d = (const uint16_t*)(st + g.hdr_off + TQ_ELL_OFF) + 64 * gw + lane;
-        const uint8_t* ell_c = st + g.hdr_off + TQ_ELL_COL_OFF + 64 * gw + lane;
+        const uint16_t* ell_d = (const uint16_t*)(st + g.hdr_off + TQ_ELL_OFF) + TPW * gw + lane;
+        const uint8_t* ell_c = st + g.hdr_off + TQ_ELL_COL_OFF + TPW * gw + lane;
 #pragma unroll
         for (int j = 0; j < TQ_ELL_SLOTS; ++j) {
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < NI; ++i) {
             const float delta = __half2float(__ushort_as_half(ell_d[j * 256 + 32 * i]));
             const float* qrow = qc + (int)ell_c[j * 256 + 32 * i] * G;
             if (G >= 4) {
@@ -825,16 +836,18 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       // the widest channels of the page: their table rounding error, times a large
       // weight, would show in the scores, so it is added back here token by token
       {
-        const uint16_t* side = (const uint16_t*)(st + g.hdr_off + TQ_SIDE_OFF) + 64 * gw;
-        const uint32_t sd[2] = {side[lane], side[32 + lane]};
+        const uint16_t* side = (const uint16_t*)(st + g.hdr_off + TQ_SIDE_OFF) + TPW * gw;
+        uint32_t sd[NI];
+#pragma unroll
+        for (int i = 0; i < NI; ++i) sd[i] = side[32 * i + lane];
 #pragma unroll
         for (int j = 0; j < TQ_WIDE; ++j) {
           const int wch = hdr->wide[j];
           const float sc = scale[wch];
           const float* qrow = qc + q_row(wch) * G;
-          float dl[2];
+          float dl[NI];
 #pragma unroll
-          for (int i = 0; i < 2; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
+          for (int i = 0; i < NI; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
           float qv[G];
           if (G >= 4) {
 #pragma unroll
@@ -849,11 +862,11 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 #pragma unroll
           for (int gg = 0; gg < G; ++gg)
 #pragma unroll
-            for (int i = 0; i < 2; ++i) cacc[i][gg] += qv[gg] * dl[i];
+            for (int i = 0; i < NI; ++i) cacc[i][gg] += qv[gg] * dl[i];
         }
       }
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < NI; ++i)
 #pragma unroll
         for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + 32 * i + lane] = cacc[i][gg];
     };
@@ -862,8 +875,9 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       // list from the pool: a lane per entry, equal tokens summed across lanes by a segmented
       // reduction (fixed order, so the result does not depend on timing), and the first lane
       // of each token adds the sum to the strip.
-      const int s0 = spilled ? 0 : (int)hdr->ovf_start[gw];
-      const int s1 = spilled ? (int)hdr->cnt : (int)hdr->ovf_start[gw + 1];
+      // (the page lists its overflow entries by 64-token quarter)
+      const int s0 = spilled ? 0 : (int)hdr->ovf_start[(TPW * gw) >> 6];
+      const int s1 = spilled ? (int)hdr->cnt : (int)hdr->ovf_start[((TPW * gw) >> 6) + 1];
       if (s1 > s0) {
         const uint32_t* list =
             spilled ? a.pool_dec + (unit0 + tl.u) * (size_t)g.pool_entries + hdr->off
@@ -874,7 +888,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           const bool valid = e < s1;
           const uint32_t wv = valid ? list[e] : 0u;
           const int tok = valid ? (int)(wv >> 24) : -1 - lane;
-          const bool mine = valid && (tok >> 6) == gw;
+          const bool mine = valid && tok / TPW == gw;
           const float delta =
               mine ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
           const float* qrow = qc + q_row((wv >> 16) & 127) * G;
@@ -894,7 +908,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           const int prev = __shfl_up_sync(0xffffffffu, tok, 1);
           if (mine && (lane == 0 || prev != tok)) {
 #pragma unroll
-            for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + (tok & 63)] += pv[gg];
+            for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + (tok & (TPW - 1))] += pv[gg];
           }
         }
         __syncwarp();
@@ -922,8 +936,12 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       const float* corr[NH];
 #pragma unroll
       for (int nh = 0; nh < NH; ++nh) {
-        const float4 b4 = *(const float4*)(bias_s + hc[nh] * GW);
-        bias[nh] = (b4.x + b4.y) + (b4.z + b4.w);
+        bias[nh] = 0.0f;
+#pragma unroll
+        for (int w4 = 0; w4 < GW / 4; ++w4) {
+          const float4 b4 = *(const float4*)(bias_s + hc[nh] * GW + 4 * w4);
+          bias[nh] += (b4.x + b4.y) + (b4.z + b4.w);
+        }
         corr[nh] = corr_w + hc[nh] * SM::CORR_STRIDE + r;
       }
       const float* norms = (const float*)(st + g.norm_off);
@@ -935,7 +953,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       // scheduler can fill the lookup and tensor-core latencies of one with the other.
       float C[NH][2][4];
       auto score_phase = [&](int half) {
-        const int T0 = 64 * gw + 16 * half;
+        const int T0 = TPW * gw + 16 * half;
         uint32_t kw[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
@@ -962,7 +980,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         }
       };
       auto value_phase = [&](int half, uint32_t pb0, uint32_t pb1) {
-        const int gq = 4 * gw + half;
+        const int gq = HALVES * gw + half;
         if (VB == 4) {
           const uint8_t* gb = vcodes + gq * 1024 + lane * 16;
           const uint4 r0 = *(const uint4*)gb, r1 = *(const uint4*)(gb + 512);
@@ -1002,43 +1020,24 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         }
       };
       {
-        float sv[4][NH][2];
-        score_phase(0);
+        float sv[HALVES][NH][2];
 #pragma unroll
-        for (int nh = 0; nh < NH; ++nh) {
-          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
-          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
-          sv[0][nh][0] = s0 + (bias[nh] + corr[nh][16 * 0]);
-          sv[0][nh][1] = s1 + (bias[nh] + corr[nh][16 * 0 + 8]);
-        }
-        score_phase(1);
+        for (int half = 0; half < HALVES; ++half) {
+          score_phase(half);
 #pragma unroll
-        for (int nh = 0; nh < NH; ++nh) {
-          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
-          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
-          sv[1][nh][0] = s0 + (bias[nh] + corr[nh][16 * 1]);
-          sv[1][nh][1] = s1 + (bias[nh] + corr[nh][16 * 1 + 8]);
-        }
-        score_phase(2);
-#pragma unroll
-        for (int nh = 0; nh < NH; ++nh) {
-          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
-          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
-          sv[2][nh][0] = s0 + (bias[nh] + corr[nh][16 * 2]);
-          sv[2][nh][1] = s1 + (bias[nh] + corr[nh][16 * 2 + 8]);
-        }
-        score_phase(3);
-#pragma unroll
-        for (int nh = 0; nh < NH; ++nh) {
-          const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
-          const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
-          sv[3][nh][0] = s0 + (bias[nh] + corr[nh][16 * 3]);
-          sv[3][nh][1] = s1 + (bias[nh] + corr[nh][16 * 3 + 8]);
+          for (int nh = 0; nh < NH; ++nh) {
+            // columns 2c, 2c+1 of the tile: the hi and lo weight parts of the lane's head (heads
+            // beyond the group carry zero weights: finite scores nobody reads)
+            const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
+            const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
+            sv[half][nh][0] = s0 + (bias[nh] + corr[nh][16 * half]);
+            sv[half][nh][1] = s1 + (bias[nh] + corr[nh][16 * half + 8]);
+          }
         }
         softmax_many(sv);
 #pragma unroll
-        for (int half = 0; half < 4; ++half) {
-          const int T0 = 64 * gw + 16 * half;
+        for (int half = 0; half < HALVES; ++half) {
+          const int T0 = TPW * gw + 16 * half;
           uint32_t pb0, pb1;
           prob_frags(sv[half], norms[T0 + r], norms[T0 + r + 8], pb0, pb1);
           value_phase(half, pb0, pb1);
