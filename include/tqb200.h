@@ -203,6 +203,28 @@ int32_t tq_export_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
                         int32_t* n_outliers, uint8_t* value_indices, float* value_norms,
                         void* stream);
 
+/* The inverse of tq_export_block: writes cold block `block` of (layer, seq) from HOST arrays in
+ * the reference's container layout (same arrays and orders as tq_export_block; key_mean is
+ * the full [H*D] zero-point, zeros for symmetric NF4), i.e. what the reference's connector
+ * reads back from a stored block (connectors/vllm_v1.py:150-196) without going through dense
+ * tensors.  The cache of (layer, seq) must be cleared (length 0); blocks may be imported in
+ * any order; tq_restore_hot then sets the length.  TQ_ERR_CAPACITY when the block or its
+ * outliers do not fit.  Synchronises `stream`. */
+int32_t tq_import_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
+                        const uint8_t* key_indices, const float* key_scale, const float* key_mean,
+                        const int32_t* outlier_idx, const uint16_t* outlier_val,
+                        int32_t n_outliers, const uint8_t* value_indices,
+                        const float* value_norms, void* stream);
+
+/* Completes a restore: (layer, seq) holds `n_tokens` tokens, of which the cold blocks were
+ * imported with tq_import_block and the newest n_tokens - 256 * n_cold_blocks are given here
+ * as DEVICE arrays hot_k / hot_v [tokens][n_kv_heads][128] of the context's K/V dtype, with
+ * element strides tok_stride / head_stride (the hot window of TurboQuantKVCache,
+ * core.py:986-1030, which the reference keeps uncompressed). */
+int32_t tq_restore_hot(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t n_tokens,
+                       const void* hot_k, const void* hot_v, int64_t tok_stride,
+                       int64_t head_stride, void* stream);
+
 /* Tokens currently held by (layer, seq): total, in cold blocks, in the hot window
  * (TurboQuantKVCache.length / cold_length / hot_length, core.py:971-984). */
 int32_t tq_seq_lengths(const tq_ctx* ctx, int32_t layer, int32_t seq, int32_t* total,

@@ -100,3 +100,41 @@ def test_reader_refusals():
     np.savez(buf, **members)
     with pytest.raises(ValueError, match="unexpected member"):
         blob_to_block(buf.getvalue())
+
+
+def test_parsed_blob_gives_back_the_container_arrays():
+    """blob -> arrays for KVContext.import_block: the reference's blob yields exactly the
+    oracle's containers; the other zero-point forms are brought back to full scale / mean."""
+    from turboquant_pro_b200.kv_blob import block_from_parsed
+
+    g = load_golden("blob_ref.npz")
+    want = _oracle_block(g)
+    got = block_from_parsed(blob_to_block(g["blob"].tobytes()), geom=(2, 8, 128, 3))
+    for name in ("key_indices", "nf4_scale", "nf4_mean", "outlier_idx", "value_indices",
+                 "value_norms"):
+        assert np.array_equal(np.asarray(got[name]).reshape(-1),
+                              np.asarray(want[name]).reshape(-1)), name
+    assert np.array_equal(np.asarray(got["outlier_val"]).view(np.uint16),
+                          np.asarray(want["outlier_val"]).view(np.uint16))
+    with pytest.raises(ValueError):
+        block_from_parsed(blob_to_block(g["blob"].tobytes()), geom=(2, 8, 128, 4))
+    with pytest.raises(ValueError):  # an NF4 blob into a context with the uniform grid
+        block_from_parsed(blob_to_block(g["blob"].tobytes()), key_mode="uniform")
+    mask = np.arange(128) % 2 == 0
+    sparse = blob_to_block(block_to_blob(want, zero_point="sparse", mean_mask=mask, rope_theta=1e4))
+    back = block_from_parsed(sparse, mean_mask=mask)
+    assert np.array_equal(back["nf4_mean"][..., mask], want["nf4_mean"][..., mask])
+    assert not back["nf4_mean"][..., ~mask].any()
+    with pytest.raises(ValueError):
+        block_from_parsed(sparse)
+    bias = blob_to_block(block_to_blob(want, zero_point="bias", rope_theta=1e4))
+    with pytest.raises(ValueError):
+        block_from_parsed(bias)
+    given = np.full((2, 128), 0.25, np.float32)
+    assert np.array_equal(block_from_parsed(bias, bias_means=given)["nf4_mean"][0], given)
+    uni = blob_to_block(block_to_blob(want, key_mode="uniform"))
+    back = block_from_parsed(uni, key_mode="uniform")
+    assert np.array_equal(back["nf4_scale"], want["nf4_scale"])
+    assert np.array_equal(back["nf4_mean"], want["nf4_mean"])
+    sym = blob_to_block(block_to_blob(want, key_mode="nf4"))
+    assert not block_from_parsed(sym, key_mode="nf4")["nf4_mean"].any()

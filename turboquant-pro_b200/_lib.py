@@ -79,6 +79,11 @@ SIGNATURES = {
     "tq_export_block": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                     C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tq_import_block": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                    C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tq_restore_hot": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                   C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "tq_seq_lengths": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32),
                                    C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "tq_memory_stats": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_double),

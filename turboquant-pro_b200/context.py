@@ -340,6 +340,73 @@ class KVContext:
                              rope_theta=rope_theta,
                              position_start=block * self.geom.block_tokens, dtype=dt)
 
+    def import_block(self, layer: int, seq: int, block: int, blk: dict) -> None:
+        """The inverse of :meth:`export_block`: writes cold block ``block`` of a cleared cache
+        from the container arrays (``nf4_mean`` is the full ``(1, H, D)`` zero-point).
+        :meth:`restore_hot` then sets the length."""
+        g = self.geom
+        h, s, d = g.n_kv_heads, g.block_tokens, g.head_dim
+        key_idx = np.ascontiguousarray(blk["key_indices"], dtype=np.uint8).reshape(-1)
+        scale = np.ascontiguousarray(blk["nf4_scale"], dtype=np.float32).reshape(-1)
+        mean = np.ascontiguousarray(blk["nf4_mean"], dtype=np.float32).reshape(-1)
+        val_idx = np.ascontiguousarray(blk["value_indices"], dtype=np.uint8).reshape(-1)
+        norms = np.ascontiguousarray(blk["value_norms"], dtype=np.float32).reshape(-1)
+        if key_idx.size != h * s * d // 2 or scale.size != h * d or mean.size != h * d \
+                or val_idx.size != h * s * d * g.value_bits // 8 or norms.size != h * s:
+            raise ValueError("container arrays do not match this context's block shape "
+                             f"(H={h}, S={s}, D={d}, value_bits={g.value_bits})")
+        oidx = blk.get("outlier_idx")
+        n_out = 0
+        if oidx is not None and len(oidx):
+            oidx = np.ascontiguousarray(oidx, dtype=np.int32)
+            oval = np.ascontiguousarray(blk["outlier_val"]).view(np.uint16).reshape(-1)
+            if oval.size != oidx.size:
+                raise ValueError("outlier_idx and outlier_val differ in length")
+            n_out = int(oidx.size)
+        with _torch().cuda.device(self.device):
+            check(self._lib.tq_import_block(
+                self._h, layer, seq, block, key_idx.ctypes.data, scale.ctypes.data,
+                mean.ctypes.data, oidx.ctypes.data if n_out else None,
+                oval.ctypes.data if n_out else None, n_out, val_idx.ctypes.data,
+                norms.ctypes.data, self._stream()))
+
+    def restore_hot(self, layer: int, seq: int, n_tokens: int, hot_k, hot_v) -> None:
+        """Completes a restore: the cache holds ``n_tokens`` tokens, its cold blocks were
+        imported, and ``hot_k`` / ``hot_v`` (tensors ``[tokens, n_kv_heads, D]``) are the tokens after the last cold block."""
+        torch = _torch()
+        g = self.geom
+        n_hot = n_tokens - self.cold_blocks(n_tokens) * g.block_tokens
+        for t in (hot_k, hot_v):
+            if tuple(t.shape) != (n_hot, g.n_kv_heads, g.head_dim):
+                raise ValueError(f"expected hot tensors of shape "
+                                 f"{(n_hot, g.n_kv_heads, g.head_dim)}, got {tuple(t.shape)}")
+        k = hot_k.to(device=self.device, dtype=self.kv_dtype).contiguous()
+        v = hot_v.to(device=self.device, dtype=self.kv_dtype).contiguous()
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_restore_hot(self._h, layer, seq, n_tokens, k.data_ptr(),
+                                           v.data_ptr(), k.stride(0), k.stride(1),
+                                           self._stream()))
+
+    def cold_blocks(self, n_tokens: int) -> int:
+        """Cold blocks of a cache that holds ``n_tokens`` tokens (the reference's flush rule:
+        the oldest half of an over-full hot window becomes a block)."""
+        g = self.geom
+        return 0 if n_tokens <= g.hot_window else 1 + (n_tokens - g.hot_window - 1) // g.block_tokens
+
+    def import_blob(self, layer: int, seq: int, block: int, blob: bytes,
+                    bias_means=None) -> None:
+        """Writes cold block ``block`` from a ``tqp-kv-npz/1`` byte string (see
+        :mod:`turboquant_pro_b200.kv_blob`).  A blob with the ``sparse`` zero-point needs this
+        context's channel mask (:meth:`set_key_mean_mask`); one with the ``bias`` zero-point
+        stores no means, so ``bias_means`` ``(n_kv_heads, D)`` of this block must be given."""
+        from .kv_blob import blob_to_block, block_from_parsed
+
+        parsed = blob_to_block(blob)
+        self.import_block(layer, seq, block, block_from_parsed(
+            parsed, key_mode=self.key_mode, mean_mask=self.key_mean_mask, bias_means=bias_means,
+            geom=(self.geom.n_kv_heads, self.geom.block_tokens, self.geom.head_dim,
+                  self.geom.value_bits)))
+
     # -- bookkeeping -----------------------------------------------------------------
     def lengths(self, layer: int, seq: int):
         """(total, cold, hot) token counts of one cache."""

@@ -6,6 +6,24 @@
 
 #include "common.cuh"
 
+// the NF4 levels (float32), as the reference's table holds them
+static const float nf4[16] = {-1.0f,
+    -0.6961928009986877f,
+    -0.5250730514526367f,
+    -0.39491748809814453f,
+    -0.28444138169288635f,
+    -0.18477343022823334f,
+    -0.09105003625154495f,
+    0.0f,
+    0.07958029955625534f,
+    0.16093020141124725f,
+    0.24611230194568634f,
+    0.33791524171829224f,
+    0.44070982933044434f,
+    0.5626170039176941f,
+    0.7229568362236023f,
+    1.0f};
+
 static thread_local std::string g_last_error;
 
 void tq_set_error(const std::string& msg) { g_last_error = msg; }
@@ -151,22 +169,6 @@ int32_t tq_ctx_create(const tq_geom* g, const tq_buffers* bufs, int32_t device, 
     t->centroids[i] = i < nc ? centroids[i] : 0.0f;
     t->boundaries[i] = i < nc - 1 ? boundaries[i] : INFINITY;
   }
-  static const float nf4[16] = {-1.0f,
-                                -0.6961928009986877f,
-                                -0.5250730514526367f,
-                                -0.39491748809814453f,
-                                -0.28444138169288635f,
-                                -0.18477343022823334f,
-                                -0.09105003625154495f,
-                                0.0f,
-                                0.07958029955625534f,
-                                0.16093020141124725f,
-                                0.24611230194568634f,
-                                0.33791524171829224f,
-                                0.44070982933044434f,
-                                0.5626170039176941f,
-                                0.7229568362236023f,
-                                1.0f};
   for (int i = 0; i < 16; ++i) t->grid[i] = g->key_mode == TQ_KEYS_UNIFORM ? (float)i : nf4[i];
   std::memset(t->mean_mask, 1, sizeof(t->mean_mask));
   cudaError_t e = cudaMemcpyAsync(bufs->tables, t, sizeof(Tables), cudaMemcpyHostToDevice, st);
@@ -464,6 +466,210 @@ int32_t tq_export_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
       if (outlier_val) outlier_val[i] = ent[i].second;
     }
   }
+  return TQ_OK;
+}
+
+// Writes code (t, d) of a 16-token group into its records (the inverse of v_get_code; the
+// group's bytes start zeroed).
+static void v_put_code(uint8_t* grp, int bits, int t, int d, int code) {
+  const int l = v_lane(t, d), p = v_pair(t, d), odd = t & 1;
+  if (bits == 4) {
+    grp[v_record_byte_off(4, l, p)] |= (uint8_t)(code << (odd * 4));
+    return;
+  }
+  const int bit = 6 * p + 3 * odd;
+  const int w = code << (bit & 7);
+  grp[v_record_byte_off(3, l, bit >> 3)] |= (uint8_t)w;
+  if ((w >> 8) != 0) grp[v_record_byte_off(3, l, (bit >> 3) + 1)] |= (uint8_t)(w >> 8);
+}
+
+int32_t tq_import_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
+                        const uint8_t* key_indices, const float* key_scale, const float* key_mean,
+                        const int32_t* outlier_idx, const uint16_t* outlier_val,
+                        int32_t n_outliers, const uint8_t* value_indices,
+                        const float* value_norms, void* stream) {
+  TQ_REQUIRE(good_ctx(ctx, layer), TQ_ERR_INVALID, "bad context or layer");
+  const tq_geom& g = ctx->g;
+  TQ_REQUIRE(seq >= 0 && seq < g.n_seqs, TQ_ERR_INVALID, "bad sequence");
+  TQ_REQUIRE(ctx->len[(size_t)layer * g.n_seqs + seq] == 0, TQ_ERR_INVALID,
+             "blocks are imported into a cleared cache, before tq_restore_hot sets its length");
+  TQ_REQUIRE(block >= 0 && block < g.max_blocks, TQ_ERR_CAPACITY, "block index out of range");
+  TQ_REQUIRE(key_indices && key_scale && key_mean && value_indices && value_norms,
+             TQ_ERR_INVALID, "null container array");
+  TQ_REQUIRE(n_outliers >= 0 && (n_outliers == 0 || (outlier_idx && outlier_val)),
+             TQ_ERR_INVALID, "outlier arrays missing");
+  const int H = g.n_kv_heads, S = g.block_tokens, D = TQ_D, vb = g.value_bits;
+  for (int i = 0; i < n_outliers; ++i) {
+    TQ_REQUIRE(outlier_idx[i] >= 0 && outlier_idx[i] < H * S * D &&
+                   (i == 0 || outlier_idx[i] > outlier_idx[i - 1]),
+               TQ_ERR_INVALID, "outlier indices must ascend inside the (H, S, D) block");
+  }
+  TQ_CUDA(cudaSetDevice(ctx->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* cursor_d = (uint32_t*)((uint8_t*)ctx->b.state + state_cursor_off(g)) +
+                       unit_index(g, layer, seq, 0);
+  std::vector<uint32_t> cursor(H);
+  TQ_CUDA(cudaMemcpyAsync(cursor.data(), cursor_d, H * 4, cudaMemcpyDeviceToHost, st));
+  TQ_CUDA(cudaStreamSynchronize(st));
+
+  std::vector<uint8_t> pages((size_t)H * g.page_bytes, 0);
+  std::vector<PageMeta> meta(H);
+  std::vector<std::vector<uint32_t>> dec(H);
+  std::vector<std::vector<uint16_t>> val(H);
+  bool pool_short = false;
+  int oi = 0;  // position in the outlier arrays (sorted by head, token, channel)
+  for (int h = 0; h < H; ++h) {
+    uint8_t* pg = pages.data() + (size_t)h * g.page_bytes;
+    // key codes: the container holds bit-reversed nibbles, first channel of a pair on top
+    for (int s = 0; s < S; ++s)
+      for (int j = 0; j < D / 2; ++j) {
+        const uint8_t b = key_indices[((size_t)h * S + s) * (D / 2) + j];
+        pg[s * (D / 2) + j] = (uint8_t)(rev4(b >> 4) | (rev4(b & 15) << 4));
+      }
+    float* scale = (float*)(pg + g.scale_off);
+    float* mean = (float*)(pg + g.mean_off);
+    std::memcpy(scale, key_scale + (size_t)h * D, D * 4);
+    std::memcpy(mean, key_mean + (size_t)h * D, D * 4);
+    std::memcpy(pg + g.norm_off, value_norms + (size_t)h * S, S * 4);
+    // value codes: LSB-first bit stream over (token, channel) -> tensor-core records
+    {
+      const uint8_t* src = value_indices + (size_t)h * S * D * vb / 8;
+      uint8_t* vpg = pg + g.v_off;
+      for (int s = 0; s < S; ++s) {
+        uint8_t* grp = vpg + (size_t)(s / TQ_GROUP_TOK) * v_group_bytes(vb);
+        for (int d = 0; d < D; ++d) {
+          const size_t bit = ((size_t)s * D + d) * vb;
+          int w = src[bit >> 3];
+          if ((bit & 7) + vb > 8) w |= src[(bit >> 3) + 1] << 8;
+          v_put_code(grp, vb, s % TQ_GROUP_TOK, d, (w >> (bit & 7)) & ((1 << vb) - 1));
+        }
+      }
+    }
+    // header: the four widest channels (largest scale first, ties to the lower channel) and
+    // a second copy of their codes, token by token
+    PageHeader* hdr = (PageHeader*)(pg + g.hdr_off);
+    {
+      int order[TQ_D];
+      for (int d = 0; d < D; ++d) order[d] = d;
+      std::stable_sort(order, order + D, [&](int x, int y) { return scale[x] > scale[y]; });
+      uint16_t* side = (uint16_t*)(pg + g.hdr_off + TQ_SIDE_OFF);
+      for (int rk = 0; rk < TQ_WIDE; ++rk) {
+        const int d = order[rk];
+        hdr->wide[rk] = (uint8_t)d;
+        for (int t = 0; t < S; ++t) {
+          const int code = (pg[t * (D / 2) + (d >> 1)] >> (4 * (d & 1))) & 15;
+          side[t] |= (uint16_t)(code << (4 * rk));
+        }
+      }
+    }
+    // outliers of this head, grouped by token: the first TQ_ELL_SLOTS of a token go to its
+    // fixed slots, the rest to the page's overflow list; all of them to the pool
+    const int first = oi;
+    while (oi < n_outliers && outlier_idx[oi] < (h + 1) * S * D) ++oi;
+    const int n = oi - first;
+    uint16_t* ell_delta = (uint16_t*)(pg + g.hdr_off + TQ_ELL_OFF);
+    uint8_t* ell_col = pg + g.hdr_off + TQ_ELL_COL_OFF;
+    uint32_t* ovf = (uint32_t*)(pg + g.hdr_off + TQ_OVF_OFF);
+    int n_ovf = 0, tok_prev = -1, in_tok = 0;
+    uint16_t ovf_start[5] = {0, 0, 0, 0, 0};
+    dec[h].resize(n);
+    val[h].resize(n);
+    for (int i = 0; i < n; ++i) {
+      const int flat = outlier_idx[first + i] - h * S * D;
+      const int t = flat / D, d = flat % D;
+      in_tok = t == tok_prev ? in_tok + 1 : 0;
+      tok_prev = t;
+      const int code = (pg[t * (D / 2) + (d >> 1)] >> (4 * (d & 1))) & 15;
+      const float gl = g.key_mode == TQ_KEYS_UNIFORM ? (float)code : nf4[code];
+      volatile float sl = scale[d] * gl;  // rounded to float32 on its own, like the encoder
+      volatile float dense = g.key_mode == TQ_KEYS_NF4 ? (float)sl : mean[d] + sl;
+      const __half hv = __ushort_as_half(outlier_val[first + i]);
+      volatile float diff = __half2float(hv) - dense;
+      const uint16_t delta = __half_as_ushort(__float2half_rn(diff));
+      const uint32_t ent = (uint32_t)delta | ((uint32_t)d << 16) | ((uint32_t)t << 24);
+      dec[h][i] = ent;
+      val[h][i] = outlier_val[first + i];
+      if (in_tok < TQ_ELL_SLOTS) {
+        ell_delta[in_tok * 256 + t] = delta;
+        ell_col[in_tok * 256 + t] = (uint8_t)q_row(d);
+      } else {
+        // (entries are visited in token order, so the list comes out ordered by token)
+        for (int q4 = t / 64 + 1; q4 < 5; ++q4) ++ovf_start[q4];
+        if (n_ovf < TQ_OVF_CAP) ovf[n_ovf] = ent;
+        ++n_ovf;
+      }
+    }
+    for (int q4 = 0; q4 < 5; ++q4) hdr->ovf_start[q4] = (uint16_t)std::min<int>(ovf_start[q4], TQ_OVF_CAP);
+    hdr->ovf_n = (uint16_t)std::min(n_ovf, TQ_OVF_CAP);
+    // the page's slice of the (layer, seq, head) pool slab, allocated like the encoder does
+    uint32_t off = 0;
+    int alloc = 0;
+    if (n > 0) {
+      const int n4 = (n + 3) & ~3;
+      off = cursor[h];
+      cursor[h] += (uint32_t)n4;
+      if (off >= (uint32_t)g.pool_entries) {
+        off = 0;
+      } else {
+        alloc = std::min(n4, g.pool_entries - (int)off);
+      }
+      if (alloc < n4) pool_short = true;
+    }
+    meta[h].off = off;
+    meta[h].cnt = (uint32_t)std::min(n, alloc);
+    hdr->off = meta[h].off;
+    hdr->cnt = meta[h].cnt;
+    hdr->flags = (n_ovf > TQ_OVF_CAP || alloc < n) ? TQ_PAGE_SPILLED : 0;
+  }
+  // upload: pages, page metadata, pool entries, cursors
+  for (int h = 0; h < H; ++h) {
+    TQ_CUDA(cudaMemcpyAsync((uint8_t*)ctx->b.pages + page_offset(g, layer, seq, h, block),
+                            pages.data() + (size_t)h * g.page_bytes, g.page_bytes,
+                            cudaMemcpyHostToDevice, st));
+    const size_t mi = unit_index(g, layer, seq, h) * g.max_blocks + block;
+    TQ_CUDA(cudaMemcpyAsync((PageMeta*)ctx->b.page_meta + mi, &meta[h], sizeof(PageMeta),
+                            cudaMemcpyHostToDevice, st));
+    if (meta[h].cnt > 0) {
+      const size_t slab = unit_index(g, layer, seq, h) * (size_t)g.pool_entries + meta[h].off;
+      TQ_CUDA(cudaMemcpyAsync((uint32_t*)ctx->b.pool_dec + slab, dec[h].data(), meta[h].cnt * 4,
+                              cudaMemcpyHostToDevice, st));
+      TQ_CUDA(cudaMemcpyAsync((uint16_t*)ctx->b.pool_val + slab, val[h].data(), meta[h].cnt * 2,
+                              cudaMemcpyHostToDevice, st));
+    }
+  }
+  TQ_CUDA(cudaMemcpyAsync(cursor_d, cursor.data(), H * 4, cudaMemcpyHostToDevice, st));
+  TQ_CUDA(cudaStreamSynchronize(st));  // the staging vectors go out of scope
+  TQ_REQUIRE(!pool_short, TQ_ERR_CAPACITY, "the outlier pool of this sequence is full");
+  return TQ_OK;
+}
+
+int32_t tq_restore_hot(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t n_tokens,
+                       const void* hot_k, const void* hot_v, int64_t tok_stride,
+                       int64_t head_stride, void* stream) {
+  TQ_REQUIRE(good_ctx(ctx, layer), TQ_ERR_INVALID, "bad context or layer");
+  const tq_geom& g = ctx->g;
+  TQ_REQUIRE(seq >= 0 && seq < g.n_seqs, TQ_ERR_INVALID, "bad sequence");
+  int32_t& len = ctx->len[(size_t)layer * g.n_seqs + seq];
+  TQ_REQUIRE(len == 0, TQ_ERR_INVALID, "the cache must be cleared before it is restored");
+  TQ_REQUIRE(n_tokens >= 0 && n_tokens <= g.max_tokens_per_seq, TQ_ERR_CAPACITY,
+             "n_tokens exceeds max_tokens_per_seq");
+  if (n_tokens == 0) return TQ_OK;
+  const int nb = n_cold_blocks(n_tokens, g.hot_window, g.block_tokens);
+  TQ_REQUIRE(nb <= g.max_blocks, TQ_ERR_CAPACITY, "more cold blocks than the context holds");
+  const int hot_start = nb * g.block_tokens, hot_n = n_tokens - hot_start;
+  TQ_REQUIRE(hot_k != nullptr && hot_v != nullptr, TQ_ERR_INVALID,
+             "hot_k and hot_v must be device pointers");
+  TQ_CUDA(cudaSetDevice(ctx->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  // the ring writer places tokens by position: start it at the first hot position, with no
+  // new cold blocks to encode
+  int32_t* len_d = (int32_t*)((uint8_t*)ctx->b.state + state_len_off(g)) + layer * g.n_seqs + seq;
+  TQ_CUDA(cudaMemcpyAsync(len_d, &hot_start, 4, cudaMemcpyHostToDevice, st));
+  TQ_CUDA(cudaStreamSynchronize(st));  // (hot_start is a stack variable)
+  int rc = tq_launch_encode(ctx, layer, seq, 1, hot_k, hot_v, hot_n, 0, tok_stride, head_stride,
+                            0, st);
+  if (rc != TQ_OK) return rc;
+  len = n_tokens;
   return TQ_OK;
 }
 

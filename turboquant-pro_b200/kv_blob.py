@@ -8,7 +8,8 @@ produced here can be consumed by the reference and the other way round.  No pick
 involved in either direction; the reader refuses what it does not know instead of guessing
 (codec string, size limits, dtype whitelist), as the reference's reader does.
 
-Not covered: loading a blob back into device pages.
+``block_from_parsed`` turns a parsed blob back into the arrays ``KVContext.import_block``
+takes, so a stored block goes into device pages without passing through dense tensors.
 """
 
 from __future__ import annotations
@@ -21,7 +22,7 @@ import numpy as np
 CODEC = "tqp-kv-npz/1"
 _OK_DTYPES = {"uint8", "int8", "int16", "int32", "int64", "float16", "float32", "float64", "bool"}
 
-__all__ = ["CODEC", "block_to_blob", "blob_to_block"]
+__all__ = ["CODEC", "block_to_blob", "blob_to_block", "block_from_parsed"]
 
 
 def _tuple(v):
@@ -141,3 +142,63 @@ def blob_to_block(blob: bytes, max_bytes: int = 1 << 30) -> dict:
     meta = {k: header[k] for k in ("codec", "shape", "dtype", "num_tokens", "head_dim", "n_heads")}
     meta["shape"] = tuple(meta["shape"])
     return {"header": meta, "key": key, "value": value}
+
+
+def block_from_parsed(parsed: dict, *, key_mode: str = "nf4_asym", mean_mask=None,
+                      bias_means=None, geom=None) -> dict:
+    """The arrays of ``KVContext.import_block`` from the result of :func:`blob_to_block`.
+
+    The key scalars are brought back to one full ``(1, H, D)`` scale and zero-point: the
+    uniform grid's ``scale`` / ``zero``; symmetric NF4 with zeros; the ``sparse`` zero-point
+    scattered to the ``mean_mask`` channels; the ``bias`` zero-point from ``bias_means``
+    ``(H, D)`` (the blob stores none: the reader recomputes it from the model's k-bias, the
+    block's first position and ``rope_theta``).  ``geom`` ``(H, S, D, value_bits)``, when given,
+    is checked against the blob's header.
+    """
+    key, value, meta = parsed["key"], parsed["value"], parsed["header"]
+    _, h, s, d = meta["shape"]
+    if geom is not None and (h, s, d, int(value["bits"])) != tuple(geom):
+        raise ValueError(f"blob holds a block of (H, S, D, value_bits) = "
+                         f"{(h, s, d, int(value['bits']))}, the context expects {tuple(geom)}")
+    if int(key["bits"]) != 4 or not key.get("packed", True) or not value.get("packed", True):
+        raise ValueError("only packed blocks with 4-bit keys can be imported")
+    uniform = "scale" in key and key.get("nf4_scale") is None
+    if uniform != (key_mode == "uniform"):
+        raise ValueError("the blob's key grid differs from the context's key_mode")
+    if uniform:
+        scale = np.asarray(key["scale"], np.float32).reshape(1, h, d)
+        mean = np.asarray(key["zero"], np.float32).reshape(1, h, d)
+    else:
+        scale = np.asarray(key["nf4_scale"], np.float32).reshape(1, h, d)
+        zp = key.get("zp_mode", "calibrated")
+        stored = key.get("nf4_mean")
+        if key_mode == "nf4":
+            if stored is not None:
+                raise ValueError("the blob holds key means, the context is symmetric NF4")
+            mean = np.zeros((1, h, d), np.float32)
+        elif zp == "sparse":
+            if mean_mask is None:
+                raise ValueError("a sparse zero-point needs the context's channel mask")
+            mask = np.asarray(mean_mask, bool)
+            stored = np.asarray(stored, np.float32)
+            if stored.shape[-1] != int(mask.sum()):
+                raise ValueError("the blob's sparse means do not match the channel mask")
+            mean = np.zeros((1, h, d), np.float32)
+            mean[:, :, mask] = stored.reshape(1, h, -1)
+        elif zp == "bias":
+            if bias_means is None:
+                raise ValueError("a bias zero-point stores no means: pass bias_means")
+            mean = np.asarray(bias_means, np.float32).reshape(1, h, d)
+        else:
+            if stored is None:
+                raise ValueError("the blob holds no key means, the context expects them")
+            mean = np.asarray(stored, np.float32).reshape(1, h, d)
+    oidx = key.get("outlier_idx")
+    return {
+        "key_indices": np.asarray(key["indices"], np.uint8), "nf4_scale": scale, "nf4_mean": mean,
+        "outlier_idx": None if oidx is None else np.asarray(oidx, np.int32),
+        "outlier_val": None if oidx is None else np.asarray(key["outlier_val"]),
+        "value_indices": np.asarray(value["indices"], np.uint8),
+        "value_norms": np.asarray(value["norms"], np.float32),
+        "shape": (1, h, s, d), "key_bits": 4, "value_bits": int(value["bits"]),
+    }
