@@ -162,3 +162,20 @@ def test_fused_form_equals_dequantise_then_attend():
     out = orc.merge_partials(parts)
     assert np.allclose(out, g["attn"], atol=2e-4)
     assert np.allclose(out, g["fused"], atol=2e-5)
+
+
+def test_unfused_rotation_stays_within_the_encoder_slack():
+    """The value encoder on the GPU first rotates with fused multiply-adds and recomputes a
+    coordinate in the reference's unfused order only where a boundary lies within 4e-5 of it.
+    That is sound if the unfused float32 result is within 7.7e-6 of the exact dot product
+    (so is the fused one); measured here on random unit vectors it is ~50x inside."""
+    rng = np.random.default_rng(0)
+    pi, pi_t = orc.rotation(128, 3)
+    x = rng.standard_normal((4, 64, 128)).astype(np.float32)
+    x[0, 0] = 0.0
+    x[0, 1, 5] = 1e4  # one dominant coordinate
+    unit = (x / np.maximum(np.linalg.norm(x, axis=-1, keepdims=True), 1e-30)).astype(np.float32)
+    y32 = orc._rotate(unit, pi_t)
+    y64 = unit.astype(np.float64) @ pi_t.astype(np.float64)
+    assert np.abs(y32 - y64).max() < 7.7e-6
+    assert np.abs(np.linalg.norm(pi.astype(np.float64), axis=1) - 1.0).max() < 1e-5

@@ -37,9 +37,14 @@ struct TokenSource {
   const void* in;
   int n0, cap;
   int64_t tok_stride;
+  // one load from a selected address (no branch: loads of several positions can then be
+  // in flight together)
   TQ_DEV float ld(int pos, int d) const {
-    if (pos < n0) return Elem<DT>::ld(ring, (size_t)(pos % cap) * TQ_D + d);
-    return Elem<DT>::ld(in, (size_t)(pos - n0) * tok_stride + d);
+    const bool old = pos < n0;
+    const void* base = old ? ring : in;
+    const size_t idx =
+        old ? (size_t)(pos % cap) * TQ_D + d : (size_t)(pos - n0) * tok_stride + d;
+    return Elem<DT>::ld(base, idx);
   }
 };
 
@@ -314,38 +319,36 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 
 // ---------------------------------------------------------------------------------------
 // Rotation of 16 vectors held transposed in shared memory (us[d][t]) by column e of the
-// matrix in shared memory (pit[d][e]): acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every
-// product and sum rounded to float32 separately.  The loop is kept rolled (a fully unrolled
-// body does not fit the instruction cache) and each step issues its 16 independent products
-// before the 16 sums that depend on them.
-// ---------------------------------------------------------------------------------------
-TQ_DEV void rotate16(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, float* acc) {
-  {
-    const float p = pit[e];
+// matrix in shared memory (pit[d][e]).  The reference's result is the unfused sequential sum
+// acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every product and sum rounded to float32
+// separately (rotate_one below).  rotate16_fused is the same sum with fused multiply-adds:
+// half the arithmetic, and a result within ROT_SLACK of the unfused one.  Both forms round
+// 128 products and 127 sums of terms whose absolute values add up to at most
+// |u| |column| <= 1: each is within 127 * 2^-24 + 2^-24 < 7.7e-6 of the exact dot product,
+// so they differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.
+constexpr float ROT_SLACK = 4.0e-5f;
+TQ_DEV void rotate16_fused(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, float* acc) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float4 u = *(const float4*)&us[0][4 * q];
-      acc[4 * q + 0] = __fmul_rn(u.x, p);
-      acc[4 * q + 1] = __fmul_rn(u.y, p);
-      acc[4 * q + 2] = __fmul_rn(u.z, p);
-      acc[4 * q + 3] = __fmul_rn(u.w, p);
-    }
-  }
+  for (int t = 0; t < TQ_GROUP_TOK; ++t) acc[t] = 0.0f;
 #pragma unroll 4
-  for (int dd = 1; dd < TQ_D; ++dd) {
+  for (int dd = 0; dd < TQ_D; ++dd) {
     const float p = pit[dd * TQ_D + e];
-    float m[TQ_GROUP_TOK];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float4 u = *(const float4*)&us[dd][4 * q];
-      m[4 * q + 0] = __fmul_rn(u.x, p);
-      m[4 * q + 1] = __fmul_rn(u.y, p);
-      m[4 * q + 2] = __fmul_rn(u.z, p);
-      m[4 * q + 3] = __fmul_rn(u.w, p);
+      acc[4 * q + 0] = fmaf(u.x, p, acc[4 * q + 0]);
+      acc[4 * q + 1] = fmaf(u.y, p, acc[4 * q + 1]);
+      acc[4 * q + 2] = fmaf(u.z, p, acc[4 * q + 2]);
+      acc[4 * q + 3] = fmaf(u.w, p, acc[4 * q + 3]);
     }
-#pragma unroll
-    for (int t = 0; t < TQ_GROUP_TOK; ++t) acc[t] = __fadd_rn(acc[t], m[t]);
   }
+}
+// one coordinate of the unfused rotation: token t of the group, output channel e
+TQ_DEV float rotate_one(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, int t) {
+  float y = __fmul_rn(us[0][t], pit[e]);
+#pragma unroll 8
+  for (int dd = 1; dd < TQ_D; ++dd) y = __fadd_rn(y, __fmul_rn(us[dd][t], pit[dd * TQ_D + e]));
+  return y;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -356,6 +359,9 @@ TQ_DEV void rotate16(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, f
 //   u    = x / max(norm, 1e-30)
 //   y_e  = sequential, unfused sum over d of u_d * PiT[d][e]
 //   code = #{ j : boundary_j < y_e }
+// The rotation first runs with fused multiply-adds; a coordinate whose code could depend on
+// the difference (a boundary within ROT_SLACK of it: a few per thousand) is then recomputed
+// in the unfused order, so every code is the one the unfused arithmetic gives.
 // ---------------------------------------------------------------------------------------
 constexpr int ENCV_HALVES = 2;
 struct EncvHalf {
@@ -402,10 +408,16 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
 
     half_sync();  // previous item fully consumed
-#pragma unroll 4
-    for (int t = 0; t < TQ_GROUP_TOK; ++t) {
-      int tt = gq * TQ_GROUP_TOK + t;
-      hs->xs[t][e] = tt < S ? src.ld(blk * S + tt, e) : 0.0f;
+    {
+      float xv[TQ_GROUP_TOK];  // all rows requested before the first is used
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) {
+        const int tt = min(gq * TQ_GROUP_TOK + t, S - 1);
+        xv[t] = src.ld(blk * S + tt, e);
+      }
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t)
+        hs->xs[t][e] = gq * TQ_GROUP_TOK + t < S ? xv[t] : 0.0f;
     }
     hs->img[e] = 0u;
     hs->img[e + 128] = 0u;
@@ -438,13 +450,28 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     }
     half_sync();
     float acc[TQ_GROUP_TOK];
-    rotate16(hs->us, pit, e, acc);
+    rotate16_fused(hs->us, pit, e, acc);
     int code[TQ_GROUP_TOK];
+    unsigned redo = 0u;  // tokens whose coordinate has a boundary within the slack
 #pragma unroll
     for (int t = 0; t < TQ_GROUP_TOK; ++t) {
-      int c = 0;
-      for (int j = 0; j < n_bnd; ++j) c += (s_bnd[j] < acc[t]) ? 1 : 0;
+      const float lo = acc[t] - ROT_SLACK, hi = acc[t] + ROT_SLACK;
+      int c = 0, ch = 0;
+      for (int j = 0; j < n_bnd; ++j) {
+        c += (s_bnd[j] < lo) ? 1 : 0;
+        ch += (s_bnd[j] < hi) ? 1 : 0;
+      }
       code[t] = c;
+      redo |= (c != ch) ? (1u << t) : 0u;
+    }
+    while (redo) {
+      const int t = __ffs((int)redo) - 1;
+      redo &= redo - 1;
+      const float y = rotate_one(hs->us, pit, e, t);
+      int c = 0;
+      for (int j = 0; j < n_bnd; ++j) c += (s_bnd[j] < y) ? 1 : 0;
+#pragma unroll
+      for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? c : code[tt];
     }
     // pack this channel's 8 token pairs into the group image
     uint32_t* img = hs->img;
