@@ -140,3 +140,37 @@ def test_restore_with_heavy_tokens_and_through_the_wire_format(torch_cuda):
     bad = dict(blk, outlier_idx=blk["outlier_idx"][::-1].copy())
     with pytest.raises(ValueError):
         dst.import_block(0, 0, 0, bad)
+
+
+@pytest.mark.parametrize("dt", ["float16", "bfloat16", "float32"])
+def test_export_state_import_state_round_trip(torch_cuda, dt):
+    """The offload pair: one call takes everything a cache holds, one call puts it back into
+    another context (here: another sequence slot of another context)."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, n = 2, 2, 1000
+    kw = dict(n_layers=1, n_seqs=2, n_kv_heads=h, n_q_heads=h * grp, value_bits=3,
+              hot_window=512, max_tokens_per_seq=n + 8, kv_dtype=dt, seed=2)
+    src, dst = KVContext(**kw), KVContext(**kw)
+    k, v = make_kv(9, h, n, dtype=np.float32)
+    kt, vt = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+    src.append(0, kt[None], vt[None])
+    state = src.export_state(0, 0)
+    assert state["n_tokens"] == n and len(state["blocks"]) == 2
+    assert all(isinstance(b, bytes) for b in state["blocks"])
+    dst.import_state(0, 1, state)
+    assert dst.lengths(0, 1) == src.lengths(0, 0) and dst.lengths(0, 0)[0] == 0
+    ks, vs = src.dequant(0, 0, 0, n)
+    kd, vd = dst.dequant(0, 1, 0, n)
+    assert torch.equal(ks, kd) and torch.equal(vs, vd)
+    q = torch.from_numpy(np.stack([make_q(1, h * grp)] * 2)).cuda()
+    dst.append(0, kt[None, :3], vt[None, :3])  # the untouched slot gets a few tokens of its own
+    src.append(0, kt[None, :3], vt[None, :3], seq_begin=1)
+    assert torch.allclose(dst.decode(0, q)[1], src.decode(0, q)[0], rtol=1e-5, atol=1e-6)
+    empty = KVContext(**kw).export_state(0, 0)
+    dst.import_state(0, 1, empty)
+    assert dst.lengths(0, 1) == (0, 0, 0)
+    with pytest.raises(ValueError):
+        KVContext(**dict(kw, value_bits=4)).import_state(0, 0, state)

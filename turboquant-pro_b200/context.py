@@ -407,6 +407,52 @@ class KVContext:
             geom=(self.geom.n_kv_heads, self.geom.block_tokens, self.geom.head_dim,
                   self.geom.value_bits)))
 
+    def export_state(self, layer: int, seq: int, rope_theta: float | None = None,
+                     zero_point: str = "calibrated") -> dict:
+        """Everything one cache holds, for offload: its cold blocks as ``tqp-kv-npz/1`` byte
+        strings and the uncompressed hot window as raw 16/32-bit words.  :meth:`import_state`
+        of a context with the same geometry, seed and key format restores it exactly."""
+        total, cold, _hot = self.lengths(layer, seq)
+        nb = cold // self.geom.block_tokens
+        blocks = [self.export_blob(layer, seq, b, rope_theta=rope_theta, zero_point=zero_point)
+                  for b in range(nb)]
+        torch = _torch()
+        if total > cold:  # the window's values are stored exactly
+            hk, hv = self.dequant(layer, seq, cold, total)
+        else:
+            hk = hv = torch.empty((self.geom.n_kv_heads, 0, self.geom.head_dim), device=self.device)
+        raw = []
+        for t in (hk, hv):
+            t = t.permute(1, 0, 2).to(self.kv_dtype).contiguous().cpu()
+            word = _torch().int32 if t.element_size() == 4 else _torch().int16
+            raw.append(t.view(word).numpy().copy())
+        return {"n_tokens": total, "blocks": blocks, "hot_k": raw[0], "hot_v": raw[1],
+                "kv_dtype": str(self.kv_dtype).replace("torch.", ""),
+                "geom": (self.geom.n_kv_heads, self.geom.block_tokens, self.geom.head_dim,
+                         self.geom.value_bits), "key_mode": self.key_mode}
+
+    def import_state(self, layer: int, seq: int, state: dict, bias_means=None) -> None:
+        """Replaces the cache of ``(layer, seq)`` by an exported one (see :meth:`export_state`).
+        ``bias_means`` ``[n_blocks, n_kv_heads, D]`` is needed for blocks written with the
+        ``bias`` zero-point."""
+        torch = _torch()
+        g = self.geom
+        mine = (g.n_kv_heads, g.block_tokens, g.head_dim, g.value_bits)
+        if tuple(state["geom"]) != mine or state["key_mode"] != self.key_mode \
+                or state["kv_dtype"] != str(self.kv_dtype).replace("torch.", ""):
+            raise ValueError("the exported cache has another geometry, key format or dtype")
+        n = int(state["n_tokens"])
+        if len(state["blocks"]) != self.cold_blocks(n):
+            raise ValueError("block count does not match the token count")
+        self.clear(layer, seq)
+        for b, blob in enumerate(state["blocks"]):
+            self.import_blob(layer, seq, b, blob,
+                             bias_means=None if bias_means is None else bias_means[b])
+        if n:
+            hot = [torch.from_numpy(np.ascontiguousarray(state[name])).view(self.kv_dtype)
+                   for name in ("hot_k", "hot_v")]
+            self.restore_hot(layer, seq, n, hot[0], hot[1])
+
     # -- bookkeeping -----------------------------------------------------------------
     def lengths(self, layer: int, seq: int):
         """(total, cold, hot) token counts of one cache."""
