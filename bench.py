@@ -79,7 +79,45 @@ class ClockSampler:
         self._stop = threading.Event()
         self._t = None
 
+    def _run_nvml(self) -> bool:
+        """Reads the same fields through NVML (read-only queries, a few microseconds each, so
+        a short timed region still gets many samples).  False if NVML is not usable."""
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            try:  # the device this process computes on, whatever the visible-device order
+                import torch
+
+                h = nv.nvmlDeviceGetHandleByUUID("GPU-" + str(
+                    torch.cuda.get_device_properties(torch.cuda.current_device()).uuid))
+            except Exception:  # noqa: BLE001
+                h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) \
+                or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            get_reasons(h)
+        except Exception:  # noqa: BLE001
+            return False
+        bits = ((0x8, 2), (0x40, 3), (0x20, 4), (0x4, 5))  # hw, hw thermal, sw thermal, power cap
+        while not self._stop.is_set():
+            try:
+                r = get_reasons(h)
+                row = [str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(mx),
+                       "Not Active", "Not Active", "Not Active", "Not Active"]
+                for bit, col in bits:
+                    if r & bit:
+                        row[col] = "Active"
+                self.samples.append(row)
+            except Exception:  # noqa: BLE001 - sampling must never break the benchmark
+                pass
+            self._stop.wait(0.005)
+        return True
+
     def _run(self):
+        if self._run_nvml():
+            return
         while not self._stop.is_set():
             try:
                 out = subprocess.run(
