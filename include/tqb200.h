@@ -240,12 +240,18 @@ int32_t tq_memory_stats(tq_ctx* ctx, int32_t layer, int32_t seq, double* cold_by
  * every sequence of the layer. */
 int32_t tq_clear(tq_ctx* ctx, int32_t layer, int32_t seq, void* stream);
 
-/* Reads and clears the device status word (bit 0: an outlier pool overflowed and a block
- * kept a truncated side-list).  Synchronises `stream`. */
+/* Reads and clears the device status word.  Synchronises `stream`.
+ *   bit 0 (1): an outlier pool overflowed and a block kept a truncated side-list;
+ *   bit 1 (2): a bounded wait inside the tensor-core decode kernel ran out (a tile copy did
+ *              not arrive within the limit).  The kernel then stops waiting and returns, so
+ *              the device stays usable, but the `out` / `mlo` of that call is undefined:
+ *              tq_decode itself has already returned TQ_OK (it does not synchronise), so a
+ *              caller that wants the guarantee reads the status after the call. */
 int32_t tq_status(tq_ctx* ctx, int32_t* flags, void* stream);
 
 /* Algorithmic bytes one tq_decode of `layer` reads (reference container sizes of every
- * cold block + the hot windows + q and out), for roofline accounting. */
+ * cold block + the hot windows + q at the element size of the most recent decode's q_dtype,
+ * float32 before the first one, + the float32 out), for roofline accounting. */
 int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes);
 
 /* Number of kernels the most recent tq_decode / tq_append of this context launched. */
@@ -282,10 +288,25 @@ int32_t tq_set_key_mean_mask(tq_ctx* ctx, const uint8_t* mask, void* stream);
 int32_t tq_set_key_bias_means(tq_ctx* ctx, const float* means, void* stream);
 
 /* Selects the decode kernel: 0 = automatic (the tensor-core kernel where the geometry
- * allows: 256-token blocks, GQA group 1/2/4/8; else the general-shape kernel), 1 = always
- * the general-shape float32 kernel.  Both compute the same function; tests compare them.
- * No counterpart in the reference. */
+ * allows: 256-token blocks, GQA group 1/2/4/8, any number of sequences; else the
+ * general-shape kernel), 1 = always the general-shape float32 kernel.  Both compute the same
+ * function; tests compare them; tq_last_kernel tells which one ran.  No counterpart in the
+ * reference. */
 int32_t tq_set_kernel(tq_ctx* ctx, int32_t which);
+
+/* Which kernel the most recent tq_decode / tq_decode_partial / tq_decode_static_scratch of
+ * this context ran: 0 none yet, 1 the tensor-core kernel, 2 the general-shape kernel.  The
+ * reference likewise lets callers see which path served a call (it dispatches by capability,
+ * kv_fused_pck.py:216-236); no direct counterpart. */
+int32_t tq_last_kernel(const tq_ctx* ctx);
+
+/* Test hook for the bounded waits of the tensor-core decode kernel (no counterpart in the
+ * reference).  `wait_limit` > 0 replaces the number of probes a wait makes before it gives up
+ * (0 restores the default, about half a second); `withhold_tile` >= 0 makes the first CTA of
+ * later decodes never start the copy of that tile of its share, so that the wait for it runs
+ * out and bit 1 of the status word is set (-1 switches this off).  Nothing faults and nothing
+ * spins without bound; used by the tests of the error path. */
+int32_t tq_debug_wait(tq_ctx* ctx, int32_t wait_limit, int32_t withhold_tile);
 
 /* Pipeline trace of the tensor-core decode kernel (debugging aid, no counterpart in the
  * reference).  `on` switches stamping on or off for later tq_decode calls; if `stamps` is

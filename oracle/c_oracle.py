@@ -10,7 +10,7 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_SO = os.path.join(_HERE, "_ref", "libtq_oracle.so")
+_SO = os.path.join(_HERE, "_build", "libtq_oracle.so")
 _lib = None
 
 

@@ -155,6 +155,19 @@ def test_config2_long_context_split(torch_cuda):
     slow = ctx.decode(0, q).cpu().numpy()
     ctx.set_kernel("auto")
     assert np.allclose(full, slow, rtol=RTOL, atol=ATOL), np.abs(full - slow).max()
+    # the longest softmax of the configurations against the CPU oracle (dequantise-then-attend
+    # in the C restatement) on two of the KV heads: their 8 query heads
+    from oracle import c_oracle as co
+
+    for head in (0, 5):
+        kd, vd = ctx.dequant(0, 0, 0, n)
+        keys = kd[head:head + 1].cpu().numpy()
+        vals = vd[head:head + 1].cpu().numpy()
+        del kd, vd
+        qh = q[0, 4 * head:4 * head + 4].float().cpu().numpy()
+        want = co.attention(qh, keys, vals)
+        got = full[0, 4 * head:4 * head + 4]
+        assert np.allclose(got, want, rtol=RTOL, atol=ATOL), (head, np.abs(got - want).max())
     for world in (2, 4, 8):
         parts = [ctx.decode_partial(0, q, 510 * r // world, 510 * (r + 1) // world,
                                     with_hot=(r == world - 1)).clone() for r in range(world)]
@@ -369,3 +382,84 @@ def test_random_geometries_kernels_agree(torch_cuda, seed):
     merged = ctx.lse_combine(parts.reshape(2, n_seqs * h * grp, 130)).cpu().numpy()
     live = np.repeat(np.asarray(lens) > 0, h * grp)
     assert np.allclose(merged[live], fast.reshape(-1, 128)[live], rtol=1e-3, atol=1e-4)
+
+
+def test_many_units_take_the_tensor_core_kernel(torch_cuda):
+    """More (sequence, KV head) units than one launch's plan holds (65 sequences x 8 KV heads =
+    520): the layer is served by several launches of the tensor-core kernel, not by the
+    general-shape one, and both kernels agree."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+
+    B, h, grp = 65, 8, 4
+    ctx = KVContext(n_layers=1, n_seqs=B, n_kv_heads=h, n_q_heads=h * grp, value_bits=3,
+                    hot_window=512, max_tokens_per_seq=1400, kv_dtype="float16", seed=6)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(6)
+    lens = [int(x) for x in torch.randint(1, 1400, (B,), generator=gen, device="cuda").cpu()]
+    lens[3], lens[64] = 1400, 1337  # a long one in each launch
+    for s0 in range(B):
+        k = torch.randn((1, lens[s0], h, 128), generator=gen, device="cuda").half()
+        v = torch.randn((1, lens[s0], h, 128), generator=gen, device="cuda").half()
+        ctx.append(0, k, v, seq_begin=s0)
+    q = torch.randn((B, h * grp, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    fast = ctx.decode(0, q).cpu().numpy()
+    assert ctx.last_kernel() == "tensor-core"
+    assert ctx.last_launches() == 4  # two attention launches, two combines
+    ctx.set_kernel("general")
+    slow = ctx.decode(0, q).cpu().numpy()
+    assert ctx.last_kernel() == "general"
+    assert np.allclose(fast, slow, rtol=RTOL, atol=ATOL), np.abs(fast - slow).max()
+    assert ctx.status() == 0
+
+
+def test_decode_bits_depend_on_the_tokens_only(torch_cuda):
+    """Two encodes of the same tokens (separate contexts, different append chunking) give the
+    same page images, so the decode outputs are equal bit for bit."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, n = 2, 4, 2100
+    k, v = make_kv(77, h, n, dtype=np.float16)
+    kt, vt = torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda()
+    kw = dict(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h * grp, value_bits=3, hot_window=512,
+              max_tokens_per_seq=n, kv_dtype="float16", seed=77)
+    a, b = KVContext(**kw), KVContext(**kw)
+    a.append(0, kt, vt)
+    for t0 in range(0, n, 333):
+        b.append(0, kt[:, t0:t0 + 333], vt[:, t0:t0 + 333])
+    q = torch.from_numpy(make_q(77, h * grp))[None].cuda()
+    assert torch.equal(a.decode(0, q), b.decode(0, q))
+    a.set_kernel("general")
+    b.set_kernel("general")
+    assert torch.equal(a.decode(0, q), b.decode(0, q))
+
+
+def test_wait_that_runs_out_is_reported_and_leaves_the_context_usable(torch_cuda):
+    """The bounded waits of the tensor-core kernel: the test hook withholds the copy of one
+    tile (nothing else is disturbed) and shortens the probe limit; the kernel returns, the
+    status word carries bit 1, ``check_status`` raises, and the next decode is correct."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200._lib import TqError
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    h, grp, n = 2, 4, 3000
+    k, v = make_kv(8, h, n, dtype=np.float16)
+    ctx = KVContext(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h * grp, value_bits=3,
+                    hot_window=512, max_tokens_per_seq=n, kv_dtype="float16", seed=8)
+    ctx.append(0, torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda())
+    q = torch.from_numpy(make_q(8, h * grp))[None].cuda()
+    good = ctx.decode(0, q).clone()
+    assert ctx.last_kernel() == "tensor-core" and ctx.status() == 0
+    ctx.debug_wait(wait_limit=64, withhold_tile=0)
+    with pytest.raises(TqError, match="wait"):
+        ctx.decode(0, q, check_status=True)
+    assert ctx.status() == 0  # reading the flags cleared them
+    ctx.decode(0, q)
+    torch.cuda.synchronize()
+    assert ctx.status() & 2
+    ctx.debug_wait()  # defaults: nothing withheld
+    again = ctx.decode(0, q, check_status=True)
+    assert torch.equal(again, good)

@@ -80,8 +80,10 @@ def test_restored_cache_equals_the_original(torch_cuda, mode, frac, vb, dt, w, n
     kd, vd = dst.dequant(layer, seq, 0, n)
     assert torch.equal(ks, kd) and torch.equal(vs, vd)
     q = torch.from_numpy(np.stack([make_q(3, h * grp), make_q(4, h * grp)])).cuda()
+    # a token's outliers are stored in channel order by the encoder and by the importer alike,
+    # so equal containers mean equal page images and the decode agrees bit for bit
     a, b = src.decode(layer, q)[seq], dst.decode(layer, q)[seq]
-    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+    assert torch.equal(a, b)
     # both go on: the next cold blocks (pool cursors, ring positions) come out the same
     src.clear(layer, 0)
     dst.clear(layer, 0)
@@ -93,8 +95,10 @@ def test_restored_cache_equals_the_original(torch_cuda, mode, frac, vb, dt, w, n
     assert nb2 > nb
     for blk in range(nb2):
         _same_block(src.export_block(layer, seq, blk), dst.export_block(layer, seq, blk))
+    # a token's outliers are stored in channel order by the encoder and by the importer alike,
+    # so equal containers mean equal page images and the decode agrees bit for bit
     a, b = src.decode(layer, q)[seq], dst.decode(layer, q)[seq]
-    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+    assert torch.equal(a, b)
     assert src.status() == 0 and dst.status() == 0
 
 
@@ -126,7 +130,7 @@ def test_restore_with_heavy_tokens_and_through_the_wire_format(torch_cuda):
     for c in (dst, dst2):
         for b in range(nb):
             _same_block(src.export_block(0, 0, b), c.export_block(0, 0, b))
-        assert torch.allclose(c.decode(0, q), want, rtol=1e-5, atol=1e-6)
+        assert torch.equal(c.decode(0, q), want)
         c.set_kernel("general")
         assert torch.allclose(c.decode(0, q), want, rtol=2e-2, atol=2e-3)
         assert c.status() == 0

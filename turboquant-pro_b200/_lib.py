@@ -93,6 +93,8 @@ SIGNATURES = {
     "tq_decode_bytes": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_double)]),
     "tq_last_launches": (C.c_int32, [C.c_void_p]),
     "tq_set_kernel": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "tq_last_kernel": (C.c_int32, [C.c_void_p]),
+    "tq_debug_wait": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32]),
     "tq_set_key_mean_mask": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "tq_set_key_bias_means": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "tq_debug_trace": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),

@@ -211,25 +211,52 @@ class KVContext:
                                       k.stride(2), self._stream()))
 
     # -- decode ----------------------------------------------------------------------
-    def decode(self, layer: int, q, out=None):
-        """One decode step of attention on the codes for every sequence of ``layer``.
-
-        ``q``: CUDA tensor ``[n_seqs, n_q_heads, D]`` (float32 / float16 / bfloat16).
-        Returns float32 ``[n_seqs, n_q_heads, D]``.
-        """
-        torch = _torch()
+    def _check_q(self, q):
         g = self.geom
         if tuple(q.shape) != (g.n_seqs, g.n_q_heads, g.head_dim):
             raise ValueError(f"expected q of shape {(g.n_seqs, g.n_q_heads, g.head_dim)}, "
                              f"got {tuple(q.shape)}")
-        q = q.contiguous()
-        if out is None:
-            out = torch.empty((g.n_seqs, g.n_q_heads, g.head_dim), dtype=torch.float32,
-                              device=self.device)
+        if q.device != self.device:
+            raise ValueError(f"q lives on {q.device}, the context on {self.device}")
+        return q.contiguous()
+
+    def _check_result(self, t, shape, name):
+        torch = _torch()
+        if t is None:
+            return torch.empty(shape, dtype=torch.float32, device=self.device)
+        if tuple(t.shape) != tuple(shape) or t.dtype != torch.float32 or t.device != self.device \
+                or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous float32 tensor of shape {tuple(shape)} "
+                             f"on {self.device}")
+        return t
+
+    def decode(self, layer: int, q, out=None, check_status: bool = False):
+        """One decode step of attention on the codes for every sequence of ``layer``.
+
+        ``q``: CUDA tensor ``[n_seqs, n_q_heads, D]`` (float32 / float16 / bfloat16).
+        Returns float32 ``[n_seqs, n_q_heads, D]``.  With ``check_status`` the call
+        synchronises and raises :class:`TqError` if the kernel reported a wait that ran out
+        (status bit 1: the output is then undefined).
+        """
+        torch = _torch()
+        g = self.geom
+        q = self._check_q(q)
+        out = self._check_result(out, (g.n_seqs, g.n_q_heads, g.head_dim), "out")
         with torch.cuda.device(self.device):
             check(self._lib.tq_decode(self._h, layer, q.data_ptr(), _dtype_code(q.dtype),
                                       out.data_ptr(), self._stream()))
+        if check_status:
+            self.raise_on_timeout()
         return out
+
+    def raise_on_timeout(self) -> int:
+        """Reads the status word (synchronises); raises if a bounded wait of a decode kernel ran
+        out since the last read, else returns the other flags."""
+        flags = self.status()
+        if flags & 2:
+            raise _lib.TqError(-3, "a bounded wait inside the decode kernel ran out; the "
+                                   "output of that call is undefined")
+        return flags
 
     def decode_static_scratch(self, layer: int, q, out=None):
         """:meth:`decode` for callers that may not allocate or lend working memory: the
@@ -238,13 +265,8 @@ class KVContext:
         be passed by such callers; it is created here only as a convenience."""
         torch = _torch()
         g = self.geom
-        if tuple(q.shape) != (g.n_seqs, g.n_q_heads, g.head_dim):
-            raise ValueError(f"expected q of shape {(g.n_seqs, g.n_q_heads, g.head_dim)}, "
-                             f"got {tuple(q.shape)}")
-        q = q.contiguous()
-        if out is None:
-            out = torch.empty((g.n_seqs, g.n_q_heads, g.head_dim), dtype=torch.float32,
-                              device=self.device)
+        q = self._check_q(q)
+        out = self._check_result(out, (g.n_seqs, g.n_q_heads, g.head_dim), "out")
         with torch.cuda.device(self.device):
             check(self._lib.tq_decode_static_scratch(self._h, layer, q.data_ptr(),
                                                      _dtype_code(q.dtype), out.data_ptr(),
@@ -257,10 +279,8 @@ class KVContext:
         (+ the hot window): float32 ``[n_seqs, n_q_heads, 2 + D]``."""
         torch = _torch()
         g = self.geom
-        q = q.contiguous()
-        if mlo is None:
-            mlo = torch.empty((g.n_seqs, g.n_q_heads, 2 + g.head_dim), dtype=torch.float32,
-                              device=self.device)
+        q = self._check_q(q)
+        mlo = self._check_result(mlo, (g.n_seqs, g.n_q_heads, 2 + g.head_dim), "mlo")
         with torch.cuda.device(self.device):
             check(self._lib.tq_decode_partial(self._h, layer, q.data_ptr(), _dtype_code(q.dtype),
                                               block_begin, block_end, int(bool(with_hot)),
@@ -270,10 +290,13 @@ class KVContext:
     def lse_combine(self, mlo, out=None):
         """Merge gathered states ``[n_parts, n_rows, 2 + D]`` into ``[n_rows, D]``."""
         torch = _torch()
+        if mlo.dim() != 3 or mlo.shape[2] != 2 + self.geom.head_dim or mlo.dtype != torch.float32 \
+                or mlo.device != self.device:
+            raise ValueError(f"expected float32 states [n_parts, n_rows, {2 + self.geom.head_dim}] "
+                             f"on {self.device}, got {tuple(mlo.shape)} {mlo.dtype} on {mlo.device}")
         mlo = mlo.contiguous()
         n_parts, n_rows, w = mlo.shape
-        if out is None:
-            out = torch.empty((n_rows, w - 2), dtype=torch.float32, device=mlo.device)
+        out = self._check_result(out, (n_rows, w - 2), "out")
         with torch.cuda.device(self.device):
             check(self._lib.tq_lse_combine(mlo.data_ptr(), n_parts, n_rows, w - 2,
                                            out.data_ptr(), self._stream()))
@@ -473,7 +496,8 @@ class KVContext:
             check(self._lib.tq_clear(self._h, layer, seq, self._stream()))
 
     def status(self) -> int:
-        """Device status flags (bit 0: an outlier pool overflowed); clears them."""
+        """Device status flags (bit 0: an outlier pool overflowed; bit 1: a bounded wait of the
+        tensor-core decode kernel ran out and that call's output is undefined); clears them."""
         f = C.c_int32()
         with _torch().cuda.device(self.device):
             check(self._lib.tq_status(self._h, C.byref(f), self._stream()))
@@ -521,6 +545,16 @@ class KVContext:
         """``"auto"``: tensor-core kernel where the geometry allows; ``"general"``: always the
         general-shape float32 kernel."""
         check(self._lib.tq_set_kernel(self._h, {"auto": 0, "general": 1}[which]))
+
+    def last_kernel(self) -> str:
+        """Which kernel served the most recent decode: ``"tensor-core"``, ``"general"`` or
+        ``"none"``."""
+        return {0: "none", 1: "tensor-core", 2: "general"}[int(self._lib.tq_last_kernel(self._h))]
+
+    def debug_wait(self, wait_limit: int = 0, withhold_tile: int = -1) -> None:
+        """Test hook of the decode kernel's bounded waits: a shorter probe limit and a tile of
+        the first CTA whose copy is never started (see ``tq_debug_wait``)."""
+        check(self._lib.tq_debug_wait(self._h, int(wait_limit), int(withhold_tile)))
 
     def trace(self, on: bool, read: bool = False):
         """Switch the decode kernel's pipeline stamping on/off; with ``read`` return the

@@ -33,8 +33,18 @@ constexpr int TQ_OVF_CAP = 112;
 constexpr int TQ_TAIL_BYTES = TQ_OVF_OFF + TQ_OVF_CAP * 4;  // 4096
 constexpr int TQ_PAGE_SPILLED = 1;  // header flag: use the pool's list, not the in-page copy
 
-// bit 0 of the device status word: an outlier pool overflowed
+// device status word: bit 0, an outlier pool overflowed; bit 1, a bounded wait of the
+// tensor-core decode kernel ran out (the call's output is then undefined)
 constexpr int TQ_STATUS_POOL_OVERFLOW = 1;
+constexpr int TQ_STATUS_WAIT_TIMEOUT = 2;
+
+// which decode kernel served the most recent call (tq_last_kernel)
+constexpr int TQ_KERNEL_NONE = 0, TQ_KERNEL_TENSOR_CORE = 1, TQ_KERNEL_GENERAL = 2;
+
+// head of the scratch region as the tensor-core path uses it: trace stamps, then per launch a
+// plan block followed by that launch's partials
+constexpr size_t TQ_MMA_TRACE_BYTES = 4096;
+constexpr size_t TQ_MMA_PLAN_BYTES = 8192;
 
 // ---------------------------------------------------------------------------------------
 // Device memory layout
@@ -100,8 +110,12 @@ struct tq_ctx {
   // one kernels read, both are advanced together by tq_append
   std::vector<int32_t> len;
   int last_launches;
-  bool force_generic = false;
-  bool trace_on = false;       // the tensor-core decode kernel stamps its pipeline phases  // route every decode through the general-shape kernel
+  int last_kernel = TQ_KERNEL_NONE;
+  int last_q_dtype = TQ_F32;   // query element type of the most recent decode (byte accounting)
+  bool force_generic = false;  // route every decode through the general-shape kernel
+  bool trace_on = false;       // the tensor-core decode kernel stamps its pipeline phases
+  int wait_limit = 0;          // probes per bounded wait of the decode kernel; 0 = default
+  int withhold_tile = -1;      // test hook: the copy of this tile of CTA 0 is never started
   // optional per-kernel timing: event triples (before attention, after it, after combine)
   bool prof_on = false;
   int prof_n = 0;

@@ -249,13 +249,24 @@ int32_t tq_set_kernel(tq_ctx* ctx, int32_t which) {
   return TQ_OK;
 }
 
+int32_t tq_last_kernel(const tq_ctx* ctx) { return ctx ? ctx->last_kernel : TQ_KERNEL_NONE; }
+
+int32_t tq_debug_wait(tq_ctx* ctx, int32_t wait_limit, int32_t withhold_tile) {
+  TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
+  TQ_REQUIRE(wait_limit >= 0 && withhold_tile >= -1, TQ_ERR_INVALID,
+             "wait_limit must be >= 0 and withhold_tile >= -1");
+  ctx->wait_limit = wait_limit;
+  ctx->withhold_tile = withhold_tile;
+  return TQ_OK;
+}
+
 int32_t tq_debug_trace(tq_ctx* ctx, int32_t on, uint64_t* stamps, void* stream) {
   TQ_REQUIRE(ctx != nullptr, TQ_ERR_INVALID, "null context");
   ctx->trace_on = on != 0;
   if (stamps != nullptr) {
     TQ_CUDA(cudaSetDevice(ctx->device));
     cudaStream_t st = (cudaStream_t)stream;
-    TQ_CUDA(cudaMemcpyAsync(stamps, (const uint8_t*)ctx->b.scratch + 8192, 4096,
+    TQ_CUDA(cudaMemcpyAsync(stamps, (const uint8_t*)ctx->b.scratch, TQ_MMA_TRACE_BYTES,
                             cudaMemcpyDeviceToHost, st));
     TQ_CUDA(cudaStreamSynchronize(st));
   }
@@ -322,6 +333,7 @@ int32_t tq_decode(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype, fl
   TQ_REQUIRE(q_dtype == TQ_F32 || q_dtype == TQ_F16 || q_dtype == TQ_BF16, TQ_ERR_INVALID,
              "bad q_dtype");
   TQ_CUDA(cudaSetDevice(ctx->device));
+  ctx->last_q_dtype = q_dtype;
   return tq_launch_decode(ctx, layer, q, q_dtype, 0, -1, 1, out, nullptr, (cudaStream_t)stream);
 }
 
@@ -334,6 +346,7 @@ int32_t tq_decode_partial(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_d
              "bad q_dtype");
   TQ_REQUIRE(block_begin >= 0 && block_end >= block_begin, TQ_ERR_INVALID, "bad block range");
   TQ_CUDA(cudaSetDevice(ctx->device));
+  ctx->last_q_dtype = q_dtype;
   return tq_launch_decode(ctx, layer, q, q_dtype, block_begin, block_end, with_hot ? 1 : 0,
                           nullptr, mlo, (cudaStream_t)stream);
 }
@@ -747,7 +760,7 @@ int32_t tq_decode_bytes(const tq_ctx* ctx, int32_t layer, double* bytes) {
     if (n == 0) continue;
     int nb = n_cold_blocks(n, g.hot_window, S);
     total += g.n_kv_heads * (nb * blk + 2.0 * (n - nb * S) * D * elem_size(g.kv_dtype));
-    total += (double)g.n_q_heads * D * (4 + 4);
+    total += (double)g.n_q_heads * D * (elem_size(ctx->last_q_dtype) + 4);
   }
   *bytes = total;
   return TQ_OK;

@@ -530,6 +530,7 @@ int tq_launch_decode(tq_ctx* ctx, int layer, const void* q, int q_dtype, int blo
     tq_prof_commit(ctx);
   }
   ctx->last_launches = 2;
+  ctx->last_kernel = TQ_KERNEL_GENERAL;
   TQ_CUDA(cudaGetLastError());
   return TQ_OK;
 }
@@ -636,6 +637,8 @@ extern "C" int32_t tq_decode_static_scratch(tq_ctx* ctx, int32_t layer, const vo
   }
   combine_kernel<<<n_units, TQ_D, 0, st>>>(a);
   ctx->last_launches = 2;
+  ctx->last_kernel = TQ_KERNEL_GENERAL;
+  ctx->last_q_dtype = q_dtype;
   TQ_CUDA(cudaGetLastError());
   return TQ_OK;
 }

@@ -47,11 +47,10 @@ constexpr int TPW = 256 / GW;        // tokens of a cold page per warp
 constexpr int HALVES = TPW / 16;     // 16-token tiles per warp and page
 static_assert(GW == 4 || GW == 8, "a warp owns 64 or 32 tokens of a page");
 constexpr int MAX_NG = 3;            // most consumer groups
-constexpr int MAX_UNITS = 512;
+constexpr int MAX_UNITS = 512;       // (sequence, KV head) units per launch; larger layers take several
 constexpr int BLK = 256;             // tokens per cold page
 constexpr float NEG_BIG = -1.0e30f;
-constexpr int SPIN_LIMIT = 1 << 18;  // probes per wait; each may suspend up to ~2 us
-constexpr int STATUS_TIMEOUT = 2;
+constexpr int SPIN_LIMIT = 1 << 18;  // default probes per wait; each may suspend up to ~2 us
 
 struct MmaArgs {
   tq_geom g;
@@ -69,9 +68,12 @@ struct MmaArgs {
   int32_t* status;
   unsigned long long* trace;  // optional: SM clock stamps of CTA 0's first 64 tiles
   int layer, q_dtype, n_units, n_cta;
+  int unit_base;  // first unit of the layer this launch covers (a multiple of the KV head count)
   int use_tmap;  // 16-bit hot tiles arrive through the tensor maps, 128-byte swizzled
   int n_groups;  // consumer groups of the attention kernel (the combine enumerates their slots)
   int block_begin, block_end, with_hot;
+  int spin_limit;     // probes a bounded wait makes before it gives up
+  int withhold_tile;  // test hook: CTA 0 never starts the copy of this tile of its share (-1: off)
   float scale_log2;
 };
 
@@ -226,7 +228,7 @@ TQ_DEV int hot_tile_tokens(int dt) { return dt == TQ_F32 ? 32 : 64; }
 TQ_DEV void unit_tiles(const MmaArgs& a, int unit, int& nb, int& ht, int& b0, int& hot_start,
                        int& hot_len) {
   const tq_geom& g = a.g;
-  const int seq = unit / g.n_kv_heads;
+  const int seq = (a.unit_base + unit) / g.n_kv_heads;
   const int N = a.seq_len[a.layer * g.n_seqs + seq];
   const int nbt = n_cold_blocks(N, g.hot_window, BLK);
   b0 = min(a.block_begin, nbt);
@@ -300,17 +302,18 @@ TQ_DEV int find_unit(const Plan* plan, int n_units, int pos) {
 struct Waiter {
   volatile int* abort_flag;
   int32_t* status;
+  int limit;
   TQ_DEV void wait(uint32_t bar, uint32_t parity) const {
-    for (int i = 0; i < SPIN_LIMIT; ++i) {
+    for (int i = 0; i < limit; ++i) {
       if (mbar_try(bar, parity)) return;
       if ((i & 15) == 15 && *abort_flag) return;
     }
     *abort_flag = 1;
-    atomicOr(status, STATUS_TIMEOUT);
+    atomicOr(status, TQ_STATUS_WAIT_TIMEOUT);
   }
   // bounded wait that ignores the abort flag
   TQ_DEV void drain(uint32_t bar, uint32_t parity) const {
-    for (int i = 0; i < SPIN_LIMIT; ++i)
+    for (int i = 0; i < limit; ++i)
       if (mbar_try(bar, parity)) return;
   }
 };
@@ -410,7 +413,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   }
   if (lo >= hi) return;
   TQ_TRACE_PHASE(3);
-  const Waiter waiter{abort_flag, a.status};
+  const Waiter waiter{abort_flag, a.status, a.spin_limit};
   const int htt = hot_tile_tokens(g.kv_dtype);
   const int esz = elem_size(g.kv_dtype);
 
@@ -438,7 +441,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   };
   // units of this layer are numbered (sequence, KV head) row-major, and so are their pages,
   // hot rings, pool lists and query rows: no division by the head count is ever needed
-  const size_t unit0 = (size_t)a.layer * g.n_seqs * g.n_kv_heads;
+  const size_t unit0 = (size_t)a.layer * g.n_seqs * g.n_kv_heads + a.unit_base;
 
   // The copy of tile t of this CTA's share: describe() works out addresses and sizes (it can
   // run before the stage is free), fire() starts it (the stage must be free: never used, or
@@ -448,12 +451,14 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     const uint8_t* src2;  // second source of a hot tile (the value rows), else null
     uint32_t bytes, dst, bar;
     int row;  // hot tile: its first row in the ring seen as one 2-D array
+    int t;    // index of the tile in the CTA's share
   };
   const int total = hi - lo;
   auto describe = [&](int t, Cursor& cu) -> CopyDesc {
     const Tile tl = tile_at(lo + t, cu);
     const size_t unit = unit0 + tl.u;
     CopyDesc d;
+    d.t = t;
     d.dst = smem_addr(stages + (size_t)(t % NSTAGE) * SM::DATA_BYTES);
     d.bar = full0 + 8 * (t % (2 * NSTAGE));
     if (tl.kind == 0) {
@@ -470,7 +475,11 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     }
     return d;
   };
+  int last_fired = -1;  // the latest tile whose copy this thread started
   auto fire = [&](const CopyDesc& d) {
+    // (test hook: a withheld copy leaves its barrier incomplete, so the wait for it runs out)
+    if (blockIdx.x == 0 && d.t == a.withhold_tile) return;
+    last_fired = d.t;
     if (d.src2 == nullptr) {
       mbar_arrive_expect_tx(d.bar, d.bytes);
       bulk_g2s(d.dst, d.src, d.bytes, d.bar);
@@ -725,7 +734,8 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         // thread d of the group loads channel d of the G rows: coalesced, independent loads.
         // The softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
         // bias and corrections come out already scaled.
-        const size_t q0 = (size_t)tl.u * (G * TQ_D) + gtid;  // query heads follow their KV head
+        // query heads follow their KV head
+        const size_t q0 = (size_t)(a.unit_base + tl.u) * (G * TQ_D) + gtid;
         float qv[G];
         if (a.q_dtype == TQ_F32) {
 #pragma unroll
@@ -1190,11 +1200,10 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   // A group's last tile is among the last NG of the share, so no refill is owed here.  After
   // a timed-out wait copies may still be in flight: they are waited for (bounded) before the
   // CTA gives up its shared memory.
-  if (*abort_flag) {
-    if (lane == 0)  // every copy this thread started signals one of these barriers
-      for (int t = max(0, total - 2 * NSTAGE); t < total; ++t)
-        waiter.drain(full0 + 8 * (t % (2 * NSTAGE)), (t / (2 * NSTAGE)) & 1);
-  }
+  // (a thread starts a copy only after the tile it started before that has been consumed, so
+  // its latest one is the only one that can still be under way)
+  if (*abort_flag && last_fired >= 0)
+    waiter.drain(full0 + 8 * (last_fired % (2 * NSTAGE)), (last_fired / (2 * NSTAGE)) & 1);
 }
 
 // Combine for the tensor-core kernel: one CTA per (sequence, KV head) merges the partials of
@@ -1208,7 +1217,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   constexpr int RP = G >= 8 ? 8 : (G >= 4 ? 16 : 32);  // partials per round
   const tq_geom& g = a.g;
   const int unit = blockIdx.x, e = threadIdx.x, lane = e & 31, wid = e >> 5;
-  const int seq = unit / g.n_kv_heads, head = unit % g.n_kv_heads;
+  const int seq = (a.unit_base + unit) / g.n_kv_heads, head = (a.unit_base + unit) % g.n_kv_heads;
   __shared__ float cs[G][TQ_D];
   __shared__ const float* s_ptr[TQ_D];  // partials of the current chunk of candidates
   __shared__ unsigned char s_cold[TQ_D];
@@ -1357,8 +1366,17 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   }
 }
 
+// Units of a layer one launch covers: the largest multiple of the KV head count that fits
+// the shared-memory plan.  A layer with more units takes several launches, each with its own
+// plan and partial slots in the scratch region.
+int chunk_units(const tq_geom& g) { return MAX_UNITS / g.n_kv_heads * g.n_kv_heads; }
+size_t chunk_bytes(const tq_geom& g, size_t units) {
+  return TQ_MMA_PLAN_BYTES +
+         align_up((units + 192) * 2 * MAX_NG * (size_t)g.group * TQ_PART_STRIDE * sizeof(float), 256);
+}
+
 template <int G, int VB>
-int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
+int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx, bool first, bool last) {
   using CF = Cfg<G, VB>;
   using SM = typename CF::SM;
   static bool attr_set[16] = {};
@@ -1368,7 +1386,11 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL));
     attr_set[dev & 15] = true;
   }
-  cudaEvent_t e0 = tq_prof_event(ctx, 0), e1 = tq_prof_event(ctx, 1), e2 = tq_prof_event(ctx, 2);
+  // per-kernel timing brackets the attention kernel and the combine kernel of a one-launch
+  // layer; with several launches the first bracket also holds the earlier launches' combines
+  cudaEvent_t e0 = first ? tq_prof_event(ctx, 0) : nullptr;
+  cudaEvent_t e1 = last ? tq_prof_event(ctx, 1) : nullptr;
+  cudaEvent_t e2 = last ? tq_prof_event(ctx, 2) : nullptr;
   if (e0) cudaEventRecord(e0, st);
   a.n_groups = CF::NG;
   // Either kernel may be scheduled before its predecessor in the stream has finished (where
@@ -1396,7 +1418,7 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx) {
     cudaEventRecord(e2, st);
     tq_prof_commit(ctx);
   }
-  ctx->last_launches = 2;
+  ctx->last_launches += 2;
   TQ_CUDA(cudaGetLastError());
   return TQ_OK;
 }
@@ -1444,7 +1466,10 @@ static void build_hot_tensor_maps(tq_ctx* ctx) {
 
 // Bytes of scratch the tensor-core path needs for `units` (sequence, KV head) pairs.
 size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
-  return 8192 + 4096 + (units + 192) * 2 * MAX_NG * (size_t)g.group * TQ_PART_STRIDE * sizeof(float);
+  const size_t cu = (size_t)std::max(chunk_units(g), 1);
+  size_t bytes = TQ_MMA_TRACE_BYTES;
+  for (size_t u0 = 0; u0 < units; u0 += cu) bytes += chunk_bytes(g, std::min(cu, units - u0));
+  return bytes;
 }
 
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
@@ -1455,8 +1480,8 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   const int n_units = g.n_seqs * g.n_kv_heads;
   const int G = g.group;
   if (ctx->force_generic) return TQ_OK;
-  if (g.block_tokens != BLK || (G != 1 && G != 2 && G != 4 && G != 8) || n_units > MAX_UNITS ||
-      g.hot_cap % 64 != 0)
+  if (g.block_tokens != BLK || (G != 1 && G != 2 && G != 4 && G != 8) ||
+      g.n_kv_heads > MAX_UNITS || g.hot_cap % 64 != 0)
     return TQ_OK;
   int sm_count = 148;
   cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
@@ -1469,28 +1494,41 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   a.seq_len = (const int32_t*)((const uint8_t*)ctx->b.state + state_len_off(g));
   a.tables = (const Tables*)ctx->b.tables;
   a.q = q;
-  a.plan_g = (int*)ctx->b.scratch;  // first 8 KB of the scratch region, then 4 KB of trace
-  a.trace = ctx->trace_on ? (unsigned long long*)((uint8_t*)ctx->b.scratch + 8192) : nullptr;
-  a.partials = (float*)((uint8_t*)ctx->b.scratch + 8192 + 4096);
+  // scratch region: 4 KB of trace stamps, then per launch {8 KB plan for the combine, partials}
+  a.trace = ctx->trace_on ? (unsigned long long*)ctx->b.scratch : nullptr;
   a.out = out;
   a.mlo = mlo;
   a.status = (int32_t*)((uint8_t*)ctx->b.state + state_status_off(g));
   a.layer = layer;
   a.q_dtype = q_dtype;
-  a.n_units = n_units;
   a.n_cta = std::min(sm_count, 192);
   a.block_begin = block_begin;
   a.block_end = block_end;
   a.with_hot = with_hot;
   a.scale_log2 = 1.4426950408889634f / sqrtf((float)TQ_D);
+  a.spin_limit = ctx->wait_limit > 0 ? ctx->wait_limit : SPIN_LIMIT;
+  a.withhold_tile = ctx->withhold_tile;
   if (ctx->tmap_state == 0) build_hot_tensor_maps(ctx);
   a.use_tmap = ctx->tmap_state == 1 ? 1 : 0;
   *handled = true;
+  ctx->last_launches = 0;
+  ctx->last_kernel = TQ_KERNEL_TENSOR_CORE;
+  const int cu = chunk_units(g);
+  uint8_t* region = (uint8_t*)ctx->b.scratch + TQ_MMA_TRACE_BYTES;
+  for (int u0 = 0; u0 < n_units; u0 += cu) {
+    a.unit_base = u0;
+    a.n_units = std::min(cu, n_units - u0);
+    a.plan_g = (int*)region;
+    a.partials = (float*)(region + TQ_MMA_PLAN_BYTES);
+    region += chunk_bytes(g, (size_t)a.n_units);
+    const bool first = u0 == 0, last = u0 + cu >= n_units;
+    int rc = TQ_ERR_UNSUPPORTED;
 #define TQ_CASE(GG, VV) \
-  if (G == GG && g.value_bits == VV) return launch_t<GG, VV>(a, st, ctx);
-  TQ_CASE(1, 3) TQ_CASE(2, 3) TQ_CASE(4, 3) TQ_CASE(8, 3)
-  TQ_CASE(1, 4) TQ_CASE(2, 4) TQ_CASE(4, 4) TQ_CASE(8, 4)
+  if (G == GG && g.value_bits == VV) rc = launch_t<GG, VV>(a, st, ctx, first, last);
+    TQ_CASE(1, 3) TQ_CASE(2, 3) TQ_CASE(4, 3) TQ_CASE(8, 3)
+    TQ_CASE(1, 4) TQ_CASE(2, 4) TQ_CASE(4, 4) TQ_CASE(8, 4)
 #undef TQ_CASE
-  *handled = false;
+    if (rc != TQ_OK) return rc;
+  }
   return TQ_OK;
 }

@@ -94,13 +94,12 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   __shared__ int s_count;
   __shared__ uint32_t s_off;
   __shared__ int s_alloc;
-  __shared__ int s_tok_cnt[256];    // outliers per token, then the running fill position
+  __shared__ int s_tok_cnt[256];    // outliers per token
+  __shared__ unsigned char s_cnt_w[256][TQ_D / 32];  // ... of which on the channels of warp w
   __shared__ int s_row[257];        // start of every token's outliers in the side-list
   __shared__ int s_orow[257];       // start of every token's entries in the page's overflow list
   __shared__ int s_warp_sum[TQ_D / 32];
   if (d == 0) s_count = 0;
-  s_tok_cnt[d] = 0;
-  s_tok_cnt[d + TQ_D] = 0;
   __shared__ float s_scale[TQ_D];       // channel scales, to rank the widest channels
   __shared__ unsigned int s_side[256];  // per token: the codes of the four widest channels
   s_side[d] = 0u;
@@ -150,10 +149,11 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   for (int t = 0; t < S; ++t) {
     float x = src.ld(pos0 + t, d);
     amax = fmaxf(amax, fabsf(mode == TQ_KEYS_NF4_ASYM ? __fsub_rn(x, mu) : x));
-    if (kk > 0 && fabsf(x) >= kth) {
-      ++my_out;
-      atomicAdd(&s_tok_cnt[t], 1);
-    }
+    const bool is_out = kk > 0 && fabsf(x) >= kth;
+    my_out += is_out ? 1 : 0;
+    // (the loop is uniform over the warp: every lane takes part in the vote)
+    const unsigned vote = __ballot_sync(0xffffffffu, is_out);
+    if ((d & 31) == 0) s_cnt_w[t][d >> 5] = (unsigned char)__popc(vote);
   }
   amax = fmaxf(amax, 1e-8f);
   if (mode == TQ_KEYS_UNIFORM) amax = __fdiv_rn(fmaxf(__fsub_rn(xmax, xmin), 1e-8f), 15.0f);
@@ -184,6 +184,14 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   if (rank < TQ_WIDE) hdr->wide[rank] = (uint8_t)d;
   if (kk > 0) atomicAdd(&s_count, my_out);
   __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int t = 2 * d + i;
+    int n = 0;
+#pragma unroll
+    for (int w = 0; w < TQ_D / 32; ++w) n += t < S ? (int)s_cnt_w[t][w] : 0;
+    s_tok_cnt[t] = n;
+  }
   if (d == 0) {
     int n = s_count;
     uint32_t off = 0;
@@ -247,8 +255,6 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
   }
   __syncthreads();
-  s_tok_cnt[2 * d] = s_row[2 * d];  // becomes the fill cursor of the token
-  s_tok_cnt[2 * d + 1] = s_row[2 * d + 1];
   if (d < 5) hdr->ovf_start[d] = (uint16_t)min(s_orow[64 * d], TQ_OVF_CAP);
   if (d == 5) {
     // the in-page copy is complete unless the overflow list is too long or the pool slab
@@ -282,8 +288,15 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     if (rank < 4) atomicOr(&s_side[t], (unsigned int)best << (4 * rank));
     int other = __shfl_down_sync(0xffffffffu, best, 1);
     if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
-    if (kk > 0 && fabsf(x) >= kth) {
-      int slot = atomicAdd(&s_tok_cnt[t], 1);  // grouped by token, any order inside a token
+    // A token's outliers are stored in channel order (the order of the reference's flat
+    // indices), so the side-list, and with it every bit the decoder computes, is a function
+    // of the tokens alone: this channel's place is the count of outlier channels below it.
+    const bool is_out = kk > 0 && fabsf(x) >= kth;
+    const unsigned vote = __ballot_sync(0xffffffffu, is_out);
+    if (is_out) {
+      int below = __popc(vote & ((1u << (d & 31)) - 1u));
+      for (int w = 0; w < (d >> 5); ++w) below += (int)s_cnt_w[t][w];
+      const int slot = s_row[t] + below;
       __half hv = __float2half_rn(x);
       // the decoder's value of this position (the level, recomputed: indexing lev[] with a
       // runtime index would move the whole array out of registers)

@@ -49,6 +49,112 @@ def gather_states(mlo, group=None):
     return out.reshape((world,) + tuple(mlo.shape))
 
 
+def n_cold_blocks(n_tokens: int, hot_window: int) -> int:
+    """Cold blocks of a cache holding ``n_tokens`` tokens (the reference's flush rule,
+    ``turboquant_pro/core.py:1008-1014``: once the window overflows, its oldest half becomes
+    a block)."""
+    f = (hot_window + 1) // 2
+    return 0 if n_tokens <= hot_window else 1 + (n_tokens - hot_window - 1) // f
+
+
+def sequence_shard(n_tokens: int, hot_window: int, rank: int, world: int):
+    """What rank ``rank`` of ``world`` stores of one sequence of ``n_tokens`` tokens under the
+    sequence split: ``(tok_lo, tok_hi, n_blocks, with_hot)``.
+
+    The sequence's cold blocks are divided into contiguous, balanced ranges.  A rank feeds
+    tokens ``[tok_lo, tok_hi)`` to a cache of its own; that cache then holds exactly
+    ``n_blocks`` cold blocks, and they are the global blocks of the rank's range bit for bit
+    (a block is encoded from its own tokens only, and ``tok_lo`` is a block boundary).  To
+    make the cache flush its last block, a rank other than the last feeds
+    ``hot_window + 1 - block`` tokens beyond its range; they stay in that cache's window and
+    are never attended (``with_hot`` is False).  The last rank stores everything from its
+    first block to the end of the sequence: its window is the sequence's window, and new
+    tokens are appended there."""
+    f = (hot_window + 1) // 2
+    nb = n_cold_blocks(n_tokens, hot_window)
+    lo, hi = shard_range(nb, rank, world)
+    if rank == world - 1:
+        return lo * f, n_tokens, hi - lo, True
+    if hi == lo:
+        return lo * f, lo * f, 0, False
+    return lo * f, hi * f + (hot_window + 1 - f), hi - lo, False
+
+
+class ShardedSequenceCache:
+    """Sequence split with sharded storage: every rank of the process group keeps only its own
+    contiguous range of each sequence's cold blocks (plus, on the last rank, the hot window),
+    in a :class:`KVContext` of its own.  Storage, encode work and decode traffic per rank are
+    ``1 / world`` of the sequence; a decode step is one partial decode per rank, one
+    ``all_gather`` of the ``(m, l, o)`` states and the LSE merge in rank order.
+
+    The sequences of one cache must have the same length (a decode step attends them together).
+    Tokens appended after the prefill go to the last rank, which also keeps the blocks they
+    later flush into: the split is balanced at prefill time.
+    """
+
+    def __init__(self, ctx, group=None):
+        import torch.distributed as dist
+
+        self.ctx = ctx
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.n_tokens = [0] * ctx.n_layers      # global length per layer
+        self.prefilled = [False] * ctx.n_layers
+
+    @staticmethod
+    def local_capacity(n_tokens: int, hot_window: int, rank: int, world: int, extra: int = 0):
+        """``max_tokens_per_seq`` a rank's context needs for a sequence of ``n_tokens`` tokens
+        plus ``extra`` tokens appended later."""
+        lo, hi, _nb, last = sequence_shard(n_tokens, hot_window, rank, world)
+        return max(hi - lo + (extra if last else 0), hot_window + 1)
+
+    def shard(self, n_tokens: int):
+        return sequence_shard(n_tokens, self.ctx.geom.hot_window, self.rank, self.world)
+
+    def prefill(self, layer: int, n_tokens: int, make_tokens, chunk: int = 16384) -> None:
+        """Fills ``layer`` of an empty cache with a sequence of ``n_tokens`` tokens.
+        ``make_tokens(t0, t1)`` returns the ``(k, v)`` CUDA tensors ``[n_seqs, t1 - t0, H, D]``
+        of tokens ``[t0, t1)``; it is asked only for this rank's share."""
+        if self.prefilled[layer] or self.n_tokens[layer]:
+            raise RuntimeError("prefill needs an empty layer")
+        lo, hi, _nb, _last = self.shard(n_tokens)
+        for t0 in range(lo, hi, chunk):
+            k, v = make_tokens(t0, min(hi, t0 + chunk))
+            self.ctx.append(layer, k, v)
+        self.n_tokens[layer] = n_tokens
+        self.prefilled[layer] = True
+
+    def append(self, layer: int, k, v) -> None:
+        """Appends new tokens (``[n_seqs, T, H, D]``, the same on every rank): only the last
+        rank, the owner of the hot window, stores them."""
+        if self.rank == self.world - 1:
+            self.ctx.append(layer, k, v)
+        self.n_tokens[layer] += k.shape[1]
+
+    def local_blocks(self, layer: int) -> int:
+        """Cold blocks this rank holds, all of which it attends, in ``layer``."""
+        _total, cold, _hot = self.ctx.lengths(layer, 0)
+        return cold // self.ctx.geom.block_tokens
+
+    def decode_partial(self, layer: int, q, mlo=None):
+        """This rank's un-normalised state over its own blocks (+ the window on the last
+        rank): ``[n_seqs, n_q_heads, 2 + D]``."""
+        last = self.rank == self.world - 1
+        return self.ctx.decode_partial(layer, q, 0, self.local_blocks(layer), last, mlo=mlo)
+
+    def decode(self, layer: int, q, out=None):
+        """One decode step for every sequence: ``[n_seqs, n_q_heads, D]`` on every rank."""
+        mlo = self.decode_partial(layer, q)
+        rows = mlo.shape[0] * mlo.shape[1]
+        if self.world == 1:
+            gathered = mlo.reshape(1, rows, mlo.shape[2])
+        else:
+            gathered = gather_states(mlo.reshape(rows, mlo.shape[2]), self.group)
+        res = self.ctx.lse_combine(gathered, out=None if out is None else out.reshape(rows, -1))
+        return res.reshape(mlo.shape[0], mlo.shape[1], -1)
+
+
 class SequenceSplitDecoder:
     """Decode step of one long sequence whose cold blocks are split over the ranks of a
     process group.
