@@ -1,7 +1,8 @@
 """The transformers cache adapter: a tiny random Llama generates with its K/V held in the
-compressed GPU context.  Decode steps attended on the codes must agree with the same cache
-handing the model dense (dequantised) K/V — the reference adapter's behaviour — and stay close
-to the exact DynamicCache."""
+compressed GPU context.  Decode steps attended on the codes must agree with the model run on
+dense K/V that the CPU oracle dequantised from the same tokens (stock SDPA attention, nothing
+of the GPU library on that side), with the adapter's own dense mode, and stay close to the
+exact DynamicCache."""
 
 from __future__ import annotations
 
@@ -18,6 +19,58 @@ def _tiny_llama(torch, dtype):
                       max_position_embeddings=2048, rms_norm_eps=1e-5, tie_word_embeddings=False)
     torch.manual_seed(0)
     return LlamaForCausalLM(cfg).to(device="cuda", dtype=dtype).eval()
+
+
+def _oracle_cache(torch, model, seed, hot_window, value_bits):
+    """A cache whose layers keep every sequence in the CPU oracle's two-tier cache and hand the
+    model the dense dequantised history (the reference adapter's behaviour, with the oracle
+    as the compressor); a prompt into an empty cache is attended on its own K/V."""
+    import numpy as np
+    from transformers.cache_utils import Cache, CacheLayerMixin
+
+    from oracle import tq_oracle as orc
+
+    class OracleLayer(CacheLayerMixin):
+        is_compileable = False
+        is_sliding = False
+
+        def __init__(self):
+            super().__init__()
+            self.caches = None
+            self.n = 0
+            self.is_initialized = False
+
+        def lazy_initialization(self, key_states, value_states):
+            b, h, _t, d = key_states.shape
+            self.caches = [orc.OracleCache(d, h, 4, value_bits, hot_window, 0.02, seed)
+                           for _ in range(b)]
+            self.is_initialized = True
+
+        def update(self, key_states, value_states, *args, **kwargs):
+            if not self.is_initialized:
+                self.lazy_initialization(key_states, value_states)
+            k = key_states.float().cpu().numpy()
+            v = value_states.float().cpu().numpy()
+            for s, c in enumerate(self.caches):
+                for t in range(k.shape[2]):
+                    c.append(k[s, :, t], v[s, :, t])
+            prev, self.n = self.n, self.n + k.shape[2]
+            if prev == 0:
+                return key_states, value_states
+            ks = np.stack([c.keys() for c in self.caches])
+            vs = np.stack([c.values() for c in self.caches])
+            return (torch.from_numpy(ks).to(key_states), torch.from_numpy(vs).to(value_states))
+
+        def get_seq_length(self):
+            return self.n
+
+        def get_mask_sizes(self, query_length):
+            return self.n + query_length, 0
+
+        def get_max_cache_shape(self):
+            return -1
+
+    return Cache(layers=[OracleLayer() for _ in range(model.config.num_hidden_layers)])
 
 
 def _run(torch, model, cache, ids, steps):
@@ -61,9 +114,53 @@ def test_generate_on_codes_matches_dense_history(dtype_name):
 
     # same stored codes, two ways of attending them
     assert torch.allclose(fused, dense, rtol=2e-2, atol=2e-2), (fused - dense).abs().max()
+    # the independent side: tokens compressed and dequantised by the CPU oracle, attended by
+    # the stock SDPA implementation
+    model.config._attn_implementation = "sdpa"
+    want = _run(torch, model, _oracle_cache(torch, model, 0, 512, 4), ids, steps)
+    model.config._attn_implementation = "turboquant"
+    assert torch.allclose(fused, want, rtol=2e-2, atol=2e-2), (fused - want).abs().max()
     # and the compression itself keeps the logits near the uncompressed cache
     cos = torch.nn.functional.cosine_similarity(fused.flatten(1), exact.flatten(1), dim=1)
     assert bool((cos > 0.98).all()), cos
     assert fused_cache.get_seq_length() == 605
     fused_cache.crop(300)
     assert fused_cache.get_seq_length() == 300 and ctx.lengths(0, 0)[0] == 300
+
+
+def test_two_caches_and_uncached_calls_do_not_cross():
+    """The attention function reaches a cache only through the key tensor that cache's update
+    returned: a second cache of the same model, and a forward without any cache, see their own
+    tokens (not the history the first cache stored for the same layer index)."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    from turboquant_pro_b200.hf_cache import TurboQuantCache, enable_turboquant_cache
+
+    model = _tiny_llama(torch, torch.float16)
+    gen = torch.Generator().manual_seed(3)
+    ids_a = torch.randint(0, 97, (1, 40), generator=gen).cuda()
+    ids_b = torch.randint(0, 97, (1, 25), generator=gen).cuda()
+    tok = torch.randint(0, 97, (1, 1), generator=gen).cuda()
+    a = enable_turboquant_cache(model, hot_window=512, value_bits=4, max_tokens=128)
+    b = TurboQuantCache(model.config, hot_window=512, value_bits=4, max_tokens=128)
+    with torch.no_grad():
+        model(input_ids=ids_a, past_key_values=a, use_cache=True)
+        model(input_ids=ids_b, past_key_values=b, use_cache=True)
+        alone = model(input_ids=tok, use_cache=False).logits  # no history at all
+        model.config._attn_implementation = "sdpa"
+        alone_ref = model(input_ids=tok, use_cache=False).logits
+        model.config._attn_implementation = "turboquant"
+        step_a = model(input_ids=tok, past_key_values=a, use_cache=True).logits[:, -1].float()
+        step_b = model(input_ids=tok, past_key_values=b, use_cache=True).logits[:, -1].float()
+        # the same two steps with each cache alone in its own run
+        a2 = TurboQuantCache(model.config, hot_window=512, value_bits=4, max_tokens=128)
+        model(input_ids=ids_a, past_key_values=a2, use_cache=True)
+        want_a = model(input_ids=tok, past_key_values=a2, use_cache=True).logits[:, -1].float()
+        b2 = TurboQuantCache(model.config, hot_window=512, value_bits=4, max_tokens=128)
+        model(input_ids=ids_b, past_key_values=b2, use_cache=True)
+        want_b = model(input_ids=tok, past_key_values=b2, use_cache=True).logits[:, -1].float()
+    assert torch.allclose(alone, alone_ref, rtol=1e-3, atol=1e-3)
+    assert torch.equal(step_a, want_a) and torch.equal(step_b, want_b)
+    assert not torch.allclose(step_a, step_b, atol=1e-3)

@@ -47,9 +47,30 @@ from .context import KVContext
 __all__ = ["TurboQuantCache", "TurboQuantLayer", "enable_turboquant_cache",
            "turboquant_attention_forward"]
 
-# layer index -> the cache layer that was updated last for it (the attention function is
-# called right after `update` in the same forward and has no other way to reach the cache)
-_ACTIVE: dict[int, "weakref.ReferenceType[TurboQuantLayer]"] = {}
+# How the attention function finds the cache: `update` stamps the key tensor it returns with a
+# weak reference to its layer and the length before the append, and the model passes that very
+# tensor on to the attention function in the same forward.  A key tensor without the stamp
+# (use_cache=False, another cache class, a second model) is attended densely as given, so two
+# caches or two models in one process cannot reach each other's history.
+_STAMP = "_turboquant_layer"
+
+# decision "this mask hides nothing" for the mask object of the current forward: every layer
+# of a step receives the same tensor, so the device is asked once per step, not per layer
+_MASK_MEMO: list = [None, False]
+
+
+def _mask_is_open(mask) -> bool:
+    if mask is None:
+        return True
+    ref = _MASK_MEMO[0]
+    if ref is not None and ref() is mask:
+        return _MASK_MEMO[1]
+    if mask.dtype == torch.bool:
+        is_open = bool(mask.all())
+    else:
+        is_open = not bool((mask < 0).any())
+    _MASK_MEMO[0], _MASK_MEMO[1] = weakref.ref(mask), is_open
+    return is_open
 
 
 class _SharedContext:
@@ -110,9 +131,9 @@ class TurboQuantLayer(CacheLayerMixin):
                         value_states.permute(0, 2, 1, 3))
         self._prev_len = self._seq_len
         self._seq_len += int(key_states.shape[-2])
-        _ACTIVE[self.layer_idx] = weakref.ref(self)
         if self.dense and self._prev_len > 0:
             return self.full()
+        setattr(key_states, _STAMP, (weakref.ref(self), self._seq_len))
         return key_states, value_states
 
     def full(self):
@@ -220,25 +241,31 @@ def turboquant_attention_forward(module, query, key, value, attention_mask, drop
     right for a prompt into an empty cache; other cases switch the layer to dense K/V)."""
     from transformers.integrations.sdpa_attention import sdpa_attention_forward
 
-    ref = _ACTIVE.get(getattr(module, "layer_idx", -1))
-    layer = ref() if ref is not None else None
-    fused = (layer is not None and not layer.dense and query.shape[2] == 1
-             and key.shape[2] == 1 and layer.get_seq_length() > 0)
+    # the key tensor is the one TurboQuantLayer.update returned in this forward, or the call
+    # has nothing to do with a compressed cache
+    stamp = getattr(key, _STAMP, None)
+    layer = stamp[0]() if stamp is not None else None
+    if layer is not None and (layer.get_seq_length() != stamp[1]
+                              or layer.layer_idx != getattr(module, "layer_idx", layer.layer_idx)):
+        layer = None  # a stale tensor: the cache has moved on since it was stamped
+    # what the codes-only kernel does not implement goes to the dense path: windows, score
+    # capping, any scale other than 1/sqrt(head_dim)
+    plain = (not kwargs.get("sliding_window") and not kwargs.get("softcap")
+             and not getattr(module, "sliding_window", None)
+             and not getattr(module, "is_sliding", False))
+    fused = (layer is not None and not layer.dense and plain and query.shape[2] == 1
+             and key.shape[2] == 1 and layer.get_seq_length() > 1)
     if fused:
         d = query.shape[-1]
         if scaling is not None and abs(scaling * d ** 0.5 - 1.0) > 1e-3:
             raise NotImplementedError("the decode kernel uses the 1/sqrt(head_dim) scale")
-        if attention_mask is not None and attention_mask.dtype == torch.bool \
-                and not bool(attention_mask.all()):
-            fused = False
-        elif attention_mask is not None and attention_mask.dtype != torch.bool \
-                and bool((attention_mask < 0).any()):
-            fused = False
+        fused = _mask_is_open(attention_mask)
     if fused:
         out = layer.ctx.decode(layer.layer_idx, query[:, :, 0, :])  # [B, Hq, D] float32
         return out.to(query.dtype)[:, None, :, :], None
-    if layer is not None and not layer.dense and key.shape[2] != layer.get_seq_length():
-        # a multi-token query on top of stored history, or a masked batch: dense history
+    if layer is not None and key.shape[2] != layer.get_seq_length():
+        # a multi-token query on top of stored history, a masked batch, a windowed or capped
+        # layer: the dense history
         key, value = layer.full()
     return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout,
                                   scaling=scaling, is_causal=is_causal, **kwargs)
