@@ -43,12 +43,6 @@ namespace {
 // warps per consumer group: 4 (three groups, 168 registers per thread); 8 (two groups, 128
 // registers) builds and runs but measured 30 % slower on the common geometry
 constexpr int GW = TQ_GW;
-// where in a cold tile's attention the next tile's operands are built: 0 before the score
-// tiles, 1 between the score and the value tiles, 2 after the value tiles, 3 by warp (one
-// before, two between, one after: the four warps of a group then take turns)
-#ifndef TQ_PREP_POS
-#define TQ_PREP_POS 1
-#endif
 constexpr int TPW = 256 / GW;        // tokens of a cold page per warp
 constexpr int HALVES = TPW / 16;     // 16-token tiles per warp and page
 static_assert(GW == 4 || GW == 8, "a warp owns 64 or 32 tokens of a page");
@@ -383,15 +377,26 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     else if (tid < 32) small[tid] = a.tables->centroids[tid - 16];
     __syncthreads();
     if (tid < 16) dtab[tid] = small[tid] - __half2float(__float2half_rn(small[tid]));
-    for (int i = tid; i < 256 * 32; i += THREADS) {
-      int b = i >> 5;
-      ((uint32_t*)lutk_p)[i] = pack_h2(small[b & 15], small[b >> 4]);
-    }
+    // an entry is one word repeated 32 times (a copy per lane): a thread computes the word of
+    // its entries once and stores it as eight 16-byte vectors
     constexpr int NV = VB == 3 ? 64 : 256;
-    for (int i = tid; i < NV * 32; i += THREADS) {
-      int b = i >> 5;
-      int ca = VB == 3 ? (b & 7) : (b & 15), cb = VB == 3 ? (b >> 3) : (b >> 4);
-      ((uint32_t*)lutv_p)[i] = pack_h2(small[16 + ca], small[16 + cb]);
+    for (int en = tid; en < 256 + NV; en += THREADS) {
+      uint32_t w;
+      uint4* dst;
+      if (en < 256) {
+        w = pack_h2(small[en & 15], small[en >> 4]);
+        dst = (uint4*)lutk_p + en * 8;
+      } else {
+        const int b = en - 256;
+        const int ca = VB == 3 ? (b & 7) : (b & 15), cb = VB == 3 ? (b >> 3) : (b >> 4);
+        w = pack_h2(small[16 + ca], small[16 + cb]);
+        dst = (uint4*)lutv_p + b * 8;
+      }
+      const uint4 w4 = make_uint4(w, w, w, w);
+      // (the lanes of a warp write different 16-byte columns of their 128-byte entries in
+      // every step, which spreads a store over all banks)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[(i + lane) & 7] = w4;
     }
   }
   // Both kernels of a decode call are launched with programmatic stream serialization: this
@@ -710,17 +715,62 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     pb1 = transpose8x8(w1);  // tokens 8-15
   };
 
-  // ---- the operands of a tile, built one tile ahead -------------------------------------------
-  // What depends on both the query and the page: w = q * scale as fp16 hi/lo B fragments (each
-  // warp builds two of the eight k-steps), bias = q . mean, and for a cold page the outlier
-  // corrections of the warp's own 64 tokens.  A group builds them for its NEXT tile while it
-  // attends the current one (that tile has landed by then: its stage was refilled when the
-  // group before this one finished with it), so the short dependent chains of this work run
-  // in the shadow of the attention loop and no barrier separates a landing tile from its use.
-  auto prepare = [&](int t, const Tile& tl) {
-    const uint8_t* st = stages + (size_t)(t % NSTAGE) * SM::DATA_BYTES;
-    waiter.wait(full0 + 8 * (t % (2 * NSTAGE)), (t / (2 * NSTAGE)) & 1);
-    __syncwarp();  // this warp's reads of its previous correction strip are complete
+  Cursor u_cur = {u_first, 0, 0, 0, 0};
+  int cur_u = -1, cur_kind = -1, q_unit = -1;
+  for (int pos = lo + gi; pos < hi; pos += NG) {
+    const int t = pos - lo, s = t % NSTAGE;
+    const uint32_t full_bar = full0 + 8 * (t % (2 * NSTAGE));
+    const uint32_t full_par = (t / (2 * NSTAGE)) & 1;
+    const Tile tl = tile_at(pos, u_cur);
+    if (tl.u != cur_u || tl.kind != cur_kind) {
+      if (cur_u >= 0) flush(cur_u, cur_kind);
+      reset_state();
+      cur_u = tl.u;
+      cur_kind = tl.kind;
+    }
+    // The stage of the group's previous tile is refilled once all four warps are done with
+    // it; the warps take turns at starting the copy and describe it before the barrier.
+    const bool refill = lane == 0 && gw == (t / NG) % GW && t >= NG && t - NG + NSTAGE < total;
+    CopyDesc cd;
+    if (refill) cd = describe(t - NG + NSTAGE, u_iss);
+    // the group is done with the fragments, bias, query copy and stage of its previous tile
+    group_sync();
+    if (refill && !*abort_flag) {
+      fire(cd);
+      TQ_TRACE(1);
+    }
+    if (tl.u != q_unit) {  // new unit: reload its query rows
+      q_unit = tl.u;
+      if (gtid < TQ_D) {
+        // thread d of the group loads channel d of the G rows: coalesced, independent loads.
+        // The softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
+        // bias and corrections come out already scaled.
+        // query heads follow their KV head
+        const size_t q0 = (size_t)(a.unit_base + tl.u) * (G * TQ_D) + gtid;
+        float qv[G];
+        if (a.q_dtype == TQ_F32) {
+#pragma unroll
+          for (int rr = 0; rr < G; ++rr) qv[rr] = ((const float*)a.q)[q0 + rr * TQ_D];
+        } else if (a.q_dtype == TQ_F16) {
+#pragma unroll
+          for (int rr = 0; rr < G; ++rr)
+            qv[rr] = __half2float(((const __half*)a.q)[q0 + rr * TQ_D]);
+        } else {
+#pragma unroll
+          for (int rr = 0; rr < G; ++rr)
+            qv[rr] = __bfloat162float(((const __nv_bfloat16*)a.q)[q0 + rr * TQ_D]);
+        }
+#pragma unroll
+        for (int rr = 0; rr < G; ++rr) qc[q_row(gtid) * G + rr] = a.scale_log2 * qv[rr];
+      }
+      group_sync();
+    }
+    const uint8_t* st = stages + (size_t)s * SM::DATA_BYTES;
+    if (warp == 0) TQ_TRACE(2);
+    waiter.wait(full_bar, full_par);
+    if (warp == 0) TQ_TRACE(3);
+
+    // ---- operands that depend on the query and the page ------------------------------------
     const bool cold = tl.kind == 0;
     const float* scale = (const float*)(st + g.scale_off);
     {
@@ -889,66 +939,9 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
       fixed_corrections();
       overflow_corrections();
     }
-  };
-  int q_unit = -1;
-  // the group's copy of a unit's query rows, [channel][query head]; the caller synchronises
-  auto load_query = [&](int u) {
-    q_unit = u;
-      if (gtid < TQ_D) {
-        // thread d of the group loads channel d of the G rows: coalesced, independent loads.
-        // The softmax scale (1/sqrt(D), in the log2 domain) rides on the query, so scores,
-        // bias and corrections come out already scaled.
-        // query heads follow their KV head
-        const size_t q0 = (size_t)(a.unit_base + u) * (G * TQ_D) + gtid;
-        float qv[G];
-        if (a.q_dtype == TQ_F32) {
-#pragma unroll
-          for (int rr = 0; rr < G; ++rr) qv[rr] = ((const float*)a.q)[q0 + rr * TQ_D];
-        } else if (a.q_dtype == TQ_F16) {
-#pragma unroll
-          for (int rr = 0; rr < G; ++rr)
-            qv[rr] = __half2float(((const __half*)a.q)[q0 + rr * TQ_D]);
-        } else {
-#pragma unroll
-          for (int rr = 0; rr < G; ++rr)
-            qv[rr] = __bfloat162float(((const __nv_bfloat16*)a.q)[q0 + rr * TQ_D]);
-        }
-#pragma unroll
-        for (int rr = 0; rr < G; ++rr) qc[q_row(gtid) * G + rr] = a.scale_log2 * qv[rr];
-      }
-  };
+    group_sync();  // fragments and bias of all four warps are in place
+    if (warp == 0) TQ_TRACE(4);
 
-  Cursor u_cur = {u_first, 0, 0, 0, 0};
-  Tile tl = {0, 0, 0};
-  if (gi < total) {  // the group's first tile has nobody to prepare it ahead
-    tl = tile_at(lo + gi, u_cur);
-    load_query(tl.u);
-    group_sync();
-    prepare(gi, tl);
-  }
-  for (int t = gi; t < total; t += NG) {
-    const int s = t % NSTAGE;
-    const bool has_next = t + NG < total;
-    const Tile tln = has_next ? tile_at(lo + t + NG, u_cur) : tl;
-    // the group's last tile of a (unit, kind): its state is written out after it, and the
-    // next tile's operands are built after that (the merge uses the operand areas)
-    const bool boundary = !has_next || tln.u != tl.u || tln.kind != tl.kind;
-    // The stage of the group's previous tile is refilled once all four warps are done with
-    // it; the warps take turns at starting the copy and describe it before the barrier.
-    const bool refill = lane == 0 && gw == (t / NG) % GW && t >= NG && t - NG + NSTAGE < total;
-    CopyDesc cd;
-    if (refill) cd = describe(t - NG + NSTAGE, u_iss);
-    // every warp is done with the stage of the group's previous tile and has built its part
-    // of this tile's operands
-    group_sync();
-    if (refill && !*abort_flag) {
-      fire(cd);
-      TQ_TRACE(1);
-    }
-    const uint8_t* st = stages + (size_t)s * SM::DATA_BYTES;
-    const bool cold = tl.kind == 0;
-    if (warp == 0) TQ_TRACE(3);
-    // this tile's operands move to registers ...
     uint32_t breg[NH][8][2];
 #pragma unroll
     for (int nh = 0; nh < NH; ++nh)
@@ -959,31 +952,19 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         breg[nh][j][1] = f.y;
       }
 
-    float corrv[HALVES][NH][2];  // bias + outlier correction of the lane's tokens and heads
     if (cold) {
+      float bias[NH];
+      const float* corr[NH];
 #pragma unroll
       for (int nh = 0; nh < NH; ++nh) {
-        float bias = 0.0f;
+        bias[nh] = 0.0f;
 #pragma unroll
         for (int w4 = 0; w4 < GW / 4; ++w4) {
           const float4 b4 = *(const float4*)(bias_s + hc[nh] * GW + 4 * w4);
-          bias += (b4.x + b4.y) + (b4.z + b4.w);
+          bias[nh] += (b4.x + b4.y) + (b4.z + b4.w);
         }
-        const float* corr = corr_w + hc[nh] * SM::CORR_STRIDE + r;
-#pragma unroll
-        for (int half = 0; half < HALVES; ++half) {
-          corrv[half][nh][0] = bias + corr[16 * half];
-          corrv[half][nh][1] = bias + corr[16 * half + 8];
-        }
+        corr[nh] = corr_w + hc[nh] * SM::CORR_STRIDE + r;
       }
-    }
-    // ... so that the shared copies are free for the next tile's
-    group_sync();
-    if (warp == 0) TQ_TRACE(4);
-    if (cold && !boundary && (TQ_PREP_POS == 0 || (TQ_PREP_POS == 3 && gw == 0)))
-      prepare(t + NG, tln);
-
-    if (cold) {
       const float* norms = (const float*)(st + g.norm_off);
       const uint8_t* vcodes = st + g.v_off;
       // Score tiles of 16 tokens (the lane looks up the codes of tokens r and r + 8; even and
@@ -1070,14 +1051,11 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
             // beyond the group carry zero weights: finite scores nobody reads)
             const float s0 = (C[nh][0][0] + C[nh][1][0]) + (C[nh][0][1] + C[nh][1][1]);
             const float s1 = (C[nh][0][2] + C[nh][1][2]) + (C[nh][0][3] + C[nh][1][3]);
-            sv[half][nh][0] = s0 + corrv[half][nh][0];
-            sv[half][nh][1] = s1 + corrv[half][nh][1];
+            sv[half][nh][0] = s0 + (bias[nh] + corr[nh][16 * half]);
+            sv[half][nh][1] = s1 + (bias[nh] + corr[nh][16 * half + 8]);
           }
         }
         softmax_many(sv);
-        // the operands of the group's next tile, between this tile's two passes
-        if (!boundary && (TQ_PREP_POS == 1 || (TQ_PREP_POS == 3 && (gw == 1 || gw == 2))))
-          prepare(t + NG, tln);
 #pragma unroll
         for (int half = 0; half < HALVES; ++half) {
           const int T0 = TPW * gw + 16 * half;
@@ -1223,27 +1201,13 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         mma16816(acc[mt], af, pb0, pb1);
       }
     }
-    if (!boundary && (!cold || TQ_PREP_POS == 2 || (TQ_PREP_POS == 3 && gw == 3)))
-      prepare(t + NG, tln);
     // every read of the stage is complete before the group's next barrier, after which the
     // stage is refilled
     asm volatile("" ::: "memory");
     __syncwarp();
     if (warp == 0) TQ_TRACE(7);
-    if (boundary) {
-      flush(tl.u, tl.kind);
-      reset_state();
-      if (has_next) {
-        group_sync();  // the merge scratch lies over the operand areas
-        if (tln.u != q_unit) {
-          load_query(tln.u);
-          group_sync();
-        }
-        prepare(t + NG, tln);
-      }
-    }
-    tl = tln;
   }
+  if (cur_u >= 0) flush(cur_u, cur_kind);
   // A group's last tile is among the last NG of the share, so no refill is owed here.  After
   // a timed-out wait copies may still be in flight: they are waited for (bounded) before the
   // CTA gives up its shared memory.
