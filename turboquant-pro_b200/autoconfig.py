@@ -186,6 +186,26 @@ class AutoConfig:
             key_rope_theta=self.rope_theta if zp != "calibrated" else None,
             key_k_bias=k_bias if zp == "bias" else None, **kwargs)
 
+    def build_manager(self, hot_window: int = 512, use_gpu: bool = True, **kwargs):
+        """A :class:`TurboQuantKVManager` over all layers of this model
+        (``autoconfig.py:516-537``); GPU-resident whatever ``use_gpu`` says."""
+        from .manager import TurboQuantKVManager
+
+        return TurboQuantKVManager(n_layers=self.n_layers, n_kv_heads=self.n_kv_heads,
+                                   head_dim=self.head_dim, bits=self.value_bits,
+                                   key_bits=self.key_bits, value_bits=self.value_bits,
+                                   hot_window=hot_window, **kwargs)
+
+    def build_quantizer(self, use_gpu: bool = False, seed: int | None = None):
+        """The reference returns its stateless ``TurboQuantKV`` tensor quantiser here
+        (``autoconfig.py:359-378``).  This package implements the cache path only: the
+        stateless quantiser lives behind the cache (``build_cache``) and the block
+        export / import calls, so there is nothing to hand out."""
+        raise NotImplementedError(
+            "the stateless TurboQuantKV quantiser is not part of the GPU cache path; use "
+            "build_cache() / build_context(), or the reference package for tensor-level "
+            "compress / decompress")
+
     def build_context(self, n_seqs: int, max_tokens_per_seq: int | None = None,
                       hot_window: int = 512, seed: int | None = None,
                       outlier_frac: float = 0.02, kv_dtype="float16", n_layers: int | None = None,

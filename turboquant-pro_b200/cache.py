@@ -17,12 +17,100 @@ side-list, PolarQuant values at 3 or 4 bits; asymmetric NF4 also with the ``spar
 from __future__ import annotations
 
 import logging
+from dataclasses import dataclass, field
+from types import SimpleNamespace
 
 import numpy as np
 
 from .context import KVContext
 
 logger = logging.getLogger(__name__)
+
+
+@dataclass
+class CompressedPerChannelKV:
+    """A cold key block in the reference's container layout (``per_channel_kv.py:103-143``):
+    the same field names, so code that walks ``cache._cold_keys`` keeps working.  The arrays
+    are host copies made when the block is first asked for."""
+
+    indices: np.ndarray            # uint8, bit-reversed nibbles of _pack_indices
+    scale: np.ndarray | None       # uniform grid: (B, H, 1, D) step
+    zero: np.ndarray | None        # uniform grid: (B, H, 1, D) minimum
+    bits: int
+    shape: tuple
+    packed: bool = True
+    levels: np.ndarray | None = None
+    nf4_scale: np.ndarray | None = None   # NF4 family: (B, H, D)
+    nf4_mean: np.ndarray | None = None    # asymmetric NF4: (B, H, D), or the kept channels only
+    original_dtype: np.dtype = field(default_factory=lambda: np.dtype("float32"))
+    outlier_idx: np.ndarray | None = None
+    outlier_val: np.ndarray | None = None
+    zp_mode: str = "calibrated"
+    rope_theta: float | None = None
+    position_start: int = 0
+
+    def nbytes(self) -> int:
+        return sum(a.nbytes for a in (self.indices, self.scale, self.zero, self.levels,
+                                      self.nf4_scale, self.nf4_mean, self.outlier_idx,
+                                      self.outlier_val) if a is not None)
+
+    def compression_ratio(self, head_dim: int) -> float:
+        return int(np.prod(self.shape)) * self.original_dtype.itemsize / max(self.nbytes(), 1)
+
+
+@dataclass
+class CompressedKV:
+    """A cold value block in the reference's container layout (``core.py:96-136``)."""
+
+    indices: np.ndarray
+    norms: np.ndarray
+    bits: int
+    original_dtype: np.dtype = field(default_factory=lambda: np.dtype("float32"))
+    packed: bool = True
+    n_values: int = 0
+    shape: tuple = ()
+
+    def nbytes(self) -> int:
+        return self.indices.nbytes + self.norms.nbytes
+
+    def original_nbytes(self, head_dim: int) -> int:
+        return int(np.prod(self.norms.shape)) * head_dim * self.original_dtype.itemsize
+
+    def compression_ratio(self, head_dim: int) -> float:
+        return self.original_nbytes(head_dim) / max(self.nbytes(), 1)
+
+
+class _ColdView:
+    """``cache._cold_keys`` / ``_cold_values`` / ``_cold_lengths``: a read-only sequence over
+    the cold blocks, materialised block by block from the device on first access (cold
+    blocks never change until the cache is cleared)."""
+
+    def __init__(self, cache, what):
+        self._cache, self._what = cache, what
+
+    def __len__(self):
+        return self._cache.cold_length // self._cache._ctx.block_tokens
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return [self[j] for j in range(*i.indices(len(self)))]
+        n = len(self)
+        if i < 0:
+            i += n
+        if not 0 <= i < n:
+            raise IndexError("cold block index out of range")
+        if self._what == "lengths":
+            return self._cache._ctx.block_tokens
+        return self._cache._cold_block(i)[0 if self._what == "keys" else 1]
+
+    def __iter__(self):
+        return (self[i] for i in range(len(self)))
+
+    def __bool__(self):
+        return len(self) > 0
+
+    def __eq__(self, other):
+        return list(self) == other
 
 
 class TurboQuantKVCache:
@@ -108,6 +196,62 @@ class TurboQuantKVCache:
             self._ctx.set_key_bias_means(np.stack(
                 [rope_averaged_bias(kb, key_rope_theta, head_dim, b * f, f) for b in range(nb)]))
         self.key_outlier_frac = key_outlier_frac
+        self.key_rope_theta = key_rope_theta
+        self._blocks: dict = {}
+        # the two quantisers the reference cache is built from, as far as callers read them:
+        # the value rotation and codebook, the key format
+        cent, bnd = self._ctx.centroids, self._ctx.boundaries
+        self._tq = SimpleNamespace(head_dim=head_dim, n_heads=n_heads, bits=self.value_bits,
+                                   key_bits=self.key_bits, value_bits=self.value_bits,
+                                   _Pi=self._ctx.pi, _Pi_T=self._ctx.pi_t,
+                                   _codebooks={self.value_bits: (cent, bnd)}, use_gpu=True)
+        self._kq = SimpleNamespace(head_dim=head_dim, n_heads=n_heads, bits=self.key_bits,
+                                   nf4=key_nf4, nf4_asym=key_nf4_asym, nuq=False,
+                                   outlier_frac=key_outlier_frac, zero_point=key_zero_point,
+                                   rope_theta=key_rope_theta)
+
+    # ------------------------------------------------------- the reference's block lists --
+    def _cold_block(self, i: int):
+        """(key container, value container) of cold block ``i`` (host copies, cached)."""
+        if i not in self._blocks:
+            g = self._ctx.geom
+            b = self._ctx.export_block(0, 0, i)
+            shape = (1, g.n_kv_heads, g.block_tokens, g.head_dim)
+            dt = np.dtype({0: "float32", 1: "float16", 2: "float32"}[g.kv_dtype])
+            kw = dict(indices=b["key_indices"], bits=self.key_bits, shape=shape, packed=True,
+                      original_dtype=dt, outlier_idx=b["outlier_idx"],
+                      outlier_val=b["outlier_val"], position_start=i * g.block_tokens)
+            if self.key_mode == "uniform":
+                ck = CompressedPerChannelKV(scale=b["nf4_scale"][:, :, None, :],
+                                            zero=b["nf4_mean"][:, :, None, :], **kw)
+            else:
+                mean = b["nf4_mean"] if self.key_mode == "nf4_asym" else None
+                if self.key_zero_point == "sparse":
+                    mean = mean[:, :, self._ctx.key_mean_mask]
+                elif self.key_zero_point == "bias":
+                    mean = None
+                ck = CompressedPerChannelKV(scale=None, zero=None, nf4_scale=b["nf4_scale"],
+                                            nf4_mean=mean, zp_mode=self.key_zero_point,
+                                            rope_theta=self.key_rope_theta, **kw)
+            cv = CompressedKV(indices=b["value_indices"], norms=b["value_norms"],
+                              bits=self.value_bits, original_dtype=dt, packed=True,
+                              n_values=int(np.prod(shape)), shape=shape)
+            self._blocks[i] = (ck, cv)
+        return self._blocks[i]
+
+    @property
+    def _cold_keys(self):
+        """The cold key blocks as ``CompressedPerChannelKV`` containers (``core.py:1011-1038``
+        keeps them in a list of this name)."""
+        return _ColdView(self, "keys")
+
+    @property
+    def _cold_values(self):
+        return _ColdView(self, "values")
+
+    @property
+    def _cold_lengths(self):
+        return _ColdView(self, "lengths")
 
     # ------------------------------------------------------------------ properties --
     @property
@@ -216,3 +360,4 @@ class TurboQuantKVCache:
     def clear(self) -> None:
         """Reset the cache to empty."""
         self._ctx.clear(0, 0)
+        self._blocks.clear()

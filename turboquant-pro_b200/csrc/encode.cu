@@ -74,7 +74,11 @@ TQ_DEV TokenSource<DT> make_source(const EncodeArgs& a, const void* ring_base, c
 //   code = clip(round-half-even(fl(fl(x - min) / scale)), 0, 15).
 // All modes: outliers are every token whose |x| reaches the channel's k-th largest magnitude.
 // ---------------------------------------------------------------------------------------
-template <int DT>
+// With STAGED the block's tokens are first brought into shared memory (every row with
+// independent 16-byte loads, all in flight together) and the three passes read them from
+// there; without it each pass reads global memory, one dependent load per token (kept for
+// float32 tokens, whose block would take 128 KB).
+template <int DT, bool STAGED>
 __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   const tq_geom& g = a.g;
   const int seq = a.seq_begin + blockIdx.z;
@@ -90,6 +94,35 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   const TokenSource<DT> src = make_source<DT>(a, a.hot_k, a.k, seq, head, n0);
   uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
   const int kk = g.outlier_k;
+
+  extern __shared__ __align__(16) uint8_t enck_rows[];  // [S][D] tokens of the block (STAGED)
+  if (STAGED) {
+    using T = typename Elem<DT>::type;
+    constexpr int CH = TQ_D * (int)sizeof(T) / 16;  // 16-byte chunks per row
+    const int n_chunks = S * CH;
+#pragma unroll 8
+    for (int i = d; i < n_chunks; i += TQ_D) {
+      const int t = i / CH, c = i % CH;
+      const int pos = pos0 + t;
+      const bool old = pos < n0;
+      const T* row = old ? (const T*)src.ring + (size_t)(pos % src.cap) * TQ_D
+                         : (const T*)src.in + (size_t)(pos - n0) * src.tok_stride;
+      uint4 v;
+      if (((uintptr_t)row & 15) == 0) {
+        v = ((const uint4*)row)[c];
+      } else {  // rows of an oddly strided caller tensor: element by element
+        T tmp[16 / sizeof(T)];
+#pragma unroll
+        for (int e = 0; e < (int)(16 / sizeof(T)); ++e) tmp[e] = row[c * (16 / sizeof(T)) + e];
+        v = *(const uint4*)tmp;
+      }
+      ((uint4*)enck_rows)[i] = v;
+    }
+  }
+  // token t of this thread's channel
+  auto ldx = [&](int t) -> float {
+    return STAGED ? Elem<DT>::ld(enck_rows, (size_t)t * TQ_D + d) : src.ld(pos0 + t, d);
+  };
 
   __shared__ int s_count;
   __shared__ uint32_t s_off;
@@ -111,7 +144,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 #pragma unroll
   for (int i = 0; i < TQ_MAX_K_OUT; ++i) top[i] = -1.0f;
   const int mode = g.key_mode;
-  float acc = src.ld(pos0, d);
+  float acc = ldx(0);
   float xmin = acc, xmax = acc;
   if (kk > 0) {
     float a0 = fabsf(acc);
@@ -120,7 +153,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     top[i] = a0;
   }
   for (int t = 1; t < S; ++t) {
-    float x = src.ld(pos0 + t, d);
+    float x = ldx(t);
     acc = __fadd_rn(acc, x);
     xmin = fminf(xmin, x);
     xmax = fmaxf(xmax, x);
@@ -147,7 +180,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   float amax = 0.0f;
   int my_out = 0;
   for (int t = 0; t < S; ++t) {
-    float x = src.ld(pos0 + t, d);
+    float x = ldx(t);
     amax = fmaxf(amax, fabsf(mode == TQ_KEYS_NF4_ASYM ? __fsub_rn(x, mu) : x));
     const bool is_out = kk > 0 && fabsf(x) >= kth;
     my_out += is_out ? 1 : 0;
@@ -269,7 +302,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 
   // pass 3: codes and outlier entries
   for (int t = 0; t < S; ++t) {
-    float x = src.ld(pos0 + t, d);
+    float x = ldx(t);
     int best = 0;
     if (mode == TQ_KEYS_UNIFORM) {
       const float qv = rintf(__fdiv_rn(__fsub_rn(x, mu), amax));  // ties to even, like np.round
@@ -556,7 +589,18 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
   const tq_geom& g = a.g;
   if (a.max_new_blocks > 0) {
     dim3 grid(a.max_new_blocks, g.n_kv_heads, a.seq_count);
-    encode_keys_kernel<DT><<<grid, TQ_D, 0, st>>>(a);
+    if (DT == TQ_F32) {
+      encode_keys_kernel<DT, false><<<grid, TQ_D, 0, st>>>(a);
+    } else {
+      const int stage_bytes = g.block_tokens * TQ_D * elem_size(DT);
+      static bool keys_attr_set[16] = {};
+      if (!keys_attr_set[device & 15]) {
+        TQ_CUDA(cudaFuncSetAttribute(encode_keys_kernel<DT, true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * TQ_D * 2));
+        keys_attr_set[device & 15] = true;
+      }
+      encode_keys_kernel<DT, true><<<grid, TQ_D, stage_bytes, st>>>(a);
+    }
     int groups = g.block_tokens_pad / TQ_GROUP_TOK;
     long total = (long)a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
     // one wave: two CTAs per SM, each working on two 16-token groups at a time
