@@ -240,9 +240,12 @@ TQ_DEV void unit_tiles(const MmaArgs& a, int unit, int& nb, int& ht, int& b0, in
   ht = (hot_len + htt - 1) / htt;
 }
 
-// Fills the plan; every thread of the CTA must call it.  `tot` is scratch for one int per
-// 32-unit chunk.
-TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int* tot, int tid, int nthreads) {
+// Fills the plan; every thread of the CTA must call it.  `scratch` takes the chunk totals of
+// the scan (16 x 8 bytes) and, from byte 256 on, nbp[0 .. n_units]: the prefix sums of the
+// units' cold tiles (tile positions + cold tiles before them = the cost a CTA's share is cut by).
+TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, void* scratch, int tid, int nthreads) {
+  unsigned long long* tot = (unsigned long long*)scratch;
+  int* nbp = (int*)scratch + 64;
   for (int u = tid; u < a.n_units; u += nthreads) {
     int nb, ht, b0, hs, hl;
     unit_tiles(a, u, nb, ht, b0, hs, hl);
@@ -257,23 +260,47 @@ TQ_DEV void build_plan(const MmaArgs& a, Plan* plan, int* tot, int tid, int nthr
   const int lane = tid & 31, n_chunks = (a.n_units + 31) / 32;
   for (int ch = tid >> 5; ch < n_chunks; ch += nthreads >> 5) {
     const int i = 32 * ch + lane;
-    int v = i < a.n_units ? plan->P[i + 1] : 0;
+    // tiles in the low word, cold tiles in the high word: one scan for both
+    unsigned long long v = i < a.n_units ? (unsigned long long)(unsigned)plan->P[i + 1] |
+                                               ((unsigned long long)(unsigned)plan->nb[i] << 32)
+                                         : 0ull;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      int n = __shfl_up_sync(0xffffffffu, v, o);
+      unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
       if (lane >= o) v += n;
     }
-    if (i < a.n_units) plan->P[i + 1] = v;
+    if (i < a.n_units) {
+      plan->P[i + 1] = (int)(unsigned)v;
+      nbp[i + 1] = (int)(v >> 32);
+    }
     if (lane == 31) tot[ch] = v;
   }
-  if (tid == 0) plan->P[0] = 0;
-  __syncthreads();
-  for (int i = tid; i < a.n_units; i += nthreads) {
-    int base = 0;
-    for (int ch = 0; ch < (i >> 5); ++ch) base += tot[ch];
-    plan->P[i + 1] += base;
+  if (tid == 0) {
+    plan->P[0] = 0;
+    nbp[0] = 0;
   }
   __syncthreads();
+  for (int i = tid; i < a.n_units; i += nthreads) {
+    unsigned long long base = 0;
+    for (int ch = 0; ch < (i >> 5); ++ch) base += tot[ch];
+    plan->P[i + 1] += (int)(unsigned)base;
+    nbp[i + 1] += (int)(base >> 32);
+  }
+  __syncthreads();
+}
+
+// First tile of the share that starts at cost `v`.  A cold tile costs two units and a hot
+// tile one (a hot tile takes about half the time of a page), so unit u spans the costs
+// P[u] + nbp[u] .. P[u+1] + nbp[u+1] and a tile belongs to the share its first unit falls in.
+TQ_DEV int tile_at_cost(const Plan* plan, const int* nbp, int n_units, int v) {
+  if (v >= plan->P[n_units] + nbp[n_units]) return plan->P[n_units];
+  int lo = 0, hi = n_units - 1;  // largest u whose first cost is <= v
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (plan->P[mid] + nbp[mid] <= v) lo = mid; else hi = mid - 1;
+  }
+  const int local = v - (plan->P[lo] + nbp[lo]), nb = plan->nb[lo];
+  return plan->P[lo] + (local < 2 * nb ? (local + 1) >> 1 : local - nb);
 }
 
 TQ_DEV int find_unit(const Plan* plan, int n_units, int pos) {
@@ -407,21 +434,25 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   TQ_TRACE_PHASE(2);
   // (contains the __syncthreads that publish all of the above; the groups' area is free)
-  build_plan(a, plan, (int*)groups, tid, THREADS);
+  build_plan(a, plan, groups, tid, THREADS);
   // the combine kernel that follows may be scheduled wherever an SM frees up
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  const int T = plan->P[a.n_units];
-  const int Q = (T + a.n_cta - 1) / a.n_cta;
-  const int lo = min((int)blockIdx.x * Q, T), hi = min(lo + Q, T);
+  // The tile list is cut into shares of equal cost (cold tile 2, hot tile 1), one per CTA.
+  const int* nbp = (const int*)groups + 64;
+  const int VT = plan->P[a.n_units] + nbp[a.n_units];
+  const int Q = (VT + a.n_cta - 1) / a.n_cta;
+  const int lo = tile_at_cost(plan, nbp, a.n_units, min((int)blockIdx.x * Q, VT));
+  const int hi = tile_at_cost(plan, nbp, a.n_units, min((int)(blockIdx.x + 1) * Q, VT));
   if (blockIdx.x == 0) {  // the combine kernel reads the plan instead of rebuilding it
-    if (tid == 0) {
-      a.plan_g[0] = T;
-      a.plan_g[1] = max(Q, 1);
-    }
+    if (tid == 0) a.plan_g[0] = a.n_cta;
     for (int u = tid; u <= a.n_units; u += THREADS) a.plan_g[2 + u] = plan->P[u];
     for (int u = tid; u < a.n_units; u += THREADS) a.plan_g[3 + a.n_units + u] = plan->nb[u];
+    // ... and where every CTA's share starts
+    for (int i = tid; i <= a.n_cta; i += THREADS)
+      a.plan_g[3 + 2 * a.n_units + i] = tile_at_cost(plan, nbp, a.n_units, min(i * Q, VT));
   }
+  __syncthreads();  // the cold-tile sums lie in the area the groups take over now
   if (lo >= hi) return;
   TQ_TRACE_PHASE(3);
   const Waiter waiter{abort_flag, a.status, a.spin_limit};
@@ -893,9 +924,9 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
     };
     auto overflow_corrections = [&]() {
       // Entries beyond the fixed slots (ordered by token), or, for a spilled page, the whole
-      // list from the pool: a lane per entry, equal tokens summed across lanes by a segmented
-      // reduction (fixed order, so the result does not depend on timing), and the first lane
-      // of each token adds the sum to the strip.
+      // list from the pool: a lane per entry, the entries of a token summed by the first lane
+      // of their run (fixed order, so the result does not depend on timing), which adds the
+      // sum to the strip.
       // (the page lists its overflow entries by 64-token quarter)
       const int s0 = spilled ? 0 : (int)hdr->ovf_start[(TPW * gw) >> 6];
       const int s1 = spilled ? (int)hdr->cnt : (int)hdr->ovf_start[((TPW * gw) >> 6) + 1];
@@ -914,20 +945,34 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
               mine ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
           const float* qrow = qc + q_row((wv >> 16) & 127) * G;
           float pv[G];
+          if (G >= 4) {
 #pragma unroll
-          for (int gg = 0; gg < G; ++gg) pv[gg] = qrow[gg] * delta;
+            for (int g4 = 0; g4 < G / 4; ++g4) {
+              const float4 qv = *(const float4*)(qrow + 4 * g4);
+              pv[4 * g4] = qv.x * delta; pv[4 * g4 + 1] = qv.y * delta;
+              pv[4 * g4 + 2] = qv.z * delta; pv[4 * g4 + 3] = qv.w * delta;
+            }
+          } else {
 #pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const int tk = __shfl_down_sync(0xffffffffu, tok, o);
-            const bool same = lane + o < 32 && tk == tok;
+            for (int gg = 0; gg < G; ++gg) pv[gg] = qrow[gg] * delta;
+          }
+          // Entries of one token are neighbours (the list is ordered by token); the first lane
+          // of each run adds up its run in lane order.  Runs are short (a token rarely has more
+          // than two entries here), so this takes one or two rounds of shuffles.
+          const int prev = __shfl_up_sync(0xffffffffu, tok, 1);
+          const bool first = lane == 0 || prev != tok;
+          const unsigned starts = __ballot_sync(0xffffffffu, first);
+          const unsigned later = lane == 31 ? 0u : (starts >> (lane + 1)) << (lane + 1);
+          const int run_end = later ? __ffs((int)later) - 1 : 32;  // first lane of the next run
+          const int longest = __reduce_max_sync(0xffffffffu, first ? run_end - lane : 0);
+          for (int o = 1; o < longest; ++o) {
 #pragma unroll
             for (int gg = 0; gg < G; ++gg) {
               const float nv = __shfl_down_sync(0xffffffffu, pv[gg], o);
-              if (same) pv[gg] += nv;
+              if (first && lane + o < run_end) pv[gg] += nv;
             }
           }
-          const int prev = __shfl_up_sync(0xffffffffu, tok, 1);
-          if (mine && (lane == 0 || prev != tok)) {
+          if (mine && first) {
 #pragma unroll
             for (int gg = 0; gg < G; ++gg) corr_w[gg * SM::CORR_STRIDE + (tok & (TPW - 1))] += pv[gg];
           }
@@ -1223,18 +1268,21 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 // (acc @ Pi) and writes the output or the (m, l, o) state.  Partial maxima are in the log2
 // domain.  Built for short dependency chains: the candidate slots are tested in parallel and
 // compacted in order, and a round's maxima, sums and accumulator rows are loaded together.
-template <int G>
+// A CTA merges GH of the unit's G query heads (blockIdx.y picks which): all of them where a
+// layer has many units, one where it has few and the merge is on the critical path.
+template <int G, int GH>
 __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
-  constexpr int RP = G >= 8 ? 8 : (G >= 4 ? 16 : 32);  // partials per round
+  constexpr int RP = GH >= 8 ? 8 : (GH >= 4 ? 16 : 32);  // partials per round
+  const int g0 = blockIdx.y * GH;  // first head of this CTA
   const tq_geom& g = a.g;
   const int unit = blockIdx.x, e = threadIdx.x, lane = e & 31, wid = e >> 5;
   const int seq = (a.unit_base + unit) / g.n_kv_heads, head = (a.unit_base + unit) % g.n_kv_heads;
-  __shared__ float cs[G][TQ_D];
+  __shared__ float cs[GH][TQ_D];
   __shared__ const float* s_ptr[TQ_D];  // partials of the current chunk of candidates
   __shared__ unsigned char s_cold[TQ_D];
   __shared__ int s_wcount[TQ_D / 32];
-  __shared__ float s_m[RP][G], s_l[RP][G], s_wgt[RP][G];
-  __shared__ float s_M[G], s_L[G], s_scale[G];
+  __shared__ float s_m[RP][GH], s_l[RP][GH], s_wgt[RP][GH];
+  __shared__ float s_M[GH], s_L[GH], s_scale[GH];
   // This kernel is launched while the attention kernel may still be running (programmatic
   // dependent launch): its column of the rotation matrix, which no kernel writes, is fetched
   // first; everything the attention kernel produces is read after the wait.
@@ -1243,18 +1291,39 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   for (int d = 0; d < TQ_D; ++d) pcol[d] = a.tables->pi[d * TQ_D + e];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int Q = a.plan_g[1];
+  const int n_cta = a.plan_g[0];
+  // first tile of every CTA's share, and the end of the last one (one round trip to global
+  // memory, then searched in shared memory)
+  __shared__ int share[200];
+  for (int i = e; i <= n_cta; i += TQ_D) share[i] = a.plan_g[3 + 2 * a.n_units + i];
+  __syncthreads();
   const int p0 = a.plan_g[2 + unit], p1 = a.plan_g[3 + unit];
   const int pc = p0 + a.plan_g[3 + a.n_units + unit];
   const int NG = a.n_groups;
-  const int i0 = p1 > p0 ? p0 / Q : 0, i1 = p1 > p0 ? (p1 - 1) / Q : -1;
-  if (e < G) {
+  // the CTAs whose shares meet the unit's tiles [p0, p1): i0 = the last one that starts at or
+  // before p0, i1 = the last one that starts before p1
+  int i0 = 0, i1 = -1;
+  if (p1 > p0) {
+    int lo_i = 0, hi_i = n_cta - 1;
+    while (lo_i < hi_i) {
+      const int mid = (lo_i + hi_i + 1) >> 1;
+      if (share[mid] <= p0) lo_i = mid; else hi_i = mid - 1;
+    }
+    i0 = lo_i;
+    hi_i = n_cta - 1;
+    while (lo_i < hi_i) {
+      const int mid = (lo_i + hi_i + 1) >> 1;
+      if (share[mid] < p1) lo_i = mid; else hi_i = mid - 1;
+    }
+    i1 = lo_i;
+  }
+  if (e < GH) {
     s_M[e] = NEG_BIG;
     s_L[e] = 0.0f;
   }
-  float C[G], Hh[G];
+  float C[GH], Hh[GH];
 #pragma unroll
-  for (int gg = 0; gg < G; ++gg) C[gg] = Hh[gg] = 0.0f;
+  for (int gg = 0; gg < GH; ++gg) C[gg] = Hh[gg] = 0.0f;
   // candidate t = ((cta - i0) * 2 + kind) * NG + group, tested 128 at a time
   const int n_cand = (i1 - i0 + 1) * 2 * NG;
   for (int base = 0; base < n_cand; base += TQ_D) {
@@ -1268,7 +1337,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
       const int i = i0 + (ck >> 1);
       // tiles of this kind that CTA i holds for the unit: positions [ra, rb); the tile at
       // position p belongs to consumer group (p - lo) % NG
-      const int lo = i * Q, hi = lo + Q;
+      const int lo = share[i], hi = share[i + 1];
       const int ra = kind == 0 ? max(lo, p0) : max(lo, pc);
       const int rb = kind == 0 ? min(hi, pc) : min(hi, p1);
       const int cnt = rb - ra;
@@ -1297,21 +1366,21 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
       const int nr = min(RP, n_chunk - r0);
       // this round's accumulator rows (all loads independent; rows past the end repeat the
       // last one and are ignored), maxima and sums
-      float av[RP][G];
+      float av[RP][GH];
 #pragma unroll
       for (int j = 0; j < RP; ++j) {
         const float* pp = s_ptr[r0 + min(j, nr - 1)] + 2 + e;
 #pragma unroll
-        for (int gg = 0; gg < G; ++gg) av[j][gg] = pp[gg * TQ_PART_STRIDE];
+        for (int gg = 0; gg < GH; ++gg) av[j][gg] = pp[(g0 + gg) * TQ_PART_STRIDE];
       }
-      if (e < nr * G) {
-        const int j = e / G, gg = e % G;
-        const float* pp = s_ptr[r0 + j] + gg * TQ_PART_STRIDE;
+      if (e < nr * GH) {
+        const int j = e / GH, gg = e % GH;
+        const float* pp = s_ptr[r0 + j] + (g0 + gg) * TQ_PART_STRIDE;
         s_m[j][gg] = pp[0];
         s_l[j][gg] = pp[1];
       }
       __syncthreads();
-      if (e < G) {
+      if (e < GH) {
         float M = s_M[e];
         for (int j = 0; j < nr; ++j)
           if (s_l[j][e] > 0.0f) M = fmaxf(M, s_m[j][e]);
@@ -1328,7 +1397,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
       }
       __syncthreads();
 #pragma unroll
-      for (int gg = 0; gg < G; ++gg) {
+      for (int gg = 0; gg < GH; ++gg) {
         C[gg] *= s_scale[gg];
         Hh[gg] *= s_scale[gg];
       }
@@ -1337,7 +1406,7 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
         if (j < nr) {
           const bool cold = s_cold[r0 + j] != 0;
 #pragma unroll
-          for (int gg = 0; gg < G; ++gg) {
+          for (int gg = 0; gg < GH; ++gg) {
             const float wgt = s_wgt[j][gg];
             const float v = wgt > 0.0f ? av[j][gg] * wgt : 0.0f;
             if (cold) C[gg] += v; else Hh[gg] += v;
@@ -1348,19 +1417,19 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
     }
   }
 #pragma unroll
-  for (int gg = 0; gg < G; ++gg) cs[gg][e] = C[gg];
+  for (int gg = 0; gg < GH; ++gg) cs[gg][e] = C[gg];
   __syncthreads();
-  float o[G];
+  float o[GH];
 #pragma unroll
-  for (int gg = 0; gg < G; ++gg) o[gg] = 0.0f;
+  for (int gg = 0; gg < GH; ++gg) o[gg] = 0.0f;
 #pragma unroll
   for (int d = 0; d < TQ_D; ++d) {
 #pragma unroll
-    for (int gg = 0; gg < G; ++gg) o[gg] += cs[gg][d] * pcol[d];
+    for (int gg = 0; gg < GH; ++gg) o[gg] += cs[gg][d] * pcol[d];
   }
 #pragma unroll
-  for (int gg = 0; gg < G; ++gg) {
-    const size_t row = (size_t)seq * g.n_q_heads + head * G + gg;
+  for (int gg = 0; gg < GH; ++gg) {
+    const size_t row = (size_t)seq * g.n_q_heads + head * G + g0 + gg;
     const float val = o[gg] + Hh[gg];
     const float L = s_L[gg];
     if (a.mlo != nullptr) {
@@ -1421,10 +1490,15 @@ int launch_t(MmaArgs a, cudaStream_t st, tq_ctx* ctx, bool first, bool last) {
   std::memcpy(&tmv, ctx->tmap_hot[1], sizeof(CUtensorMap));
   TQ_CUDA(cudaLaunchKernelEx(&cfg, decode_mma_kernel<G, VB>, a, tmk, tmv));
   if (e1) cudaEventRecord(e1, st);
-  cfg.gridDim = dim3((unsigned)a.n_units);
   cfg.blockDim = dim3(TQ_D);
   cfg.dynamicSmemBytes = 0;
-  TQ_CUDA(cudaLaunchKernelEx(&cfg, combine_mma_kernel<G>, a));
+  if (G > 1 && a.n_units <= 64) {  // few units: a CTA per query head, the merge is latency
+    cfg.gridDim = dim3((unsigned)a.n_units, G);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, combine_mma_kernel<G, 1>, a));
+  } else {
+    cfg.gridDim = dim3((unsigned)a.n_units);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, combine_mma_kernel<G, G>, a));
+  }
   if (e2) {
     cudaEventRecord(e2, st);
     tq_prof_commit(ctx);

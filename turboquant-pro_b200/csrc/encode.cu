@@ -139,33 +139,38 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   s_side[d + TQ_D] = 0u;
   __syncthreads();
 
-  // pass 1: sequential sum and the k largest magnitudes (ascending; top[0] is the k-th)
-  float top[TQ_MAX_K_OUT];
+  // pass 1: sequential sum and the k largest magnitudes.  Up to eight of them (the usual
+  // case: k = 5 at 256-token blocks) are kept in an ascending register array updated without
+  // branches, t[j] <- min(max(|x|, t[j]), t[j+1]); larger k takes the insertion loop.
+  constexpr int TK = 8;
+  const bool small_k = kk <= TK;  // uniform over the grid
+  float t8[TK];
+#pragma unroll
+  for (int i = 0; i < TK; ++i) t8[i] = -1.0f;
+  float top[TQ_MAX_K_OUT];  // ascending; top[0] is the k-th largest (k > 8 only)
 #pragma unroll
   for (int i = 0; i < TQ_MAX_K_OUT; ++i) top[i] = -1.0f;
   const int mode = g.key_mode;
-  float acc = ldx(0);
-  float xmin = acc, xmax = acc;
-  if (kk > 0) {
-    float a0 = fabsf(acc);
-    int i = 0;
-    while (i + 1 < kk && top[i + 1] < a0) { top[i] = top[i + 1]; ++i; }
-    top[i] = a0;
-  }
-  for (int t = 1; t < S; ++t) {
-    float x = ldx(t);
-    acc = __fadd_rn(acc, x);
-    xmin = fminf(xmin, x);
-    xmax = fmaxf(xmax, x);
-    if (kk > 0) {
-      float ax = fabsf(x);
-      if (ax > top[0]) {
-        int i = 0;
-        while (i + 1 < kk && top[i + 1] < ax) { top[i] = top[i + 1]; ++i; }
-        top[i] = ax;
-      }
+  float acc = 0.0f, xmin = 0.0f, xmax = 0.0f;
+  for (int t = 0; t < S; ++t) {
+    const float x = ldx(t);
+    acc = t == 0 ? x : __fadd_rn(acc, x);
+    xmin = t == 0 ? x : fminf(xmin, x);
+    xmax = t == 0 ? x : fmaxf(xmax, x);
+    const float ax = fabsf(x);
+    if (small_k) {
+#pragma unroll
+      for (int j = 0; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
+      t8[TK - 1] = fmaxf(ax, t8[TK - 1]);
+    } else if (ax > top[0]) {
+      int i = 0;
+      while (i + 1 < kk && top[i + 1] < ax) { top[i] = top[i + 1]; ++i; }
+      top[i] = ax;
     }
   }
+  float kth_small = -1.0f;  // the k-th largest = element TK - k of the ascending eight
+#pragma unroll
+  for (int j = 0; j < TK; ++j) kth_small = (j == TK - kk) ? t8[j] : kth_small;
   // (the "sparse" zero-point keeps the mean on the masked channels only)
   const float mu = mode == TQ_KEYS_NF4_ASYM
                        ? (a.bias_means != nullptr
@@ -174,7 +179,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
                                                    : 0.0f)
                    : mode == TQ_KEYS_NF4 ? 0.0f
                                          : xmin;
-  const float kth = (kk >= S) ? -1.0f : top[0];
+  const float kth = (kk >= S || kk == 0) ? -1.0f : (small_k ? kth_small : top[0]);
 
   // pass 2: scale, and how many outliers this channel keeps
   float amax = 0.0f;
@@ -300,56 +305,79 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   const size_t slab = unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + s_off;
   const int alloc = s_alloc;
 
-  // pass 3: codes and outlier entries
-  for (int t = 0; t < S; ++t) {
-    float x = ldx(t);
-    int best = 0;
+  // pass 3: codes and outlier entries.  The nearest level of a token is found by a
+  // tournament over the 16 distances in which the lower index wins a tie at every round (the
+  // first minimum, like a strict-less scan from level 0, in four dependent steps instead of
+  // fifteen), and two tokens are worked on together so that their chains overlap.
+  auto nearest = [&](float x) -> int {
     if (mode == TQ_KEYS_UNIFORM) {
       const float qv = rintf(__fdiv_rn(__fsub_rn(x, mu), amax));  // ties to even, like np.round
-      best = (int)fminf(fmaxf(qv, 0.0f), 15.0f);
-    } else {
-      float bd = fabsf(__fsub_rn(x, lev[0]));
+      return (int)fminf(fmaxf(qv, 0.0f), 15.0f);
+    }
+    float dv[16];
 #pragma unroll
-      for (int l = 1; l < 16; ++l) {
-        float dd = fabsf(__fsub_rn(x, lev[l]));
-        if (dd < bd) {
-          bd = dd;
-          best = l;
-        }
+    for (int l = 0; l < 16; ++l) dv[l] = fabsf(__fsub_rn(x, lev[l]));
+    int ix[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool up = dv[2 * j + 1] < dv[2 * j];
+      dv[j] = up ? dv[2 * j + 1] : dv[2 * j];
+      ix[j] = 2 * j + (up ? 1 : 0);
+    }
+#pragma unroll
+    for (int w = 4; w >= 1; w >>= 1) {
+#pragma unroll
+      for (int j = 0; j < w; ++j) {
+        const bool up = dv[2 * j + 1] < dv[2 * j];
+        dv[j] = up ? dv[2 * j + 1] : dv[2 * j];
+        ix[j] = up ? ix[2 * j + 1] : ix[2 * j];
       }
     }
-    if (rank < 4) atomicOr(&s_side[t], (unsigned int)best << (4 * rank));
-    int other = __shfl_down_sync(0xffffffffu, best, 1);
-    if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
-    // A token's outliers are stored in channel order (the order of the reference's flat
-    // indices), so the side-list, and with it every bit the decoder computes, is a function
-    // of the tokens alone: this channel's place is the count of outlier channels below it.
-    const bool is_out = kk > 0 && fabsf(x) >= kth;
-    const unsigned vote = __ballot_sync(0xffffffffu, is_out);
-    if (is_out) {
-      int below = __popc(vote & ((1u << (d & 31)) - 1u));
-      for (int w = 0; w < (d >> 5); ++w) below += (int)s_cnt_w[t][w];
-      const int slot = s_row[t] + below;
-      __half hv = __float2half_rn(x);
-      // the decoder's value of this position (the level, recomputed: indexing lev[] with a
-      // runtime index would move the whole array out of registers)
-      const float sl = __fmul_rn(amax, a.tables->grid[best]);
-      float dense = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
-      __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
-      const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
-                           ((uint32_t)t << 24);
-      if (slot < alloc) {
-        a.pool_dec[slab + slot] = ent;
-        a.pool_val[slab + slot] = __half_as_ushort(hv);
+    return ix[0];
+  };
+  for (int t0 = 0; t0 < S; t0 += 2) {
+    const float xa = ldx(t0), xb = ldx(min(t0 + 1, S - 1));
+    const int best_a = nearest(xa), best_b = nearest(xb);
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+      const int t = t0 + sub;
+      if (t >= S) break;  // uniform
+      const float x = sub ? xb : xa;
+      const int best = sub ? best_b : best_a;
+      if (rank < 4) atomicOr(&s_side[t], (unsigned int)best << (4 * rank));
+      int other = __shfl_down_sync(0xffffffffu, best, 1);
+      if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = (uint8_t)(best | (other << 4));
+      // A token's outliers are stored in channel order (the order of the reference's flat
+      // indices), so the side-list, and with it every bit the decoder computes, is a function
+      // of the tokens alone: this channel's place is the count of outlier channels below it.
+      const bool is_out = kk > 0 && fabsf(x) >= kth;
+      const unsigned vote = __ballot_sync(0xffffffffu, is_out);
+      if (is_out) {
+        int below = __popc(vote & ((1u << (d & 31)) - 1u));
+        for (int w = 0; w < (d >> 5); ++w) below += (int)s_cnt_w[t][w];
+        const int slot = s_row[t] + below;
+        __half hv = __float2half_rn(x);
+        // the decoder's value of this position (the level, recomputed: indexing lev[] with a
+        // runtime index would move the whole array out of registers)
+        const float sl = __fmul_rn(amax, a.tables->grid[best]);
+        float dense = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
+        __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
+        const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
+                             ((uint32_t)t << 24);
+        if (slot < alloc) {
+          a.pool_dec[slab + slot] = ent;
+          a.pool_val[slab + slot] = __half_as_ushort(hv);
+        }
+        const int j = slot - s_row[t];  // which of the token's outliers this is
+        if (j < TQ_ELL_SLOTS) {
+          ell_delta[j * 256 + t] = __half_as_ushort(delta);
+          ell_col[j * 256 + t] = (uint8_t)q_row(d);
+        } else {
+          const int oi = s_orow[t] + j - TQ_ELL_SLOTS;
+          if (oi < TQ_OVF_CAP) ovf[oi] = ent;
+        }
       }
-      const int j = slot - s_row[t];  // which of the token's outliers this is
-      if (j < TQ_ELL_SLOTS) {
-        ell_delta[j * 256 + t] = __half_as_ushort(delta);
-        ell_col[j * 256 + t] = (uint8_t)q_row(d);
-      } else {
-        const int oi = s_orow[t] + j - TQ_ELL_SLOTS;
-        if (oi < TQ_OVF_CAP) ovf[oi] = ent;
-      }
+
     }
   }
   __syncthreads();
@@ -367,25 +395,48 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 // Rotation of 16 vectors held transposed in shared memory (us[d][t]) by column e of the
 // matrix in shared memory (pit[d][e]).  The reference's result is the unfused sequential sum
 // acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every product and sum rounded to float32
-// separately (rotate_one below).  rotate16_fused is the same sum with fused multiply-adds:
-// half the arithmetic, and a result within ROT_SLACK of the unfused one.  Both forms round
-// 128 products and 127 sums of terms whose absolute values add up to at most
-// |u| |column| <= 1: each is within 127 * 2^-24 + 2^-24 < 7.7e-6 of the exact dot product,
-// so they differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.
+// separately (rotate_one below).  rotate16_pair computes the same sum with fused multiply-adds
+// in two halves of 64 terms: half the arithmetic, and a result within ROT_SLACK of the unfused
+// one.  Either form rounds at most 128 products and 127 sums of terms whose absolute values add
+// up to at most |u| |column| <= 1: each is within 127 * 2^-24 + 2^-24 < 7.7e-6 of the exact dot
+// product, so they differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.
 constexpr float ROT_SLACK = 4.0e-5f;
-TQ_DEV void rotate16_fused(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, float* acc) {
+// Two float32 lanes in one 64-bit register and the packed fused multiply-add on them.
+TQ_DEV unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+TQ_DEV void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+TQ_DEV unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+// Half of the fused rotation for two neighbouring output channels c0, c0 + 1 (c0 even): the
+// input channels [d0, d0 + 64) of 16 tokens.  acc[ch][i] holds tokens 2i, 2i+1 of channel
+// c0 + ch.  One 8-byte load brings the two matrix entries of a row and four 16-byte loads the
+// 16 unit-vector entries, for 32 multiply-adds issued as 16 packed instructions: half the
+// loads and half the arithmetic instructions per multiply-add of the one-channel form.
+TQ_DEV void rotate16_pair(const float (*us)[TQ_GROUP_TOK], const float* pit, int c0, int d0,
+                          unsigned long long (&acc)[2][8]) {
 #pragma unroll
-  for (int t = 0; t < TQ_GROUP_TOK; ++t) acc[t] = 0.0f;
+  for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[ch][i] = 0ull;
 #pragma unroll 4
-  for (int dd = 0; dd < TQ_D; ++dd) {
-    const float p = pit[dd * TQ_D + e];
+  for (int dd = d0; dd < d0 + TQ_D / 2; ++dd) {
+    const float2 p = *(const float2*)&pit[dd * TQ_D + c0];
+    const unsigned long long b0 = pack2(p.x, p.x), b1 = pack2(p.y, p.y);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float4 u = *(const float4*)&us[dd][4 * q];
-      acc[4 * q + 0] = fmaf(u.x, p, acc[4 * q + 0]);
-      acc[4 * q + 1] = fmaf(u.y, p, acc[4 * q + 1]);
-      acc[4 * q + 2] = fmaf(u.z, p, acc[4 * q + 2]);
-      acc[4 * q + 3] = fmaf(u.w, p, acc[4 * q + 3]);
+      const ulonglong2 u = *(const ulonglong2*)&us[dd][4 * q];  // tokens (4q, 4q+1), (4q+2, 4q+3)
+      acc[0][2 * q] = ffma2(u.x, b0, acc[0][2 * q]);
+      acc[0][2 * q + 1] = ffma2(u.y, b0, acc[0][2 * q + 1]);
+      acc[1][2 * q] = ffma2(u.x, b1, acc[1][2 * q]);
+      acc[1][2 * q + 1] = ffma2(u.y, b1, acc[1][2 * q + 1]);
     }
   }
 }
@@ -495,8 +546,32 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
         hs->us[8 * i + j][t] = __fdiv_rn(hs->xs[t][8 * i + j], safe);
     }
     half_sync();
+    // Fused rotation: thread (hh, ep) sums the input channels [64 hh, 64 hh + 64) for the two
+    // output channels 2 ep, 2 ep + 1; the two threads of a channel pair then swap one partial
+    // sum each (through the row buffer, which is no longer needed), after which thread
+    // (hh, ep) owns output channel ch = 2 ep + hh with all 128 terms.
+    const int hh = e >> 6, ep = e & 63, ch = 2 * ep + hh;
     float acc[TQ_GROUP_TOK];
-    rotate16_fused(hs->us, pit, e, acc);
+    {
+      unsigned long long part[2][8];
+      rotate16_pair(hs->us, pit, 2 * ep, (TQ_D / 2) * hh, part);
+      float* ex = &hs->xs[0][0];  // [token][thread]
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {  // the channel this thread gives away
+        float lo, hi;
+        unpack2(hh ? part[0][i] : part[1][i], lo, hi);
+        ex[(2 * i) * TQ_D + e] = lo;
+        ex[(2 * i + 1) * TQ_D + e] = hi;
+      }
+      half_sync();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {  // ... and the partner's half of the one it keeps
+        float lo, hi;
+        unpack2(hh ? part[1][i] : part[0][i], lo, hi);
+        acc[2 * i] = lo + ex[(2 * i) * TQ_D + (e ^ 64)];
+        acc[2 * i + 1] = hi + ex[(2 * i + 1) * TQ_D + (e ^ 64)];
+      }
+    }
     int code[TQ_GROUP_TOK];
     unsigned redo = 0u;  // tokens whose coordinate has a boundary within the slack
 #pragma unroll
@@ -513,7 +588,7 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     while (redo) {
       const int t = __ffs((int)redo) - 1;
       redo &= redo - 1;
-      const float y = rotate_one(hs->us, pit, e, t);
+      const float y = rotate_one(hs->us, pit, ch, t);
       int c = 0;
       for (int j = 0; j < n_bnd; ++j) c += (s_bnd[j] < y) ? 1 : 0;
 #pragma unroll
@@ -521,7 +596,7 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     }
     // pack this channel's 8 token pairs into the group image
     uint32_t* img = hs->img;
-    const int dq = e & 7, i16 = e >> 3;  // record lane group and slot of channel e
+    const int dq = ch & 7, i16 = ch >> 3;  // record lane group and slot of this thread's channel
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
 #pragma unroll
