@@ -1,8 +1,10 @@
 """Generate the golden fixtures in this directory by running the REFERENCE itself.
 
-Usage (only where the reference checkout is available)::
+Usage (only where the reference is available)::
 
     TQ_REF_PATH=/path/to/turboquant-pro python tests/golden/make_golden.py
+
+Without ``TQ_REF_PATH`` the copy that ``make -C oracle ref`` puts under ``oracle/_ref`` is used.
 
 The reference is imported, never copied: this script feeds it seeded inputs through
 its public API (``PerChannelKV.compress``, ``TurboQuantKV.compress``,
@@ -19,7 +21,7 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("TQ_REF_PATH", "/root/reference")
+REF = os.environ.get("TQ_REF_PATH") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "oracle", "_ref")
 sys.path.insert(0, REF)
 
 from turboquant_pro.core import TurboQuantKV, TurboQuantKVCache  # noqa: E402

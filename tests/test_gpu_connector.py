@@ -45,7 +45,7 @@ def test_paged_save_load_attend_evict(torch_cuda):
     conn = TurboQuantKVConnector(store=store)
     k, v = make_kv(21, h, n, dtype=np.float16)
     kt, vt = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
-    table = [5, 2, 60, 61] + list(range(8, 8 + 53))  # 57 blocks of 16 tokens, out of order
+    table = [5, 2, 62, 63] + list(range(8, 8 + 53))  # 57 distinct blocks of 16 tokens, out of order
     kv_layer = _paged(torch, kt, vt, bs, table, 64)
     meta = SimpleNamespace(request_id="req-a", block_table=table, num_tokens=n)
     conn.save_kv_layer("model.layers.1.self_attn.attn", kv_layer, meta)

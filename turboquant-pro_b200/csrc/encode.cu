@@ -181,12 +181,15 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
                                          : xmin;
   const float kth = (kk >= S || kk == 0) ? -1.0f : (small_k ? kth_small : top[0]);
 
-  // pass 2: scale, and how many outliers this channel keeps
-  float amax = 0.0f;
+  // The scale max_s |fl(x_s - mu)| is reached at the smallest or the largest token (rounding is
+  // monotone), so it needs no pass of its own.
+  float amax = mode == TQ_KEYS_NF4_ASYM
+                   ? fmaxf(fabsf(__fsub_rn(xmax, mu)), fabsf(__fsub_rn(xmin, mu)))
+                   : fmaxf(fabsf(xmax), fabsf(xmin));
+  // pass 2: how many outliers this channel keeps, and which tokens they fall on
   int my_out = 0;
   for (int t = 0; t < S; ++t) {
     float x = ldx(t);
-    amax = fmaxf(amax, fabsf(mode == TQ_KEYS_NF4_ASYM ? __fsub_rn(x, mu) : x));
     const bool is_out = kk > 0 && fabsf(x) >= kth;
     my_out += is_out ? 1 : 0;
     // (the loop is uniform over the warp: every lane takes part in the vote)
@@ -401,6 +404,10 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 // up to at most |u| |column| <= 1: each is within 127 * 2^-24 + 2^-24 < 7.7e-6 of the exact dot
 // product, so they differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.
 constexpr float ROT_SLACK = 4.0e-5f;
+// Row strides of the value encoder's shared arrays, chosen so that its 8-threads-per-token
+// phases (norms, unit vectors) touch 32 different banks: token rows 136 floats apart,
+// transposed rows 20 floats apart (still 16-byte aligned for the rotation's vector loads).
+constexpr int ENCV_XS = TQ_D + 8, ENCV_US = TQ_GROUP_TOK + 4;
 // Two float32 lanes in one 64-bit register and the packed fused multiply-add on them.
 TQ_DEV unsigned long long pack2(float lo, float hi) {
   unsigned long long r;
@@ -420,7 +427,7 @@ TQ_DEV unsigned long long ffma2(unsigned long long a, unsigned long long b, unsi
 // c0 + ch.  One 8-byte load brings the two matrix entries of a row and four 16-byte loads the
 // 16 unit-vector entries, for 32 multiply-adds issued as 16 packed instructions: half the
 // loads and half the arithmetic instructions per multiply-add of the one-channel form.
-TQ_DEV void rotate16_pair(const float (*us)[TQ_GROUP_TOK], const float* pit, int c0, int d0,
+TQ_DEV void rotate16_pair(const float (*us)[ENCV_US], const float* pit, int c0, int d0,
                           unsigned long long (&acc)[2][8]) {
 #pragma unroll
   for (int ch = 0; ch < 2; ++ch)
@@ -441,7 +448,7 @@ TQ_DEV void rotate16_pair(const float (*us)[TQ_GROUP_TOK], const float* pit, int
   }
 }
 // one coordinate of the unfused rotation: token t of the group, output channel e
-TQ_DEV float rotate_one(const float (*us)[TQ_GROUP_TOK], const float* pit, int e, int t) {
+TQ_DEV float rotate_one(const float (*us)[ENCV_US], const float* pit, int e, int t) {
   float y = __fmul_rn(us[0][t], pit[e]);
 #pragma unroll 8
   for (int dd = 1; dd < TQ_D; ++dd) y = __fadd_rn(y, __fmul_rn(us[dd][t], pit[dd * TQ_D + e]));
@@ -462,12 +469,12 @@ TQ_DEV float rotate_one(const float (*us)[TQ_GROUP_TOK], const float* pit, int e
 // ---------------------------------------------------------------------------------------
 constexpr int ENCV_HALVES = 2;
 struct EncvHalf {
-  float xs[TQ_GROUP_TOK][TQ_D];
-  float us[TQ_D][TQ_GROUP_TOK];
+  float xs[TQ_GROUP_TOK][ENCV_XS];
+  float us[TQ_D][ENCV_US];
   uint32_t img[256];
   float norm[TQ_GROUP_TOK];
 };
-constexpr int ENCV_SMEM = TQ_D * TQ_D * 4 + ENCV_HALVES * (int)sizeof(EncvHalf) + 64;
+constexpr int ENCV_SMEM = TQ_D * TQ_D * 4 + ENCV_HALVES * (int)sizeof(EncvHalf) + 128;
 
 template <int DT>
 __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(EncodeArgs a) {
@@ -481,11 +488,15 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
   extern __shared__ __align__(16) uint8_t encv_smem[];
   float* pit = (float*)encv_smem;                                   // [D][D]
   EncvHalf* hs = (EncvHalf*)(encv_smem + TQ_D * TQ_D * 4) + half;
+  // s_bnd[0] = -inf, s_bnd[1 + j] = boundary j, +inf beyond the last one: a coordinate with
+  // code c lies in (s_bnd[c], s_bnd[c + 1]]
   float* s_bnd = (float*)(encv_smem + TQ_D * TQ_D * 4 + ENCV_HALVES * sizeof(EncvHalf));
   auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
 
   for (int i = threadIdx.x; i < TQ_D * TQ_D; i += ENCV_HALVES * TQ_D) pit[i] = a.tables->pi_t[i];
-  if (threadIdx.x < 16) s_bnd[threadIdx.x] = a.tables->boundaries[threadIdx.x];
+  if (threadIdx.x < 16) s_bnd[1 + threadIdx.x] = a.tables->boundaries[threadIdx.x];
+  if (threadIdx.x == 16) s_bnd[0] = -INFINITY;
+  if (threadIdx.x == 17) s_bnd[17] = INFINITY;
   __syncthreads();
 
   for (int w = blockIdx.x * ENCV_HALVES + half; w < total; w += gridDim.x * ENCV_HALVES) {
@@ -572,25 +583,28 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
         acc[2 * i + 1] = hi + ex[(2 * i + 1) * TQ_D + (e ^ 64)];
       }
     }
+    // code = number of boundaries below the coordinate (one boundary load serves the 16
+    // tokens); a token whose coordinate has a boundary within the slack is done again
     int code[TQ_GROUP_TOK];
-    unsigned redo = 0u;  // tokens whose coordinate has a boundary within the slack
+#pragma unroll
+    for (int t = 0; t < TQ_GROUP_TOK; ++t) code[t] = 0;
+    for (int j = 0; j < n_bnd; ++j) {
+      const float b = s_bnd[1 + j];
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) code[t] += (b < acc[t]) ? 1 : 0;
+    }
+    unsigned redo = 0u;
 #pragma unroll
     for (int t = 0; t < TQ_GROUP_TOK; ++t) {
-      const float lo = acc[t] - ROT_SLACK, hi = acc[t] + ROT_SLACK;
-      int c = 0, ch = 0;
-      for (int j = 0; j < n_bnd; ++j) {
-        c += (s_bnd[j] < lo) ? 1 : 0;
-        ch += (s_bnd[j] < hi) ? 1 : 0;
-      }
-      code[t] = c;
-      redo |= (c != ch) ? (1u << t) : 0u;
+      const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
+      redo |= (acc[t] - below < ROT_SLACK || above - acc[t] < ROT_SLACK) ? (1u << t) : 0u;
     }
     while (redo) {
       const int t = __ffs((int)redo) - 1;
       redo &= redo - 1;
       const float y = rotate_one(hs->us, pit, ch, t);
       int c = 0;
-      for (int j = 0; j < n_bnd; ++j) c += (s_bnd[j] < y) ? 1 : 0;
+      for (int j = 0; j < n_bnd; ++j) c += (s_bnd[1 + j] < y) ? 1 : 0;
 #pragma unroll
       for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? c : code[tt];
     }
