@@ -88,3 +88,28 @@ def test_shard_ranges_cover_everything():
                 [False] * (world - 1) + [True]
     with pytest.raises(ValueError):
         shard_range(4, 2, 2)
+
+
+def test_sequence_shard_gives_each_rank_exactly_its_blocks():
+    """Sharded storage of the sequence split: the tokens a rank feeds to its own cache make
+    that cache flush exactly the rank's range of the sequence's cold blocks (the reference's
+    flush rule applied to the rank's tokens), the ranges tile the sequence's blocks, token
+    ranges start on block boundaries, and only the last rank holds the hot window."""
+    from turboquant_pro_b200.parallel import n_cold_blocks, sequence_shard, shard_range
+
+    for w in (512, 16, 7, 5):
+        f = (w + 1) // 2
+        for n in (0, 3, w, w + 1, w + 2, 3000, 8192, 131072, 131071):
+            nb = n_cold_blocks(n, w)
+            for world in (1, 2, 3, 4, 8):
+                total = 0
+                for r in range(world):
+                    lo, hi, k, with_hot = sequence_shard(n, w, r, world)
+                    b_lo, b_hi = shard_range(nb, r, world)
+                    assert k == b_hi - b_lo and lo == b_lo * f and hi <= n
+                    assert n_cold_blocks(hi - lo, w) == k  # what the rank's cache will flush
+                    assert with_hot == (r == world - 1)
+                    if with_hot:
+                        assert hi == n  # the last rank stores through the end of the sequence
+                    total += k
+                assert total == nb

@@ -77,19 +77,25 @@ TQ_DEV TokenSource<DT> make_source(const EncodeArgs& a, const void* ring_base, c
 // With STAGED the block's tokens are first brought into shared memory (every row with
 // independent 16-byte loads, all in flight together) and the three passes read them from
 // there; without it each pass reads global memory, one dependent load per token (kept for
-// float32 tokens, whose block would take 128 KB).
+// float32 tokens, whose block would take 128 KB).  A staged CTA runs two threads per channel
+// (blockDim.x = 256): only the channel's sum has to visit the tokens in order, so the second
+// thread takes the second half of the block in everything else and the two merge their
+// running statistics once.
 template <int DT, bool STAGED>
-__global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
+__global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
   const tq_geom& g = a.g;
   const int seq = a.seq_begin + blockIdx.z;
   const int head = blockIdx.y;
-  const int d = threadIdx.x;
+  const int tid = threadIdx.x, d = tid & (TQ_D - 1), hf = tid >> 7, n_hf = blockDim.x >> 7;
   const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
   const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
   const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
   const int blk = nb0 + blockIdx.x;
   if (blk >= nb1) return;
   const int S = g.block_tokens;
+  // this thread's tokens [t_lo, t_hi): the halves meet at an even token
+  const int s_half = n_hf == 1 ? S : ((S / 2 + 1) & ~1);
+  const int t_lo = min(hf * s_half, S), t_hi = hf == n_hf - 1 ? S : min((hf + 1) * s_half, S);
   const int pos0 = blk * S;
   const TokenSource<DT> src = make_source<DT>(a, a.hot_k, a.k, seq, head, n0);
   uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     constexpr int CH = TQ_D * (int)sizeof(T) / 16;  // 16-byte chunks per row
     const int n_chunks = S * CH;
 #pragma unroll 8
-    for (int i = d; i < n_chunks; i += TQ_D) {
+    for (int i = tid; i < n_chunks; i += (int)blockDim.x) {
       const int t = i / CH, c = i % CH;
       const int pos = pos0 + t;
       const bool old = pos < n0;
@@ -132,11 +138,14 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   __shared__ int s_row[257];        // start of every token's outliers in the side-list
   __shared__ int s_orow[257];       // start of every token's entries in the page's overflow list
   __shared__ int s_warp_sum[TQ_D / 32];
-  if (d == 0) s_count = 0;
+  if (tid == 0) s_count = 0;
   __shared__ float s_scale[TQ_D];       // channel scales, to rank the widest channels
   __shared__ unsigned int s_side[256];  // per token: the codes of the four widest channels
-  s_side[d] = 0u;
-  s_side[d + TQ_D] = 0u;
+  __shared__ float s_stat[10][TQ_D];  // running statistics on their way between the two halves
+  if (hf == 0) {
+    s_side[d] = 0u;
+    s_side[d + TQ_D] = 0u;
+  }
   __syncthreads();
 
   // pass 1: sequential sum and the k largest magnitudes.  Up to eight of them (the usual
@@ -151,21 +160,69 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
 #pragma unroll
   for (int i = 0; i < TQ_MAX_K_OUT; ++i) top[i] = -1.0f;
   const int mode = g.key_mode;
-  float acc = 0.0f, xmin = 0.0f, xmax = 0.0f;
-  for (int t = 0; t < S; ++t) {
+  // (the first thread of a channel also carries the sum, over all tokens in order; more than
+  // eight outliers per channel are tracked by that thread alone, over all tokens)
+  float acc = 0.0f, xmin = INFINITY, xmax = -INFINITY;
+  const int p1_hi = hf == 0 ? S : t_hi;
+  for (int t = t_lo; t < p1_hi; ++t) {
     const float x = ldx(t);
-    acc = t == 0 ? x : __fadd_rn(acc, x);
-    xmin = t == 0 ? x : fminf(xmin, x);
-    xmax = t == 0 ? x : fmaxf(xmax, x);
+    if (hf == 0) acc = t == 0 ? x : __fadd_rn(acc, x);
+    const bool own = t < t_hi || !small_k;
     const float ax = fabsf(x);
+    if (own) {
+      xmin = fminf(xmin, x);
+      xmax = fmaxf(xmax, x);
+    }
     if (small_k) {
+      if (own) {
 #pragma unroll
-      for (int j = 0; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
-      t8[TK - 1] = fmaxf(ax, t8[TK - 1]);
-    } else if (ax > top[0]) {
+        for (int j = 0; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
+        t8[TK - 1] = fmaxf(ax, t8[TK - 1]);
+      }
+    } else if (hf == 0 && ax > top[0]) {
       int i = 0;
       while (i + 1 < kk && top[i + 1] < ax) { top[i] = top[i + 1]; ++i; }
       top[i] = ax;
+    }
+  }
+  if (n_hf > 1) {
+    // Both threads of a channel end up with the statistics of the whole block: the second
+    // hands over its eight largest and its extremes, the first merges them into its own and
+    // hands the result back together with the sum (and the k-th largest when k > 8); the sum
+    // and that value travel in the token-count array, which is not in use yet.
+    float* s_sum = (float*)s_tok_cnt;
+    if (hf == 1) {
+#pragma unroll
+      for (int j = 0; j < TK; ++j) s_stat[j][d] = t8[j];
+      s_stat[8][d] = xmin;
+      s_stat[9][d] = xmax;
+    }
+    __syncthreads();
+    if (hf == 0) {
+      xmin = fminf(xmin, s_stat[8][d]);
+      xmax = fmaxf(xmax, s_stat[9][d]);
+#pragma unroll
+      for (int i = 0; i < TK; ++i) {  // the other half's eight largest, inserted one by one
+        const float ax = s_stat[i][d];
+#pragma unroll
+        for (int j = 0; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
+        t8[TK - 1] = fmaxf(ax, t8[TK - 1]);
+      }
+#pragma unroll
+      for (int j = 0; j < TK; ++j) s_stat[j][d] = t8[j];
+      s_stat[8][d] = xmin;
+      s_stat[9][d] = xmax;
+      s_sum[d] = acc;
+      s_sum[TQ_D + d] = top[0];
+    }
+    __syncthreads();
+    if (hf == 1) {
+#pragma unroll
+      for (int j = 0; j < TK; ++j) t8[j] = s_stat[j][d];
+      xmin = s_stat[8][d];
+      xmax = s_stat[9][d];
+      acc = s_sum[d];
+      top[0] = s_sum[TQ_D + d];
     }
   }
   float kth_small = -1.0f;  // the k-th largest = element TK - k of the ascending eight
@@ -188,7 +245,7 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
                    : fmaxf(fabsf(xmax), fabsf(xmin));
   // pass 2: how many outliers this channel keeps, and which tokens they fall on
   int my_out = 0;
-  for (int t = 0; t < S; ++t) {
+  for (int t = t_lo; t < t_hi; ++t) {
     float x = ldx(t);
     const bool is_out = kk > 0 && fabsf(x) >= kth;
     my_out += is_out ? 1 : 0;
@@ -206,10 +263,11 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     lev[l] = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
   }
 
-  ((float*)(page + g.scale_off))[d] = amax;
-  ((float*)(page + g.mean_off))[d] = mu;
-
-  s_scale[d] = amax;
+  if (hf == 0) {
+    ((float*)(page + g.scale_off))[d] = amax;
+    ((float*)(page + g.mean_off))[d] = mu;
+    s_scale[d] = amax;
+  }
   // allocate this page's slice of the (layer, seq, head) outlier slab
   __syncthreads();
   // Rank of this channel by scale (0 = widest; ties go to the lower channel).  The codes of
@@ -222,18 +280,20 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     rank += (so > amax || (so == amax && o < d)) ? 1 : 0;
   }
   PageHeader* hdr = (PageHeader*)(page + g.hdr_off);
-  if (rank < TQ_WIDE) hdr->wide[rank] = (uint8_t)d;
+  if (rank < TQ_WIDE && hf == 0) hdr->wide[rank] = (uint8_t)d;
   if (kk > 0) atomicAdd(&s_count, my_out);
   __syncthreads();
+  if (hf == 0) {
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int t = 2 * d + i;
-    int n = 0;
+    for (int i = 0; i < 2; ++i) {
+      const int t = 2 * d + i;
+      int n = 0;
 #pragma unroll
-    for (int w = 0; w < TQ_D / 32; ++w) n += t < S ? (int)s_cnt_w[t][w] : 0;
-    s_tok_cnt[t] = n;
+      for (int w = 0; w < TQ_D / 32; ++w) n += t < S ? (int)s_cnt_w[t][w] : 0;
+      s_tok_cnt[t] = n;
+    }
   }
-  if (d == 0) {
+  if (tid == 0) {
     int n = s_count;
     uint32_t off = 0;
     int alloc = 0;
@@ -260,20 +320,27 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
   uint16_t* ell_delta = (uint16_t*)(page + g.hdr_off + TQ_ELL_OFF);  // [slot][token]
   uint8_t* ell_col = page + g.hdr_off + TQ_ELL_COL_OFF;               // [slot][token]
   uint32_t* ovf = (uint32_t*)(page + g.hdr_off + TQ_OVF_OFF);
-  {  // exclusive prefix sums over tokens of the outlier counts and of the counts beyond the
-     // fixed slots (both in one word: each total stays below 65536); thread d owns tokens
-     // 2d and 2d+1
-    const int c0 = s_tok_cnt[2 * d], c1 = s_tok_cnt[2 * d + 1];
-    const int o0 = max(c0 - TQ_ELL_SLOTS, 0), o1 = max(c1 - TQ_ELL_SLOTS, 0);
-    const uint32_t mine = (uint32_t)(c0 + c1) | ((uint32_t)(o0 + o1) << 16);
-    uint32_t v = mine;
+  // exclusive prefix sums over tokens of the outlier counts and of the counts beyond the
+  // fixed slots (both in one word: each total stays below 65536); the first thread of channel
+  // d owns tokens 2d and 2d+1
+  int c0 = 0, c1 = 0, o0 = 0;
+  uint32_t mine = 0u, v = 0u;
+  if (hf == 0) {
+    c0 = s_tok_cnt[2 * d];
+    c1 = s_tok_cnt[2 * d + 1];
+    o0 = max(c0 - TQ_ELL_SLOTS, 0);
+    const int o1 = max(c1 - TQ_ELL_SLOTS, 0);
+    mine = (uint32_t)(c0 + c1) | ((uint32_t)(o0 + o1) << 16);
+    v = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       uint32_t nv = __shfl_up_sync(0xffffffffu, v, o);
       if ((d & 31) >= o) v += nv;
     }
     if ((d & 31) == 31) s_warp_sum[d >> 5] = (int)v;
-    __syncthreads();
+  }
+  __syncthreads();
+  if (hf == 0) {
     uint32_t base = 0;
     for (int w = 0; w < (d >> 5); ++w) base += (uint32_t)s_warp_sum[w];
     const uint32_t excl = base + v - mine;
@@ -296,8 +363,8 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
   }
   __syncthreads();
-  if (d < 5) hdr->ovf_start[d] = (uint16_t)min(s_orow[64 * d], TQ_OVF_CAP);
-  if (d == 5) {
+  if (tid < 5) hdr->ovf_start[tid] = (uint16_t)min(s_orow[64 * tid], TQ_OVF_CAP);
+  if (tid == 5) {
     // the in-page copy is complete unless the overflow list is too long or the pool slab
     // could not take every entry (then the pool's shorter list is the cache's content)
     const int n_ovf = s_orow[256];
@@ -338,13 +405,13 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
     return ix[0];
   };
-  for (int t0 = 0; t0 < S; t0 += 2) {
+  for (int t0 = t_lo; t0 < t_hi; t0 += 2) {
     const float xa = ldx(t0), xb = ldx(min(t0 + 1, S - 1));
     const int best_a = nearest(xa), best_b = nearest(xb);
 #pragma unroll
     for (int sub = 0; sub < 2; ++sub) {
       const int t = t0 + sub;
-      if (t >= S) break;  // uniform
+      if (t >= t_hi) break;  // uniform over the warp
       const float x = sub ? xb : xa;
       const int best = sub ? best_b : best_a;
       if (rank < 4) atomicOr(&s_side[t], (unsigned int)best << (4 * rank));
@@ -384,14 +451,14 @@ __global__ void __launch_bounds__(TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
   }
   __syncthreads();
-  {
+  if (hf == 0) {
     uint16_t* side = (uint16_t*)(page + g.hdr_off + TQ_SIDE_OFF);
     side[2 * d] = (uint16_t)s_side[2 * d];
     side[2 * d + 1] = (uint16_t)s_side[2 * d + 1];
+    // padded token rows (block_tokens not a multiple of 16) keep code 0
+    for (int t = S; t < g.block_tokens_pad; ++t)
+      if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = 0;
   }
-  // padded token rows (block_tokens not a multiple of 16) keep code 0
-  for (int t = S; t < g.block_tokens_pad; ++t)
-    if ((d & 1) == 0) page[t * (TQ_D / 2) + (d >> 1)] = 0;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -679,7 +746,7 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
   if (a.max_new_blocks > 0) {
     dim3 grid(a.max_new_blocks, g.n_kv_heads, a.seq_count);
     if (DT == TQ_F32) {
-      encode_keys_kernel<DT, false><<<grid, TQ_D, 0, st>>>(a);
+      encode_keys_kernel<DT, false><<<grid, TQ_D, 0, st>>>(a);  // one thread per channel
     } else {
       const int stage_bytes = g.block_tokens * TQ_D * elem_size(DT);
       static bool keys_attr_set[16] = {};
@@ -688,7 +755,7 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * TQ_D * 2));
         keys_attr_set[device & 15] = true;
       }
-      encode_keys_kernel<DT, true><<<grid, TQ_D, stage_bytes, st>>>(a);
+      encode_keys_kernel<DT, true><<<grid, 2 * TQ_D, stage_bytes, st>>>(a);
     }
     int groups = g.block_tokens_pad / TQ_GROUP_TOK;
     long total = (long)a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
