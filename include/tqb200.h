@@ -264,8 +264,10 @@ int32_t tq_last_launches(const tq_ctx* ctx);
  * context's scratch region; nothing is allocated or freed.  Limit: n_seqs * n_q_heads <=
  * 1024, otherwise TQ_ERR_CAPACITY.  The array is shared by all contexts and streams of the
  * process on that GPU, so calls must not overlap on the device.  The first call on a device
- * resolves the array's device address; make it before any stream capture.  Always runs the
- * general-shape kernel; same result as tq_decode within rounding. */
+ * resolves the array's device address; make it before any stream capture, and do not let two
+ * threads make their first call on the same device at the same time (later calls only read
+ * the remembered address).  Always runs the general-shape kernel; same result as tq_decode
+ * within rounding. */
 int32_t tq_decode_static_scratch(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype,
                                  float* out, void* stream);
 
