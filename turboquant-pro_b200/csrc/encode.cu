@@ -541,6 +541,8 @@ struct EncvHalf {
   uint32_t img[256];
   float norm[TQ_GROUP_TOK];
 };
+static_assert(TQ_D * TQ_GROUP_TOK * 3 + TQ_D * 4 * (TQ_D / 32) <= (int)sizeof(float) * TQ_GROUP_TOK * ENCV_XS,
+              "the recomputation's list, codes and products fit in the row buffer");
 constexpr int ENCV_SMEM = TQ_D * TQ_D * 4 + ENCV_HALVES * (int)sizeof(EncvHalf) + 128;
 
 template <int DT>
@@ -666,14 +668,61 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
       const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
       redo |= (acc[t] - below < ROT_SLACK || above - acc[t] < ROT_SLACK) ? (1u << t) : 0u;
     }
-    while (redo) {
-      const int t = __ffs((int)redo) - 1;
-      redo &= redo - 1;
-      const float y = rotate_one(hs->us, pit, ch, t);
-      int c = 0;
-      for (int j = 0; j < n_bnd; ++j) c += (s_bnd[1 + j] < y) ? 1 : 0;
+    // The coordinates to be done again (a handful per group) go on a list in the row buffer,
+    // which is free by now; the group's four warps take them in turn.  A warp computes the
+    // 128 products of one coordinate in parallel (four per lane; the matrix column is a row
+    // of the untransposed matrix in global memory, one cache line per 32 products) and one
+    // lane adds them up in the reference's order from shared memory: the chain of 127 rounded
+    // additions cannot be shortened, but it no longer drags 31 idle lanes through 128
+    // multiply-adds and 256 loads of their own.
+    {
+      unsigned short* wl = (unsigned short*)&hs->xs[0][0];              // (channel, token) items
+      unsigned char* fixed = (unsigned char*)(wl + TQ_D * TQ_GROUP_TOK);  // [token][channel] codes
+      float* prod = (float*)(fixed + TQ_D * TQ_GROUP_TOK) + (e >> 5) * TQ_D;  // this warp's
+      int* wl_n = (int*)&hs->norm[0];  // the norms have been used: their first word counts
+      const float* pi_rows = a.tables->pi;  // pi[c][d] == pit[d][c]
+      half_sync();                     // every thread is done with the exchange buffer
+      if (e == 0) *wl_n = 0;
+      half_sync();
+      unsigned todo = redo;
+      while (todo) {
+        const int t = __ffs((int)todo) - 1;
+        todo &= todo - 1;
+        wl[atomicAdd(wl_n, 1)] = (unsigned short)(ch | (t << 8));
+      }
+      half_sync();
+      const int n_items = *wl_n;
+      const int wl_lane = e & 31;
+      for (int it = e >> 5; it < n_items; it += TQ_D / 32) {
+        const int item = wl[it], c2 = item & 255, t2 = item >> 8;
 #pragma unroll
-      for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? c : code[tt];
+        for (int k = 0; k < 4; ++k) {
+          const int dd = 32 * k + wl_lane;
+          prod[dd] = __fmul_rn(hs->us[dd][t2], __ldg(&pi_rows[c2 * TQ_D + dd]));
+        }
+        __syncwarp();
+        if (wl_lane == 0) {
+          float4 p4 = *(const float4*)&prod[0];
+          float y = __fadd_rn(__fadd_rn(__fadd_rn(p4.x, p4.y), p4.z), p4.w);
+#pragma unroll 8
+          for (int q = 1; q < TQ_D / 4; ++q) {
+            p4 = *(const float4*)&prod[4 * q];
+            y = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(y, p4.x), p4.y), p4.z), p4.w);
+          }
+          int c = 0;
+          for (int j = 0; j < n_bnd; ++j) c += (s_bnd[1 + j] < y) ? 1 : 0;
+          fixed[t2 * TQ_D + c2] = (unsigned char)c;
+        }
+        __syncwarp();
+      }
+      half_sync();
+      while (redo) {
+        const int t = __ffs((int)redo) - 1;
+        redo &= redo - 1;
+        const int c = fixed[t * TQ_D + ch];
+#pragma unroll
+        for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? c : code[tt];
+      }
     }
     // pack this channel's 8 token pairs into the group image
     uint32_t* img = hs->img;
