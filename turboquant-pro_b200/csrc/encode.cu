@@ -462,107 +462,110 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Rotation of 16 vectors held transposed in shared memory (us[d][t]) by column e of the
-// matrix in shared memory (pit[d][e]).  The reference's result is the unfused sequential sum
-// acc[t] = ((u0*P0 + u1*P1) + u2*P2) + ... with every product and sum rounded to float32
-// separately (rotate_one below).  rotate16_pair computes the same sum with fused multiply-adds
-// in two halves of 64 terms: half the arithmetic, and a result within ROT_SLACK of the unfused
-// one.  Either form rounds at most 128 products and 127 sums of terms whose absolute values add
-// up to at most |u| |column| <= 1: each is within 127 * 2^-24 + 2^-24 < 7.7e-6 of the exact dot
-// product, so they differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.
+// Rotation of the value encoder on tensor cores.  The reference's result is the unfused
+// sequential float32 sum y_ch = ((u0*P0 + u1*P1) + u2*P2) + ... with every product and sum
+// rounded separately; it lies within 127 * 2^-24 + 2^-24 < 7.7e-6 of the exact dot product
+// (the absolute values of the 128 terms add up to at most |u| |column| <= 1).  The tensor-core
+// form splits every operand into two fp16 parts, x = hi + lo * 2^-11 with hi = fp16(x) and
+// lo = fp16((x - hi) * 2^11) (what is left is below 2^-24 |x|), and sums hi*hi into one
+// float32 accumulator and hi*lo + lo*hi into another; the products are exact in float32, the
+// dropped lo*lo term is below 2^-24 of a term, and the accumulators add eight (sixteen)
+// 16-term tiles.  That result lies within a few 1e-6 of the exact dot product, so the two
+// differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.  A coordinate
+// with a quantisation boundary inside the slack is computed again in the reference's order.
 constexpr float ROT_SLACK = 4.0e-5f;
-// Row strides of the value encoder's shared arrays, chosen so that its 8-threads-per-token
-// phases (norms, unit vectors) touch 32 different banks: token rows 136 floats apart,
-// transposed rows 20 floats apart (still 16-byte aligned for the rotation's vector loads).
-constexpr int ENCV_XS = TQ_D + 8, ENCV_US = TQ_GROUP_TOK + 4;
-// Two float32 lanes in one 64-bit register and the packed fused multiply-add on them.
-TQ_DEV unsigned long long pack2(float lo, float hi) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
+// Row stride (floats) of the token rows: the 8-threads-per-token phases (norms, unit vectors)
+// then touch 32 different banks; and (halves) of the fp16 unit-vector rows: eight rows of an
+// 8x8 matrix load then fall into eight different 16-byte bank groups.
+constexpr int ENCV_XS = TQ_D + 8, ENCV_UH = TQ_D + 8;
+
+TQ_DEV void enc_mma16816(float* c, const uint4& a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
-TQ_DEV void unpack2(unsigned long long v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+TQ_DEV void enc_ldsm_x4(uint32_t* v, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "r"(addr));
 }
-TQ_DEV unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-  unsigned long long d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
+// x = hi + lo * 2^-11, both fp16
+TQ_DEV void split_h(float x, __half& hi, __half& lo) {
+  hi = __float2half_rn(x);
+  lo = __float2half_rn((x - __half2float(hi)) * 2048.0f);
 }
-// Half of the fused rotation for two neighbouring output channels c0, c0 + 1 (c0 even): the
-// input channels [d0, d0 + 64) of 16 tokens.  acc[ch][i] holds tokens 2i, 2i+1 of channel
-// c0 + ch.  One 8-byte load brings the two matrix entries of a row and four 16-byte loads the
-// 16 unit-vector entries, for 32 multiply-adds issued as 16 packed instructions: half the
-// loads and half the arithmetic instructions per multiply-add of the one-channel form.
-TQ_DEV void rotate16_pair(const float (*us)[ENCV_US], const float* pit, int c0, int d0,
-                          unsigned long long (&acc)[2][8]) {
-#pragma unroll
-  for (int ch = 0; ch < 2; ++ch)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[ch][i] = 0ull;
-#pragma unroll 4
-  for (int dd = d0; dd < d0 + TQ_D / 2; ++dd) {
-    const float2 p = *(const float2*)&pit[dd * TQ_D + c0];
-    const unsigned long long b0 = pack2(p.x, p.x), b1 = pack2(p.y, p.y);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const ulonglong2 u = *(const ulonglong2*)&us[dd][4 * q];  // tokens (4q, 4q+1), (4q+2, 4q+3)
-      acc[0][2 * q] = ffma2(u.x, b0, acc[0][2 * q]);
-      acc[0][2 * q + 1] = ffma2(u.y, b0, acc[0][2 * q + 1]);
-      acc[1][2 * q] = ffma2(u.x, b1, acc[1][2 * q]);
-      acc[1][2 * q + 1] = ffma2(u.y, b1, acc[1][2 * q + 1]);
-    }
-  }
-}
-// one coordinate of the unfused rotation: token t of the group, output channel e
-TQ_DEV float rotate_one(const float (*us)[ENCV_US], const float* pit, int e, int t) {
-  float y = __fmul_rn(us[0][t], pit[e]);
-#pragma unroll 8
-  for (int dd = 1; dd < TQ_D; ++dd) y = __fadd_rn(y, __fmul_rn(us[dd][t], pit[dd * TQ_D + e]));
-  return y;
+TQ_DEV uint32_t h2_bits(__half lo, __half hi) {
+  return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
 }
 
 // ---------------------------------------------------------------------------------------
-// Value encoder.  Persistent CTAs of two 128-thread halves that share one copy of Pi^T in
-// shared memory; each half works on its own 16-token group of a new cold block, thread e of
-// the half owns output channel e.
+// Value encoder.  Persistent CTAs of two 128-thread halves that share one copy of the
+// rotation matrix in shared memory (as ready-made tensor-core fragments); each half works on
+// its own 16-token group of a new cold block.
 //   norm = sqrt(pairwise sum of fl(x*x))      (numpy's 8-accumulator order for n = 128)
 //   u    = x / max(norm, 1e-30)
-//   y_e  = sequential, unfused sum over d of u_d * PiT[d][e]
-//   code = #{ j : boundary_j < y_e }
-// The rotation first runs with fused multiply-adds; a coordinate whose code could depend on
-// the difference (a boundary within ROT_SLACK of it: a few per thousand) is then recomputed
-// in the unfused order, so every code is the one the unfused arithmetic gives.
+//   y_ch = sequential, unfused sum over d of u_d * Pi[ch][d]
+//   code = #{ j : boundary_j < y_ch }
+// The rotation runs as Y^T = Pi . U^T on m16n8k16 tiles (rows: 16 channels, columns: 8
+// tokens): warp w of the half owns channels 32w .. 32w+31, and lane (r, c) ends up with
+// channels 16mt + r, 16mt + r + 8 and tokens 2c, 2c+1, 2c+8, 2c+9 - exactly the codes of
+// its own lane record of the page's value layout, which it packs and stores itself.
 // ---------------------------------------------------------------------------------------
 constexpr int ENCV_HALVES = 2;
 struct EncvHalf {
-  float xs[TQ_GROUP_TOK][ENCV_XS];
-  float us[TQ_D][ENCV_US];
+  float xs[TQ_GROUP_TOK][ENCV_XS];     // the group's rows
+  // unit vectors, [token][channel]: fp16 hi part, then lo part; once the rotation is done
+  // the area holds the list, codes and products of the recomputation
+  __half uh[2][TQ_GROUP_TOK][ENCV_UH];
   uint32_t img[256];
   float norm[TQ_GROUP_TOK];
+  int wl_n;
+  int pad_[3];
 };
-static_assert(TQ_D * TQ_GROUP_TOK * 3 + TQ_D * 4 * (TQ_D / 32) <= (int)sizeof(float) * TQ_GROUP_TOK * ENCV_XS,
-              "the recomputation's list, codes and products fit in the row buffer");
-constexpr int ENCV_SMEM = TQ_D * TQ_D * 4 + ENCV_HALVES * (int)sizeof(EncvHalf) + 128;
+constexpr int ENCV_PI_BYTES = TQ_D * TQ_D * 2 * 2;  // fp16 hi and lo fragments of Pi
+constexpr int ENCV_SMEM = ENCV_PI_BYTES + ENCV_HALVES * (int)sizeof(EncvHalf) + 128;
+static_assert(TQ_D * TQ_GROUP_TOK * 3 + TQ_D * 4 * (TQ_D / 32) <= (int)sizeof(EncvHalf::uh),
+              "the recomputation's list, codes and products fit in the unit-vector area");
 
 template <int DT>
 __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(EncodeArgs a) {
   const tq_geom& g = a.g;
   const int e = threadIdx.x & (TQ_D - 1), half = threadIdx.x >> 7;
+  const int wq = e >> 5, lane = e & 31, r = lane >> 2, c = lane & 3;
   const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
   const int total = a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
   const int vb = g.value_bits;
   const int n_bnd = (1 << vb) - 1;
 
   extern __shared__ __align__(16) uint8_t encv_smem[];
-  float* pit = (float*)encv_smem;                                   // [D][D]
-  EncvHalf* hs = (EncvHalf*)(encv_smem + TQ_D * TQ_D * 4) + half;
+  // Pi as A fragments: [16-channel tile][16-input-channel step][hi | lo][lane] x 16 bytes
+  uint4* pif = (uint4*)encv_smem;
+  EncvHalf* hs = (EncvHalf*)(encv_smem + ENCV_PI_BYTES) + half;
   // s_bnd[0] = -inf, s_bnd[1 + j] = boundary j, +inf beyond the last one: a coordinate with
   // code c lies in (s_bnd[c], s_bnd[c + 1]]
-  float* s_bnd = (float*)(encv_smem + TQ_D * TQ_D * 4 + ENCV_HALVES * sizeof(EncvHalf));
+  float* s_bnd = (float*)(encv_smem + ENCV_PI_BYTES + ENCV_HALVES * sizeof(EncvHalf));
   auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
+  const float* pi_rows = a.tables->pi;  // pi[ch][d]
 
-  for (int i = threadIdx.x; i < TQ_D * TQ_D; i += ENCV_HALVES * TQ_D) pit[i] = a.tables->pi_t[i];
+  for (int idx = threadIdx.x; idx < 8 * 8 * 32; idx += ENCV_HALVES * TQ_D) {
+    const int L = idx & 31, ks = (idx >> 5) & 7, MT = idx >> 8;
+    const int ch0 = 16 * MT + (L >> 2), d0 = 16 * ks + 2 * (L & 3);
+    // a0: (row r, k 2c..), a1: (row r+8, k 2c..), a2: (row r, k 2c+8..), a3: (row r+8, k 2c+8..)
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 p = *(const float2*)&pi_rows[(ch0 + 8 * (q & 1)) * TQ_D + d0 + 8 * (q >> 1)];
+      __half h0, l0, h1, l1;
+      split_h(p.x, h0, l0);
+      split_h(p.y, h1, l1);
+      hi[q] = h2_bits(h0, h1);
+      lo[q] = h2_bits(l0, l1);
+    }
+    pif[((MT * 8 + ks) * 2 + 0) * 32 + L] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    pif[((MT * 8 + ks) * 2 + 1) * 32 + L] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
   if (threadIdx.x < 16) s_bnd[1 + threadIdx.x] = a.tables->boundaries[threadIdx.x];
   if (threadIdx.x == 16) s_bnd[0] = -INFINITY;
   if (threadIdx.x == 17) s_bnd[17] = INFINITY;
@@ -570,11 +573,11 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
 
   for (int w = blockIdx.x * ENCV_HALVES + half; w < total; w += gridDim.x * ENCV_HALVES) {
     int gq = w % groups;
-    int r = w / groups;
-    int jb = r % a.max_new_blocks;
-    r /= a.max_new_blocks;
-    int head = r % g.n_kv_heads;
-    int seq = a.seq_begin + r / g.n_kv_heads;
+    int rr = w / groups;
+    int jb = rr % a.max_new_blocks;
+    rr /= a.max_new_blocks;
+    int head = rr % g.n_kv_heads;
+    int seq = a.seq_begin + rr / g.n_kv_heads;
     const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
     const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
     const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
@@ -596,159 +599,185 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
       for (int t = 0; t < TQ_GROUP_TOK; ++t)
         hs->xs[t][e] = gq * TQ_GROUP_TOK + t < S ? xv[t] : 0.0f;
     }
-    hs->img[e] = 0u;
-    hs->img[e + 128] = 0u;
     half_sync();
     {  // norms: 8 threads per token, accumulator j sums elements j, j+8, j+16, ...
       int t = e >> 3, j = e & 7;
       float v0 = hs->xs[t][j];
-      float rr = __fmul_rn(v0, v0);
+      float sq = __fmul_rn(v0, v0);
 #pragma unroll
       for (int i = 1; i < TQ_D / 8; ++i) {
         float vv = hs->xs[t][8 * i + j];
-        rr = __fadd_rn(rr, __fmul_rn(vv, vv));
+        sq = __fadd_rn(sq, __fmul_rn(vv, vv));
       }
-      rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 1));  // (r0+r1), (r2+r3), ...
-      rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 2));  // (r0+r1)+(r2+r3), ...
-      rr = __fadd_rn(rr, __shfl_xor_sync(0xffffffffu, rr, 4));
-      float nrm = __fsqrt_rn(rr);
+      sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 1));  // (r0+r1), (r2+r3), ...
+      sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 2));  // (r0+r1)+(r2+r3), ...
+      sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 4));
+      float nrm = __fsqrt_rn(sq);
       if (j == 0) {
         hs->norm[t] = nrm;
         ((float*)(page + g.norm_off))[gq * TQ_GROUP_TOK + t] = nrm;
       }
     }
     half_sync();
-    {  // unit vectors, stored transposed for the broadcast reads of the rotation
+    {  // unit vectors as fp16 hi / lo parts, [token][channel]
       int t = e >> 3, j = e & 7;
       float safe = fmaxf(hs->norm[t], 1e-30f);
 #pragma unroll
-      for (int i = 0; i < TQ_D / 8; ++i)
-        hs->us[8 * i + j][t] = __fdiv_rn(hs->xs[t][8 * i + j], safe);
+      for (int i = 0; i < TQ_D / 8; ++i) {
+        __half h, l;
+        split_h(__fdiv_rn(hs->xs[t][8 * i + j], safe), h, l);
+        hs->uh[0][t][8 * i + j] = h;
+        hs->uh[1][t][8 * i + j] = l;
+      }
     }
     half_sync();
-    // Fused rotation: thread (hh, ep) sums the input channels [64 hh, 64 hh + 64) for the two
-    // output channels 2 ep, 2 ep + 1; the two threads of a channel pair then swap one partial
-    // sum each (through the row buffer, which is no longer needed), after which thread
-    // (hh, ep) owns output channel ch = 2 ep + hh with all 128 terms.
-    const int hh = e >> 6, ep = e & 63, ch = 2 * ep + hh;
-    float acc[TQ_GROUP_TOK];
+    // Rotation.  y[mt][nt][i]: channel 32 wq + 16 mt + r + 8 (i >> 1), token 8 nt + 2c + (i & 1)
+    float y[2][2][4];
     {
-      unsigned long long part[2][8];
-      rotate16_pair(hs->us, pit, 2 * ep, (TQ_D / 2) * hh, part);
-      float* ex = &hs->xs[0][0];  // [token][thread]
+      float cx[2][2][4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {  // the channel this thread gives away
-        float lo, hi;
-        unpack2(hh ? part[0][i] : part[1][i], lo, hi);
-        ex[(2 * i) * TQ_D + e] = lo;
-        ex[(2 * i + 1) * TQ_D + e] = hi;
-      }
-      half_sync();
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {  // ... and the partner's half of the one it keeps
-        float lo, hi;
-        unpack2(hh ? part[1][i] : part[0][i], lo, hi);
-        acc[2 * i] = lo + ex[(2 * i) * TQ_D + (e ^ 64)];
-        acc[2 * i + 1] = hi + ex[(2 * i + 1) * TQ_D + (e ^ 64)];
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) y[mt][nt][i] = cx[mt][nt][i] = 0.0f;
+      // lanes 8m .. 8m+7 address the rows of matrix m: tokens 8 (m >> 1) + 0..7, input
+      // channels 16 ks + 8 (m & 1) + 0..7; the four matrices are the B fragments {b0, b1} of
+      // the two 8-token tiles
+      const int m_tok = 8 * (lane >> 4) + (lane & 7), m_d = 8 * ((lane >> 3) & 1);
+      const uint32_t ub_hi = (uint32_t)__cvta_generic_to_shared(&hs->uh[0][m_tok][m_d]);
+      const uint32_t ub_lo = (uint32_t)__cvta_generic_to_shared(&hs->uh[1][m_tok][m_d]);
+      const uint4* pa = pif + (size_t)(2 * wq) * 8 * 2 * 32 + lane;
+#pragma unroll 2
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t bh[4], bl[4];
+        enc_ldsm_x4(bh, ub_hi + ks * 32);
+        enc_ldsm_x4(bl, ub_lo + ks * 32);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          const uint4 ah = pa[((mt * 8 + ks) * 2 + 0) * 32], al = pa[((mt * 8 + ks) * 2 + 1) * 32];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            enc_mma16816(y[mt][nt], ah, bh[2 * nt], bh[2 * nt + 1]);
+            enc_mma16816(cx[mt][nt], ah, bl[2 * nt], bl[2 * nt + 1]);
+            enc_mma16816(cx[mt][nt], al, bh[2 * nt], bh[2 * nt + 1]);
+          }
+        }
       }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            y[mt][nt][i] = fmaf(cx[mt][nt][i], 1.0f / 2048.0f, y[mt][nt][i]);
     }
-    // code = number of boundaries below the coordinate (one boundary load serves the 16
-    // tokens); a token whose coordinate has a boundary within the slack is done again
-    int code[TQ_GROUP_TOK];
+    // code = number of boundaries below the coordinate (one boundary load serves the lane's 16
+    // coordinates); a coordinate with a boundary within the slack is done again.
+    // Coordinate k = 8 mt + 4 nt + i of the lane.
+    int code[16];
 #pragma unroll
-    for (int t = 0; t < TQ_GROUP_TOK; ++t) code[t] = 0;
+    for (int k = 0; k < 16; ++k) code[k] = 0;
     for (int j = 0; j < n_bnd; ++j) {
       const float b = s_bnd[1 + j];
 #pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t) code[t] += (b < acc[t]) ? 1 : 0;
+      for (int k = 0; k < 16; ++k) code[k] += (b < y[k >> 3][(k >> 2) & 1][k & 3]) ? 1 : 0;
     }
     unsigned redo = 0u;
 #pragma unroll
-    for (int t = 0; t < TQ_GROUP_TOK; ++t) {
-      const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
-      redo |= (acc[t] - below < ROT_SLACK || above - acc[t] < ROT_SLACK) ? (1u << t) : 0u;
+    for (int k = 0; k < 16; ++k) {
+      const float yy = y[k >> 3][(k >> 2) & 1][k & 3];
+      const float below = s_bnd[code[k]], above = s_bnd[code[k] + 1];
+      redo |= (yy - below < ROT_SLACK || above - yy < ROT_SLACK) ? (1u << k) : 0u;
     }
-    // The coordinates to be done again (a handful per group) go on a list in the row buffer,
-    // which is free by now; the group's four warps take them in turn.  A warp computes the
-    // 128 products of one coordinate in parallel (four per lane; the matrix column is a row
-    // of the untransposed matrix in global memory, one cache line per 32 products) and one
-    // lane adds them up in the reference's order from shared memory: the chain of 127 rounded
-    // additions cannot be shortened, but it no longer drags 31 idle lanes through 128
-    // multiply-adds and 256 loads of their own.
+    // The coordinates to be done again (a handful per group) go on a list in the unit-vector
+    // area, which is free by now; the half's four warps take them in turn.  A warp computes
+    // the 128 products of one coordinate in parallel (four per lane, the unit vector formed
+    // again from the row by the same division) and one lane adds them up in the reference's
+    // order from shared memory.
     {
-      unsigned short* wl = (unsigned short*)&hs->xs[0][0];              // (channel, token) items
-      unsigned char* fixed = (unsigned char*)(wl + TQ_D * TQ_GROUP_TOK);  // [token][channel] codes
-      float* prod = (float*)(fixed + TQ_D * TQ_GROUP_TOK) + (e >> 5) * TQ_D;  // this warp's
-      int* wl_n = (int*)&hs->norm[0];  // the norms have been used: their first word counts
-      const float* pi_rows = a.tables->pi;  // pi[c][d] == pit[d][c]
-      half_sync();                     // every thread is done with the exchange buffer
-      if (e == 0) *wl_n = 0;
+      unsigned short* wl = (unsigned short*)&hs->uh[0][0][0];             // (channel, token) items
+      unsigned char* fixed = (unsigned char*)(wl + TQ_D * TQ_GROUP_TOK);   // [token][channel] codes
+      float* prod = (float*)(fixed + TQ_D * TQ_GROUP_TOK) + wq * TQ_D;     // this warp's products
+      half_sync();  // every warp is done with the unit vectors
+      if (e == 0) hs->wl_n = 0;
       half_sync();
       unsigned todo = redo;
       while (todo) {
-        const int t = __ffs((int)todo) - 1;
+        const int k = __ffs((int)todo) - 1;
         todo &= todo - 1;
-        wl[atomicAdd(wl_n, 1)] = (unsigned short)(ch | (t << 8));
+        const int ch = 32 * wq + 16 * (k >> 3) + r + 8 * ((k >> 1) & 1);
+        const int t = 8 * ((k >> 2) & 1) + 2 * c + (k & 1);
+        wl[atomicAdd(&hs->wl_n, 1)] = (unsigned short)(ch | (t << 8));
       }
       half_sync();
-      const int n_items = *wl_n;
-      const int wl_lane = e & 31;
-      for (int it = e >> 5; it < n_items; it += TQ_D / 32) {
+      const int n_items = hs->wl_n;
+      for (int it = wq; it < n_items; it += TQ_D / 32) {
         const int item = wl[it], c2 = item & 255, t2 = item >> 8;
+        const float safe = fmaxf(hs->norm[t2], 1e-30f);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const int dd = 32 * k + wl_lane;
-          prod[dd] = __fmul_rn(hs->us[dd][t2], __ldg(&pi_rows[c2 * TQ_D + dd]));
+          const int dd = 32 * k + lane;
+          prod[dd] = __fmul_rn(__fdiv_rn(hs->xs[t2][dd], safe), __ldg(&pi_rows[c2 * TQ_D + dd]));
         }
         __syncwarp();
-        if (wl_lane == 0) {
+        if (lane == 0) {
           float4 p4 = *(const float4*)&prod[0];
-          float y = __fadd_rn(__fadd_rn(__fadd_rn(p4.x, p4.y), p4.z), p4.w);
+          float yy = __fadd_rn(__fadd_rn(__fadd_rn(p4.x, p4.y), p4.z), p4.w);
 #pragma unroll 8
           for (int q = 1; q < TQ_D / 4; ++q) {
             p4 = *(const float4*)&prod[4 * q];
-            y = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(y, p4.x), p4.y), p4.z), p4.w);
+            yy = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(yy, p4.x), p4.y), p4.z), p4.w);
           }
-          int c = 0;
-          for (int j = 0; j < n_bnd; ++j) c += (s_bnd[1 + j] < y) ? 1 : 0;
-          fixed[t2 * TQ_D + c2] = (unsigned char)c;
+          int cd = 0;
+          for (int j = 0; j < n_bnd; ++j) cd += (s_bnd[1 + j] < yy) ? 1 : 0;
+          fixed[t2 * TQ_D + c2] = (unsigned char)cd;
         }
         __syncwarp();
       }
       half_sync();
       while (redo) {
-        const int t = __ffs((int)redo) - 1;
+        const int k = __ffs((int)redo) - 1;
         redo &= redo - 1;
-        const int c = fixed[t * TQ_D + ch];
+        const int ch = 32 * wq + 16 * (k >> 3) + r + 8 * ((k >> 1) & 1);
+        const int t = 8 * ((k >> 2) & 1) + 2 * c + (k & 1);
+        const int cd = fixed[t * TQ_D + ch];
 #pragma unroll
-        for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? c : code[tt];
+        for (int kk = 0; kk < 16; ++kk) code[kk] = kk == k ? cd : code[kk];
       }
     }
-    // pack this channel's 8 token pairs into the group image
-    uint32_t* img = hs->img;
-    const int dq = ch & 7, i16 = ch >> 3;  // record lane group and slot of this thread's channel
+    // The lane's codes are pairs 4 MT .. 4 MT + 3 of its own lane record (MT = 2 wq + mt):
+    // (channel r, tokens 2c, 2c+1), (r, 2c+8, 2c+9), (r + 8, 2c, 2c+1), (r + 8, 2c+8, 2c+9);
+    // every byte of the group image is written by exactly one lane.
+    uint8_t* img = (uint8_t*)hs->img;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int mt = 0; mt < 2; ++mt) {
+      const int MT = 2 * wq + mt;
+      // pair q = 2 h + nt holds coordinates k = 8 mt + 4 nt + 2 h, + 1
+      if (vb == 4) {
+        uint32_t wv = 0u;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        int ta = 2 * c + 8 * h;
-        int l = dq * 4 + c, p = 2 * i16 + h;
-        if (vb == 4) {
-          ((uint8_t*)img)[v_record_byte_off(4, l, p)] = (uint8_t)(code[ta] | (code[ta + 1] << 4));
-        } else {
-          uint32_t f = (uint32_t)(code[ta] | (code[ta + 1] << 3));
-          int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
-          atomicOr(&img[((wd >> 1) * 256 + l * 8 + (wd & 1) * 4) >> 2], f << sh);
-          if (sh > 26)
-            atomicOr(&img[((((wd + 1) >> 1)) * 256 + l * 8 + ((wd + 1) & 1) * 4) >> 2],
-                     f >> (32 - sh));
+        for (int q = 0; q < 4; ++q) {
+          const int k = 8 * mt + 4 * (q & 1) + 2 * (q >> 1);
+          wv |= (uint32_t)(code[k] | (code[k + 1] << 4)) << (8 * q);
         }
+        *(uint32_t*)(img + v_record_byte_off(4, lane, 4 * MT)) = wv;
+      } else {
+        uint32_t wv = 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int k = 8 * mt + 4 * (q & 1) + 2 * (q >> 1);
+          wv |= (uint32_t)(code[k] | (code[k + 1] << 3)) << (6 * q);
+        }
+#pragma unroll
+        for (int bq = 0; bq < 3; ++bq)
+          img[v_record_byte_off(3, lane, 3 * MT + bq)] = (uint8_t)(wv >> (8 * bq));
       }
     }
     half_sync();
     uint32_t* dst = (uint32_t*)(page + g.v_off + (size_t)gq * v_group_bytes(vb));
     const int words = v_group_bytes(vb) / 4;
-    for (int i = e; i < words; i += TQ_D) dst[i] = img[i];
+    for (int i = e; i < words; i += TQ_D) dst[i] = hs->img[i];
   }
 }
 
