@@ -82,7 +82,7 @@ TQ_DEV TokenSource<DT> make_source(const EncodeArgs& a, const void* ring_base, c
 // thread takes the second half of the block in everything else and the two merge their
 // running statistics once.
 template <int DT, bool STAGED>
-__global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
+__global__ void __launch_bounds__(2 * TQ_D, 3) encode_keys_kernel(EncodeArgs a) {
   const tq_geom& g = a.g;
   const int seq = a.seq_begin + blockIdx.z;
   const int head = blockIdx.y;
@@ -135,18 +135,51 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
   __shared__ int s_alloc;
   __shared__ int s_tok_cnt[256];    // outliers per token
   __shared__ unsigned char s_cnt_w[256][TQ_D / 32];  // ... of which on the channels of warp w
-  __shared__ int s_row[257];        // start of every token's outliers in the side-list
-  __shared__ int s_orow[257];       // start of every token's entries in the page's overflow list
+  __shared__ unsigned short s_row[258];   // start of every token's outliers in the side-list
+  __shared__ unsigned short s_orow[258];  // start of every token's entries in the page's overflow list
   __shared__ int s_warp_sum[TQ_D / 32];
+  // The level grid, and for 64 equal bins of [-1, 1] the grid cell (nearest level) that holds
+  // the bin's left edge, a little to the left of it: pass 3 finds a token's two candidate
+  // levels with it.  Usable when the cell borders lie further apart than a bin is wide.
+  __shared__ float s_grid[16];
+  __shared__ unsigned char s_bin[64];
+  constexpr float BIN_EPS = 1.0e-4f;
   if (tid == 0) s_count = 0;
+  if (tid < 16) s_grid[tid] = a.tables->grid[tid];
   __shared__ float s_scale[TQ_D];       // channel scales, to rank the widest channels
   __shared__ unsigned int s_side[256];  // per token: the codes of the four widest channels
   __shared__ float s_stat[10][TQ_D];  // running statistics on their way between the two halves
+  // Once the halves have merged, the same words hold the block's outliers as pass 3 meets them
+  // (token | channel << 8 | outlier channels below it in its warp << 16 | code << 24); they are
+  // worked off afterwards, one per thread, instead of by one or two lanes of a warp at a time.
+  uint32_t* s_list = (uint32_t*)&s_stat[0][0];
+  constexpr int LIST_CAP = 10 * TQ_D;
+  __shared__ int s_n_list;
+  __shared__ float s_mu[TQ_D];
+  if (tid == 0) s_n_list = 0;
   if (hf == 0) {
     s_side[d] = 0u;
     s_side[d + TQ_D] = 0u;
   }
   __syncthreads();
+  bool grid_regular = true;  // ascending, cell borders at least 1.5 bins apart
+  {
+    float prev_mid = -2.0f;
+#pragma unroll
+    for (int l = 0; l < 15; ++l) {
+      const float mid = 0.5f * (s_grid[l] + s_grid[l + 1]);
+      grid_regular = grid_regular && s_grid[l] < s_grid[l + 1] && mid - prev_mid > 1.5f / 32.0f;
+      prev_mid = mid;
+    }
+    grid_regular = grid_regular && s_grid[0] >= -1.0f && s_grid[15] <= 1.0f;
+    if (tid < 64) {
+      const float left = -1.0f + (float)tid * (1.0f / 32.0f) - BIN_EPS;
+      int cell = 0;
+#pragma unroll
+      for (int l = 0; l < 15; ++l) cell += (0.5f * (s_grid[l] + s_grid[l + 1]) < left) ? 1 : 0;
+      s_bin[tid] = (unsigned char)cell;
+    }
+  }
 
   // pass 1: sequential sum and the k largest magnitudes.  Up to eight of them (the usual
   // case: k = 5 at 256-token blocks) are kept in an ascending register array updated without
@@ -162,12 +195,16 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
   const int mode = g.key_mode;
   // (the first thread of a channel also carries the sum, over all tokens in order; more than
   // eight outliers per channel are tracked by that thread alone, over all tokens)
+  // The first thread visits every token for the sum, so it takes the smaller share of the
+  // other statistics: the shares are cut where the two threads' instruction counts meet.
   float acc = 0.0f, xmin = INFINITY, xmax = -INFINITY;
-  const int p1_hi = hf == 0 ? S : t_hi;
-  for (int t = t_lo; t < p1_hi; ++t) {
+  const bool k5 = kk <= 5;  // uniform: the five largest suffice, kept in t8[3..7]
+  const int own_cut = (n_hf == 1 || !small_k) ? S : ((S * (k5 ? 88 : 101)) >> 8) & ~1;
+  const int p1_lo = hf == 0 ? 0 : (small_k ? own_cut : t_lo);
+  for (int t = p1_lo; t < S; ++t) {
     const float x = ldx(t);
     if (hf == 0) acc = t == 0 ? x : __fadd_rn(acc, x);
-    const bool own = t < t_hi || !small_k;
+    const bool own = hf != 0 || t < own_cut;
     const float ax = fabsf(x);
     if (own) {
       xmin = fminf(xmin, x);
@@ -175,8 +212,12 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
     if (small_k) {
       if (own) {
+        if (!k5) {
 #pragma unroll
-        for (int j = 0; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
+          for (int j = 0; j < 3; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
+        }
+#pragma unroll
+        for (int j = 3; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
         t8[TK - 1] = fmaxf(ax, t8[TK - 1]);
       }
     } else if (hf == 0 && ax > top[0]) {
@@ -267,6 +308,7 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
     ((float*)(page + g.scale_off))[d] = amax;
     ((float*)(page + g.mean_off))[d] = mu;
     s_scale[d] = amax;
+    s_mu[d] = mu;
   }
   // allocate this page's slice of the (layer, seq, head) outlier slab
   __syncthreads();
@@ -344,13 +386,13 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
     uint32_t base = 0;
     for (int w = 0; w < (d >> 5); ++w) base += (uint32_t)s_warp_sum[w];
     const uint32_t excl = base + v - mine;
-    s_row[2 * d] = (int)(excl & 0xffffu);
-    s_row[2 * d + 1] = (int)(excl & 0xffffu) + c0;
-    s_orow[2 * d] = (int)(excl >> 16);
-    s_orow[2 * d + 1] = (int)(excl >> 16) + o0;
+    s_row[2 * d] = (unsigned short)(excl & 0xffffu);
+    s_row[2 * d + 1] = (unsigned short)((excl & 0xffffu) + c0);
+    s_orow[2 * d] = (unsigned short)(excl >> 16);
+    s_orow[2 * d + 1] = (unsigned short)((excl >> 16) + o0);
     if (d == TQ_D - 1) {
-      s_row[256] = (int)((base + v) & 0xffffu);
-      s_orow[256] = (int)((base + v) >> 16);
+      s_row[256] = (unsigned short)((base + v) & 0xffffu);
+      s_orow[256] = (unsigned short)((base + v) >> 16);
     }
     // slots the tokens do not use hold a zero delta on channel 0
     for (int j = c0; j < TQ_ELL_SLOTS; ++j) {
@@ -363,11 +405,11 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
   }
   __syncthreads();
-  if (tid < 5) hdr->ovf_start[tid] = (uint16_t)min(s_orow[64 * tid], TQ_OVF_CAP);
+  if (tid < 5) hdr->ovf_start[tid] = (uint16_t)min((int)s_orow[64 * tid], TQ_OVF_CAP);
   if (tid == 5) {
     // the in-page copy is complete unless the overflow list is too long or the pool slab
     // could not take every entry (then the pool's shorter list is the cache's content)
-    const int n_ovf = s_orow[256];
+    const int n_ovf = (int)s_orow[256];
     hdr->ovf_n = (uint16_t)min(n_ovf, TQ_OVF_CAP);
     hdr->flags = (n_ovf > TQ_OVF_CAP || s_alloc < s_count) ? TQ_PAGE_SPILLED : 0;
   }
@@ -379,10 +421,29 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
   // tournament over the 16 distances in which the lower index wins a tie at every round (the
   // first minimum, like a strict-less scan from level 0, in four dependent steps instead of
   // fifteen), and two tokens are worked on together so that their chains overlap.
+  // Where the levels of a channel are well separated (the scale is not tiny against the
+  // mean, so that rounding cannot merge or reorder them) only two levels can be the nearest:
+  // those of the one or two grid cells that meet the token's bin.  Every other level is
+  // further away by at least BIN_EPS of the scale, far more than the rounding of a
+  // difference, so comparing those two the way the reference does (rounded differences, the
+  // lower index on a tie) gives the reference's first minimum.
+  const float mu_eff = mode == TQ_KEYS_NF4 ? 0.0f : mu;
+  const bool two_cand = grid_regular && mode != TQ_KEYS_UNIFORM && amax >= fabsf(mu_eff) * (1.0f / 512.0f);
+  const float inv32 = 32.0f / amax;
+  auto level_of = [&](int l) -> float {
+    const float sl = __fmul_rn(amax, s_grid[l]);
+    return mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
+  };
   auto nearest = [&](float x) -> int {
     if (mode == TQ_KEYS_UNIFORM) {
       const float qv = rintf(__fdiv_rn(__fsub_rn(x, mu), amax));  // ties to even, like np.round
       return (int)fminf(fmaxf(qv, 0.0f), 15.0f);
+    }
+    if (two_cand) {
+      const int bin = min(max(__float2int_rd(fmaf(x - mu_eff, inv32, 32.0f)), 0), 63);
+      const int i0 = s_bin[bin], i1 = min(i0 + 1, 15);
+      const float d0 = fabsf(__fsub_rn(x, level_of(i0))), d1 = fabsf(__fsub_rn(x, level_of(i1)));
+      return d1 < d0 ? i1 : i0;
     }
     float dv[16];
 #pragma unroll
@@ -405,6 +466,33 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
     }
     return ix[0];
   };
+  // Stores outlier (token t, channel dch, value x, code `code`).  A token's outliers are stored
+  // in channel order (the order of the reference's flat indices), so the side-list, and with it
+  // every bit the decoder computes, is a function of the tokens alone: the entry's place is the
+  // count of outlier channels below it (`bw` of them in its own group of 32 channels).
+  auto put_outlier = [&](int t, int dch, int bw, int code, float x) {
+    int below = bw;
+    for (int w = 0; w < (dch >> 5); ++w) below += (int)s_cnt_w[t][w];
+    const int slot = (int)s_row[t] + below;
+    const __half hv = __float2half_rn(x);
+    // the decoder's value of this position
+    const float sl = __fmul_rn(s_scale[dch], s_grid[code]);
+    const float dense = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(s_mu[dch], sl);
+    const __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
+    const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)dch << 16) |
+                         ((uint32_t)t << 24);
+    if (slot < alloc) {
+      a.pool_dec[slab + slot] = ent;
+      a.pool_val[slab + slot] = __half_as_ushort(hv);
+    }
+    if (below < TQ_ELL_SLOTS) {
+      ell_delta[below * 256 + t] = __half_as_ushort(delta);
+      ell_col[below * 256 + t] = (uint8_t)q_row(dch);
+    } else {
+      const int oi = (int)s_orow[t] + below - TQ_ELL_SLOTS;
+      if (oi < TQ_OVF_CAP) ovf[oi] = ent;
+    }
+  };
   for (int t0 = t_lo; t0 < t_hi; t0 += 2) {
     const float xa = ldx(t0), xb = ldx(min(t0 + 1, S - 1));
     const int best_a = nearest(xa), best_b = nearest(xb);
@@ -423,31 +511,24 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
       const bool is_out = kk > 0 && fabsf(x) >= kth;
       const unsigned vote = __ballot_sync(0xffffffffu, is_out);
       if (is_out) {
-        int below = __popc(vote & ((1u << (d & 31)) - 1u));
-        for (int w = 0; w < (d >> 5); ++w) below += (int)s_cnt_w[t][w];
-        const int slot = s_row[t] + below;
-        __half hv = __float2half_rn(x);
-        // the decoder's value of this position (the level, recomputed: indexing lev[] with a
-        // runtime index would move the whole array out of registers)
-        const float sl = __fmul_rn(amax, a.tables->grid[best]);
-        float dense = mode == TQ_KEYS_NF4 ? sl : __fadd_rn(mu, sl);
-        __half delta = __float2half_rn(__fsub_rn(__half2float(hv), dense));
-        const uint32_t ent = (uint32_t)__half_as_ushort(delta) | ((uint32_t)d << 16) |
-                             ((uint32_t)t << 24);
-        if (slot < alloc) {
-          a.pool_dec[slab + slot] = ent;
-          a.pool_val[slab + slot] = __half_as_ushort(hv);
-        }
-        const int j = slot - s_row[t];  // which of the token's outliers this is
-        if (j < TQ_ELL_SLOTS) {
-          ell_delta[j * 256 + t] = __half_as_ushort(delta);
-          ell_col[j * 256 + t] = (uint8_t)q_row(d);
-        } else {
-          const int oi = s_orow[t] + j - TQ_ELL_SLOTS;
-          if (oi < TQ_OVF_CAP) ovf[oi] = ent;
+        const int bw = __popc(vote & ((1u << (d & 31)) - 1u));
+        const int li = atomicAdd(&s_n_list, 1);
+        if (li < LIST_CAP) {
+          s_list[li] = (uint32_t)t | ((uint32_t)d << 8) | ((uint32_t)bw << 16) | ((uint32_t)best << 24);
+        } else {  // (a block with more outliers than the list holds: in place)
+          put_outlier(t, d, bw, best, x);
         }
       }
-
+    }
+  }
+  __syncthreads();
+  {
+    const int n_list = min(s_n_list, LIST_CAP);
+    for (int li = tid; li < n_list; li += (int)blockDim.x) {
+      const uint32_t ent = s_list[li];
+      const int t = (int)(ent & 255u), dch = (int)((ent >> 8) & 127u);
+      const float x = STAGED ? Elem<DT>::ld(enck_rows, (size_t)t * TQ_D + dch) : src.ld(pos0 + t, dch);
+      put_outlier(t, dch, (int)((ent >> 16) & 31u), (int)(ent >> 24), x);
     }
   }
   __syncthreads();
@@ -470,7 +551,8 @@ __global__ void __launch_bounds__(2 * TQ_D) encode_keys_kernel(EncodeArgs a) {
 // lo = fp16((x - hi) * 2^11) (what is left is below 2^-24 |x|), and sums hi*hi into one
 // float32 accumulator and hi*lo + lo*hi into another; the products are exact in float32, the
 // dropped lo*lo term is below 2^-24 of a term, and the accumulators add eight (sixteen)
-// 16-term tiles.  That result lies within a few 1e-6 of the exact dot product, so the two
+// 16-term tiles; the unit vector it rotates is x * (1 / norm), within 2^-22 of x / norm.
+// That result lies within a few 1e-6 of the exact dot product, so the two
 // differ by less than 1.6e-5; ROT_SLACK leaves a factor 2.5 on top of that.  A coordinate
 // with a quantisation boundary inside the slack is computed again in the reference's order.
 constexpr float ROT_SLACK = 4.0e-5f;
@@ -619,13 +701,15 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
       }
     }
     half_sync();
-    {  // unit vectors as fp16 hi / lo parts, [token][channel]
+    {  // unit vectors as fp16 hi / lo parts, [token][channel].  The tensor-core rotation only
+       // has to land within the slack, so it takes x * (1 / norm), one or two units in the
+       // last place from the reference's x / norm; the recomputation divides.
       int t = e >> 3, j = e & 7;
-      float safe = fmaxf(hs->norm[t], 1e-30f);
+      const float inv = 1.0f / fmaxf(hs->norm[t], 1e-30f);
 #pragma unroll
       for (int i = 0; i < TQ_D / 8; ++i) {
         __half h, l;
-        split_h(__fdiv_rn(hs->xs[t][8 * i + j], safe), h, l);
+        split_h(hs->xs[t][8 * i + j] * inv, h, l);
         hs->uh[0][t][8 * i + j] = h;
         hs->uh[1][t][8 * i + j] = l;
       }
@@ -675,13 +759,14 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     // code = number of boundaries below the coordinate (one boundary load serves the lane's 16
     // coordinates); a coordinate with a boundary within the slack is done again.
     // Coordinate k = 8 mt + 4 nt + i of the lane.
+    // (the boundaries ascend, so the count is found by bisection: value_bits comparisons)
     int code[16];
 #pragma unroll
     for (int k = 0; k < 16; ++k) code[k] = 0;
-    for (int j = 0; j < n_bnd; ++j) {
-      const float b = s_bnd[1 + j];
+    for (int step = (n_bnd + 1) >> 1; step > 0; step >>= 1) {
 #pragma unroll
-      for (int k = 0; k < 16; ++k) code[k] += (b < y[k >> 3][(k >> 2) & 1][k & 3]) ? 1 : 0;
+      for (int k = 0; k < 16; ++k)
+        code[k] += (s_bnd[code[k] + step] < y[k >> 3][(k >> 2) & 1][k & 3]) ? step : 0;
     }
     unsigned redo = 0u;
 #pragma unroll
