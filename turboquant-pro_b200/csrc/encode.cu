@@ -63,6 +63,28 @@ TQ_DEV TokenSource<DT> make_source(const EncodeArgs& a, const void* ring_base, c
   return s;
 }
 
+// Packed minimum / maximum of two 16-bit floats (fp16 or bf16 by BF): the statistics of two
+// tokens of a channel in one instruction.  The values are the tokens themselves, so nothing
+// is rounded.
+template <bool BF>
+TQ_DEV uint32_t max2_16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (BF) asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool BF>
+TQ_DEV uint32_t min2_16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (BF) asm("min.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("min.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool BF>
+TQ_DEV float f16bits_to_float(uint32_t h) {
+  return BF ? __uint_as_float(h << 16) : __half2float(__ushort_as_half((unsigned short)h));
+}
+
 // ---------------------------------------------------------------------------------------
 // Key encoder.  One CTA per new cold block of one KV head, one thread per channel.
 // Asymmetric NF4 (TQ_KEYS_NF4_ASYM):
@@ -199,12 +221,59 @@ __global__ void __launch_bounds__(2 * TQ_D, 3) encode_keys_kernel(EncodeArgs a) 
   // other statistics: the shares are cut where the two threads' instruction counts meet.
   float acc = 0.0f, xmin = INFINITY, xmax = -INFINITY;
   const bool k5 = kk <= 5;  // uniform: the five largest suffice, kept in t8[3..7]
-  const int own_cut = (n_hf == 1 || !small_k) ? S : ((S * (k5 ? 88 : 101)) >> 8) & ~1;
-  const int p1_lo = hf == 0 ? 0 : (small_k ? own_cut : t_lo);
+  // Staged 16-bit tokens are taken two at a time with packed instructions (even tokens in the
+  // low halves, odd ones in the high halves: two top lists, merged at the end).
+  constexpr bool PACKED = STAGED && DT != TQ_F32;
+  const bool packed = PACKED && small_k && (S & 1) == 0;  // uniform
+  const int own_cut = (n_hf == 1 || !small_k) ? S
+                      : packed ? ((S * (k5 ? 96 : 108)) >> 8) & ~1
+                               : ((S * (k5 ? 88 : 101)) >> 8) & ~1;
+  int p1_lo = hf == 0 ? 0 : (small_k ? own_cut : t_lo);
+  if (PACKED && packed) {
+    constexpr bool BF = DT == TQ_BF16;
+    constexpr uint32_t NEG1 = BF ? 0xBF80BF80u : 0xBC00BC00u;     // (-1, -1)
+    constexpr uint32_t PINF = BF ? 0x7F807F80u : 0x7C007C00u, NINF = PINF | 0x80008000u;
+    const unsigned short* rows16 = (const unsigned short*)enck_rows;
+    uint32_t h8[TK], mn = PINF, mx = NINF;
+#pragma unroll
+    for (int i = 0; i < TK; ++i) h8[i] = NEG1;
+    const int o_lo = hf == 0 ? 0 : own_cut, o_hi = hf == 0 ? own_cut : S;
+    for (int t = o_lo; t < o_hi; t += 2) {
+      const uint32_t b0 = rows16[(size_t)t * TQ_D + d], b1 = rows16[(size_t)(t + 1) * TQ_D + d];
+      if (hf == 0) {
+        const float x0 = f16bits_to_float<BF>(b0), x1 = f16bits_to_float<BF>(b1);
+        acc = t == 0 ? x0 : __fadd_rn(acc, x0);
+        acc = __fadd_rn(acc, x1);
+      }
+      const uint32_t xx = b0 | (b1 << 16), ax = xx & 0x7FFF7FFFu;
+      mn = min2_16<BF>(mn, xx);
+      mx = max2_16<BF>(mx, xx);
+      if (!k5) {
+#pragma unroll
+        for (int j = 0; j < 3; ++j) h8[j] = min2_16<BF>(max2_16<BF>(ax, h8[j]), h8[j + 1]);
+      }
+#pragma unroll
+      for (int j = 3; j < TK - 1; ++j) h8[j] = min2_16<BF>(max2_16<BF>(ax, h8[j]), h8[j + 1]);
+      h8[TK - 1] = max2_16<BF>(ax, h8[TK - 1]);
+    }
+    // the even tokens' list, then the odd tokens' largest inserted one by one
+#pragma unroll
+    for (int j = 0; j < TK; ++j) t8[j] = f16bits_to_float<BF>(h8[j] & 0xFFFFu);
+#pragma unroll
+    for (int i = 0; i < TK; ++i) {
+      const float ax = f16bits_to_float<BF>(h8[i] >> 16);
+#pragma unroll
+      for (int j = 0; j < TK - 1; ++j) t8[j] = fminf(fmaxf(ax, t8[j]), t8[j + 1]);
+      t8[TK - 1] = fmaxf(ax, t8[TK - 1]);
+    }
+    xmin = fminf(f16bits_to_float<BF>(mn & 0xFFFFu), f16bits_to_float<BF>(mn >> 16));
+    xmax = fmaxf(f16bits_to_float<BF>(mx & 0xFFFFu), f16bits_to_float<BF>(mx >> 16));
+    p1_lo = hf == 0 ? own_cut : S;  // what is left for the loop below: the rest of the sum
+  }
   for (int t = p1_lo; t < S; ++t) {
     const float x = ldx(t);
     if (hf == 0) acc = t == 0 ? x : __fadd_rn(acc, x);
-    const bool own = hf != 0 || t < own_cut;
+    const bool own = (hf != 0 || t < own_cut) && !packed;
     const float ax = fabsf(x);
     if (own) {
       xmin = fminf(xmin, x);
