@@ -699,6 +699,12 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
   float* s_bnd = (float*)(encv_smem + ENCV_PI_BYTES + ENCV_HALVES * sizeof(EncvHalf));
   auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
   const float* pi_rows = a.tables->pi;  // pi[ch][d]
+  // whether every row of the caller's tensor starts on a 16-byte boundary (the ring's do)
+  const bool rows_aligned = [&]() {
+    const int64_t epc = 16 / (int64_t)sizeof(typename Elem<DT>::type);
+    return ((uintptr_t)a.v & 15) == 0 && a.seq_stride % epc == 0 && a.tok_stride % epc == 0 &&
+           a.head_stride % epc == 0;
+  }();
 
   for (int idx = threadIdx.x; idx < 8 * 8 * 32; idx += ENCV_HALVES * TQ_D) {
     const int L = idx & 31, ks = (idx >> 5) & 7, MT = idx >> 8;
@@ -738,47 +744,79 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     const TokenSource<DT> src = make_source<DT>(a, a.hot_v, a.v, seq, head, n0);
     uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
 
-    half_sync();  // previous item fully consumed
+    // (No barrier here: the last reads of the previous item's rows, unit vectors and lists lie
+    // before its last two barriers, and its image is overwritten only after three more.)
+    if (e == 0) hs->wl_n = 0;
     {
-      float xv[TQ_GROUP_TOK];  // all rows requested before the first is used
+      // The group's 16 rows are consecutive positions: the ring slot of the first one is worked
+      // out once (one division), the others follow by increments.  Rows past the end of the
+      // block (a block length that is no multiple of 16) read the block's last row and count
+      // as zero.
+      using T = typename Elem<DT>::type;
+      const int tok0 = gq * TQ_GROUP_TOK, pos0 = blk * S + tok0;
+      const int ring0 = pos0 % src.cap;
+      auto row_of = [&](int t) -> const T* {  // token t of the group (clamped)
+        const int te = min(t, S - 1 - tok0);
+        const int pos = pos0 + te;
+        int ri = ring0 + te;
+        ri -= ri >= src.cap ? src.cap : 0;
+        return pos < n0 ? (const T*)src.ring + (size_t)ri * TQ_D
+                        : (const T*)src.in + (size_t)(pos - n0) * src.tok_stride;
+      };
+      if (rows_aligned) {
+        // 16-byte pieces, all requested before the first is used
+        constexpr int EPC = 16 / (int)sizeof(T), CH = TQ_D / EPC, NCH = TQ_GROUP_TOK * CH / TQ_D;
+        uint4 raw[NCH];
 #pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t) {
-        const int tt = min(gq * TQ_GROUP_TOK + t, S - 1);
-        xv[t] = src.ld(blk * S + tt, e);
+        for (int i = 0; i < NCH; ++i) {
+          const int id = e + TQ_D * i;
+          raw[i] = *(const uint4*)(row_of(id / CH) + (id % CH) * EPC);
+        }
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+          const int id = e + TQ_D * i, t = id / CH, c0 = (id % CH) * EPC;
+          const bool live = tok0 + t < S;
+          const T* pv = (const T*)&raw[i];
+          float f[EPC];
+#pragma unroll
+          for (int k = 0; k < EPC; ++k) f[k] = live ? Elem<DT>::ld(pv, k) : 0.0f;
+#pragma unroll
+          for (int k = 0; k < EPC; k += 4)
+            *(float4*)&hs->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
+        }
+      } else {
+        float xv[TQ_GROUP_TOK];
+#pragma unroll
+        for (int t = 0; t < TQ_GROUP_TOK; ++t) xv[t] = Elem<DT>::ld(row_of(t), e);
+#pragma unroll
+        for (int t = 0; t < TQ_GROUP_TOK; ++t) hs->xs[t][e] = tok0 + t < S ? xv[t] : 0.0f;
       }
-#pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t)
-        hs->xs[t][e] = gq * TQ_GROUP_TOK + t < S ? xv[t] : 0.0f;
     }
     half_sync();
     {  // norms: 8 threads per token, accumulator j sums elements j, j+8, j+16, ...
-      int t = e >> 3, j = e & 7;
-      float v0 = hs->xs[t][j];
-      float sq = __fmul_rn(v0, v0);
+      const int t = e >> 3, j = e & 7;
+      float xr[TQ_D / 8];
 #pragma unroll
-      for (int i = 1; i < TQ_D / 8; ++i) {
-        float vv = hs->xs[t][8 * i + j];
-        sq = __fadd_rn(sq, __fmul_rn(vv, vv));
-      }
+      for (int i = 0; i < TQ_D / 8; ++i) xr[i] = hs->xs[t][8 * i + j];
+      float sq = __fmul_rn(xr[0], xr[0]);
+#pragma unroll
+      for (int i = 1; i < TQ_D / 8; ++i) sq = __fadd_rn(sq, __fmul_rn(xr[i], xr[i]));
       sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 1));  // (r0+r1), (r2+r3), ...
       sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 2));  // (r0+r1)+(r2+r3), ...
       sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 4));
-      float nrm = __fsqrt_rn(sq);
+      const float nrm = __fsqrt_rn(sq);  // (the same bits in all eight threads of the token)
       if (j == 0) {
         hs->norm[t] = nrm;
         ((float*)(page + g.norm_off))[gq * TQ_GROUP_TOK + t] = nrm;
       }
-    }
-    half_sync();
-    {  // unit vectors as fp16 hi / lo parts, [token][channel].  The tensor-core rotation only
-       // has to land within the slack, so it takes x * (1 / norm), one or two units in the
-       // last place from the reference's x / norm; the recomputation divides.
-      int t = e >> 3, j = e & 7;
-      const float inv = 1.0f / fmaxf(hs->norm[t], 1e-30f);
+      // unit vectors as fp16 hi / lo parts, [token][channel].  The tensor-core rotation only
+      // has to land within the slack, so it takes x * (1 / norm), one or two units in the
+      // last place from the reference's x / norm; the recomputation divides.
+      const float inv = 1.0f / fmaxf(nrm, 1e-30f);
 #pragma unroll
       for (int i = 0; i < TQ_D / 8; ++i) {
         __half h, l;
-        split_h(hs->xs[t][8 * i + j] * inv, h, l);
+        split_h(xr[i] * inv, h, l);
         hs->uh[0][t][8 * i + j] = h;
         hs->uh[1][t][8 * i + j] = l;
       }
@@ -853,9 +891,8 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
       unsigned short* wl = (unsigned short*)&hs->uh[0][0][0];             // (channel, token) items
       unsigned char* fixed = (unsigned char*)(wl + TQ_D * TQ_GROUP_TOK);   // [token][channel] codes
       float* prod = (float*)(fixed + TQ_D * TQ_GROUP_TOK) + wq * TQ_D;     // this warp's products
-      half_sync();  // every warp is done with the unit vectors
-      if (e == 0) hs->wl_n = 0;
-      half_sync();
+      half_sync();  // every warp is done with the unit vectors (the list's counter was zeroed
+                    // at the top of the item, two barriers ago)
       unsigned todo = redo;
       while (todo) {
         const int k = __ffs((int)todo) - 1;
