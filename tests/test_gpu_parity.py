@@ -156,6 +156,7 @@ def test_cache_matches_reference(torch_cuda, name, vb, bulk):
     (2, 4, 1500, 512, 3, "float16"),     # GQA 4, K4/V3 (Llama-3-8B shape)
     (1, 8, 1100, 512, 4, "float16"),     # GQA 8 (Llama-3-70B shape)
     (2, 4, 300, 512, 3, "bfloat16"),     # hot only
+    (2, 4, 1300, 512, 4, "bfloat16"),    # bfloat16 tokens through both encoders (3 cold blocks)
     (2, 2, 770, 512, 3, "float16"),      # exactly at a flush boundary + 1
     (1, 7, 200, 64, 3, "float32"),       # odd group (Qwen2.5-7B shape), small window
     (1, 16, 150, 32, 4, "float16"),      # group 16
@@ -188,6 +189,42 @@ def test_decode_vs_oracle(torch_cuda, h, grp, n, w, vb, dt):
         err = np.abs(got - want_q).max()
         assert np.allclose(got, want_q, rtol=RTOL, atol=ATOL), f"{qdt}: max abs err {err}"
     assert want.shape == (h * grp, 128)
+
+
+@pytest.mark.parametrize("dt", ["float16", "float32"])
+def test_rows_off_the_16_byte_grid_encode_the_same(torch_cuda, dt):
+    """Tokens handed over as a view whose rows start one element past a 16-byte boundary (the
+    encoders then load element by element) give the same pages, bit for bit, as the same tokens
+    in a contiguous tensor."""
+    torch = torch_cuda
+    from turboquant_pro_b200.synth import make_kv
+
+    h, n, w, vb = 2, 1100, 512, 3
+    k, v = make_kv(77, h, n, dtype=np.float16)
+    tdt = getattr(torch, dt)
+    kt, vt = torch.from_numpy(k).to(tdt).cuda(), torch.from_numpy(v).to(tdt).cuda()
+    wide_k = torch.zeros((1, n, h, 129), dtype=tdt, device="cuda")
+    wide_v = torch.zeros((1, n, h, 129), dtype=tdt, device="cuda")
+    wide_k[0, :, :, 1:] = kt
+    wide_v[0, :, :, 1:] = vt
+    blocks = []
+    for src_k, src_v in ((kt[None], vt[None]), (wide_k[..., 1:], wide_v[..., 1:])):
+        ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h, value_bits=vb, hot_window=w,
+                   max_tokens_per_seq=n + 8, kv_dtype=dt, seed=5)
+        assert src_k.stride(3) == 1
+        ctx.append(0, src_k, src_v)
+        assert ctx.status() == 0
+        nb = ctx.lengths(0, 0)[1] // 256
+        assert nb >= 2
+        blocks.append([ctx.export_block(0, 0, i) for i in range(nb)])
+    assert len(blocks[0]) == len(blocks[1])
+    for a, b in zip(*blocks):
+        assert a.keys() == b.keys()
+        for name in a:
+            if a[name] is None:
+                assert b[name] is None
+            else:
+                assert np.array_equal(np.asarray(a[name]), np.asarray(b[name])), name
 
 
 def test_batched_layers_ragged(torch_cuda):
