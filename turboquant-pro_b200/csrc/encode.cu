@@ -974,31 +974,50 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
 
 // ---------------------------------------------------------------------------------------
 // Hot-ring writer: the new tokens that stay uncompressed go to slot (position % hot_cap).
-// grid = (tokens, heads, seqs); token index counts back from the newest.
+// grid = (tokens, heads, seqs); token index counts back from the newest.  The CTA that
+// finishes last then adds the new tokens to the sequence lengths: every kernel of the append
+// (the encoders before this one in the stream, and every CTA of this one) has read the old
+// lengths by then.  The kernel may be launched with programmatic stream serialization: it
+// waits for the kernel before it in the stream before it reads or writes anything.
 // ---------------------------------------------------------------------------------------
 template <int DT>
 __global__ void __launch_bounds__(TQ_D) ring_write_kernel(EncodeArgs a) {
   using T = typename Elem<DT>::type;
   const tq_geom& g = a.g;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int seq = a.seq_begin + blockIdx.z;
   const int head = blockIdx.y;
   const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
   const int n1 = n0 + a.n_tokens;
   const int pos = n1 - 1 - (int)blockIdx.x;
   const int hot_start = n_cold_blocks(n1, g.hot_window, g.block_tokens) * g.block_tokens;
-  if (pos < n0 || pos < hot_start) return;
-  const size_t in = (size_t)(seq - a.seq_begin) * a.seq_stride + (size_t)(pos - n0) * a.tok_stride +
-                    (size_t)head * a.head_stride + threadIdx.x;
-  const size_t out =
-      hot_offset_elems(g, a.layer, seq, head) + (size_t)(pos % g.hot_cap) * TQ_D + threadIdx.x;
-  ((T*)a.hot_k)[out] = ((const T*)a.k)[in];
-  ((T*)a.hot_v)[out] = ((const T*)a.v)[in];
-}
-
-__global__ void advance_len_kernel(int32_t* seq_len, int layer, int n_seqs, int seq_begin,
-                                   int seq_count, int n_tokens) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < seq_count) seq_len[layer * n_seqs + seq_begin + i] += n_tokens;
+  if (pos >= n0 && pos >= hot_start) {
+    const size_t in = (size_t)(seq - a.seq_begin) * a.seq_stride +
+                      (size_t)(pos - n0) * a.tok_stride + (size_t)head * a.head_stride + threadIdx.x;
+    const size_t out =
+        hot_offset_elems(g, a.layer, seq, head) + (size_t)(pos % g.hot_cap) * TQ_D + threadIdx.x;
+    ((T*)a.hot_k)[out] = ((const T*)a.k)[in];
+    ((T*)a.hot_v)[out] = ((const T*)a.v)[in];
+  }
+  // last CTA out: the counter sits in the status word's 256-byte block and returns to zero
+  __shared__ int s_last;
+  __syncthreads();  // every thread of the CTA has read its length
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned prev = atomicAdd((unsigned*)a.status + 16, 1u);
+    s_last = prev == total - 1;
+    if (s_last) {
+      ((unsigned*)a.status)[16] = 0u;
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  if (s_last) {
+    for (int i = threadIdx.x; i < a.seq_count; i += blockDim.x)
+      a.seq_len[a.layer * g.n_seqs + a.seq_begin + i] += a.n_tokens;
+  }
 }
 
 __global__ void clear_kernel(int32_t* seq_len, uint32_t* cursor, int layer, int n_seqs,
@@ -1039,12 +1058,19 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
     encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(a);
     *launches += 2;
   }
-  dim3 grid(std::min(a.n_tokens, g.hot_window), g.n_kv_heads, a.seq_count);
-  ring_write_kernel<DT><<<grid, TQ_D, 0, st>>>(a);
-  advance_len_kernel<<<(a.seq_count + 127) / 128, 128, 0, st>>>(a.seq_len, a.layer, g.n_seqs,
-                                                                a.seq_begin, a.seq_count,
-                                                                a.n_tokens);
-  *launches += 2;
+  // (launched so that it may be scheduled while the kernel before it in the stream drains; it
+  // waits for that kernel itself)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(std::min(a.n_tokens, g.hot_window), g.n_kv_heads, a.seq_count);
+  cfg.blockDim = dim3(TQ_D);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, ring_write_kernel<DT>, a));
+  *launches += 1;
   return TQ_OK;
 }
 
