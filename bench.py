@@ -774,27 +774,69 @@ def run_cfg2(args, dst: Dist):
             else:
                 ctx.lse_combine(mlo.view(1, rows, 130), out=out[layer])
 
-    ms_eager = timed(dst, step, args.steps, args.warmup)
-    # The step is launch-bound once the sequence is spread over several GPUs (five launches
-    # and one collective per layer against a few tens of microseconds of work), so it is also
-    # captured into one CUDA graph, collectives included, and replayed.
-    ms, graphed = ms_eager, False
-    try:
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        ok = True
-    except Exception as e:  # noqa: BLE001 - a stack that cannot capture keeps the eager number
-        ok = False
-        graph_error = repr(e)[:200]
-        torch.cuda.synchronize()
-    if dst.all_ok(ok):
-        want = out.clone()
-        ms_graph = timed(dst, graph.replay, args.steps, args.warmup)
-        same = bool(torch.equal(out, want))
-        if dst.all_ok(same) and ms_graph < ms_eager:
-            ms, graphed = ms_graph, True
+    def run_transport(step_fn):
+        # The step is launch-bound once the sequence is spread over several GPUs (a handful of
+        # launches per layer against a few tens of microseconds of work), so it is also
+        # captured into one CUDA graph, the exchange included, and replayed.
+        ms_e = timed(dst, step_fn, args.steps, args.warmup)
+        ms_b, graphed_b = ms_e, False
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_fn()
+            ok = True
+        except Exception:  # noqa: BLE001 - a stack that cannot capture keeps the eager number
+            ok = False
+            torch.cuda.synchronize()
+        if dst.all_ok(ok):
+            want = out.clone()
+            ms_graph = timed(dst, graph.replay, args.steps, args.warmup)
+            same = bool(torch.equal(out, want))
+            if dst.all_ok(same) and ms_graph < ms_e:
+                ms_b, graphed_b = ms_graph, True
+        return ms_e, ms_b, graphed_b
+
+    ms_eager, ms, graphed = run_transport(step)
+    transport = "nccl" if dst.world > 1 else "none"
+    nccl_numbers = {"ms_per_step": ms, "ms_per_step_eager": ms_eager, "cuda_graph": graphed}
+    peer_numbers, xchg_us = None, None
+    if dst.world > 1:
+        # The same step with the states exchanged and merged by one kernel over peer memory
+        # (plain peer stores over NVLink, bounded waits) instead of all-gather + merge kernel.
+        from turboquant_pro_b200.parallel import PeerExchange
+
+        ex, ok = None, True
+        try:
+            ex = PeerExchange(rows, 128, dev)
+        except Exception:  # noqa: BLE001 - no peer mapping between these processes
+            ok = False
+        if dst.all_ok(ok):
+            want = out.clone()  # what the all-gather path left
+
+            def step_peer():
+                for layer in range(L):
+                    ctx.decode_partial(layer, q_all[layer], 0, nb_local[layer], last, mlo=mlo)
+                    ex.gather_merge(mlo.view(rows, 130), out=out[layer])
+
+            step_peer()
+            torch.cuda.synchronize()
+            same = bool(torch.equal(out, want)) and ex.status() == 0
+            if not dst.all_ok(same):
+                raise SystemExit("config 2 check failed: the peer-memory exchange and the "
+                                 "all-gather path give different bits")
+            p_eager, p_ms, p_graphed = run_transport(step_peer)
+            x_ms = timed(dst, lambda: [ex.gather_merge(mlo.view(rows, 130), out=out[0])
+                                       for _ in range(L)], args.steps, args.warmup)
+            xchg_us = x_ms * 1e3 / L
+            ex.check()
+            peer_numbers = {"ms_per_step": p_ms, "ms_per_step_eager": p_eager,
+                            "cuda_graph": p_graphed, "exchange_kernel_us": xchg_us,
+                            "same_bits_as_all_gather": True}
+            if p_ms < ms:
+                ms_eager, ms, graphed, transport = p_eager, p_ms, p_graphed, "peer"
+        if ex is not None:
+            ex.close()
     # the collective alone, same sizes, same stream
     ag_us = None
     if dst.world > 1:
@@ -832,6 +874,8 @@ def run_cfg2(args, dst: Dist):
         "value_GBps": L * total_bytes / (ms * 1e-3) / 1e9,
         "per_layer_us": ms * 1e3 / L,
         "all_gather_us": ag_us, "all_gather_bytes_per_rank": rows * 130 * 4,
+        "transport": transport, "nccl": nccl_numbers if dst.world > 1 else None,
+        "peer": peer_numbers,
         "rank_attention_kernel_us_max": float(t[0]) * 1e3,
         "rank_combine_kernel_us": comb_ms * 1e3,
         "rank0_blocks": nb_local[0], "rank0_GBps": rank_gbs,
@@ -840,8 +884,11 @@ def run_cfg2(args, dst: Dist):
         "check": {"split_equals_whole": True, "max_abs_err": err,
                   "what": "9000-token layer, sharded caches + all-gather + merge vs the same "
                           "layer held whole on every rank"},
-        "collective": "NCCL all_gather_into_tensor of [32][130] float32 per layer, ordered with "
-                      "the decode stream, then tq_lse_combine in rank order"
+        "collective": ("one exchange kernel per layer: peer stores of [32][130] float32 into every "
+                       "rank's region over NVLink, per-row-group flags, bounded wait, merge in "
+                       "rank order (tq_xchg_gather_merge)" if transport == "peer" else
+                       "NCCL all_gather_into_tensor of [32][130] float32 per layer, ordered with "
+                       "the decode stream, then tq_lse_combine in rank order")
                       if dst.world > 1 else "none",
     }
     del cache, ctx

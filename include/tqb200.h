@@ -182,6 +182,49 @@ int32_t tq_decode_partial(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_d
 int32_t tq_lse_combine(const float* mlo, int32_t n_parts, int32_t n_rows, int32_t head_dim,
                        float* out, void* stream);
 
+/* ---- exchange of the sequence-split states over peer memory ------------------------------
+ * The reference merges the per-page partials of one device (merge_partials,
+ * kv_fused.py:139-153) and leaves any exchange between devices to its caller.  A tq_xchg
+ * replaces "all-gather the (m, l, o) states of every rank, then tq_lse_combine" by ONE kernel
+ * per call: each rank stores its rows straight into every rank's region with peer stores
+ * over NVLink, signals per row group, waits (bounded) for the same row group of the other
+ * ranks and merges in rank order - bit-identical to tq_lse_combine on the gathered states.
+ *
+ * Life cycle, one object per rank: tq_xchg_create (allocates this rank's region with
+ * cudaMalloc, zeroed) -> publish tq_xchg_ipc_handle to the other processes (64 bytes, any
+ * transport) -> tq_xchg_open_peer for each of them (or tq_xchg_set_peer with the address
+ * from tq_xchg_base when the ranks are GPUs of one process with peer access enabled) -> a
+ * barrier of the caller's (every region must be zeroed before the first exchange) ->
+ * tq_xchg_gather_merge any number of times, the same number on every rank ->
+ * a barrier -> tq_xchg_destroy.  `rows` = n_seqs * n_q_heads; at most 16 ranks. */
+typedef struct tq_xchg tq_xchg;
+int32_t tq_xchg_create(int32_t device, int32_t rank, int32_t world, int32_t rows, int32_t head_dim,
+                       tq_xchg** out);
+int32_t tq_xchg_destroy(tq_xchg* x);
+/* Size and device address of this rank's region. */
+int64_t tq_xchg_region_bytes(const tq_xchg* x);
+void* tq_xchg_base(const tq_xchg* x);
+/* The CUDA IPC handle of this rank's region (`handle64`: 64 bytes of HOST memory). */
+int32_t tq_xchg_ipc_handle(tq_xchg* x, void* handle64);
+/* Maps the region of `peer_rank` (another process) from its IPC handle. */
+int32_t tq_xchg_open_peer(tq_xchg* x, int32_t peer_rank, const void* handle64);
+/* Uses `region` (device address valid in this process, e.g. tq_xchg_base of an object on
+ * another GPU of the same process) as the region of `peer_rank`. */
+int32_t tq_xchg_set_peer(tq_xchg* x, int32_t peer_rank, void* region);
+/* One exchange.  `mlo`: this rank's states [rows][2 + D] float32 (tq_decode_partial's
+ * output); `out`: [rows][D] float32.  `phases`: 3 = publish, wait and merge (the normal
+ * call); 1 = publish only and 2 = wait and merge only, for callers that drive several ranks
+ * from one stream and must not make a kernel wait for one that has not been launched yet.
+ * If a peer's rows do not arrive within the wait limit, bit 0 of tq_xchg_status is set and
+ * the affected rows of `out` are zero; the call itself still returns TQ_OK. */
+int32_t tq_xchg_gather_merge(tq_xchg* x, const float* mlo, float* out, int32_t phases,
+                             void* stream);
+/* Probes a wait makes before it gives up (each takes 0.1 us or more); 0 restores the default
+ * (about half a second). */
+int32_t tq_xchg_set_wait_limit(tq_xchg* x, int32_t probes);
+/* Status word of this rank's exchanges (bit 0: a wait ran out).  Synchronises `stream`. */
+int32_t tq_xchg_status(tq_xchg* x, int32_t* status, void* stream);
+
 /* Dequantised keys and values of tokens [start, end) of one sequence, float32
  * [n_kv_heads][end - start][D] each (device pointers, either may be NULL):
  * TurboQuantKVCache.get_keys / get_values (core.py:1040-1117), bit-identical to

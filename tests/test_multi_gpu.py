@@ -2,7 +2,8 @@
 
 Each rank holds the same sequence, attends its own range of cold blocks (the last rank also
 the hot window), the (m, l, o) states are all-gathered over NVLink and merged by the LSE
-combine kernel; the result must equal the single-device decode.
+combine kernel; the result must equal the single-device decode.  The same states then go
+through the peer-memory exchange kernel, which must give the same bits.
 """
 
 from __future__ import annotations
@@ -41,6 +42,18 @@ split = SequenceSplitDecoder(ctx).decode(0, q)
 torch.cuda.synchronize()
 err = (split - full).abs().max().item()
 ok = torch.allclose(split, full, rtol=1e-3, atol=1e-4) and ctx.status() == 0
+# the same states exchanged and merged by one kernel over peer memory: the same bits
+from turboquant_pro_b200.parallel import PeerExchange, split_blocks, gather_states
+nb = ctx.lengths(0, 0)[1] // ctx.block_tokens
+lo, hi, with_hot = split_blocks(nb, rank, world)
+ex = PeerExchange(h * grp, 128, ctx.device)
+for it in range(4):
+    mlo = ctx.decode_partial(0, q, lo, hi, with_hot).reshape(h * grp, 130).contiguous()
+    via_nccl = ctx.lse_combine(gather_states(mlo))
+    via_peer = ex.gather_merge(mlo)
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(via_peer, via_nccl) and ex.status() == 0
+ex.close()
 flag = torch.tensor([1 if ok else 0], device="cuda")
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 if rank == 0:

@@ -74,6 +74,18 @@ SIGNATURES = {
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "tq_lse_combine": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                    C.c_void_p]),
+    "tq_xchg_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                   C.POINTER(C.c_void_p)]),
+    "tq_xchg_destroy": (C.c_int32, [C.c_void_p]),
+    "tq_xchg_region_bytes": (C.c_int64, [C.c_void_p]),
+    "tq_xchg_base": (C.c_void_p, [C.c_void_p]),
+    "tq_xchg_ipc_handle": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "tq_xchg_open_peer": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "tq_xchg_set_peer": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "tq_xchg_gather_merge": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                         C.c_void_p]),
+    "tq_xchg_set_wait_limit": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "tq_xchg_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
     "tq_dequant_range": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                      C.c_void_p, C.c_void_p, C.c_void_p]),
     "tq_export_block": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,

@@ -1,0 +1,273 @@
+// Exchange of the per-rank attention states (m, l, o[D]) of a sequence split over several
+// GPUs, fused with their log-sum-exp merge: one kernel per decode step and layer instead of a
+// library all-gather followed by a merge kernel.
+//
+// Every rank owns one region of device memory with the same layout and maps the regions of
+// the other ranks (CUDA IPC between processes, plain pointers inside one process):
+//
+//   gather  [2 slots][world][rows][2 + D] float32   the states as written by their owners
+//   flags   [2 slots][world][TQ_XCHG_CTAS] uint32    "rank r's CTA c has written exchange e"
+//   ctrl    epoch, CTA counter, status
+//
+// Exchange number e (1, 2, ...) uses slot e & 1.  CTA c of a rank owns rows c, c + n_cta, ...:
+// it stores its rows of the local states into slot e & 1 of every rank's gather area with
+// plain peer stores over NVLink, fences at system scope and writes e into its flag on every
+// rank; then it waits until the flags of all ranks' CTA c show e in its own region and merges
+// the rows in rank order (the arithmetic of merge_partials, kv_fused.py:139-153, as in
+// lse_combine_kernel).  A CTA depends only on the same CTA of the other ranks, so nothing
+// waits on a whole grid.  Two slots suffice: a rank can start exchange e + 1 only after its
+// own exchange e is complete, which needed every other rank's flag for e, which that rank
+// wrote after its exchange e - 1 had completed (stream order), so nobody still reads the slot
+// that exchange e + 1 overwrites.
+//
+// The wait is bounded: after `spin_limit` probes the kernel sets bit 0 of the status word,
+// writes zeros for the rows it could not merge and returns.  No multicast, no multimem: plain
+// loads and stores on peer memory.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TQ_XCHG_CTAS = 32;       // most CTAs (row groups) of the exchange kernel
+constexpr int TQ_XCHG_MAX_WORLD = 16;  // most ranks
+constexpr unsigned TQ_XCHG_SPIN = 1u << 22;  // default probes per wait (each takes 0.1 us or more)
+
+struct XchgArgs {
+  float* peer[TQ_XCHG_MAX_WORLD];  // every rank's region (own included)
+  int rank, world, rows, n_cta, phases;
+  size_t flags_off, ctrl_off;      // byte offsets inside a region
+  const float* mlo;                // [rows][2 + D] local states
+  float* out;                      // [rows][D]
+  unsigned spin_limit;
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(TQ_D) xchg_kernel(XchgArgs a) {
+  const int e = threadIdx.x, c = blockIdx.x;
+  float* own = a.peer[a.rank];
+  unsigned* ctrl = (unsigned*)((uint8_t*)own + a.ctrl_off);
+  const unsigned ep = *(volatile unsigned*)&ctrl[0] + 1u;
+  const int slot = (int)(ep & 1u);
+  const size_t part = (size_t)a.rows * TQ_PART_STRIDE;  // floats of one rank's states
+
+  if (a.phases & 1) {
+    for (int row = c; row < a.rows; row += a.n_cta) {
+      const float* src = a.mlo + (size_t)row * TQ_PART_STRIDE;
+      const float v0 = src[e];
+      const float v1 = e < 2 ? src[TQ_D + e] : 0.0f;
+      for (int p = 0; p < a.world; ++p) {
+        float* dst = a.peer[p] + ((size_t)slot * a.world + a.rank) * part +
+                     (size_t)row * TQ_PART_STRIDE;
+        dst[e] = v0;
+        if (e < 2) dst[TQ_D + e] = v1;
+      }
+    }
+    __syncthreads();  // the CTA's stores are ordered before the flags of thread e below
+    if (e < a.world) {
+      // (the release store orders the CTA's row stores, which the barrier made this thread's
+      // predecessors, before the flag at system scope)
+      unsigned* flag = (unsigned*)((uint8_t*)a.peer[e] + a.flags_off) +
+                       ((size_t)slot * a.world + a.rank) * TQ_XCHG_CTAS + c;
+      st_release_sys(flag, ep);
+    }
+  }
+  if (a.phases & 2) {
+    __shared__ int s_fail;
+    if (e == 0) s_fail = 0;
+    __syncthreads();
+    if (e < a.world) {
+      const unsigned* flag = (const unsigned*)((const uint8_t*)own + a.flags_off) +
+                             ((size_t)slot * a.world + e) * TQ_XCHG_CTAS + c;
+      unsigned n = 0;
+      // (flags only grow; the signed difference keeps the test right across a wrap)
+      while ((int)(ld_acquire_sys(flag) - ep) < 0) {
+        if (++n >= a.spin_limit) {
+          s_fail = 1;
+          atomicOr(&ctrl[2], 1u);
+          break;
+        }
+        __nanosleep(32);
+      }
+    }
+    __syncthreads();
+    const bool fail = s_fail != 0;
+    const float* gat = own + (size_t)slot * a.world * part;
+    for (int row = c; row < a.rows; row += a.n_cta) {
+      float res = 0.0f;
+      if (!fail) {
+        // (read past the first-level cache: the rows were written by other GPUs)
+        float M = -INFINITY;
+        for (int p = 0; p < a.world; ++p)
+          M = fmaxf(M, __ldcg(&gat[(size_t)p * part + (size_t)row * TQ_PART_STRIDE]));
+        float L = 0.0f, A = 0.0f;
+        for (int p = 0; p < a.world; ++p) {
+          const float* r = gat + (size_t)p * part + (size_t)row * TQ_PART_STRIDE;
+          const float m = __ldcg(&r[0]);
+          const float w = m > -INFINITY ? __expf(m - M) : 0.0f;
+          L += __ldcg(&r[1]) * w;
+          A += __ldcg(&r[2 + e]) * w;
+        }
+        res = L > 0.0f ? A / L : 0.0f;
+      }
+      a.out[(size_t)row * TQ_D + e] = res;
+    }
+    // the last CTA out closes the exchange
+    __syncthreads();
+    if (e == 0) {
+      __threadfence();
+      const unsigned prev = atomicAdd(&ctrl[1], 1u);
+      if (prev == (unsigned)a.n_cta - 1u) {
+        ctrl[1] = 0u;
+        *(volatile unsigned*)&ctrl[0] = ep;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+struct tq_xchg {
+  int device, rank, world, rows, n_cta;
+  size_t bytes, flags_off, ctrl_off;
+  float* own;
+  float* peer[TQ_XCHG_MAX_WORLD];
+  bool ipc[TQ_XCHG_MAX_WORLD];
+  unsigned spin_limit;
+};
+
+extern "C" {
+
+int32_t tq_xchg_create(int32_t device, int32_t rank, int32_t world, int32_t rows, int32_t head_dim,
+                       tq_xchg** out) {
+  TQ_REQUIRE(out != nullptr, TQ_ERR_INVALID, "null argument");
+  TQ_REQUIRE(head_dim == TQ_D, TQ_ERR_UNSUPPORTED, "only head_dim == 128 is implemented");
+  TQ_REQUIRE(world >= 1 && world <= TQ_XCHG_MAX_WORLD && rank >= 0 && rank < world, TQ_ERR_INVALID,
+             "bad rank / world (at most 16 ranks)");
+  TQ_REQUIRE(rows >= 1, TQ_ERR_INVALID, "rows must be positive");
+  TQ_CUDA(cudaSetDevice(device));
+  tq_xchg* x = new tq_xchg();
+  x->device = device;
+  x->rank = rank;
+  x->world = world;
+  x->rows = rows;
+  x->n_cta = rows < TQ_XCHG_CTAS ? rows : TQ_XCHG_CTAS;
+  x->flags_off = align_up((size_t)2 * world * rows * TQ_PART_STRIDE * sizeof(float), 256);
+  x->ctrl_off = x->flags_off + align_up((size_t)2 * world * TQ_XCHG_CTAS * sizeof(unsigned), 256);
+  x->bytes = x->ctrl_off + 256;
+  x->spin_limit = TQ_XCHG_SPIN;
+  for (int p = 0; p < TQ_XCHG_MAX_WORLD; ++p) {
+    x->peer[p] = nullptr;
+    x->ipc[p] = false;
+  }
+  cudaError_t e = cudaMalloc((void**)&x->own, x->bytes);
+  if (e == cudaSuccess) e = cudaMemset(x->own, 0, x->bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    delete x;
+    return tq_cuda_fail(e, "allocating the exchange region");
+  }
+  x->peer[rank] = x->own;
+  *out = x;
+  return TQ_OK;
+}
+
+int32_t tq_xchg_destroy(tq_xchg* x) {
+  if (x == nullptr) return TQ_OK;
+  cudaSetDevice(x->device);
+  for (int p = 0; p < x->world; ++p)
+    if (x->ipc[p] && x->peer[p] != nullptr) cudaIpcCloseMemHandle(x->peer[p]);
+  cudaFree(x->own);
+  delete x;
+  return TQ_OK;
+}
+
+int64_t tq_xchg_region_bytes(const tq_xchg* x) { return x ? (int64_t)x->bytes : 0; }
+
+void* tq_xchg_base(const tq_xchg* x) { return x ? (void*)x->own : nullptr; }
+
+int32_t tq_xchg_ipc_handle(tq_xchg* x, void* handle64) {
+  TQ_REQUIRE(x != nullptr && handle64 != nullptr, TQ_ERR_INVALID, "null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  TQ_CUDA(cudaSetDevice(x->device));
+  cudaIpcMemHandle_t h;
+  TQ_CUDA(cudaIpcGetMemHandle(&h, x->own));
+  std::memcpy(handle64, &h, sizeof(h));
+  return TQ_OK;
+}
+
+int32_t tq_xchg_open_peer(tq_xchg* x, int32_t peer_rank, const void* handle64) {
+  TQ_REQUIRE(x != nullptr && handle64 != nullptr, TQ_ERR_INVALID, "null argument");
+  TQ_REQUIRE(peer_rank >= 0 && peer_rank < x->world && peer_rank != x->rank, TQ_ERR_INVALID,
+             "bad peer rank");
+  TQ_REQUIRE(x->peer[peer_rank] == nullptr, TQ_ERR_INVALID, "peer already connected");
+  TQ_CUDA(cudaSetDevice(x->device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  TQ_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  x->peer[peer_rank] = (float*)p;
+  x->ipc[peer_rank] = true;
+  return TQ_OK;
+}
+
+int32_t tq_xchg_set_peer(tq_xchg* x, int32_t peer_rank, void* region) {
+  TQ_REQUIRE(x != nullptr && region != nullptr, TQ_ERR_INVALID, "null argument");
+  TQ_REQUIRE(peer_rank >= 0 && peer_rank < x->world && peer_rank != x->rank, TQ_ERR_INVALID,
+             "bad peer rank");
+  x->peer[peer_rank] = (float*)region;
+  x->ipc[peer_rank] = false;
+  return TQ_OK;
+}
+
+int32_t tq_xchg_set_wait_limit(tq_xchg* x, int32_t probes) {
+  TQ_REQUIRE(x != nullptr, TQ_ERR_INVALID, "null argument");
+  x->spin_limit = probes > 0 ? (unsigned)probes : TQ_XCHG_SPIN;
+  return TQ_OK;
+}
+
+int32_t tq_xchg_gather_merge(tq_xchg* x, const float* mlo, float* out, int32_t phases,
+                             void* stream) {
+  TQ_REQUIRE(x != nullptr && mlo != nullptr, TQ_ERR_INVALID, "null argument");
+  TQ_REQUIRE(phases >= 1 && phases <= 3, TQ_ERR_INVALID, "phases: 1 publish, 2 wait and merge, 3 both");
+  TQ_REQUIRE(out != nullptr || !(phases & 2), TQ_ERR_INVALID, "out must be a device pointer");
+  for (int p = 0; p < x->world; ++p)
+    TQ_REQUIRE(x->peer[p] != nullptr, TQ_ERR_INVALID, "a peer region is not connected");
+  TQ_CUDA(cudaSetDevice(x->device));
+  XchgArgs a;
+  for (int p = 0; p < TQ_XCHG_MAX_WORLD; ++p) a.peer[p] = p < x->world ? x->peer[p] : nullptr;
+  a.rank = x->rank;
+  a.world = x->world;
+  a.rows = x->rows;
+  a.n_cta = x->n_cta;
+  a.phases = phases;
+  a.flags_off = x->flags_off;
+  a.ctrl_off = x->ctrl_off;
+  a.mlo = mlo;
+  a.out = out;
+  a.spin_limit = x->spin_limit;
+  xchg_kernel<<<x->n_cta, TQ_D, 0, (cudaStream_t)stream>>>(a);
+  TQ_CUDA(cudaGetLastError());
+  return TQ_OK;
+}
+
+int32_t tq_xchg_status(tq_xchg* x, int32_t* status, void* stream) {
+  TQ_REQUIRE(x != nullptr && status != nullptr, TQ_ERR_INVALID, "null argument");
+  TQ_CUDA(cudaSetDevice(x->device));
+  unsigned v = 0;
+  TQ_CUDA(cudaMemcpyAsync(&v, (uint8_t*)x->own + x->ctrl_off + 8, 4, cudaMemcpyDeviceToHost,
+                          (cudaStream_t)stream));
+  TQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  *status = (int32_t)v;
+  return TQ_OK;
+}
+
+}  // extern "C"

@@ -9,11 +9,14 @@ The decode path shards in three ways, two of which need no communication at all:
   head-sharded for the projection that follows).
 * **sequence split** — one long sequence; rank r attends a contiguous range of cold
   blocks, the last rank also attends the hot window.  Each rank produces the
-  un-normalised state ``(m, l, o[D])`` per query head, one ``all_gather`` moves the
-  states into every rank's local memory, and the LSE-combine kernel merges them in rank
-  order (``merge_partials``, ``turboquant_pro/kv_fused.py:139-153``, is associative up
-  to rounding; a fixed order makes the result reproducible).  No kernel reads another
-  GPU's memory.
+  un-normalised state ``(m, l, o[D])`` per query head; the states reach every rank's
+  local memory and are merged there in rank order (``merge_partials``,
+  ``turboquant_pro/kv_fused.py:139-153``, is associative up to rounding; a fixed order makes
+  the result reproducible).  Two transports: :class:`PeerExchange` — one kernel per step
+  that stores the rows into every rank's memory with peer stores over NVLink, signals,
+  waits (bounded) and merges — or, where peer mappings are not to be had, one NCCL
+  ``all_gather`` followed by the LSE-combine kernel.  Both give the same bits.  No kernel
+  reads another GPU's memory; the exchange kernel writes to it.
 
 The reference has no multi-GPU path; this module is new design around its partial-merge
 algebra.
@@ -47,6 +50,122 @@ def gather_states(mlo, group=None):
     out = torch.empty(world * flat.numel(), dtype=mlo.dtype, device=mlo.device)
     dist.all_gather_into_tensor(out, flat, group=group)
     return out.reshape((world,) + tuple(mlo.shape))
+
+
+class PeerExchange:
+    """The (m, l, o) states of a sequence split, exchanged and merged by one kernel per call.
+
+    One object per rank of ``group`` (one process per GPU): the constructor allocates the
+    rank's region through the library, trades CUDA IPC handles with the other ranks
+    (an ``all_gather`` of 64 bytes), maps their regions and ends with a barrier.
+    ``gather_merge(mlo)`` then equals ``lse_combine(gather_states(mlo))`` bit for bit, with no
+    collective call: rows travel as peer stores over NVLink and a rank waits only for the rows
+    it merges.  Every rank must make the same sequence of calls.  A wait that runs out (a rank
+    that never arrives) raises ``RuntimeError`` at the next :meth:`check`.
+    """
+
+    def __init__(self, rows: int, head_dim: int = 128, device=None, group=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+
+        from ._lib import check, load
+
+        self._lib = load()
+        self._check = check
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.rows = int(rows)
+        self.head_dim = int(head_dim)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+            else torch.device(device)
+        # Every rank takes part in every collective call below whether or not its own set-up
+        # succeeded, and all ranks then raise together or none does.
+        self._h = None
+        ok, mine = 1, (C.c_uint8 * 64)()
+        try:
+            h = C.c_void_p()
+            check(self._lib.tq_xchg_create(self.device.index, self.rank, self.world, self.rows,
+                                           self.head_dim, C.byref(h)))
+            self._h = h
+            check(self._lib.tq_xchg_ipc_handle(self._h, mine))
+        except Exception as e:  # noqa: BLE001
+            ok, self._error = 0, repr(e)
+        t = torch.tensor([ok] + list(bytes(mine)), dtype=torch.uint8, device=self.device)
+        allh = torch.empty(self.world * 65, dtype=torch.uint8, device=self.device)
+        dist.all_gather_into_tensor(allh, t, group=group)
+        allh = allh.cpu().numpy().tobytes()
+        ok = int(all(allh[65 * p] == 1 for p in range(self.world)))
+        if ok:
+            try:
+                for p in range(self.world):
+                    if p != self.rank:
+                        buf = (C.c_uint8 * 64).from_buffer_copy(allh[65 * p + 1:65 * p + 65])
+                        check(self._lib.tq_xchg_open_peer(self._h, p, buf))
+            except Exception as e:  # noqa: BLE001
+                ok, self._error = 0, repr(e)
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)  # also the barrier: every
+        # region is zeroed and mapped before the first exchange
+        if int(flag.item()) != 1:
+            if self._h is not None:
+                self._lib.tq_xchg_destroy(self._h)
+                self._h = None
+            raise RuntimeError("peer-memory exchange could not be set up on every rank: "
+                               + getattr(self, "_error", "another rank failed"))
+
+    def gather_merge(self, mlo, out=None, stream=None):
+        """``mlo``: this rank's states ``[rows, 2 + D]`` float32 (CUDA, contiguous).  Returns
+        the merged attention output ``[rows, D]``."""
+        import torch
+
+        if tuple(mlo.shape) != (self.rows, 2 + self.head_dim) or mlo.dtype != torch.float32 \
+                or mlo.device != self.device or not mlo.is_contiguous():
+            raise ValueError(f"expected contiguous float32 states [{self.rows}, "
+                             f"{2 + self.head_dim}] on {self.device}")
+        if out is None:
+            out = torch.empty((self.rows, self.head_dim), dtype=torch.float32, device=self.device)
+        elif tuple(out.shape) != (self.rows, self.head_dim) or out.dtype != torch.float32 \
+                or out.device != self.device or not out.is_contiguous():
+            raise ValueError("bad out tensor")
+        st = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        with torch.cuda.device(self.device):
+            self._check(self._lib.tq_xchg_gather_merge(self._h, mlo.data_ptr(), out.data_ptr(), 3,
+                                                       st))
+        return out
+
+    def set_wait_limit(self, probes: int) -> None:
+        self._check(self._lib.tq_xchg_set_wait_limit(self._h, int(probes)))
+
+    def status(self) -> int:
+        import ctypes as C
+
+        import torch
+
+        v = C.c_int32(0)
+        with torch.cuda.device(self.device):
+            self._check(self._lib.tq_xchg_status(
+                self._h, C.byref(v), torch.cuda.current_stream(self.device).cuda_stream))
+        return v.value
+
+    def check(self) -> None:
+        """Raises if a wait of an earlier exchange ran out (synchronises the stream)."""
+        if self.status() & 1:
+            raise RuntimeError("a rank's attention states did not arrive within the wait limit")
+
+    def close(self) -> None:
+        """Unmaps the peers and frees the region; a collective call (ends with a barrier before
+        the memory goes away)."""
+        import torch
+        import torch.distributed as dist
+
+        if getattr(self, "_h", None) is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+            self._lib.tq_xchg_destroy(self._h)
+            self._h = None
 
 
 def n_cold_blocks(n_tokens: int, hot_window: int) -> int:
@@ -101,6 +220,7 @@ class ShardedSequenceCache:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.n_tokens = [0] * ctx.n_layers      # global length per layer
         self.prefilled = [False] * ctx.n_layers
+        self.exchange = None                    # PeerExchange, see use_peer_exchange()
 
     @staticmethod
     def local_capacity(n_tokens: int, hot_window: int, rank: int, world: int, extra: int = 0):
@@ -147,12 +267,44 @@ class ShardedSequenceCache:
         """One decode step for every sequence: ``[n_seqs, n_q_heads, D]`` on every rank."""
         mlo = self.decode_partial(layer, q)
         rows = mlo.shape[0] * mlo.shape[1]
+        out2 = None if out is None else out.reshape(rows, -1)
+        if self.exchange is not None:
+            res = self.exchange.gather_merge(mlo.reshape(rows, mlo.shape[2]), out=out2)
+            return res.reshape(mlo.shape[0], mlo.shape[1], -1)
         if self.world == 1:
             gathered = mlo.reshape(1, rows, mlo.shape[2])
         else:
             gathered = gather_states(mlo.reshape(rows, mlo.shape[2]), self.group)
-        res = self.ctx.lse_combine(gathered, out=None if out is None else out.reshape(rows, -1))
+        res = self.ctx.lse_combine(gathered, out=out2)
         return res.reshape(mlo.shape[0], mlo.shape[1], -1)
+
+    def use_peer_exchange(self, on: bool = True):
+        """Switches the decode step's transport to :class:`PeerExchange` (a collective call:
+        every rank of the group makes it) or back to the NCCL all-gather.  Returns whether the
+        peer transport is in use afterwards; where peer mappings cannot be set up on some
+        rank, every rank stays on the all-gather."""
+        import torch
+        import torch.distributed as dist
+
+        if self.exchange is not None:
+            self.exchange.close()
+            self.exchange = None
+        if not on or self.world == 1:
+            return False
+        g = self.ctx.geom
+        ok, ex = 1, None
+        try:
+            ex = PeerExchange(g.n_seqs * g.n_q_heads, g.head_dim, self.ctx.device, self.group)
+        except Exception:  # noqa: BLE001  (no peer access between these GPUs / processes)
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.ctx.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 1:
+            self.exchange = ex
+            return True
+        if ex is not None:
+            ex.close()
+        return False
 
 
 class SequenceSplitDecoder:
