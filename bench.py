@@ -599,10 +599,12 @@ def run_headline(args, dst: Dist, cfg, batch_local, global_batch, scaling):
 
 
 def run_e2e(args, dst: Dist, ctx, L, B, H, HQ, D, global_batch):
-    """The same step through the public API with host buffers: per layer the pinned q and new
-    K/V token go to the device, KVContext.append, KVContext.decode, the output comes back.
-    Copies run on a second stream, double-buffered, so that a layer's inputs arrive while the
-    layer before it is attended."""
+    """The same step through the public API with host buffers.  Every step its inputs (the
+    query and the new K/V token of every layer, in pinned host memory) go to the device and
+    its outputs come back: one copy per tensor and step on a second stream, double-buffered
+    over steps, so that a step's inputs arrive while the step before it is attended and its
+    outputs leave while the next one runs.  Per layer the step calls KVContext.append and
+    KVContext.decode on views of the device buffers."""
     import torch
 
     dev = dst.dev
@@ -612,46 +614,55 @@ def run_e2e(args, dst: Dist, ctx, L, B, H, HQ, D, global_batch):
     out_host = torch.empty((L, B, HQ, D), dtype=torch.float32).pin_memory()
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
-    qd = [torch.empty((B, HQ, D), dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    kd = [torch.empty((B, 1, H, D), dtype=torch.float16, device=dev) for _ in range(2)]
-    vd = [torch.empty((B, 1, H, D), dtype=torch.float16, device=dev) for _ in range(2)]
-    od = [torch.empty((B, HQ, D), dtype=torch.float32, device=dev) for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_done = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+    qd = [torch.empty((L, B, HQ, D), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    kd = [torch.empty((L, B, 1, H, D), dtype=torch.float16, device=dev) for _ in range(2)]
+    vd = [torch.empty((L, B, 1, H, D), dtype=torch.float16, device=dev) for _ in range(2)]
+    od = [torch.empty((L, B, HQ, D), dtype=torch.float32, device=dev) for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]    # inputs of buffer b have arrived
+    ev_done = [torch.cuda.Event() for _ in range(2)]  # the step that used buffer b is attended
+    ev_out = [torch.cuda.Event() for _ in range(2)]   # outputs of buffer b have left
+    state = {"step": 0, "fetched": -1}
 
-    def fetch(layer):
-        b = layer & 1
+    def fetch(step):
+        b = step & 1
         with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(ev_done[b])  # the layer that used these buffers is done
-            qd[b].copy_(q_host[layer], non_blocking=True)
-            kd[b].copy_(k_host[layer], non_blocking=True)
-            vd[b].copy_(v_host[layer], non_blocking=True)
+            copy_stream.wait_event(ev_done[b])  # the step that read these buffers is done
+            qd[b].copy_(q_host, non_blocking=True)
+            kd[b].copy_(k_host, non_blocking=True)
+            vd[b].copy_(v_host, non_blocking=True)
             ev_in[b].record(copy_stream)
+        state["fetched"] = step
 
     def e2e_step():
-        fetch(0)
+        step = state["step"]
+        b = step & 1
+        if state["fetched"] < step:
+            fetch(step)
+        main_stream.wait_event(ev_in[b])
+        main_stream.wait_event(ev_out[b])  # this buffer's previous outputs have left
+        fetch(step + 1)                    # the next step's inputs travel under this step
         for layer in range(L):
-            b = layer & 1
-            if layer + 1 < L:
-                fetch(layer + 1)
-            main_stream.wait_event(ev_in[b])
-            main_stream.wait_event(ev_out[b])  # the output buffer has left for the host
-            ctx.append(layer, kd[b], vd[b])
-            ctx.decode(layer, qd[b], out=od[b])
-            ev_done[b].record(main_stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(ev_done[b])
-                out_host[layer].copy_(od[b], non_blocking=True)
-                ev_out[b].record(copy_stream)
+            ctx.append(layer, kd[b][layer], vd[b][layer])
+            ctx.decode(layer, qd[b][layer], out=od[b][layer])
+        ev_done[b].record(main_stream)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ev_done[b])
+            out_host.copy_(od[b], non_blocking=True)
+            ev_out[b].record(copy_stream)
+        state["step"] = step + 1
+
+    def drain():
         main_stream.wait_stream(copy_stream)
+        torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
         e2e_step()
+    drain()
     dst.barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         e2e_step()
+    drain()
     dst.barrier()
     el = dst.max_ms((time.perf_counter() - t0) * 1e3) * 1e-3
     e2e_bytes = sum(ctx.decode_bytes(layer) for layer in range(L))
@@ -660,9 +671,11 @@ def run_e2e(args, dst: Dist, ctx, L, B, H, HQ, D, global_batch):
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(out_host.numel() * 4),
             "ms_per_step": el / args.steps * 1e3,
             "tokens_per_s": dst.world * B / (el / args.steps),
-            "path": "per layer: pinned q + new K/V token H2D, KVContext.append, "
-                    "KVContext.decode, output D2H; copies on a second stream, double-buffered; "
-                    "timed by the host clock around K steps between device synchronisations"}
+            "path": "per step: pinned q + new K/V token of every layer H2D (one copy per "
+                    "tensor), per layer KVContext.append + KVContext.decode, outputs D2H; copies "
+                    "on a second stream, double-buffered over steps: every step sends the next "
+                    "step's inputs, so the timed region holds K input copies, K steps and K "
+                    "output copies; timed by the host clock between device synchronisations"}
 
 
 # ------------------------------------------------------------------------------------ #
