@@ -53,6 +53,11 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 
 __global__ void __launch_bounds__(TQ_D) xchg_kernel(XchgArgs a) {
   const int e = threadIdx.x, c = blockIdx.x;
+  // launched as a programmatic dependent: scheduled while the kernel before it in the stream
+  // (the one that writes the local states) drains, it waits for that kernel here and lets
+  // the kernel after it be scheduled in turn
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   float* own = a.peer[a.rank];
   unsigned* ctrl = (unsigned*)((uint8_t*)own + a.ctrl_off);
   const unsigned ep = *(volatile unsigned*)&ctrl[0] + 1u;
@@ -254,8 +259,16 @@ int32_t tq_xchg_gather_merge(tq_xchg* x, const float* mlo, float* out, int32_t p
   a.mlo = mlo;
   a.out = out;
   a.spin_limit = x->spin_limit;
-  xchg_kernel<<<x->n_cta, TQ_D, 0, (cudaStream_t)stream>>>(a);
-  TQ_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(x->n_cta);
+  cfg.blockDim = dim3(TQ_D);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, xchg_kernel, a));
   return TQ_OK;
 }
 
