@@ -547,7 +547,11 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
   if (warp == 0 && lane < min(NSTAGE, total)) fire(describe(lane, u_iss));  // a lane per tile
   TQ_TRACE_PHASE(4);
   uint8_t* gs = groups + gi * SM::GROUP_BYTES;
-  float* qc = (float*)gs;                                   // [128][G]
+  float* qc = (float*)gs;  // [128][G]; a group of eight as two planes of [128][4]
+  // (a correction's two 16-byte loads of a row then spread over all eight 16-byte bank
+  // groups instead of four)
+  constexpr int QP = G == 8 ? 4 : G;  // heads per plane
+  auto qi = [&](int row, int h) -> int { return G == 8 ? (h >> 2) * (TQ_D * 4) + row * 4 + (h & 3) : row * G + h; };
   uint2* frag = (uint2*)(gs + SM::FRAG_OFF);                // [G/4][8 k-steps][32 lanes]
   float* bias_s = (float*)(gs + SM::BIAS_OFF);              // [8 heads][GW]
   float* corr_w = (float*)(gs + SM::CORR_OFF) + gw * (G * SM::CORR_STRIDE);  // this warp's strip
@@ -792,7 +796,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
             qv[rr] = __bfloat162float(((const __nv_bfloat16*)a.q)[q0 + rr * TQ_D]);
         }
 #pragma unroll
-        for (int rr = 0; rr < G; ++rr) qc[q_row(gtid) * G + rr] = a.scale_log2 * qv[rr];
+        for (int rr = 0; rr < G; ++rr) qc[qi(q_row(gtid), rr)] = a.scale_log2 * qv[rr];
       }
       group_sync();
     }
@@ -829,10 +833,10 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           const int hb = 4 * nh + (r >> 1);
           float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
           if (hb < G) {
-            q4.x = qc[q_row(natural ? dn : d0 + 0) * G + hb];
-            q4.y = qc[q_row(natural ? dn + 1 : d0 + 1) * G + hb];
-            q4.z = qc[q_row(natural ? dn + 8 : d0 + 2) * G + hb];
-            q4.w = qc[q_row(natural ? dn + 9 : d0 + 3) * G + hb];
+            q4.x = qc[qi(q_row(natural ? dn : d0 + 0), hb)];
+            q4.y = qc[qi(q_row(natural ? dn + 1 : d0 + 1), hb)];
+            q4.z = qc[qi(q_row(natural ? dn + 8 : d0 + 2), hb)];
+            q4.w = qc[qi(q_row(natural ? dn + 9 : d0 + 3), hb)];
           }
           bias[nh] += q4.x * m4.x + q4.y * m4.y + q4.z * m4.z + q4.w * m4.w;
           const uint4 f = frag_hilo(q4.x * s4.x, q4.y * s4.y, q4.z * s4.z, q4.w * s4.w);
@@ -868,11 +872,11 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 #pragma unroll
           for (int i = 0; i < NI; ++i) {
             const float delta = __half2float(__ushort_as_half(ell_d[j * 256 + 32 * i]));
-            const float* qrow = qc + (int)ell_c[j * 256 + 32 * i] * G;
+            const float* qrow = qc + (int)ell_c[j * 256 + 32 * i] * QP;
             if (G >= 4) {
 #pragma unroll
               for (int g4 = 0; g4 < G / 4; ++g4) {
-                const float4 qv = *(const float4*)(qrow + 4 * g4);
+                const float4 qv = *(const float4*)(qrow + (G == 8 ? g4 * (TQ_D * 4) : 4 * g4));
                 cacc[i][4 * g4 + 0] += qv.x * delta;
                 cacc[i][4 * g4 + 1] += qv.y * delta;
                 cacc[i][4 * g4 + 2] += qv.z * delta;
@@ -896,7 +900,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
         for (int j = 0; j < TQ_WIDE; ++j) {
           const int wch = hdr->wide[j];
           const float sc = scale[wch];
-          const float* qrow = qc + q_row(wch) * G;
+          const float* qrow = qc + q_row(wch) * QP;
           float dl[NI];
 #pragma unroll
           for (int i = 0; i < NI; ++i) dl[i] = dtab[(sd[i] >> (4 * j)) & 15u] * sc;
@@ -904,7 +908,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           if (G >= 4) {
 #pragma unroll
             for (int g4 = 0; g4 < G / 4; ++g4) {
-              const float4 q4 = *(const float4*)(qrow + 4 * g4);
+              const float4 q4 = *(const float4*)(qrow + (G == 8 ? g4 * (TQ_D * 4) : 4 * g4));
               qv[4 * g4] = q4.x; qv[4 * g4 + 1] = q4.y; qv[4 * g4 + 2] = q4.z; qv[4 * g4 + 3] = q4.w;
             }
           } else {
@@ -943,12 +947,12 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
           const bool mine = valid && tok / TPW == gw;
           const float delta =
               mine ? __half2float(__ushort_as_half((unsigned short)(wv & 0xffffu))) : 0.0f;
-          const float* qrow = qc + q_row((wv >> 16) & 127) * G;
+          const float* qrow = qc + q_row((wv >> 16) & 127) * QP;
           float pv[G];
           if (G >= 4) {
 #pragma unroll
             for (int g4 = 0; g4 < G / 4; ++g4) {
-              const float4 qv = *(const float4*)(qrow + 4 * g4);
+              const float4 qv = *(const float4*)(qrow + (G == 8 ? g4 * (TQ_D * 4) : 4 * g4));
               pv[4 * g4] = qv.x * delta; pv[4 * g4 + 1] = qv.y * delta;
               pv[4 * g4 + 2] = qv.z * delta; pv[4 * g4 + 3] = qv.w * delta;
             }
