@@ -848,6 +848,30 @@ def run_cfg2(args, dst: Dist):
                             "same_bits_as_all_gather": True}
             if p_ms < ms:
                 ms_eager, ms, graphed, transport = p_eager, p_ms, p_graphed, "peer"
+            # ... and with the exchange run by the merge kernel of the partial decode itself
+            # (one kernel less on the critical path)
+            def step_fused():
+                for layer in range(L):
+                    ctx.decode_exchange(layer, q_all[layer], 0, nb_local[layer], last, ex,
+                                        out=out[layer].view(1, rows, 128))
+
+            fused_ok = True
+            try:
+                step_fused()
+                torch.cuda.synchronize()
+            except NotImplementedError:
+                fused_ok = False
+            if dst.all_ok(fused_ok):
+                same = bool(torch.equal(out, want)) and ex.status() == 0
+                if not dst.all_ok(same):
+                    raise SystemExit("config 2 check failed: the merge kernel's own exchange and "
+                                     "the all-gather path give different bits")
+                f_eager, f_ms, f_graphed = run_transport(step_fused)
+                ex.check()
+                peer_numbers["fused"] = {"ms_per_step": f_ms, "ms_per_step_eager": f_eager,
+                                         "cuda_graph": f_graphed, "same_bits_as_all_gather": True}
+                if f_ms < ms:
+                    ms_eager, ms, graphed, transport = f_eager, f_ms, f_graphed, "peer-fused"
         if ex is not None:
             ex.close()
     # the collective alone, same sizes, same stream
@@ -897,8 +921,12 @@ def run_cfg2(args, dst: Dist):
         "check": {"split_equals_whole": True, "max_abs_err": err,
                   "what": "9000-token layer, sharded caches + all-gather + merge vs the same "
                           "layer held whole on every rank"},
-        "collective": ("one exchange kernel per layer: peer stores of [32][130] float32 into every "
-                       "rank's region over NVLink, per-row-group flags, bounded wait, merge in "
+        "collective": ("none: the kernel that merges the rank's own partials stores its [32][130] "
+                       "float32 rows into every rank's region over NVLink, signals per row, waits "
+                       "(bounded) and merges in rank order (tq_decode_exchange)"
+                       if transport == "peer-fused" else
+                       "one exchange kernel per layer: peer stores of [32][130] float32 into every "
+                       "rank's region over NVLink, per-row flags, bounded wait, merge in "
                        "rank order (tq_xchg_gather_merge)" if transport == "peer" else
                        "NCCL all_gather_into_tensor of [32][130] float32 per layer, ordered with "
                        "the decode stream, then tq_lse_combine in rank order")

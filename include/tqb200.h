@@ -219,6 +219,16 @@ int32_t tq_xchg_set_peer(tq_xchg* x, int32_t peer_rank, void* region);
  * the affected rows of `out` are zero; the call itself still returns TQ_OK. */
 int32_t tq_xchg_gather_merge(tq_xchg* x, const float* mlo, float* out, int32_t phases,
                              void* stream);
+/* tq_decode_partial and tq_xchg_gather_merge in one call, with one kernel less on the critical
+ * path: the kernel that merges the rank's own partials publishes its rows to the other ranks
+ * and merges theirs itself.  `out` is the final [n_seqs][n_q_heads][D] float32 output, the
+ * same bits as the two-call form.  `phases`: 3 (the normal call) or 1 (publish only; follow
+ * with tq_xchg_gather_merge(..., phases = 2), see there).  Returns TQ_ERR_UNSUPPORTED where the
+ * layer is not served by one launch of the tensor-core kernel or `xchg` was created for another
+ * row count; the two-call form works everywhere. */
+int32_t tq_decode_exchange(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype,
+                           int32_t block_begin, int32_t block_end, int32_t with_hot, tq_xchg* xchg,
+                           float* out, int32_t phases, void* stream);
 /* Probes a wait makes before it gives up (each takes 0.1 us or more); 0 restores the default
  * (about half a second). */
 int32_t tq_xchg_set_wait_limit(tq_xchg* x, int32_t probes);

@@ -150,3 +150,82 @@ def test_bad_arguments_are_refused(torch_cuda):
         assert lib.tq_xchg_region_bytes(x) >= 2 * 2 * 8 * 130 * 4
     finally:
         lib.tq_xchg_destroy(x)
+
+
+def test_merge_kernel_that_runs_the_exchange_itself(torch_cuda):
+    """Two ranks of a sequence split emulated on one GPU: the same 3 000-token sequence in two
+    contexts, each attending its half of the cold blocks (the second also the hot window).
+    Both publish through the merge kernel of their partial decode (phase 1), then both wait and
+    merge (phase 2).  The result equals the two-call form bit for bit and the whole decode
+    within the merge's rounding."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200._lib import check, load
+    from turboquant_pro_b200.parallel import split_blocks
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    lib = load()
+    st = torch.cuda.current_stream().cuda_stream
+    h, grp, n = 2, 4, 3000
+    rows = h * grp
+    k, v = make_kv(9, h, n, dtype=np.float16)
+    q = torch.from_numpy(make_q(9, rows))[None].cuda().to(torch.bfloat16)
+    ctxs = []
+    for _ in range(2):
+        c = KVContext(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=rows, value_bits=3,
+                      hot_window=512, max_tokens_per_seq=n, kv_dtype="float16", seed=9)
+        c.append(0, torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda())
+        ctxs.append(c)
+    whole = ctxs[0].decode(0, q)
+    nb = ctxs[0].lengths(0, 0)[1] // 256
+    xs = [_make(lib, r, 2, rows) for r in range(2)]
+    try:
+        check(lib.tq_xchg_set_peer(xs[0], 1, lib.tq_xchg_base(xs[1])))
+        check(lib.tq_xchg_set_peer(xs[1], 0, lib.tq_xchg_base(xs[0])))
+        for it in range(3):
+            shares = [split_blocks(nb, r, 2) for r in range(2)]
+            mlo = [ctxs[r].decode_partial(0, q, *shares[r]).reshape(rows, 2 + D).contiguous()
+                   for r in range(2)]
+            want = torch.empty((rows, D), device="cuda")
+            both = torch.stack(mlo).contiguous()
+            check(lib.tq_lse_combine(both.data_ptr(), 2, rows, D, want.data_ptr(), st))
+            out = [torch.full((rows, D), 7.0, device="cuda") for _ in range(2)]
+            for r in range(2):
+                ctxs[r].decode_exchange(0, q, *shares[r], xs[r], phases=1)
+            for r in range(2):
+                check(lib.tq_xchg_gather_merge(xs[r], mlo[r].data_ptr(), out[r].data_ptr(), 2, st))
+            torch.cuda.synchronize()
+            for r in range(2):
+                assert torch.equal(out[r], want), (it, r)
+                assert ctxs[r].last_kernel() == "tensor-core" and ctxs[r].status() == 0
+            assert torch.allclose(want.reshape(whole.shape), whole, rtol=1e-3, atol=1e-4)
+    finally:
+        torch.cuda.synchronize()
+        for x in xs:
+            lib.tq_xchg_destroy(x)
+
+
+def test_one_rank_fused_exchange_equals_decode(torch_cuda):
+    """World size 1: the fused call is a plain decode through the exchange path."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import KVContext
+    from turboquant_pro_b200._lib import load
+    from turboquant_pro_b200.synth import make_kv, make_q
+
+    lib = load()
+    h, grp, n = 2, 8, 1500
+    rows = h * grp
+    k, v = make_kv(4, h, n, dtype=np.float16)
+    q = torch.from_numpy(make_q(4, rows))[None].cuda()
+    c = KVContext(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=rows, value_bits=4,
+                  hot_window=512, max_tokens_per_seq=n, kv_dtype="float16", seed=4)
+    c.append(0, torch.from_numpy(k)[None].cuda(), torch.from_numpy(v)[None].cuda())
+    whole = c.decode(0, q)
+    x = _make(lib, 0, 1, rows)
+    try:
+        for _ in range(3):
+            got = c.decode_exchange(0, q, 0, 1 << 20, True, x)
+            torch.cuda.synchronize()
+            assert torch.allclose(got, whole, rtol=1e-5, atol=1e-6)
+    finally:
+        lib.tq_xchg_destroy(x)

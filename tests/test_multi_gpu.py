@@ -51,8 +51,10 @@ for it in range(4):
     mlo = ctx.decode_partial(0, q, lo, hi, with_hot).reshape(h * grp, 130).contiguous()
     via_nccl = ctx.lse_combine(gather_states(mlo))
     via_peer = ex.gather_merge(mlo)
+    fused = ctx.decode_exchange(0, q, lo, hi, with_hot, ex).reshape(h * grp, 128)
     torch.cuda.synchronize()
-    ok = ok and torch.equal(via_peer, via_nccl) and ex.status() == 0
+    ok = ok and torch.equal(via_peer, via_nccl) and torch.equal(fused, via_nccl) \
+        and ex.status() == 0
 ex.close()
 flag = torch.tensor([1 if ok else 0], device="cuda")
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)

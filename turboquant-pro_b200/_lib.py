@@ -84,6 +84,9 @@ SIGNATURES = {
     "tq_xchg_set_peer": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
     "tq_xchg_gather_merge": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                          C.c_void_p]),
+    "tq_decode_exchange": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
+                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
+                                       C.c_void_p]),
     "tq_xchg_set_wait_limit": (C.c_int32, [C.c_void_p, C.c_int32]),
     "tq_xchg_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
     "tq_dequant_range": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

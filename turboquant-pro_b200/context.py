@@ -287,6 +287,26 @@ class KVContext:
                                               mlo.data_ptr(), self._stream()))
         return mlo
 
+    def decode_exchange(self, layer: int, q, block_begin: int, block_end: int, with_hot: bool,
+                        exchange, out=None, phases: int = 3):
+        """``decode_partial`` over this rank's blocks and the exchange + merge of the states
+        with the other ranks (``exchange``: a :class:`~turboquant_pro_b200.parallel.PeerExchange`
+        or its raw handle) in one call: the kernel that merges the rank's own partials hands its
+        rows to the other ranks and merges theirs.  Returns the final ``[n_seqs, n_q_heads, D]``
+        output.  Raises ``NotImplementedError`` where the layer has no such fused form; the
+        two-call form (``decode_partial`` then ``PeerExchange.gather_merge``) works everywhere
+        and gives the same bits."""
+        torch = _torch()
+        g = self.geom
+        q = self._check_q(q)
+        out = self._check_result(out, (g.n_seqs, g.n_q_heads, g.head_dim), "out")
+        h = getattr(exchange, "_h", exchange)
+        with torch.cuda.device(self.device):
+            check(self._lib.tq_decode_exchange(self._h, layer, q.data_ptr(), _dtype_code(q.dtype),
+                                               block_begin, block_end, int(bool(with_hot)), h,
+                                               out.data_ptr(), phases, self._stream()))
+        return out
+
     def lse_combine(self, mlo, out=None):
         """Merge gathered states ``[n_parts, n_rows, 2 + D]`` into ``[n_rows, D]``."""
         torch = _torch()

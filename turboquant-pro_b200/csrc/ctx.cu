@@ -52,6 +52,11 @@ static bool good_ctx(const tq_ctx* c, int layer) {
   return c != nullptr && layer >= 0 && layer < c->g.n_layers;
 }
 
+struct tq_xchg;
+int tq_launch_decode_exchange(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
+                              int block_end, int with_hot, float* out, const tq_xchg* xchg,
+                              int phases, cudaStream_t st, bool* handled);
+
 extern "C" {
 
 int32_t tq_version(void) { return TQ_VERSION; }
@@ -349,6 +354,29 @@ int32_t tq_decode_partial(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_d
   ctx->last_q_dtype = q_dtype;
   return tq_launch_decode(ctx, layer, q, q_dtype, block_begin, block_end, with_hot ? 1 : 0,
                           nullptr, mlo, (cudaStream_t)stream);
+}
+
+int32_t tq_decode_exchange(tq_ctx* ctx, int32_t layer, const void* q, int32_t q_dtype,
+                           int32_t block_begin, int32_t block_end, int32_t with_hot, tq_xchg* xchg,
+                           float* out, int32_t phases, void* stream) {
+  TQ_REQUIRE(good_ctx(ctx, layer), TQ_ERR_INVALID, "bad context or layer");
+  TQ_REQUIRE(q != nullptr && xchg != nullptr, TQ_ERR_INVALID, "q and xchg must not be null");
+  TQ_REQUIRE(q_dtype == TQ_F32 || q_dtype == TQ_F16 || q_dtype == TQ_BF16, TQ_ERR_INVALID,
+             "bad q_dtype");
+  TQ_REQUIRE(block_begin >= 0 && block_end >= block_begin, TQ_ERR_INVALID, "bad block range");
+  TQ_REQUIRE(phases == 1 || phases == 3, TQ_ERR_INVALID,
+             "phases: 3 publish, wait and merge; 1 publish only (then tq_xchg_gather_merge with 2)");
+  TQ_REQUIRE(out != nullptr || phases == 1, TQ_ERR_INVALID, "out must be a device pointer");
+  TQ_CUDA(cudaSetDevice(ctx->device));
+  ctx->last_q_dtype = q_dtype;
+  bool handled = false;
+  int rc = tq_launch_decode_exchange(ctx, layer, q, q_dtype, block_begin, block_end,
+                                     with_hot ? 1 : 0, out, xchg, phases, (cudaStream_t)stream,
+                                     &handled);
+  if (rc != TQ_OK) return rc;
+  TQ_REQUIRE(handled, TQ_ERR_UNSUPPORTED,
+             "this geometry has no fused exchange: use tq_decode_partial + tq_xchg_gather_merge");
+  return TQ_OK;
 }
 
 int32_t tq_lse_combine(const float* mlo, int32_t n_parts, int32_t n_rows, int32_t head_dim,

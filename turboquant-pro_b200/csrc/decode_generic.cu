@@ -461,16 +461,26 @@ void launch_generic(const DecodeArgs& a, int n_units, cudaStream_t st) {
 
 }  // namespace
 
+struct tq_xchg;
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
                          int block_end, int with_hot, float* out, float* mlo, cudaStream_t st,
-                         bool* handled);
+                         bool* handled, const tq_xchg* xchg, int xchg_phases);
+
+// Sequence-split decode whose merge kernel runs the exchange itself (tensor-core kernel, one
+// launch per layer); `handled` tells whether that form was available.
+int tq_launch_decode_exchange(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
+                              int block_end, int with_hot, float* out, const tq_xchg* xchg,
+                              int phases, cudaStream_t st, bool* handled) {
+  return tq_launch_decode_mma(ctx, layer, q, q_dtype, block_begin, block_end, with_hot, out,
+                              nullptr, st, handled, xchg, phases);
+}
 
 int tq_launch_decode(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
                      int block_end, int with_hot, float* out, float* mlo, cudaStream_t st) {
   const tq_geom& g = ctx->g;
   bool handled = false;
   int rc = tq_launch_decode_mma(ctx, layer, q, q_dtype, block_begin, block_end, with_hot, out,
-                                mlo, st, &handled);
+                                mlo, st, &handled, nullptr, 0);
   if (rc != TQ_OK || handled) return rc;
 
   DecodeArgs a;

@@ -34,6 +34,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "xchg.cuh"
 
 namespace {
 
@@ -75,6 +76,10 @@ struct MmaArgs {
   int spin_limit;     // probes a bounded wait makes before it gives up
   int withhold_tile;  // test hook: CTA 0 never starts the copy of this tile of its share (-1: off)
   float scale_log2;
+  // Sequence split over several GPUs: the merge kernel hands its rows to the other ranks and
+  // merges theirs itself (xchg_on), instead of writing the states for a separate exchange.
+  int xchg_on;
+  XchgDev xchg;
 };
 
 // ---- PTX helpers --------------------------------------------------------------------------
@@ -1276,7 +1281,7 @@ __global__ void __launch_bounds__(Cfg<G, VB>::THREADS, 1)
 // layer has many units, one where it has few and the merge is on the critical path.
 template <int G, int GH>
 __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
-  constexpr int RP = GH >= 8 ? 8 : (GH >= 4 ? 16 : 32);  // partials per round
+  constexpr int RP = GH >= 8 ? 8 : (GH >= 4 ? 16 : (GH >= 2 ? 32 : 64));  // partials per round
   const int g0 = blockIdx.y * GH;  // first head of this CTA
   const tq_geom& g = a.g;
   const int unit = blockIdx.x, e = threadIdx.x, lane = e & 31, wid = e >> 5;
@@ -1295,14 +1300,14 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   for (int d = 0; d < TQ_D; ++d) pcol[d] = a.tables->pi[d * TQ_D + e];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // the plan: all of it requested at once (one round trip to global memory), the shares then
+  // searched in shared memory
   const int n_cta = a.plan_g[0];
-  // first tile of every CTA's share, and the end of the last one (one round trip to global
-  // memory, then searched in shared memory)
-  __shared__ int share[200];
-  for (int i = e; i <= n_cta; i += TQ_D) share[i] = a.plan_g[3 + 2 * a.n_units + i];
-  __syncthreads();
   const int p0 = a.plan_g[2 + unit], p1 = a.plan_g[3 + unit];
   const int pc = p0 + a.plan_g[3 + a.n_units + unit];
+  __shared__ int share[200];
+  for (int i = e; i <= a.n_cta; i += TQ_D) share[i] = a.plan_g[3 + 2 * a.n_units + i];
+  __syncthreads();
   const int NG = a.n_groups;
   // the CTAs whose shares meet the unit's tiles [p0, p1): i0 = the last one that starts at or
   // before p0, i1 = the last one that starts before p1
@@ -1384,20 +1389,40 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
         s_l[j][gg] = pp[1];
       }
       __syncthreads();
-      if (e < GH) {
-        float M = s_M[e];
-        for (int j = 0; j < nr; ++j)
-          if (s_l[j][e] > 0.0f) M = fmaxf(M, s_m[j][e]);
-        const float sc = exp2f(s_M[e] - M);
-        float L = s_L[e] * sc;
-        for (int j = 0; j < nr; ++j) {
-          const float wgt = s_l[j][e] > 0.0f ? exp2f(s_m[j][e] - M) : 0.0f;
-          L += s_l[j][e] * wgt;
-          s_wgt[j][e] = wgt;
+      // the round's maxima and sums: a warp per head, a lane per partial (two where a round
+      // holds 64), reduced in a fixed tree, so the result does not depend on timing
+      for (int gg = wid; gg < GH; gg += TQ_D / 32) {
+        constexpr int PL = (RP + 31) / 32;  // partials per lane
+        float mj[PL], lj[PL];
+        float mx = s_M[gg];
+#pragma unroll
+        for (int k = 0; k < PL; ++k) {
+          const int j = lane + 32 * k;
+          const bool live = j < nr && j < RP;
+          lj[k] = live ? s_l[j < RP ? j : 0][gg] : 0.0f;
+          mj[k] = live ? s_m[j < RP ? j : 0][gg] : NEG_BIG;
+          if (lj[k] > 0.0f) mx = fmaxf(mx, mj[k]);
         }
-        s_scale[e] = sc;
-        s_M[e] = M;
-        s_L[e] = L;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float ls = 0.0f;
+#pragma unroll
+        for (int k = 0; k < PL; ++k) {
+          const int j = lane + 32 * k;
+          const float wgt = lj[k] > 0.0f ? exp2f(mj[k] - mx) : 0.0f;
+          if (j < RP) s_wgt[j][gg] = wgt;
+          ls += lj[k] * wgt;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+        const float old_m = s_M[gg], old_l = s_L[gg];
+        __syncwarp();
+        if (lane == 0) {
+          const float sc = exp2f(old_m - mx);
+          s_scale[gg] = sc;
+          s_M[gg] = mx;
+          s_L[gg] = old_l * sc + ls;
+        }
       }
       __syncthreads();
 #pragma unroll
@@ -1430,6 +1455,50 @@ __global__ void __launch_bounds__(TQ_D) combine_mma_kernel(MmaArgs a) {
   for (int d = 0; d < TQ_D; ++d) {
 #pragma unroll
     for (int gg = 0; gg < GH; ++gg) o[gg] += cs[gg][d] * pcol[d];
+  }
+  if (a.xchg_on) {
+    // Publish this CTA's rows to every rank (peer stores), signal them, then wait for the same
+    // rows of the other ranks and merge in rank order; the last CTA of the grid closes the
+    // exchange.
+    const XchgDev& x = a.xchg;
+    const int row0 = seq * g.n_q_heads + head * G + g0;
+    const unsigned ep = xchg_epoch(x);
+    const int slot = (int)(ep & 1u);
+    if (x.phases & 1) {
+#pragma unroll
+      for (int gg = 0; gg < GH; ++gg) {
+        const float val = o[gg] + Hh[gg];
+        const float L = s_L[gg];
+        const float m_nat = L > 0.0f ? s_M[gg] * 0.6931471805599453f : -INFINITY;
+        for (int p = 0; p < x.world; ++p) {
+          float* dst = xchg_row(x, p, slot, x.rank, row0 + gg);
+          if (e == 0) {
+            dst[0] = m_nat;
+            dst[1] = L;
+          }
+          dst[2 + e] = val;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int gg = 0; gg < GH; ++gg) xchg_signal(x, e, slot, row0 + gg, ep);
+    }
+    if (x.phases & 2) {
+      __shared__ int s_fail;
+      if (e == 0) s_fail = 0;
+      __syncthreads();
+#pragma unroll
+      for (int gg = 0; gg < GH; ++gg)
+        if (!xchg_wait(x, e, slot, row0 + gg, ep)) s_fail = 1;
+      __syncthreads();
+      const bool fail = s_fail != 0;
+#pragma unroll
+      for (int gg = 0; gg < GH; ++gg)
+        a.out[(size_t)(row0 + gg) * TQ_D + e] = fail ? 0.0f : xchg_merge_row(x, slot, row0 + gg, e);
+      __syncthreads();
+      if (e == 0) xchg_close(x, gridDim.x * gridDim.y, ep);
+    }
+    return;
   }
 #pragma unroll
   for (int gg = 0; gg < GH; ++gg) {
@@ -1563,7 +1632,7 @@ size_t tq_mma_scratch_bytes(const tq_geom& g, size_t units) {
 
 int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int block_begin,
                          int block_end, int with_hot, float* out, float* mlo, cudaStream_t st,
-                         bool* handled) {
+                         bool* handled, const tq_xchg* xchg, int xchg_phases) {
   const tq_geom& g = ctx->g;
   *handled = false;
   const int n_units = g.n_seqs * g.n_kv_heads;
@@ -1599,6 +1668,14 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   a.withhold_tile = ctx->withhold_tile;
   if (ctx->tmap_state == 0) build_hot_tensor_maps(ctx);
   a.use_tmap = ctx->tmap_state == 1 ? 1 : 0;
+  a.xchg_on = 0;
+  if (xchg != nullptr) {
+    // (one launch must cover the layer: the exchange is closed by the last CTA of one grid)
+    if (n_units > chunk_units(g) || xchg->rows != g.n_seqs * g.n_q_heads) return TQ_OK;
+    TQ_REQUIRE(tq_xchg_view(xchg, xchg_phases, &a.xchg), TQ_ERR_INVALID,
+               "a peer region is not connected");
+    a.xchg_on = 1;
+  }
   *handled = true;
   ctx->last_launches = 0;
   ctx->last_kernel = TQ_KERNEL_TENSOR_CORE;

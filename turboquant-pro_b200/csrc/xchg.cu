@@ -6,16 +6,18 @@
 // the other ranks (CUDA IPC between processes, plain pointers inside one process):
 //
 //   gather  [2 slots][world][rows][2 + D] float32   the states as written by their owners
-//   flags   [2 slots][world][TQ_XCHG_CTAS] uint32    "rank r's CTA c has written exchange e"
+//   flags   [2 slots][world][rows] uint32           "rank r has written row i of exchange e"
 //   ctrl    epoch, CTA counter, status
 //
-// Exchange number e (1, 2, ...) uses slot e & 1.  CTA c of a rank owns rows c, c + n_cta, ...:
+// Exchange number e (1, 2, ...) uses slot e & 1.  CTA c of a rank owns rows c, c + n_cta, ...
+// (the merge kernel of the tensor-core decode, which can run the exchange itself, owns the rows
+// of its unit); flags are per row, so the two forms can be mixed:
 // it stores its rows of the local states into slot e & 1 of every rank's gather area with
-// plain peer stores over NVLink, fences at system scope and writes e into its flag on every
-// rank; then it waits until the flags of all ranks' CTA c show e in its own region and merges
-// the rows in rank order (the arithmetic of merge_partials, kv_fused.py:139-153, as in
-// lse_combine_kernel).  A CTA depends only on the same CTA of the other ranks, so nothing
-// waits on a whole grid.  Two slots suffice: a rank can start exchange e + 1 only after its
+// plain peer stores over NVLink and writes e into the rows' flags on every rank with a
+// system-scope release store; then it waits until the flags of its rows from all ranks show e
+// in its own region and merges the rows in rank order (the arithmetic of merge_partials, kv_fused.py:139-153, as in
+// lse_combine_kernel).  A CTA depends only on the rows it merges, so nothing waits on a whole
+// grid.  Two slots suffice: a rank can start exchange e + 1 only after its
 // own exchange e is complete, which needed every other rank's flag for e, which that rank
 // wrote after its exchange e - 1 had completed (stream order), so nobody still reads the slot
 // that exchange e + 1 overwrites.
@@ -25,129 +27,79 @@
 // loads and stores on peer memory.
 #include <cstring>
 
-#include "common.cuh"
+#include "xchg.cuh"
 
 namespace {
 
-constexpr int TQ_XCHG_CTAS = 32;       // most CTAs (row groups) of the exchange kernel
-constexpr int TQ_XCHG_MAX_WORLD = 16;  // most ranks
+constexpr int TQ_XCHG_CTAS = 32;             // most CTAs (row groups) of the exchange kernel
 constexpr unsigned TQ_XCHG_SPIN = 1u << 22;  // default probes per wait (each takes 0.1 us or more)
 
 struct XchgArgs {
-  float* peer[TQ_XCHG_MAX_WORLD];  // every rank's region (own included)
-  int rank, world, rows, n_cta, phases;
-  size_t flags_off, ctrl_off;      // byte offsets inside a region
-  const float* mlo;                // [rows][2 + D] local states
-  float* out;                      // [rows][D]
-  unsigned spin_limit;
+  XchgDev x;
+  int n_cta;
+  const float* mlo;  // [rows][2 + D] local states
+  float* out;        // [rows][D]
 };
-
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
 __global__ void __launch_bounds__(TQ_D) xchg_kernel(XchgArgs a) {
   const int e = threadIdx.x, c = blockIdx.x;
+  const XchgDev& x = a.x;
   // launched as a programmatic dependent: scheduled while the kernel before it in the stream
   // (the one that writes the local states) drains, it waits for that kernel here and lets
   // the kernel after it be scheduled in turn
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  float* own = a.peer[a.rank];
-  unsigned* ctrl = (unsigned*)((uint8_t*)own + a.ctrl_off);
-  const unsigned ep = *(volatile unsigned*)&ctrl[0] + 1u;
+  const unsigned ep = xchg_epoch(x);
   const int slot = (int)(ep & 1u);
-  const size_t part = (size_t)a.rows * TQ_PART_STRIDE;  // floats of one rank's states
 
-  if (a.phases & 1) {
-    for (int row = c; row < a.rows; row += a.n_cta) {
+  if (x.phases & 1) {
+    for (int row = c; row < x.rows; row += a.n_cta) {
       const float* src = a.mlo + (size_t)row * TQ_PART_STRIDE;
       const float v0 = src[e];
       const float v1 = e < 2 ? src[TQ_D + e] : 0.0f;
-      for (int p = 0; p < a.world; ++p) {
-        float* dst = a.peer[p] + ((size_t)slot * a.world + a.rank) * part +
-                     (size_t)row * TQ_PART_STRIDE;
+      for (int p = 0; p < x.world; ++p) {
+        float* dst = xchg_row(x, p, slot, x.rank, row);
         dst[e] = v0;
         if (e < 2) dst[TQ_D + e] = v1;
       }
     }
-    __syncthreads();  // the CTA's stores are ordered before the flags of thread e below
-    if (e < a.world) {
-      // (the release store orders the CTA's row stores, which the barrier made this thread's
-      // predecessors, before the flag at system scope)
-      unsigned* flag = (unsigned*)((uint8_t*)a.peer[e] + a.flags_off) +
-                       ((size_t)slot * a.world + a.rank) * TQ_XCHG_CTAS + c;
-      st_release_sys(flag, ep);
-    }
+    __syncthreads();
+    for (int row = c; row < x.rows; row += a.n_cta) xchg_signal(x, e, slot, row, ep);
   }
-  if (a.phases & 2) {
+  if (x.phases & 2) {
     __shared__ int s_fail;
     if (e == 0) s_fail = 0;
     __syncthreads();
-    if (e < a.world) {
-      const unsigned* flag = (const unsigned*)((const uint8_t*)own + a.flags_off) +
-                             ((size_t)slot * a.world + e) * TQ_XCHG_CTAS + c;
-      unsigned n = 0;
-      // (flags only grow; the signed difference keeps the test right across a wrap)
-      while ((int)(ld_acquire_sys(flag) - ep) < 0) {
-        if (++n >= a.spin_limit) {
-          s_fail = 1;
-          atomicOr(&ctrl[2], 1u);
-          break;
-        }
-        __nanosleep(32);
+    for (int row = c; row < x.rows; row += a.n_cta)
+      if (!xchg_wait(x, e, slot, row, ep)) {
+        s_fail = 1;
+        break;
       }
-    }
     __syncthreads();
     const bool fail = s_fail != 0;
-    const float* gat = own + (size_t)slot * a.world * part;
-    for (int row = c; row < a.rows; row += a.n_cta) {
-      float res = 0.0f;
-      if (!fail) {
-        // (read past the first-level cache: the rows were written by other GPUs)
-        float M = -INFINITY;
-        for (int p = 0; p < a.world; ++p)
-          M = fmaxf(M, __ldcg(&gat[(size_t)p * part + (size_t)row * TQ_PART_STRIDE]));
-        float L = 0.0f, A = 0.0f;
-        for (int p = 0; p < a.world; ++p) {
-          const float* r = gat + (size_t)p * part + (size_t)row * TQ_PART_STRIDE;
-          const float m = __ldcg(&r[0]);
-          const float w = m > -INFINITY ? __expf(m - M) : 0.0f;
-          L += __ldcg(&r[1]) * w;
-          A += __ldcg(&r[2 + e]) * w;
-        }
-        res = L > 0.0f ? A / L : 0.0f;
-      }
-      a.out[(size_t)row * TQ_D + e] = res;
-    }
-    // the last CTA out closes the exchange
+    for (int row = c; row < x.rows; row += a.n_cta)
+      a.out[(size_t)row * TQ_D + e] = fail ? 0.0f : xchg_merge_row(x, slot, row, e);
     __syncthreads();
-    if (e == 0) {
-      __threadfence();
-      const unsigned prev = atomicAdd(&ctrl[1], 1u);
-      if (prev == (unsigned)a.n_cta - 1u) {
-        ctrl[1] = 0u;
-        *(volatile unsigned*)&ctrl[0] = ep;
-      }
-    }
+    if (e == 0) xchg_close(x, (unsigned)a.n_cta, ep);
   }
 }
 
 }  // namespace
 
-struct tq_xchg {
-  int device, rank, world, rows, n_cta;
-  size_t bytes, flags_off, ctrl_off;
-  float* own;
-  float* peer[TQ_XCHG_MAX_WORLD];
-  bool ipc[TQ_XCHG_MAX_WORLD];
-  unsigned spin_limit;
-};
+bool tq_xchg_view(const tq_xchg* x, int phases, XchgDev* out) {
+  for (int p = 0; p < TQ_XCHG_MAX_WORLD; ++p) {
+    out->peer[p] = p < x->world ? x->peer[p] : nullptr;
+    if (p < x->world && x->peer[p] == nullptr) return false;
+  }
+  out->rank = x->rank;
+  out->world = x->world;
+  out->rows = x->rows;
+  out->phases = phases;
+  out->flags_off = x->flags_off;
+  out->ctrl_off = x->ctrl_off;
+  out->spin_limit = x->spin_limit;
+  return true;
+}
 
 extern "C" {
 
@@ -166,7 +118,7 @@ int32_t tq_xchg_create(int32_t device, int32_t rank, int32_t world, int32_t rows
   x->rows = rows;
   x->n_cta = rows < TQ_XCHG_CTAS ? rows : TQ_XCHG_CTAS;
   x->flags_off = align_up((size_t)2 * world * rows * TQ_PART_STRIDE * sizeof(float), 256);
-  x->ctrl_off = x->flags_off + align_up((size_t)2 * world * TQ_XCHG_CTAS * sizeof(unsigned), 256);
+  x->ctrl_off = x->flags_off + align_up((size_t)2 * world * rows * sizeof(unsigned), 256);
   x->bytes = x->ctrl_off + 256;
   x->spin_limit = TQ_XCHG_SPIN;
   for (int p = 0; p < TQ_XCHG_MAX_WORLD; ++p) {
@@ -244,21 +196,12 @@ int32_t tq_xchg_gather_merge(tq_xchg* x, const float* mlo, float* out, int32_t p
   TQ_REQUIRE(x != nullptr && mlo != nullptr, TQ_ERR_INVALID, "null argument");
   TQ_REQUIRE(phases >= 1 && phases <= 3, TQ_ERR_INVALID, "phases: 1 publish, 2 wait and merge, 3 both");
   TQ_REQUIRE(out != nullptr || !(phases & 2), TQ_ERR_INVALID, "out must be a device pointer");
-  for (int p = 0; p < x->world; ++p)
-    TQ_REQUIRE(x->peer[p] != nullptr, TQ_ERR_INVALID, "a peer region is not connected");
-  TQ_CUDA(cudaSetDevice(x->device));
   XchgArgs a;
-  for (int p = 0; p < TQ_XCHG_MAX_WORLD; ++p) a.peer[p] = p < x->world ? x->peer[p] : nullptr;
-  a.rank = x->rank;
-  a.world = x->world;
-  a.rows = x->rows;
+  TQ_REQUIRE(tq_xchg_view(x, phases, &a.x), TQ_ERR_INVALID, "a peer region is not connected");
+  TQ_CUDA(cudaSetDevice(x->device));
   a.n_cta = x->n_cta;
-  a.phases = phases;
-  a.flags_off = x->flags_off;
-  a.ctrl_off = x->ctrl_off;
   a.mlo = mlo;
   a.out = out;
-  a.spin_limit = x->spin_limit;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(x->n_cta);
   cfg.blockDim = dim3(TQ_D);

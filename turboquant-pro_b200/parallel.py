@@ -221,6 +221,7 @@ class ShardedSequenceCache:
         self.n_tokens = [0] * ctx.n_layers      # global length per layer
         self.prefilled = [False] * ctx.n_layers
         self.exchange = None                    # PeerExchange, see use_peer_exchange()
+        self._fused = None                      # whether decode_exchange serves this geometry
 
     @staticmethod
     def local_capacity(n_tokens: int, hot_window: int, rank: int, world: int, extra: int = 0):
@@ -265,6 +266,17 @@ class ShardedSequenceCache:
 
     def decode(self, layer: int, q, out=None):
         """One decode step for every sequence: ``[n_seqs, n_q_heads, D]`` on every rank."""
+        if self.exchange is not None and self._fused is not False:
+            # one call: the merge kernel of the partial decode runs the exchange itself
+            try:
+                res = self.ctx.decode_exchange(layer, q, 0, self.local_blocks(layer),
+                                               self.rank == self.world - 1, self.exchange, out=out)
+                self._fused = True
+                return res
+            except NotImplementedError:
+                if self._fused:  # it worked before: a real error
+                    raise
+                self._fused = False  # this geometry: two calls (the same on every rank)
         mlo = self.decode_partial(layer, q)
         rows = mlo.shape[0] * mlo.shape[1]
         out2 = None if out is None else out.reshape(rows, -1)
