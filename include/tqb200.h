@@ -55,8 +55,14 @@ enum { TQ_F32 = 0, TQ_F16 = 1, TQ_BF16 = 2 };
  *   TQ_KEYS_NF4_ASYM  mean over the block's tokens, scale = max|x - mean|, NF4 grid (0 keeps
  *                     the value of the field that used to be reserved)
  *   TQ_KEYS_NF4       mean = 0, scale = max|x|, NF4 grid
- *   TQ_KEYS_UNIFORM   mean = min, scale = (max - min) / 15, grid = 0..15, round-half-even */
-enum { TQ_KEYS_NF4_ASYM = 0, TQ_KEYS_NF4 = 1, TQ_KEYS_UNIFORM = 2 };
+ *   TQ_KEYS_UNIFORM   mean = min, scale = (max - min) / 15, grid = 0..15, round-half-even
+ *   TQ_KEYS_POLAR     the legacy key format (per_channel_keys=False, core.py:1022-1033): keys go
+ *                     through the value quantiser, TurboQuantKV.compress(kind="key")
+ *                     (core.py:542-607: norm + rotated Lloyd-Max codes); decode is
+ *                     _cold_partials (kv_fused.py:84-98).  key_bits must equal value_bits (the
+ *                     reference's fused_decode requires it too, core.py:1191-1192) and
+ *                     outlier_frac must be 0.  Served by the general-shape decode kernel. */
+enum { TQ_KEYS_NF4_ASYM = 0, TQ_KEYS_NF4 = 1, TQ_KEYS_UNIFORM = 2, TQ_KEYS_POLAR = 3 };
 
 /* Geometry of a context.  Fill the first block, then call tq_geom_finish(), which
  * validates it and derives the rest. */
@@ -249,7 +255,10 @@ int32_t tq_dequant_range(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t start,
  * _pack_indices, per_channel_kv.py:87-93), nf4_scale/nf4_mean [H*D], outlier_idx
  * (ascending flat index into (H,S,D)) and outlier_val (fp16 bits) with capacity
  * `outlier_cap` (count returned in *n_outliers), value_indices (_pack_bits_cpu layout,
- * core.py:350-398) and value_norms [H*S].  Synchronises `stream`. */
+ * core.py:350-398) and value_norms [H*S].  With TQ_KEYS_POLAR the key container is a
+ * CompressedKV too: key_indices receives the key codes packed like value_indices
+ * (H*S*D*key_bits/8 bytes), nf4_scale the key norms [H*S] (give it that much room), nf4_mean
+ * is left alone and there are no outliers.  Synchronises `stream`. */
 int32_t tq_export_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
                         uint8_t* key_indices, float* nf4_scale, float* nf4_mean,
                         int32_t* outlier_idx, uint16_t* outlier_val, int32_t outlier_cap,

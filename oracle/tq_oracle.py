@@ -492,7 +492,12 @@ class OracleCache:
     def __init__(self, head_dim=128, n_heads=32, key_bits=4, value_bits=4, hot_window=512,
                  outlier_frac=0.02, seed=None, key_mode="nf4_asym", rope_theta=None,
                  k_bias=None):
-        if key_bits != 4:
+        if key_mode == "polar":
+            # the legacy format (core.py:1022-1033): keys through the value quantiser
+            if key_bits != value_bits:
+                raise ValueError("PolarQuant keys are restated for key_bits == value_bits")
+            outlier_frac = 0.0
+        elif key_bits != 4:
             raise ValueError("the per-channel key formats restated here are 4-bit")
         self.key_mode = key_mode
         # rope_theta alone selects the "sparse" zero-point (means only on long-wavelength
@@ -544,8 +549,11 @@ class OracleCache:
         if self.k_bias is not None:
             given = rope_averaged_bias(self.k_bias, self.rope_theta, self.head_dim,
                                        sum(self.cold_lengths), n)
-        self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode, self._dc_mask(n),
-                                       given))
+        if self.key_mode == "polar":
+            self.cold_k.append(encode_values(kb, self.pi_t, self.boundaries))
+        else:
+            self.cold_k.append(encode_keys(kb, self.outlier_frac, self.key_mode,
+                                           self._dc_mask(n), given))
         self.cold_v.append(encode_values(vb, self.pi_t, self.boundaries))
         self.cold_lengths.append(n)
         del self.hot_k[:n]
@@ -553,9 +561,13 @@ class OracleCache:
 
     def keys(self) -> np.ndarray:
         """All keys (H, N, D) float32: dequantised cold blocks then the hot tokens."""
-        parts = [dequant_keys(b["codes"], b["scale"], b["mean"], b["out_idx"], b["out_val"],
-                              self.key_mode)
-                 for b in self.cold_k]
+        if self.key_mode == "polar":
+            parts = [dequant_values(b["codes"], b["norms"], self.centroids, self.pi)
+                     for b in self.cold_k]
+        else:
+            parts = [dequant_keys(b["codes"], b["scale"], b["mean"], b["out_idx"], b["out_val"],
+                                  self.key_mode)
+                     for b in self.cold_k]
         if self.hot_k:
             parts.append(np.stack(self.hot_k, axis=1).astype(F32))
         if not parts:
@@ -580,6 +592,9 @@ class OracleCache:
         h, d = self.n_heads, self.head_dim
         cold = 0
         for kb, vb, n in zip(self.cold_k, self.cold_v, self.cold_lengths):
+            if self.key_mode == "polar":  # two CompressedKV containers
+                cold += 2 * ((h * n * d * self.value_bits + 7) // 8 + 4 * h * n)
+                continue
             # per-channel float32 scalars: scale + mean (symmetric NF4 stores no mean)
             n_mean = (0 if self.k_bias is not None else
                       d if self.rope_theta is None else int(self._dc_mask(n).sum()))

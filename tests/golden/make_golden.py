@@ -176,6 +176,41 @@ def cache_case(name, seed, h, n_tokens, hot_window, value_bits, n_q_heads, dtype
     np.savez_compressed(os.path.join(HERE, name), **out)
 
 
+def polar_keys_case(name, seed, h, n_tokens, hot_window, bits, dtype=np.float32):
+    """The legacy key format (``per_channel_keys=False``): keys through the value quantiser.
+    Stores every cold container (both are ``CompressedKV``), the dequantised tensors, the
+    dequantise-then-attend output and ``fused_decode``."""
+    rng = np.random.default_rng(seed)
+    k, v = _scaled(rng, (h, D), n_tokens)
+    k = k.astype(dtype)
+    v = v.astype(dtype)
+    q = rng.standard_normal((h, D)).astype(np.float32)
+    cache = TurboQuantKVCache(head_dim=D, n_heads=h, bits=bits, hot_window=hot_window,
+                              use_gpu=False, seed=seed, per_channel_keys=False)
+    for t in range(n_tokens):
+        cache.append(k[t], v[t])
+    keys = cache.get_keys(0, cache.length)[0]
+    vals = cache.get_values(0, cache.length)[0]
+    st = cache.memory_stats()
+    out = {
+        "k": k, "v": v, "q": q, "seed": seed, "hot_window": hot_window, "bits": bits,
+        "n_blocks": len(cache._cold_keys),
+        "cold_lengths": np.asarray(cache._cold_lengths, dtype=np.int32),
+        "length": cache.length, "hot_length": cache.hot_length,
+        "attn": _attend(q, keys, vals), "keys_head0": keys[0], "values_head0": vals[0],
+        "pi": cache._tq._Pi,
+        "fused": np.asarray(cache.fused_decode(q), dtype=np.float32),
+        "memory_stats": np.array([st["cold_bytes"], st["hot_bytes"], st["total_bytes"],
+                                  st["uncompressed_equivalent_bytes"]], dtype=np.float64),
+    }
+    for i, (ck, cv) in enumerate(zip(cache._cold_keys, cache._cold_values)):
+        out[f"b{i}_key_indices"] = ck.indices
+        out[f"b{i}_key_norms"] = ck.norms
+        out[f"b{i}_value_indices"] = cv.indices
+        out[f"b{i}_value_norms"] = cv.norms
+    np.savez_compressed(os.path.join(HERE, name), **out)
+
+
 def pack_known_answer():
     """The reference's own known-answer 3-bit packing vector (tests/test_core.py:228-258)
     and the same codes through the other widths and through the key packer."""
@@ -208,6 +243,10 @@ def main():
     pack_known_answer()
     other_key_grids()
     blob_case()
+    polar_keys_case("cache_polar_keys_v3.npz", seed=41, h=2, n_tokens=900, hot_window=512, bits=3,
+                    dtype=np.float16)
+    polar_keys_case("cache_polar_keys_v4_w16.npz", seed=42, h=2, n_tokens=70, hot_window=16,
+                    bits=4)
     print("golden fixtures written to", HERE)
 
 

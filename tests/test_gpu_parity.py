@@ -147,6 +147,66 @@ def test_cache_matches_reference(torch_cuda, name, vb, bulk):
     assert ctx.status() == 0
 
 
+@pytest.mark.parametrize("name,bulk", [("cache_polar_keys_v3.npz", False),
+                                       ("cache_polar_keys_v3.npz", True),
+                                       ("cache_polar_keys_v4_w16.npz", False)])
+def test_polar_keys_cache_matches_reference(torch_cuda, name, bulk):
+    """``TurboQuantKVCache(per_channel_keys=False)``, the legacy key format in which keys go
+    through the value quantiser (core.py:1022-1033) and decode is ``_cold_partials``
+    (kv_fused.py:84-98): cold containers, getters and statistics of the reference bit for bit,
+    ``fused_decode`` within the attention tolerance."""
+    torch = torch_cuda
+    from turboquant_pro_b200 import TurboQuantKVCache
+
+    g = load_golden(name)
+    k, v, q = g["k"], g["v"], g["q"]
+    n, h, _ = k.shape
+    bits = int(g["bits"])
+    cache = TurboQuantKVCache(head_dim=128, n_heads=h, bits=bits, hot_window=int(g["hot_window"]),
+                              seed=int(g["seed"]), per_channel_keys=False, max_tokens=n + 8,
+                              dtype=_np_dtype_name(k))
+    assert np.array_equal(cache._tq._Pi, g["pi"])
+    if bulk:
+        cache._ctx.append(0, _dev(torch, k[None]), _dev(torch, v[None]))
+    else:
+        for t in range(n):
+            cache.append(k[t], v[t])
+    assert (cache.length, cache.hot_length) == (int(g["length"]), int(g["hot_length"]))
+    assert list(cache._cold_lengths) == g["cold_lengths"].tolist()
+    assert len(cache._cold_keys) == int(g["n_blocks"])
+    for i in range(int(g["n_blocks"])):
+        ck, cv = cache._cold_keys[i], cache._cold_values[i]
+        assert ck.bits == bits and ck.packed
+        assert np.array_equal(ck.indices, g[f"b{i}_key_indices"])
+        assert np.array_equal(ck.norms, g[f"b{i}_key_norms"])
+        assert np.array_equal(cv.indices, g[f"b{i}_value_indices"])
+        assert np.array_equal(cv.norms, g[f"b{i}_value_norms"])
+    keys = np.asarray(cache.get_keys(0, cache.length))
+    vals = np.asarray(cache.get_values(0, cache.length))
+    assert keys.shape == (1, h, n, 128)
+    assert np.array_equal(keys[0, 0], g["keys_head0"])
+    assert np.array_equal(vals[0, 0], g["values_head0"])
+    st = cache.memory_stats()
+    assert [st["cold_bytes"], st["hot_bytes"], st["total_bytes"],
+            st["uncompressed_equivalent_bytes"]] == g["memory_stats"].tolist()
+    out = np.asarray(cache.fused_decode(q))
+    assert np.allclose(out, g["attn"], rtol=RTOL, atol=ATOL), np.abs(out - g["attn"]).max()
+    assert np.allclose(out, g["fused"], rtol=RTOL, atol=ATOL)
+    assert cache._ctx.last_kernel() == "general" and cache._ctx.status() == 0
+    # the sequence-split partials of this format merge to the same output
+    ctx = cache._ctx
+    qd = _dev(torch, q[None])
+    nb = int(g["n_blocks"])
+    parts = torch.stack([ctx.decode_partial(0, qd, 0, nb // 2, False),
+                         ctx.decode_partial(0, qd, nb // 2, 1 << 20, True)])
+    merged = ctx.lse_combine(parts.reshape(2, h, 130)).cpu().numpy()
+    assert np.allclose(merged, out, rtol=1e-3, atol=1e-4)
+    # formats this key mode does not take
+    with pytest.raises(NotImplementedError):
+        TurboQuantKVCache(head_dim=128, n_heads=h, bits=3, key_bits=4, value_bits=3,
+                          per_channel_keys=False)
+
+
 # ------------------------------------------------------------------------------------ #
 # decode against the oracle on seeded synthetic tensors                                 #
 # ------------------------------------------------------------------------------------ #

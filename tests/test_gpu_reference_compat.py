@@ -212,8 +212,24 @@ def test_formats_without_a_fused_form_are_refused(Cache):
     GPU-only package refuses them when the cache is built."""
     with pytest.raises(NotImplementedError):
         _dispatch_cache(Cache, key_nuq=True)
-    with pytest.raises(NotImplementedError):
-        Cache(head_dim=D, n_heads=H, bits=4, per_channel_keys=False)
+    with pytest.raises(NotImplementedError):  # legacy keys with key_bits != value_bits
+        Cache(head_dim=D, n_heads=H, bits=4, key_bits=4, value_bits=3, per_channel_keys=False)
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_legacy_polarquant_keys_fused_decode_equals_decompress_then_attend(Cache, bits):
+    """``per_channel_keys=False`` (the reference's tests/test_kv_fused.py cases on the cache):
+    keys through the value quantiser; the fused output equals attention over the getters."""
+    rng = np.random.default_rng(43)
+    cache = Cache(head_dim=D, n_heads=H, bits=bits, seed=0, per_channel_keys=False,
+                  hot_window=16, max_tokens=256)
+    _fill(cache, 80, rng)
+    assert len(cache._cold_keys) >= 2 and cache._kq is None
+    assert cache._cold_keys[0].bits == bits and cache._cold_keys[0].norms.shape == (1, H, 8)
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    got = cache.fused_decode(q)
+    want = _cache_truth(cache, q)
+    assert np.allclose(got, want, rtol=2e-2, atol=2e-3), np.abs(got - want).max()
 
 
 def test_clear_then_empty_decode_raises(Cache):

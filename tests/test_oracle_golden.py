@@ -139,6 +139,35 @@ def test_cache_matches_reference(name, vb, mode):
             st["uncompressed_equivalent_bytes"]] == ref.tolist()
 
 
+@pytest.mark.parametrize("name", ["cache_polar_keys_v3.npz", "cache_polar_keys_v4_w16.npz"])
+def test_polar_keys_cache_matches_reference(name):
+    """The legacy key format (``per_channel_keys=False``, core.py:1022-1033): keys through the
+    value quantiser.  Codes, norms, getters, statistics and attention of the reference."""
+    g = load_golden(name)
+    k, v, q = g["k"], g["v"], g["q"]
+    h, bits = k.shape[1], int(g["bits"])
+    cache = orc.OracleCache(head_dim=128, n_heads=h, key_bits=bits, value_bits=bits,
+                            hot_window=int(g["hot_window"]), seed=int(g["seed"]),
+                            key_mode="polar")
+    cache.pi, cache.pi_t = g["pi"], np.ascontiguousarray(g["pi"].T)
+    for t in range(k.shape[0]):
+        cache.append(k[t], v[t])
+    assert cache.length == int(g["length"]) and cache.hot_length == int(g["hot_length"])
+    assert cache.cold_lengths == g["cold_lengths"].tolist()
+    for i, (kb, vb_) in enumerate(zip(cache.cold_k, cache.cold_v)):
+        assert np.array_equal(orc.pack_value_codes(kb["codes"], bits), g[f"b{i}_key_indices"])
+        assert np.array_equal(kb["norms"], g[f"b{i}_key_norms"][0])
+        assert np.array_equal(orc.pack_value_codes(vb_["codes"], bits), g[f"b{i}_value_indices"])
+        assert np.array_equal(vb_["norms"], g[f"b{i}_value_norms"][0])
+    assert np.array_equal(cache.keys()[0], g["keys_head0"])
+    assert np.array_equal(cache.values()[0], g["values_head0"])
+    assert np.allclose(cache.attend(q), g["attn"], rtol=1e-5, atol=1e-6)
+    assert np.allclose(cache.attend(q), g["fused"], rtol=1e-4, atol=1e-5)
+    st = cache.memory_stats()
+    assert [st["cold_bytes"], st["hot_bytes"], st["total_bytes"],
+            st["uncompressed_equivalent_bytes"]] == g["memory_stats"].tolist()
+
+
 def test_fused_form_equals_dequantise_then_attend():
     """The score-on-codes identity the CUDA kernel relies on, checked on the oracle and
     against the reference's own fused_decode output."""

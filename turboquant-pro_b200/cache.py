@@ -10,8 +10,9 @@ Supported formats: per-channel 4-bit keys in the three grids the reference has a
 (fused) form for — asymmetric NF4 (``key_nf4_asym=True``, ``key_zero_point="calibrated"``),
 symmetric NF4 (``key_nf4=True``) and uniform (neither flag) — with an optional fp16 outlier
 side-list, PolarQuant values at 3 or 4 bits; asymmetric NF4 also with the ``sparse`` and
-``bias`` zero-points.  Data-fit tables (``key_nuq``) and other key widths raise
-``NotImplementedError``.
+``bias`` zero-points; and the legacy key format ``per_channel_keys=False`` (keys through the
+value quantiser, ``core.py:1022-1033``) where ``key_bits == value_bits``.  Data-fit tables
+(``key_nuq``) and other key widths raise ``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -157,8 +158,29 @@ class TurboQuantKVCache:
         self.hot_window = hot_window
         self.per_channel_keys = per_channel_keys
         if not per_channel_keys:
-            raise NotImplementedError("PolarQuant keys (per_channel_keys=False) are not "
-                                      "implemented on the CUDA path")
+            # the legacy key format (core.py:1022-1033): keys through the value quantiser
+            if self.key_bits != self.value_bits:
+                raise NotImplementedError("PolarQuant keys need key_bits == value_bits on the "
+                                          "CUDA path (the reference's fused_decode does too)")
+            if self.value_bits not in (3, 4):
+                raise NotImplementedError("the CUDA path implements 3- and 4-bit PolarQuant")
+            self.key_mode = "polar"
+            self.key_zero_point = key_zero_point
+            self.key_outlier_frac = 0.0
+            self.key_rope_theta = key_rope_theta
+            self._ctx = KVContext(
+                n_layers=1, n_seqs=1, n_kv_heads=n_heads, n_q_heads=n_q_heads or n_heads,
+                head_dim=head_dim, key_bits=self.key_bits, value_bits=self.value_bits,
+                hot_window=hot_window, outlier_frac=0.0, max_tokens_per_seq=max_tokens,
+                kv_dtype=dtype, seed=seed, device=device_id, key_mode="polar")
+            self._blocks = {}
+            cent, bnd = self._ctx.centroids, self._ctx.boundaries
+            self._tq = SimpleNamespace(head_dim=head_dim, n_heads=n_heads, bits=self.value_bits,
+                                       key_bits=self.key_bits, value_bits=self.value_bits,
+                                       _Pi=self._ctx.pi, _Pi_T=self._ctx.pi_t,
+                                       _codebooks={self.value_bits: (cent, bnd)}, use_gpu=True)
+            self._kq = None  # (core.py:947: no per-channel quantiser in this mode)
+            return
         if key_nuq:
             raise NotImplementedError("data-fit key tables (key_nuq=True) have no fused form; "
                                       "they are not implemented on the CUDA path")
@@ -221,7 +243,11 @@ class TurboQuantKVCache:
             kw = dict(indices=b["key_indices"], bits=self.key_bits, shape=shape, packed=True,
                       original_dtype=dt, outlier_idx=b["outlier_idx"],
                       outlier_val=b["outlier_val"], position_start=i * g.block_tokens)
-            if self.key_mode == "uniform":
+            if self.key_mode == "polar":
+                ck = CompressedKV(indices=b["key_indices"], norms=b["key_norms"],
+                                  bits=self.key_bits, original_dtype=dt, packed=True,
+                                  n_values=int(np.prod(shape)), shape=shape)
+            elif self.key_mode == "uniform":
                 ck = CompressedPerChannelKV(scale=b["nf4_scale"][:, :, None, :],
                                             zero=b["nf4_mean"][:, :, None, :], **kw)
             else:

@@ -71,7 +71,7 @@ def _torch_dtype(name):
             "bfloat16": torch.bfloat16}[key]
 
 
-KEY_MODES = ("nf4_asym", "nf4", "uniform")  # TQ_KEYS_* of the C ABI, in order
+KEY_MODES = ("nf4_asym", "nf4", "uniform", "polar")  # TQ_KEYS_* of the C ABI, in order
 
 
 class KVContext:
@@ -83,7 +83,9 @@ class KVContext:
         head_dim: 128.
         key_bits: 4.  value_bits: 3 or 4 (PolarQuant values).
         key_mode: per-channel key grid, ``"nf4_asym"`` (default), ``"nf4"`` (symmetric) or
-            ``"uniform"`` (``per_channel_kv.py:285-401``).
+            ``"uniform"`` (``per_channel_kv.py:285-401``); or ``"polar"``, the legacy format in
+            which keys go through the value quantiser (``core.py:1022-1033``;
+            ``key_bits == value_bits``, no outliers; served by the general decode kernel).
         key_mean_mask: ``(head_dim,)`` booleans, asymmetric NF4 only: the channels that keep
             their mean as zero-point (the reference's ``zero_point="sparse"``); default all.
         hot_window: tokens kept uncompressed (2..512); a flush moves the oldest
@@ -344,8 +346,9 @@ class KVContext:
         the fields of ``CompressedPerChannelKV`` and ``CompressedKV``."""
         g = self.geom
         h, s, d = g.n_kv_heads, g.block_tokens, g.head_dim
-        key_idx = np.empty(h * s * d // 2, np.uint8)
-        scale = np.empty((1, h, d), np.float32)
+        polar = self.key_mode == "polar"
+        key_idx = np.empty(h * s * d * g.key_bits // 8 if polar else h * s * d // 2, np.uint8)
+        scale = np.empty((1, h, s) if polar else (1, h, d), np.float32)  # polar: the key norms
         mean = np.empty((1, h, d), np.float32)
         cap = h * s * d
         oidx = np.empty(cap, np.int32)
@@ -360,6 +363,11 @@ class KVContext:
                 val_idx.ctypes.data, norms.ctypes.data, self._stream()))
         n = n_out.value
         has = g.outlier_k > 0
+        if polar:
+            return {"key_indices": key_idx, "key_norms": scale, "nf4_scale": None,
+                    "nf4_mean": None, "outlier_idx": None, "outlier_val": None,
+                    "value_indices": val_idx, "value_norms": norms, "shape": (1, h, s, d),
+                    "key_bits": g.key_bits, "value_bits": g.value_bits}
         return {
             "key_indices": key_idx, "nf4_scale": scale, "nf4_mean": mean,
             "outlier_idx": oidx[:n].copy() if has else None,

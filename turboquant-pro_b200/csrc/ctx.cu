@@ -70,11 +70,17 @@ int32_t tq_geom_finish(tq_geom* g) {
   TQ_REQUIRE(g->n_q_heads >= g->n_kv_heads && g->n_q_heads % g->n_kv_heads == 0, TQ_ERR_INVALID,
              "n_q_heads must be a positive multiple of n_kv_heads");
   TQ_REQUIRE(g->head_dim == TQ_D, TQ_ERR_UNSUPPORTED, "only head_dim == 128 is implemented");
-  TQ_REQUIRE(g->key_bits == 4, TQ_ERR_UNSUPPORTED, "per-channel keys: key_bits must be 4");
-  TQ_REQUIRE(g->key_mode >= TQ_KEYS_NF4_ASYM && g->key_mode <= TQ_KEYS_UNIFORM, TQ_ERR_INVALID,
+  TQ_REQUIRE(g->key_mode >= TQ_KEYS_NF4_ASYM && g->key_mode <= TQ_KEYS_POLAR, TQ_ERR_INVALID,
              "key_mode must be one of TQ_KEYS_*");
   TQ_REQUIRE(g->value_bits == 3 || g->value_bits == 4, TQ_ERR_UNSUPPORTED,
              "value_bits must be 3 or 4");
+  if (g->key_mode == TQ_KEYS_POLAR) {
+    TQ_REQUIRE(g->key_bits == g->value_bits, TQ_ERR_UNSUPPORTED,
+               "PolarQuant keys: key_bits must equal value_bits");
+    TQ_REQUIRE(g->outlier_frac == 0.0, TQ_ERR_INVALID, "PolarQuant keys keep no outliers");
+  } else {
+    TQ_REQUIRE(g->key_bits == 4, TQ_ERR_UNSUPPORTED, "per-channel keys: key_bits must be 4");
+  }
   TQ_REQUIRE(g->hot_window >= 2 && g->hot_window <= 512, TQ_ERR_UNSUPPORTED,
              "hot_window must be in [2, 512]");
   TQ_REQUIRE(g->kv_dtype == TQ_F32 || g->kv_dtype == TQ_F16 || g->kv_dtype == TQ_BF16,
@@ -456,9 +462,29 @@ int32_t tq_export_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
     }
     TQ_CUDA(cudaStreamSynchronize(st));
   }
+  // value-layout codes of one head's page -> the reference's LSB-first bit stream
+  auto pack_stream = [&](const uint8_t* vpg, uint8_t* out, int h, int bits) {
+    size_t base_bits = (size_t)h * S * D * bits;  // multiple of 8 because D is
+    uint8_t* dst = out + base_bits / 8;
+    std::memset(dst, 0, (size_t)S * D * bits / 8);
+    for (int s = 0; s < S; ++s) {
+      const uint8_t* grp = vpg + (size_t)(s / TQ_GROUP_TOK) * v_group_bytes(bits);
+      for (int d = 0; d < D; ++d) {
+        int code = v_get_code(grp, bits, s % TQ_GROUP_TOK, d);
+        size_t bit = ((size_t)s * D + d) * bits;
+        dst[bit >> 3] |= (uint8_t)(code << (bit & 7));
+        if ((bit & 7) + bits > 8) dst[(bit >> 3) + 1] |= (uint8_t)(code >> (8 - (bit & 7)));
+      }
+    }
+  };
+  const bool polar = g.key_mode == TQ_KEYS_POLAR;
   for (int h = 0; h < H; ++h) {
     const uint8_t* pg = page.data() + (size_t)h * g.page_bytes;
-    if (key_indices) {
+    if (polar) {
+      // PolarQuant keys: the key container is a CompressedKV (codes + norms, core.py:596-607)
+      if (key_indices) pack_stream(pg, key_indices, h, g.key_bits);
+      if (nf4_scale) std::memcpy(nf4_scale + (size_t)h * S, pg + g.scale_off, S * 4);
+    } else if (key_indices) {
       for (int s = 0; s < S; ++s)
         for (int j = 0; j < D / 2; ++j) {
           uint8_t b = pg[s * (D / 2) + j];
@@ -466,25 +492,10 @@ int32_t tq_export_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
               (uint8_t)((rev4(b & 15) << 4) | rev4(b >> 4));
         }
     }
-    if (nf4_scale) std::memcpy(nf4_scale + (size_t)h * D, pg + g.scale_off, D * 4);
-    if (nf4_mean) std::memcpy(nf4_mean + (size_t)h * D, pg + g.mean_off, D * 4);
+    if (nf4_scale && !polar) std::memcpy(nf4_scale + (size_t)h * D, pg + g.scale_off, D * 4);
+    if (nf4_mean && !polar) std::memcpy(nf4_mean + (size_t)h * D, pg + g.mean_off, D * 4);
     if (value_norms) std::memcpy(value_norms + (size_t)h * S, pg + g.norm_off, S * 4);
-    if (value_indices) {
-      const int vb = g.value_bits;
-      const uint8_t* vpg = pg + g.v_off;
-      size_t base_bits = (size_t)h * S * D * vb;  // multiple of 8 because D is
-      uint8_t* dst = value_indices + base_bits / 8;
-      std::memset(dst, 0, (size_t)S * D * vb / 8);
-      for (int s = 0; s < S; ++s) {
-        const uint8_t* grp = vpg + (size_t)(s / TQ_GROUP_TOK) * v_group_bytes(vb);
-        for (int d = 0; d < D; ++d) {
-          int code = v_get_code(grp, vb, s % TQ_GROUP_TOK, d);
-          size_t bit = ((size_t)s * D + d) * vb;
-          dst[bit >> 3] |= (uint8_t)(code << (bit & 7));
-          if ((bit & 7) + vb > 8) dst[(bit >> 3) + 1] |= (uint8_t)(code >> (8 - (bit & 7)));
-        }
-      }
-    }
+    if (value_indices) pack_stream(pg + g.v_off, value_indices, h, g.value_bits);
   }
   if (n_outliers) *n_outliers = total_out;
   if (outlier_idx || outlier_val) {
@@ -530,6 +541,8 @@ int32_t tq_import_block(tq_ctx* ctx, int32_t layer, int32_t seq, int32_t block,
                         int32_t n_outliers, const uint8_t* value_indices,
                         const float* value_norms, void* stream) {
   TQ_REQUIRE(good_ctx(ctx, layer), TQ_ERR_INVALID, "bad context or layer");
+  TQ_REQUIRE(ctx->g.key_mode != TQ_KEYS_POLAR, TQ_ERR_UNSUPPORTED,
+             "import of PolarQuant-key blocks is not implemented");
   const tq_geom& g = ctx->g;
   TQ_REQUIRE(seq >= 0 && seq < g.n_seqs, TQ_ERR_INVALID, "bad sequence");
   TQ_REQUIRE(ctx->len[(size_t)layer * g.n_seqs + seq] == 0, TQ_ERR_INVALID,
@@ -735,11 +748,15 @@ int32_t tq_memory_stats(tq_ctx* ctx, int32_t layer, int32_t seq, double* cold_by
     for (int b = 0; b < nb; ++b) {
       double n_out = 0;
       for (int h = 0; h < H; ++h) n_out += meta[(size_t)h * g.max_blocks + b].cnt;
-      // symmetric NF4 containers hold no mean
-      cold += (double)H * S * D * g.key_bits / 8 +
-              4.0 * H * D +
-              (g.key_mode == TQ_KEYS_NF4 || ctx->bias_means ? 0.0 : 4.0 * H * ctx->mean_channels) +
-              6.0 * n_out;
+      if (g.key_mode == TQ_KEYS_POLAR) {
+        // a CompressedKV: packed codes + one norm per token
+        cold += (double)H * S * D * g.key_bits / 8 + 4.0 * H * S;
+      } else {
+        // symmetric NF4 containers hold no mean
+        cold += (double)H * S * D * g.key_bits / 8 + 4.0 * H * D +
+                (g.key_mode == TQ_KEYS_NF4 || ctx->bias_means ? 0.0 : 4.0 * H * ctx->mean_channels) +
+                6.0 * n_out;
+      }
       cold += (double)H * S * D * g.value_bits / 8 + 4.0 * H * S;
     }
   }

@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
   __shared__ float corr_s[GT][256];
   __shared__ float nf4_s[16], cent_s[16];
   __shared__ float p_s[WARPS][GT][TQ_GROUP_TOK];
+  __shared__ float ksc_s[WARPS][GT][TQ_GROUP_TOK];  // PolarQuant keys: a group's raw scores
+  const bool polar = g.key_mode == TQ_KEYS_POLAR;
   __shared__ float mrg_m[WARPS][GT], mrg_l[WARPS][GT];
   __shared__ float mrg_acc[WARPS][GT][TQ_D];
 
@@ -98,6 +100,24 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
                         : 0.0f;
   }
   __syncthreads();
+  if (polar) {
+    // PolarQuant keys (_cold_partials, kv_fused.py:84-98): the score of a token is
+    // norm_k * sum_d centroid[code_d] * q_rot[d] with q_rot = q @ Pi^T, formed once here
+    // (thread e: column e of Pi^T) and kept where the per-page weights of the per-channel
+    // formats go.
+    const int e = tid;
+    float r[GT];
+#pragma unroll
+    for (int gg = 0; gg < GT; ++gg) r[gg] = 0.0f;
+    for (int d = 0; d < TQ_D; ++d) {
+      const float pv = a.tables->pi_t[d * TQ_D + e];
+#pragma unroll
+      for (int gg = 0; gg < GT; ++gg) r[gg] += q_s[gg][d] * pv;
+    }
+#pragma unroll
+    for (int gg = 0; gg < GT; ++gg) w_s[gg][e] = r[gg];
+    __syncthreads();
+  }
 
   float m_run[GT], l_run[GT], acc[GT][16];
 #pragma unroll
@@ -136,6 +156,37 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
     }
   };
 
+  // a lane's record of a 16-token group of value-layout codes, and the two codes of its pair p
+  auto load_rec = [&](const uint8_t* grp_base, uint32_t (&rec)[8]) {
+    if (vb == 4) {
+      uint4 r0 = *(const uint4*)(grp_base + lane * 16);
+      uint4 r1 = *(const uint4*)(grp_base + 512 + lane * 16);
+      rec[0] = r0.x; rec[1] = r0.y; rec[2] = r0.z; rec[3] = r0.w;
+      rec[4] = r1.x; rec[5] = r1.y; rec[6] = r1.z; rec[7] = r1.w;
+    } else {
+#pragma unroll
+      for (int pt = 0; pt < 3; ++pt) {
+        uint2 r = *(const uint2*)(grp_base + pt * 256 + lane * 8);
+        rec[2 * pt] = r.x;
+        rec[2 * pt + 1] = r.y;
+      }
+      rec[6] = rec[7] = 0;
+    }
+  };
+  auto pair_codes = [&](const uint32_t (&rec)[8], int p, int& ca, int& cb) {
+    if (vb == 4) {
+      uint32_t by = (rec[p >> 2] >> (8 * (p & 3))) & 255;
+      ca = by & 15;
+      cb = by >> 4;
+    } else {
+      int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
+      uint32_t f = rec[wd] >> sh;
+      if (sh > 26) f |= rec[wd + 1] << (32 - sh);
+      ca = f & 7;
+      cb = (f >> 3) & 7;
+    }
+  };
+
   if (split < a.ns_cold) {
     int b0 = min(a.block_begin, nb);
     int b1 = a.block_end < 0 ? nb : min(a.block_end, nb);
@@ -145,7 +196,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
     for (int pg = p_lo; pg < p_hi; ++pg) {
       const uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, pg);
       __syncthreads();
-      {  // per-page query projections: w = q * scale, bias = q . mean
+      if (!polar) {  // per-page query projections: w = q * scale, bias = q . mean
         int d = tid;
         float sc = ((const float*)(page + g.scale_off))[d];
         float mu = ((const float*)(page + g.mean_off))[d];
@@ -161,7 +212,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
         for (int i = tid; i < GT * 256; i += WARPS * 32) corr_s[i / 256][i % 256] = 0.0f;
       }
       __syncthreads();
-      {  // outlier corrections, scattered by token
+      if (!polar) {  // outlier corrections, scattered by token
         PageMeta pm = a.page_meta[unit_index(g, a.layer, seq, head) * g.max_blocks + pg];
         const uint32_t* ent =
             a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
@@ -179,9 +230,46 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
         float sc[GT];
 #pragma unroll
         for (int gg = 0; gg < GT; ++gg) sc[gg] = 0.0f;
+        if (polar) {
+          // key codes in the value layout: this lane's 4 tokens x 16 channels, summed over the
+          // eight lanes that share the tokens, then handed to the token's two score lanes
+          uint32_t krec[8];
+          load_rec(page + (size_t)grp * v_group_bytes(vb), krec);
+          float part[4][GT];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int gg = 0; gg < GT; ++gg) part[k][gg] = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              int ca, cb;
+              pair_codes(krec, 2 * i + h, ca, cb);
+              const float va = cent_s[ca], vb2 = cent_s[cb];
+#pragma unroll
+              for (int gg = 0; gg < GT; ++gg) {
+                const float qv = w_s[gg][dq + 8 * i];
+                part[2 * h][gg] += va * qv;
+                part[2 * h + 1][gg] += vb2 * qv;
+              }
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int gg = 0; gg < GT; ++gg) {
+              float v = part[k][gg];
+              v += __shfl_xor_sync(0xffffffffu, v, 4);
+              v += __shfl_xor_sync(0xffffffffu, v, 8);
+              v += __shfl_xor_sync(0xffffffffu, v, 16);
+              if (dq == 0) ksc_s[warp][gg][2 * c4 + 8 * (k >> 1) + (k & 1)] = v;
+            }
+          __syncwarp();
+        }
         const uint4* row = (const uint4*)(page + (size_t)t_glob * (TQ_D / 2) + half * 32);
 #pragma unroll
-        for (int v = 0; v < 2; ++v) {
+        for (int v = 0; v < 2 && !polar; ++v) {
           uint4 cw = row[v];
           uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
@@ -201,11 +289,16 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
         }
         const bool valid = t_glob < S;
         const float nrm = ((const float*)(page + g.norm_off))[t_glob];
+        const float nrm_k = polar ? ((const float*)(page + g.scale_off))[t_glob] : 0.0f;
 #pragma unroll
         for (int gg = 0; gg < GT; ++gg) {
           float s2 = sc[gg] + __shfl_xor_sync(0xffffffffu, sc[gg], 1);
-          float bias = biasw[0][gg] + biasw[1][gg] + biasw[2][gg] + biasw[3][gg];
-          s2 = (s2 + bias + corr_s[gg][t_glob]) * a.scale;
+          if (polar) {
+            s2 = nrm_k * ksc_s[warp][gg][tok] * a.scale;
+          } else {
+            float bias = biasw[0][gg] + biasw[1][gg] + biasw[2][gg] + biasw[3][gg];
+            s2 = (s2 + bias + corr_s[gg][t_glob]) * a.scale;
+          }
           sc[gg] = valid ? s2 : -INFINITY;
         }
         softmax_step(sc, valid ? nrm : 0.0f);
@@ -213,20 +306,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
         // value accumulation on the codes
         const uint8_t* grp_base = page + g.v_off + (size_t)grp * v_group_bytes(vb);
         uint32_t rec[8];
-        if (vb == 4) {
-          uint4 r0 = *(const uint4*)(grp_base + lane * 16);
-          uint4 r1 = *(const uint4*)(grp_base + 512 + lane * 16);
-          rec[0] = r0.x; rec[1] = r0.y; rec[2] = r0.z; rec[3] = r0.w;
-          rec[4] = r1.x; rec[5] = r1.y; rec[6] = r1.z; rec[7] = r1.w;
-        } else {
-#pragma unroll
-          for (int pt = 0; pt < 3; ++pt) {
-            uint2 r = *(const uint2*)(grp_base + pt * 256 + lane * 8);
-            rec[2 * pt] = r.x;
-            rec[2 * pt + 1] = r.y;
-          }
-          rec[6] = rec[7] = 0;
-        }
+        load_rec(grp_base, rec);
 #pragma unroll
         for (int gg = 0; gg < GT; ++gg) {
           float pw[2][2];
@@ -239,18 +319,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
           for (int i = 0; i < 16; ++i) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              int p = 2 * i + h, ca, cb;
-              if (vb == 4) {
-                uint32_t by = (rec[p >> 2] >> (8 * (p & 3))) & 255;
-                ca = by & 15;
-                cb = by >> 4;
-              } else {
-                int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
-                uint32_t f = rec[wd] >> sh;
-                if (sh > 26) f |= rec[wd + 1] << (32 - sh);
-                ca = f & 7;
-                cb = (f >> 3) & 7;
-              }
+              int ca, cb;
+              pair_codes(rec, 2 * i + h, ca, cb);
               acc[gg][i] += pw[h][0] * cent_s[ca] + pw[h][1] * cent_s[cb];
             }
           }

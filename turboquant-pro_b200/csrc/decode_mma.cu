@@ -1638,6 +1638,7 @@ int tq_launch_decode_mma(tq_ctx* ctx, int layer, const void* q, int q_dtype, int
   const int n_units = g.n_seqs * g.n_kv_heads;
   const int G = g.group;
   if (ctx->force_generic) return TQ_OK;
+  if (g.key_mode == TQ_KEYS_POLAR) return TQ_OK;  // the legacy key format: general kernel
   if (g.block_tokens != BLK || (G != 1 && G != 2 && G != 4 && G != 8) ||
       g.n_kv_heads > MAX_UNITS || g.hot_cap % 64 != 0)
     return TQ_OK;

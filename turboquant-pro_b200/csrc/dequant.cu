@@ -18,6 +18,7 @@ struct DequantArgs {
   int layer, seq, start, end, n_total;
   float* k_out;  // [H][end-start][D]
   float* v_out;
+  int keys_pass;  // PolarQuant keys: the value kernel reads the key codes and writes k_out
 };
 
 TQ_DEV float ld_any(const void* p, size_t i, int dt) {
@@ -34,7 +35,7 @@ __global__ void __launch_bounds__(TQ_D) dequant_dense_kernel(DequantArgs a) {
   const int nb = n_cold_blocks(a.n_total, g.hot_window, S);
   const size_t o = ((size_t)head * (a.end - a.start) + blockIdx.x) * TQ_D + d;
   if (pos < nb * S) {
-    if (a.k_out == nullptr) return;
+    if (a.k_out == nullptr || g.key_mode == TQ_KEYS_POLAR) return;
     const int blk = pos / S, t = pos % S;
     const uint8_t* page = a.pages + page_offset(g, a.layer, a.seq, head, blk);
     const uint8_t b = page[t * (TQ_D / 2) + (d >> 1)];
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(TQ_D) dequant_values_kernel(DequantArgs a, int
   const int head = blockIdx.y, e = threadIdx.x;
   const int S = g.block_tokens, vb = g.value_bits;
   const uint8_t* page = a.pages + page_offset(g, a.layer, a.seq, head, blk);
-  const uint8_t* grp = page + g.v_off + (size_t)gq * v_group_bytes(vb);
+  const uint8_t* grp = page + (a.keys_pass ? 0 : g.v_off) + (size_t)gq * v_group_bytes(vb);
   __shared__ __align__(16) float us[TQ_D][TQ_GROUP_TOK];
   __shared__ float cent[16];
   if (e < 16) cent[e] = a.tables->centroids[e];
@@ -112,8 +113,8 @@ __global__ void __launch_bounds__(TQ_D) dequant_values_kernel(DequantArgs a, int
     const int tt = gq * TQ_GROUP_TOK + t;
     const int pos = blk * S + tt;
     if (tt < S && pos >= a.start && pos < a.end) {
-      const float nrm = ((const float*)(page + g.norm_off))[tt];
-      a.v_out[((size_t)head * (a.end - a.start) + (pos - a.start)) * TQ_D + e] =
+      const float nrm = ((const float*)(page + (a.keys_pass ? g.scale_off : g.norm_off)))[tt];
+      (a.keys_pass ? a.k_out : a.v_out)[((size_t)head * (a.end - a.start) + (pos - a.start)) * TQ_D + e] =
           __fmul_rn(acc[t], nrm);
     }
   }
@@ -140,6 +141,7 @@ int tq_launch_dequant(tq_ctx* ctx, int layer, int seq, int start, int end, float
   a.n_total = ctx->len[(size_t)layer * g.n_seqs + seq];
   a.k_out = k_out;
   a.v_out = v_out;
+  a.keys_pass = 0;
   const int S = g.block_tokens;
   const int nb = n_cold_blocks(a.n_total, g.hot_window, S);
   dim3 grid(end - start, g.n_kv_heads);
@@ -151,10 +153,14 @@ int tq_launch_dequant(tq_ctx* ctx, int layer, int seq, int start, int end, float
       dim3 go(blk1 - blk0 + 1, g.n_kv_heads);
       dequant_outlier_kernel<<<go, 256, 0, st>>>(a, blk0);
     }
-    if (v_out != nullptr) {
-      const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
-      dim3 gv((blk1 - blk0 + 1) * groups, g.n_kv_heads);
-      dequant_values_kernel<<<gv, TQ_D, 0, st>>>(a, blk0);
+    const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
+    dim3 gv((blk1 - blk0 + 1) * groups, g.n_kv_heads);
+    if (v_out != nullptr) dequant_values_kernel<<<gv, TQ_D, 0, st>>>(a, blk0);
+    if (k_out != nullptr && g.key_mode == TQ_KEYS_POLAR) {
+      // PolarQuant keys: TurboQuantKV.decompress on the key codes (core.py:619-654)
+      DequantArgs ak = a;
+      ak.keys_pass = 1;
+      dequant_values_kernel<<<gv, TQ_D, 0, st>>>(ak, blk0);
     }
   }
   TQ_CUDA(cudaGetLastError());

@@ -27,6 +27,9 @@ struct EncodeArgs {
   const void* v;
   int layer, seq_begin, seq_count, n_tokens, max_new_blocks;
   int64_t seq_stride, tok_stride, head_stride;
+  // PolarQuant keys (TQ_KEYS_POLAR): the value encoder also runs over the keys, writing their
+  // codes where the per-channel codes would go and their norms over the scale / mean arrays
+  int polar_keys_pass;
 };
 
 // Where token `pos` of (seq, head) currently lives: positions below n0 are already in the
@@ -700,9 +703,13 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
   auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
   const float* pi_rows = a.tables->pi;  // pi[ch][d]
   // whether every row of the caller's tensor starts on a 16-byte boundary (the ring's do)
+  const bool keys = a.polar_keys_pass != 0;  // this launch encodes the keys (PolarQuant keys)
+  const void* in_base = keys ? a.k : a.v;
+  const void* ring_base = keys ? a.hot_k : a.hot_v;
+  const int out_off = keys ? 0 : g.v_off, nrm_off = keys ? g.scale_off : g.norm_off;
   const bool rows_aligned = [&]() {
     const int64_t epc = 16 / (int64_t)sizeof(typename Elem<DT>::type);
-    return ((uintptr_t)a.v & 15) == 0 && a.seq_stride % epc == 0 && a.tok_stride % epc == 0 &&
+    return ((uintptr_t)in_base & 15) == 0 && a.seq_stride % epc == 0 && a.tok_stride % epc == 0 &&
            a.head_stride % epc == 0;
   }();
 
@@ -741,7 +748,7 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
     const int blk = nb0 + jb;
     if (blk >= nb1) continue;  // uniform over the half
     const int S = g.block_tokens;
-    const TokenSource<DT> src = make_source<DT>(a, a.hot_v, a.v, seq, head, n0);
+    const TokenSource<DT> src = make_source<DT>(a, ring_base, in_base, seq, head, n0);
     uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
 
     // (No barrier here: the last reads of the previous item's rows, unit vectors and lists lie
@@ -807,7 +814,7 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
       const float nrm = __fsqrt_rn(sq);  // (the same bits in all eight threads of the token)
       if (j == 0) {
         hs->norm[t] = nrm;
-        ((float*)(page + g.norm_off))[gq * TQ_GROUP_TOK + t] = nrm;
+        ((float*)(page + nrm_off))[gq * TQ_GROUP_TOK + t] = nrm;
       }
       // unit vectors as fp16 hi / lo parts, [token][channel].  The tensor-core rotation only
       // has to land within the slack, so it takes x * (1 / norm), one or two units in the
@@ -966,7 +973,7 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
       }
     }
     half_sync();
-    uint32_t* dst = (uint32_t*)(page + g.v_off + (size_t)gq * v_group_bytes(vb));
+    uint32_t* dst = (uint32_t*)(page + out_off + (size_t)gq * v_group_bytes(vb));
     const int words = v_group_bytes(vb) / 4;
     for (int i = e; i < words; i += TQ_D) dst[i] = hs->img[i];
   }
@@ -1033,7 +1040,9 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
   const tq_geom& g = a.g;
   if (a.max_new_blocks > 0) {
     dim3 grid(a.max_new_blocks, g.n_kv_heads, a.seq_count);
-    if (DT == TQ_F32) {
+    if (g.key_mode == TQ_KEYS_POLAR) {
+      // (the keys go through the value encoder, below)
+    } else if (DT == TQ_F32) {
       encode_keys_kernel<DT, false><<<grid, TQ_D, 0, st>>>(a);  // one thread per channel
     } else {
       const int stage_bytes = g.block_tokens * TQ_D * elem_size(DT);
@@ -1054,6 +1063,11 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
       TQ_CUDA(cudaFuncSetAttribute(encode_values_kernel<DT>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, ENCV_SMEM));
       attr_set[device & 15] = true;
+    }
+    if (g.key_mode == TQ_KEYS_POLAR) {
+      EncodeArgs ak = a;
+      ak.polar_keys_pass = 1;
+      encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(ak);
     }
     encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(a);
     *launches += 2;
@@ -1101,6 +1115,7 @@ int tq_launch_encode(tq_ctx* ctx, int layer, int seq_begin, int seq_count, const
   a.seq_count = seq_count;
   a.n_tokens = n_tokens;
   a.max_new_blocks = max_new_blocks;
+  a.polar_keys_pass = 0;
   a.seq_stride = seq_stride;
   a.tok_stride = tok_stride;
   a.head_stride = head_stride;
