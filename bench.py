@@ -72,8 +72,8 @@ def parse_args():
     p.add_argument("--cpu-workers", type=int, default=0, help="0: one per host core, at most 16")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--extras", default="cfg2,cfg3,cfg4",
-                   help="comma list of cfg2,cfg3,cfg4,weak, or 'none'")
+    p.add_argument("--extras", default="cfg0,cfg2,cfg3,cfg4",
+                   help="comma list of cfg0,cfg2,cfg3,cfg4,weak, or 'none'")
     p.add_argument("--seed", type=int, default=0)
     return p.parse_args()
 
@@ -679,6 +679,143 @@ def run_e2e(args, dst: Dist, ctx, L, B, H, HQ, D, global_batch):
 
 
 # ------------------------------------------------------------------------------------ #
+# config 0: the reference's own CPU-runnable case, in full on both sides                #
+# ------------------------------------------------------------------------------------ #
+
+def cfg0_inputs(seed, h=32, d=128, n=4096):
+    """Post-RoPE float32 K/V: N(0,1) times per-channel scales log-normal(0, 0.5), 2 % of the
+    key channels scaled x20; one N(0,1) query per head."""
+    rng = np.random.default_rng(seed)
+    sk = rng.lognormal(0.0, 0.5, size=(h, d)).astype(np.float32)
+    sv = rng.lognormal(0.0, 0.5, size=(h, d)).astype(np.float32)
+    hot = rng.random((h, d)) < 0.02
+    sk = np.where(hot, sk * 20.0, sk).astype(np.float32)
+    k = (rng.standard_normal((n, h, d)).astype(np.float32) * sk)
+    v = (rng.standard_normal((n, h, d)).astype(np.float32) * sv)
+    q = rng.standard_normal((h, d)).astype(np.float32)
+    return k, v, q
+
+
+def _cfg0_ref_worker(job):
+    """The reference itself on configuration 0 (TurboQuantKVCache.robust, CPU path): fills the
+    cache token by token, then times fused_decode and dequantise-then-attend."""
+    ref_root, seed, reps = job
+    sys.path.insert(0, ref_root)
+    from turboquant_pro.core import TurboQuantKVCache as RefCache
+
+    k, v, q = cfg0_inputs(seed)
+    # (bits=4 beside K4/V4: the reference's fused_decode looks its value codebook up under
+    # `bits`, core.py:1191-1192 and kv_fused.py's _rot_matrices)
+    cache = RefCache.robust(head_dim=128, n_heads=32, hot_window=512, use_gpu=False, seed=seed,
+                            bits=4)
+    t0 = time.perf_counter()
+    for t in range(k.shape[0]):
+        cache.append(k[t], v[t])
+    fill_s = time.perf_counter() - t0
+    out = np.asarray(cache.fused_decode(q), dtype=np.float32)  # builds the prepared pages
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        out = np.asarray(cache.fused_decode(q), dtype=np.float32)
+    fused_ms = (time.perf_counter() - t0) / reps * 1e3
+    t0 = time.perf_counter()
+    keys = cache.get_keys(0, cache.length)[0]
+    vals = cache.get_values(0, cache.length)[0]
+    sc = np.einsum("hd,hsd->hs", q, keys) / np.sqrt(np.float32(128.0))
+    sc -= sc.max(axis=-1, keepdims=True)
+    p = np.exp(sc)
+    dq = np.einsum("hs,hsd->hd", p / p.sum(axis=-1, keepdims=True), vals)
+    dequant_ms = (time.perf_counter() - t0) * 1e3
+    return {"out": out, "dequant_out": dq.astype(np.float32), "fill_s": fill_s,
+            "fused_ms": fused_ms, "dequant_ms": dequant_ms, "n_blocks": len(cache._cold_keys),
+            "pi": np.asarray(cache._tq._Pi)}
+
+
+def run_cfg0(args, dst: Dist):
+    """Configuration 0 of the baseline (one layer, MHA 32 heads, batch 1, context 4096,
+    robust K4/V4, float32 K/V): the drop-in cache on the GPU and, where the reference package
+    is at hand, the reference's own CPU path on the very same tensors, both in full, with the
+    outputs compared.  Rank 0 only."""
+    import torch
+
+    if dst.rank != 0:
+        return None
+    from turboquant_pro_b200 import TurboQuantKVCache
+
+    seed = args.seed + 40
+    k, v, q = cfg0_inputs(seed)
+    n, h, d = k.shape
+    ref, ref_root = None, reference_root()
+    if ref_root is not None:
+        try:
+            import multiprocessing as mp
+
+            with mp.get_context("spawn").Pool(1) as pool:
+                ref = pool.apply(_cfg0_ref_worker, ((ref_root, seed, 5),))
+        except Exception as e:  # noqa: BLE001
+            ref = {"error": repr(e)[:200]}
+    cache = TurboQuantKVCache.robust(head_dim=d, n_heads=h, hot_window=512, seed=seed,
+                                     max_tokens=n + 8, device_id=dst.local)
+    if ref is not None and "pi" in ref and not np.array_equal(ref["pi"], cache._tq._Pi):
+        raise SystemExit("config 0: the rotation matrix differs from the reference's")
+    t0 = time.perf_counter()
+    for t in range(n):
+        cache.append(k[t], v[t])
+    torch.cuda.synchronize()
+    fill_s = time.perf_counter() - t0
+    out = np.asarray(cache.fused_decode(q))
+    reps = 50
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        out = np.asarray(cache.fused_decode(q))  # numpy in, numpy out: copies included
+    facade_ms = (time.perf_counter() - t0) / reps * 1e3
+    ctx = cache._ctx
+    qd = torch.from_numpy(q)[None].to(ctx.device)
+    od = torch.empty((1, h, d), dtype=torch.float32, device=ctx.device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(5):
+        ctx.decode(0, qd, out=od)
+    e0.record()
+    for _ in range(reps):
+        ctx.decode(0, qd, out=od)
+    e1.record()
+    torch.cuda.synchronize()
+    device_ms = e0.elapsed_time(e1) / reps
+    res = {
+        "workload": "configuration 0: one layer, MHA 32 heads x head_dim 128, batch 1, context "
+                    "4096, robust K4 asym-NF4 + 2% outliers / V4, float32 K/V, hot_window 512",
+        "gpu_fused_decode_ms_numpy_in_out": facade_ms, "gpu_decode_ms_device": device_ms,
+        "gpu_fill_s_token_by_token": fill_s, "kernel": ctx.last_kernel(),
+        "n_blocks": ctx.lengths(0, 0)[1] // ctx.block_tokens,
+    }
+    if ref is None:
+        res["reference"] = "the reference package is not on this machine"
+    elif "error" in ref:
+        res["reference"] = ref["error"]
+    else:
+        err = float(np.abs(out - ref["out"]).max())
+        err_dq = float(np.abs(out - ref["dequant_out"]).max())
+        tol = bool(np.allclose(out, ref["dequant_out"], rtol=2e-2, atol=2e-3))
+        if not tol:
+            raise SystemExit(f"config 0 check failed: output differs from the reference's "
+                             f"(max abs err {err_dq:.3e})")
+        res.update({
+            "reference_fused_decode_ms": ref["fused_ms"],
+            "reference_dequantise_then_attend_ms": ref["dequant_ms"],
+            "reference_fill_s_token_by_token": ref["fill_s"],
+            "reference_n_blocks": ref["n_blocks"],
+            "max_abs_err_vs_reference_fused_decode": err,
+            "max_abs_err_vs_reference_dequantise_then_attend": err_dq,
+            "within_rtol_2e-2_atol_2e-3": tol,
+            "what": "the unmodified reference (its numpy path) run in this process's host on "
+                    "the same seeded tensors",
+        })
+    del cache
+    torch.cuda.empty_cache()
+    return res
+
+
+# ------------------------------------------------------------------------------------ #
 # config 2: one long sequence, sequence split with sharded storage                      #
 # ------------------------------------------------------------------------------------ #
 
@@ -1212,6 +1349,11 @@ def run_native(args):
                          args.batch, args.batch * dst.world, "weak")
         line["cfg1_weak"] = {k: w[k] for k in ("value", "ms_per_step", "tokens_per_s", "scaling")}
         line["cfg1_weak"]["global_batch"] = args.batch * dst.world
+    if "cfg0" in extras:
+        r0 = run_cfg0(args, dst)
+        dst.barrier()
+        if r0 is not None:
+            line["cfg0"] = r0
     if "cfg2" in extras:
         line["cfg2"] = run_cfg2(args, dst)
     if "cfg3" in extras:
