@@ -305,11 +305,20 @@ int32_t tq_clear(tq_ctx* ctx, int32_t layer, int32_t seq, void* stream);
 /* Reads and clears the device status word.  Synchronises `stream`.
  *   bit 0 (1): an outlier pool overflowed and a block kept a truncated side-list;
  *   bit 1 (2): a bounded wait inside the tensor-core decode kernel ran out (a tile copy did
- *              not arrive within the limit).  The kernel then stops waiting and returns, so
+ *              not arrive within the limit), or one inside the tcgen05 value encoder.  The kernel then stops waiting and returns, so
  *              the device stays usable, but the `out` / `mlo` of that call is undefined:
  *              tq_decode itself has already returned TQ_OK (it does not synchronise), so a
  *              caller that wants the guarantee reads the status after the call. */
 int32_t tq_status(tq_ctx* ctx, int32_t* flags, void* stream);
+
+/* Chooses, for the whole process, the kernel that rotates and quantises values (and, in
+ * TQ_KEYS_POLAR mode, keys) on tq_append — both implement PolarQuant.encode (core.py) and
+ * write identical pages:
+ *   0  (default) the rotation on warp-level mma.sync instructions;
+ *   1  the rotation on tcgen05.mma with the accumulators in tensor memory.  Its wait for the
+ *      products is bounded; if it runs out, bit 1 of the status word is set.
+ * Not part of the reference's interface: a switch for measurements and tests. */
+int32_t tq_set_value_encoder(int32_t kind);
 
 /* Algorithmic bytes one tq_decode of `layer` reads (reference container sizes of every
  * cold block + the hot windows + q at the element size of the most recent decode's q_dtype,

@@ -287,6 +287,59 @@ def test_rows_off_the_16_byte_grid_encode_the_same(torch_cuda, dt):
                 assert np.array_equal(np.asarray(a[name]), np.asarray(b[name])), name
 
 
+@pytest.mark.parametrize("dt,vb,key_mode", [("float16", 3, "nf4_asym"), ("bfloat16", 4, "nf4_asym"),
+                                            ("float32", 3, "nf4_asym"), ("float16", 4, "polar"),
+                                            ("float16", 3, "polar")])
+@pytest.mark.parametrize("aligned", [True, False])
+def test_value_encoder_on_tcgen05_writes_the_same_pages(torch_cuda, dt, vb, key_mode, aligned):
+    """The value encoder whose rotation runs on tcgen05.mma (accumulators in tensor memory)
+    writes, bit for bit, the pages of the default encoder (itself checked against the oracle
+    and the golden fixtures above), for every element type, code width and row alignment, and
+    for keys in PolarQuant form."""
+    torch = torch_cuda
+    from turboquant_pro_b200._lib import load
+    from turboquant_pro_b200.synth import make_kv
+
+    lib = load()
+    h, n, w = 2, 1100, 512
+    k, v = make_kv(78, h, n, dtype=np.float16)
+    tdt = getattr(torch, dt)
+    kt, vt = torch.from_numpy(k).to(tdt).cuda(), torch.from_numpy(v).to(tdt).cuda()
+    if aligned:
+        src_k, src_v = kt[None], vt[None]
+    else:
+        wide_k = torch.zeros((1, n, h, 129), dtype=tdt, device="cuda")
+        wide_v = torch.zeros((1, n, h, 129), dtype=tdt, device="cuda")
+        wide_k[0, :, :, 1:] = kt
+        wide_v[0, :, :, 1:] = vt
+        src_k, src_v = wide_k[..., 1:], wide_v[..., 1:]
+    extra = dict(key_mode="polar", key_bits=vb, outlier_frac=0.0) if key_mode == "polar" else {}
+    blocks = []
+    try:
+        for kind in (0, 1):
+            assert lib.tq_set_value_encoder(kind) == 0
+            ctx = _ctx(n_layers=1, n_seqs=1, n_kv_heads=h, n_q_heads=h, value_bits=vb,
+                       hot_window=w, max_tokens_per_seq=n + 8, kv_dtype=dt, seed=5, **extra)
+            # in two calls, so that the second one also reads rows from the hot ring
+            ctx.append(0, src_k[:, :700], src_v[:, :700])
+            ctx.append(0, src_k[:, 700:], src_v[:, 700:])
+            assert ctx.status() == 0
+            nb = ctx.lengths(0, 0)[1] // 256
+            assert nb >= 2
+            blocks.append([ctx.export_block(0, 0, i) for i in range(nb)])
+    finally:
+        lib.tq_set_value_encoder(0)
+    assert lib.tq_set_value_encoder(2) != 0
+    assert len(blocks[0]) == len(blocks[1])
+    for a, b in zip(*blocks):
+        assert a.keys() == b.keys()
+        for name in a:
+            if a[name] is None:
+                assert b[name] is None
+            else:
+                assert np.array_equal(np.asarray(a[name]), np.asarray(b[name])), name
+
+
 def test_batched_layers_ragged(torch_cuda):
     """Several layers and sequences with different lengths in one context; each cache is
     independent and matches its own oracle."""

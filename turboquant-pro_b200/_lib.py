@@ -105,6 +105,7 @@ SIGNATURES = {
                                     C.POINTER(C.c_double), C.c_void_p]),
     "tq_clear": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "tq_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
+    "tq_set_value_encoder": (C.c_int32, [C.c_int32]),
     "tq_decode_bytes": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_double)]),
     "tq_last_launches": (C.c_int32, [C.c_void_p]),
     "tq_set_kernel": (C.c_int32, [C.c_void_p, C.c_int32]),

@@ -980,6 +980,365 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
 }
 
 // ---------------------------------------------------------------------------------------
+// The same value encoder with the rotation on the fifth-generation tensor cores: both operands
+// of Y^T = Pi . U^T live in shared memory anyway, so the products are issued by one thread per
+// half as tcgen05.mma instructions (M = 128 channels, N = 16 tokens, K = 16 per instruction)
+// with the accumulators in tensor memory, and every thread reads back the 16 tokens of its own
+// channel with tcgen05.ld.  Operand split, slack and exact recomputation are those of the
+// kernel above; only the rotation and the ownership of the results (a thread owns a channel)
+// differ.
+//
+// Shared-memory operands are K-major without swizzling: 8 x 8 core matrices of 16-bit values
+// (8 rows of 16 bytes, 128 bytes each), "stride" 128 bytes to the next eight rows and
+// "leading" offset to the core matrix of the next eight input channels.  Pi (hi and lo parts)
+// is laid out once per CTA, the unit vectors per group.  Tensor memory: 64 columns per CTA,
+// 32 per half (16 for the hi*hi sum, 16 for the cross terms).  All waits are bounded.
+// ---------------------------------------------------------------------------------------
+TQ_DEV uint32_t enc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+TQ_DEV uint64_t umma_desc_k_major(uint32_t saddr, uint32_t leading_bytes, uint32_t stride_bytes) {
+  // start address, leading and stride byte offsets in 16-byte units; descriptor version 1;
+  // base offset 0, no swizzle
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((leading_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((stride_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+// fp16 x fp16 -> fp32, both operands K-major, M = 128, N = 16
+constexpr uint32_t UMMA_IDESC_M128_N16 = (1u << 4) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+TQ_DEV void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(UMMA_IDESC_M128_N16), "r"(accumulate)
+      : "memory");
+}
+TQ_DEV void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+TQ_DEV void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Enc5Half {
+  float xs[TQ_GROUP_TOK][ENCV_XS];  // the group's rows
+  // unit vectors as tensor-core operands, hi then lo part: [K / 8][2 token groups][8][8] fp16;
+  // once the rotation is done the area holds the list, codes and products of the recomputation
+  __align__(16) __half ub[2][TQ_GROUP_TOK * TQ_D];
+  uint32_t img[256];
+  float norm[TQ_GROUP_TOK];
+  unsigned long long bar;  // "this half's products are done"
+  int wl_n;
+  int pad_;
+};
+constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENCV_HALVES * (int)sizeof(Enc5Half) + 128 + 16;
+constexpr int ENC5_TMEM_COLS = 64;
+constexpr int ENC5_WAIT = 1 << 16;  // probes of the product barrier before a wait gives up
+
+template <int DT>
+__global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel(EncodeArgs a) {
+  const tq_geom& g = a.g;
+  const int e = threadIdx.x & (TQ_D - 1), half = threadIdx.x >> 7;
+  const int wq = e >> 5, lane = e & 31;
+  const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
+  const int total = a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
+  const int vb = g.value_bits;
+  const int n_bnd = (1 << vb) - 1;
+
+  extern __shared__ __align__(128) uint8_t enc5_smem[];
+  __half* pa = (__half*)enc5_smem;  // Pi: [hi | lo][K / 8][M / 8][8][8] fp16
+  Enc5Half* hs = (Enc5Half*)(enc5_smem + ENCV_PI_BYTES) + half;
+  float* s_bnd = (float*)(enc5_smem + ENCV_PI_BYTES + ENCV_HALVES * sizeof(Enc5Half));
+  uint32_t* s_tmem = (uint32_t*)(s_bnd + 32);
+  auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
+  const float* pi_rows = a.tables->pi;  // pi[ch][d]
+  const bool keys = a.polar_keys_pass != 0;
+  const void* in_base = keys ? a.k : a.v;
+  const void* ring_base = keys ? a.hot_k : a.hot_v;
+  const int out_off = keys ? 0 : g.v_off, nrm_off = keys ? g.scale_off : g.norm_off;
+  const bool rows_aligned = [&]() {
+    const int64_t epc = 16 / (int64_t)sizeof(typename Elem<DT>::type);
+    return ((uintptr_t)in_base & 15) == 0 && a.seq_stride % epc == 0 && a.tok_stride % epc == 0 &&
+           a.head_stride % epc == 0;
+  }();
+
+  // Pi as the A operand: element (ch, d) of part p at
+  // p * 32 KB + ((d / 8) * 16 + ch / 8) * 128 + (ch % 8) * 16 + (d % 8) * 2 bytes
+  for (int idx = threadIdx.x; idx < TQ_D * TQ_D / 2; idx += ENCV_HALVES * TQ_D) {
+    const int ch = idx >> 6, d = (idx & 63) * 2;
+    const float2 p = *(const float2*)&pi_rows[ch * TQ_D + d];
+    __half h0, l0, h1, l1;
+    split_h(p.x, h0, l0);
+    split_h(p.y, h1, l1);
+    const int off = ((d >> 3) * 16 + (ch >> 3)) * 64 + (ch & 7) * 8 + (d & 7);  // in halves
+    *(uint32_t*)&pa[off] = h2_bits(h0, h1);
+    *(uint32_t*)&pa[TQ_D * TQ_D + off] = h2_bits(l0, l1);
+  }
+  if (threadIdx.x < 16) s_bnd[1 + threadIdx.x] = a.tables->boundaries[threadIdx.x];
+  if (threadIdx.x == 16) s_bnd[0] = -INFINITY;
+  if (threadIdx.x == 17) s_bnd[17] = INFINITY;
+  if (e == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(enc_smem(&hs->bar)), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 32) {  // one warp allocates the CTA's tensor memory ...
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(enc_smem(s_tmem)),
+                 "r"(ENC5_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // Pi is read by the tensor cores
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *(volatile uint32_t*)s_tmem + (uint32_t)(half * 32);  // this half's columns
+  const uint32_t pa_addr = enc_smem(pa), ub_addr = enc_smem(&hs->ub[0][0]);
+  const uint32_t bar = enc_smem(&hs->bar);
+  unsigned phase = 0;
+
+  for (int w = blockIdx.x * ENCV_HALVES + half; w < total; w += gridDim.x * ENCV_HALVES) {
+    int gq = w % groups;
+    int rr = w / groups;
+    int jb = rr % a.max_new_blocks;
+    rr /= a.max_new_blocks;
+    int head = rr % g.n_kv_heads;
+    int seq = a.seq_begin + rr / g.n_kv_heads;
+    const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
+    const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
+    const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
+    const int blk = nb0 + jb;
+    if (blk >= nb1) continue;  // uniform over the half
+    const int S = g.block_tokens;
+    const TokenSource<DT> src = make_source<DT>(a, ring_base, in_base, seq, head, n0);
+    uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
+
+    if (e == 0) hs->wl_n = 0;
+    hs->img[e] = 0u;
+    hs->img[e + 128] = 0u;
+    {
+      using T = typename Elem<DT>::type;
+      const int tok0 = gq * TQ_GROUP_TOK, pos0 = blk * S + tok0;
+      const int ring0 = pos0 % src.cap;
+      auto row_of = [&](int t) -> const T* {  // token t of the group (clamped)
+        const int te = min(t, S - 1 - tok0);
+        const int pos = pos0 + te;
+        int ri = ring0 + te;
+        ri -= ri >= src.cap ? src.cap : 0;
+        return pos < n0 ? (const T*)src.ring + (size_t)ri * TQ_D
+                        : (const T*)src.in + (size_t)(pos - n0) * src.tok_stride;
+      };
+      if (rows_aligned) {
+        constexpr int EPC = 16 / (int)sizeof(T), CH = TQ_D / EPC, NCH = TQ_GROUP_TOK * CH / TQ_D;
+        uint4 raw[NCH];
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+          const int id = e + TQ_D * i;
+          raw[i] = *(const uint4*)(row_of(id / CH) + (id % CH) * EPC);
+        }
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+          const int id = e + TQ_D * i, t = id / CH, c0 = (id % CH) * EPC;
+          const bool live = tok0 + t < S;
+          const T* pv = (const T*)&raw[i];
+          float f[EPC];
+#pragma unroll
+          for (int k = 0; k < EPC; ++k) f[k] = live ? Elem<DT>::ld(pv, k) : 0.0f;
+#pragma unroll
+          for (int k = 0; k < EPC; k += 4)
+            *(float4*)&hs->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
+        }
+      } else {
+        float xv[TQ_GROUP_TOK];
+#pragma unroll
+        for (int t = 0; t < TQ_GROUP_TOK; ++t) xv[t] = Elem<DT>::ld(row_of(t), e);
+#pragma unroll
+        for (int t = 0; t < TQ_GROUP_TOK; ++t) hs->xs[t][e] = tok0 + t < S ? xv[t] : 0.0f;
+      }
+    }
+    half_sync();
+    {  // norms (numpy's 8-accumulator order) and the unit vectors as the B operand: element
+       // (token t, channel d) of part p at p * 4 KB + ((d / 8) * 2 + t / 8) * 128 + (t % 8) * 16
+       // + (d % 8) * 2 bytes
+      const int t = e >> 3, j = e & 7;
+      float xr[TQ_D / 8];
+#pragma unroll
+      for (int i = 0; i < TQ_D / 8; ++i) xr[i] = hs->xs[t][8 * i + j];
+      float sq = __fmul_rn(xr[0], xr[0]);
+#pragma unroll
+      for (int i = 1; i < TQ_D / 8; ++i) sq = __fadd_rn(sq, __fmul_rn(xr[i], xr[i]));
+      sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 1));
+      sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 2));
+      sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 4));
+      const float nrm = __fsqrt_rn(sq);
+      if (j == 0) {
+        hs->norm[t] = nrm;
+        ((float*)(page + nrm_off))[gq * TQ_GROUP_TOK + t] = nrm;
+      }
+      const float inv = 1.0f / fmaxf(nrm, 1e-30f);
+#pragma unroll
+      for (int i = 0; i < TQ_D / 8; ++i) {
+        __half h, l;
+        split_h(xr[i] * inv, h, l);
+        const int off = (i * 2 + (t >> 3)) * 64 + (t & 7) * 8 + j;  // in halves
+        hs->ub[0][off] = h;
+        hs->ub[1][off] = l;
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // ... read by the tensor cores
+    half_sync();
+    if (e == 0) {
+      // hi*hi into columns 0-15, hi*lo + lo*hi into columns 16-31; eight K steps each
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int kb = 0; kb < 8; ++kb) {
+        const uint64_t a_hi = umma_desc_k_major(pa_addr + kb * 4096, 2048, 128);
+        const uint64_t a_lo = umma_desc_k_major(pa_addr + TQ_D * TQ_D * 2 + kb * 4096, 2048, 128);
+        const uint64_t b_hi = umma_desc_k_major(ub_addr + kb * 512, 256, 128);
+        const uint64_t b_lo = umma_desc_k_major(ub_addr + TQ_GROUP_TOK * TQ_D * 2 + kb * 512, 256, 128);
+        umma_f16_ss(tmem, a_hi, b_hi, kb > 0);
+        umma_f16_ss(tmem + 16, a_hi, b_lo, kb > 0);
+        umma_f16_ss(tmem + 16, a_lo, b_hi, 1u);
+      }
+      umma_commit(bar);
+    }
+    {  // bounded wait for the products
+      int n = 0;
+      unsigned done = 0;
+      while (!done) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(phase)
+            : "memory");
+        if (!done && ++n >= ENC5_WAIT) {
+          atomicOr(a.status, TQ_STATUS_WAIT_TIMEOUT);
+          break;
+        }
+      }
+      phase ^= 1u;
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float y[TQ_GROUP_TOK];
+    {
+      float cx[TQ_GROUP_TOK];
+      const uint32_t taddr = tmem + ((uint32_t)(32 * wq) << 16);  // this warp's 32 lanes
+      tmem_ld16(taddr, y);
+      tmem_ld16(taddr + 16, cx);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) y[t] = fmaf(cx[t], 1.0f / 2048.0f, y[t]);
+    }
+    // thread e owns channel e: codes of its 16 tokens by bisection, exact recomputation where a
+    // boundary lies within the slack
+    const int ch = 32 * wq + lane;
+    int code[TQ_GROUP_TOK];
+#pragma unroll
+    for (int t = 0; t < TQ_GROUP_TOK; ++t) code[t] = 0;
+    for (int step = (n_bnd + 1) >> 1; step > 0; step >>= 1) {
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t)
+        code[t] += (s_bnd[code[t] + step] < y[t]) ? step : 0;
+    }
+    unsigned redo = 0u;
+#pragma unroll
+    for (int t = 0; t < TQ_GROUP_TOK; ++t) {
+      const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
+      redo |= (y[t] - below < ROT_SLACK || above - y[t] < ROT_SLACK) ? (1u << t) : 0u;
+    }
+    {
+      // (every thread has seen the products complete, so the operand area is free)
+      unsigned short* wl = (unsigned short*)&hs->ub[0][0];                // (channel, token) items
+      unsigned char* fixed = (unsigned char*)(wl + TQ_D * TQ_GROUP_TOK);   // [token][channel] codes
+      float* prod = (float*)(fixed + TQ_D * TQ_GROUP_TOK) + wq * TQ_D;     // this warp's products
+      unsigned todo = redo;
+      while (todo) {
+        const int t = __ffs((int)todo) - 1;
+        todo &= todo - 1;
+        wl[atomicAdd(&hs->wl_n, 1)] = (unsigned short)(ch | (t << 8));
+      }
+      half_sync();
+      const int n_items = hs->wl_n;
+      for (int it = wq; it < n_items; it += TQ_D / 32) {
+        const int item = wl[it], c2 = item & 255, t2 = item >> 8;
+        const float safe = fmaxf(hs->norm[t2], 1e-30f);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int dd = 32 * k + lane;
+          prod[dd] = __fmul_rn(__fdiv_rn(hs->xs[t2][dd], safe), __ldg(&pi_rows[c2 * TQ_D + dd]));
+        }
+        __syncwarp();
+        if (lane == 0) {
+          float4 p4 = *(const float4*)&prod[0];
+          float yy = __fadd_rn(__fadd_rn(__fadd_rn(p4.x, p4.y), p4.z), p4.w);
+#pragma unroll 8
+          for (int q = 1; q < TQ_D / 4; ++q) {
+            p4 = *(const float4*)&prod[4 * q];
+            yy = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(yy, p4.x), p4.y), p4.z), p4.w);
+          }
+          int cd = 0;
+          for (int j = 0; j < n_bnd; ++j) cd += (s_bnd[1 + j] < yy) ? 1 : 0;
+          fixed[t2 * TQ_D + c2] = (unsigned char)cd;
+        }
+        __syncwarp();
+      }
+      half_sync();
+      while (redo) {
+        const int t = __ffs((int)redo) - 1;
+        redo &= redo - 1;
+        const int cd = fixed[t * TQ_D + ch];
+#pragma unroll
+        for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? cd : code[tt];
+      }
+    }
+    // pack this channel's 8 token pairs into the group image
+    uint32_t* img = hs->img;
+    const int dq = ch & 7, i16 = ch >> 3;  // record lane group and slot of this thread's channel
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int ta = 2 * c + 8 * h;
+        const int l = dq * 4 + c, p = 2 * i16 + h;
+        if (vb == 4) {
+          ((uint8_t*)img)[v_record_byte_off(4, l, p)] = (uint8_t)(code[ta] | (code[ta + 1] << 4));
+        } else {
+          const uint32_t f = (uint32_t)(code[ta] | (code[ta + 1] << 3));
+          const int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
+          atomicOr(&img[((wd >> 1) * 256 + l * 8 + (wd & 1) * 4) >> 2], f << sh);
+          if (sh > 26)
+            atomicOr(&img[((((wd + 1) >> 1)) * 256 + l * 8 + ((wd + 1) & 1) * 4) >> 2],
+                     f >> (32 - sh));
+        }
+      }
+    }
+    half_sync();
+    uint32_t* dst = (uint32_t*)(page + out_off + (size_t)gq * v_group_bytes(vb));
+    const int words = v_group_bytes(vb) / 4;
+    for (int i = e; i < words; i += TQ_D) dst[i] = img[i];
+    half_sync();  // the image is zeroed again at the top of the next item
+  }
+  // ... and the same warp gives the tensor memory back
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*(volatile uint32_t*)s_tmem),
+                 "r"(ENC5_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Hot-ring writer: the new tokens that stay uncompressed go to slot (position % hot_cap).
 // grid = (tokens, heads, seqs); token index counts back from the newest.  The CTA that
 // finishes last then adds the new tokens to the sequence lengths: every kernel of the append
@@ -1035,6 +1394,8 @@ __global__ void clear_kernel(int32_t* seq_len, uint32_t* cursor, int layer, int 
     cursor[((size_t)layer * n_seqs + seq_begin) * n_heads + i] = 0u;
 }
 
+int g_value_encoder = 0;  // 0: rotation on mma.sync; 1: on tcgen05.mma (tq_set_value_encoder)
+
 template <int DT>
 int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t st, int* launches) {
   const tq_geom& g = a.g;
@@ -1064,12 +1425,25 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, ENCV_SMEM));
       attr_set[device & 15] = true;
     }
+    static bool attr5_set[16] = {};
+    const bool tc5 = g_value_encoder == 1;
+    if (tc5 && !attr5_set[device & 15]) {
+      TQ_CUDA(cudaFuncSetAttribute(encode_values_tc5_kernel<DT>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, ENC5_SMEM));
+      attr5_set[device & 15] = true;
+    }
+    auto values = [&](const EncodeArgs& av) {
+      if (tc5)
+        encode_values_tc5_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENC5_SMEM, st>>>(av);
+      else
+        encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(av);
+    };
     if (g.key_mode == TQ_KEYS_POLAR) {
       EncodeArgs ak = a;
       ak.polar_keys_pass = 1;
-      encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(ak);
+      values(ak);
     }
-    encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(a);
+    values(a);
     *launches += 2;
   }
   // (launched so that it may be scheduled while the kernel before it in the stream drains; it
@@ -1089,6 +1463,12 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
 }
 
 }  // namespace
+
+extern "C" int32_t tq_set_value_encoder(int32_t kind) {
+  TQ_REQUIRE(kind == 0 || kind == 1, TQ_ERR_INVALID, "value encoder: 0 (mma.sync) or 1 (tcgen05)");
+  g_value_encoder = kind;
+  return TQ_OK;
+}
 
 int tq_launch_encode(tq_ctx* ctx, int layer, int seq_begin, int seq_count, const void* k,
                      const void* v, int n_tokens, int64_t seq_stride, int64_t tok_stride,
