@@ -1027,51 +1027,85 @@ TQ_DEV void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-struct Enc5Half {
+// One CTA per SM: four independent parts of 128 threads share one copy of Pi.  A part works
+// on two 16-token groups at a time: while the tensor cores rotate group i + 1 and the rows of
+// group i + 2 are on their way from global memory, its threads turn the products of group i
+// into codes.
+//
+// A product that lies within the slack of a boundary is not recomputed on the spot: the part
+// puts (row, destination, norm, channel, token, code) on a list, and the list is worked off
+// when the part has run out of groups (or the list is full): a thread per entry computes the
+// exact sum in the reference's order and, where the code differs, flips the bits of the code in
+// the page.
+// The main loop then has three barriers per group and no serial tail.
+constexpr int ENC5_PARTS = 4;
+constexpr int ENC5_LIST = 160;  // entries of a part's list
+struct Enc5Stage {
   float xs[TQ_GROUP_TOK][ENCV_XS];  // the group's rows
   // unit vectors as tensor-core operands, hi then lo part: [K / 8][2 token groups][8][8] fp16;
   // once the rotation is done the area holds the list, codes and products of the recomputation
   __align__(16) __half ub[2][TQ_GROUP_TOK * TQ_D];
   uint32_t img[256];
   float norm[TQ_GROUP_TOK];
-  unsigned long long bar;  // "this half's products are done"
-  int wl_n;
-  int pad_;
+  unsigned long long bar;  // "this stage's products are done"
+  const void* rowp[TQ_GROUP_TOK];  // where each token's row came from (null: padding)
+  uint32_t* dst;                   // the group's codes in the page
+  int pad_[2];
 };
-constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENCV_HALVES * (int)sizeof(Enc5Half) + 128 + 16;
-constexpr int ENC5_TMEM_COLS = 64;
-constexpr int ENC5_WAIT = 1 << 16;  // probes of the product barrier before a wait gives up
+struct Enc5Part {
+  Enc5Stage st[2];
+};
+struct Enc5List {
+  const void* row[ENC5_LIST];
+  uint32_t* dst[ENC5_LIST];
+  float norm[ENC5_LIST];
+  uint32_t meta[ENC5_LIST];  // channel | token << 8 | code << 12
+  int cnt;                   // appends tried (may exceed the capacity)
+  int pad_[3];
+};
+static_assert(sizeof(Enc5Stage) % 16 == 0 && sizeof(Enc5List) % 16 == 0, "16-byte operands");
+constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENC5_PARTS * (int)(sizeof(Enc5Part) + sizeof(Enc5List)) +
+                          128 + 16;
+static_assert(ENC5_SMEM <= 227 * 1024, "shared memory of one CTA");
+constexpr int ENC5_TMEM_COLS = 256;  // 4 parts x 2 stages x (16 + 16) columns
+constexpr int ENC5_WAIT = 1 << 16;   // probes of the product barrier before a wait gives up
 
 template <int DT>
-__global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel(EncodeArgs a) {
+__global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(EncodeArgs a) {
+  using T = typename Elem<DT>::type;
+  constexpr int EPC = 16 / (int)sizeof(T), CH = TQ_D / EPC, NCH = TQ_GROUP_TOK * CH / TQ_D;
   const tq_geom& g = a.g;
-  const int e = threadIdx.x & (TQ_D - 1), half = threadIdx.x >> 7;
+  const int e = threadIdx.x & (TQ_D - 1), part = threadIdx.x >> 7;
   const int wq = e >> 5, lane = e & 31;
   const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
   const int total = a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
   const int vb = g.value_bits;
   const int n_bnd = (1 << vb) - 1;
+  const int S = g.block_tokens;
 
   extern __shared__ __align__(128) uint8_t enc5_smem[];
   __half* pa = (__half*)enc5_smem;  // Pi: [hi | lo][K / 8][M / 8][8][8] fp16
-  Enc5Half* hs = (Enc5Half*)(enc5_smem + ENCV_PI_BYTES) + half;
-  float* s_bnd = (float*)(enc5_smem + ENCV_PI_BYTES + ENCV_HALVES * sizeof(Enc5Half));
+  Enc5Part* ps = (Enc5Part*)(enc5_smem + ENCV_PI_BYTES) + part;
+  Enc5List* df =
+      (Enc5List*)(enc5_smem + ENCV_PI_BYTES + ENC5_PARTS * sizeof(Enc5Part)) + part;
+  float* s_bnd =
+      (float*)(enc5_smem + ENCV_PI_BYTES + ENC5_PARTS * (sizeof(Enc5Part) + sizeof(Enc5List)));
   uint32_t* s_tmem = (uint32_t*)(s_bnd + 32);
-  auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(TQ_D) : "memory"); };
+  auto part_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + part), "n"(TQ_D) : "memory"); };
   const float* pi_rows = a.tables->pi;  // pi[ch][d]
   const bool keys = a.polar_keys_pass != 0;
   const void* in_base = keys ? a.k : a.v;
   const void* ring_base = keys ? a.hot_k : a.hot_v;
   const int out_off = keys ? 0 : g.v_off, nrm_off = keys ? g.scale_off : g.norm_off;
   const bool rows_aligned = [&]() {
-    const int64_t epc = 16 / (int64_t)sizeof(typename Elem<DT>::type);
+    const int64_t epc = EPC;
     return ((uintptr_t)in_base & 15) == 0 && a.seq_stride % epc == 0 && a.tok_stride % epc == 0 &&
            a.head_stride % epc == 0;
   }();
 
   // Pi as the A operand: element (ch, d) of part p at
   // p * 32 KB + ((d / 8) * 16 + ch / 8) * 128 + (ch % 8) * 16 + (d % 8) * 2 bytes
-  for (int idx = threadIdx.x; idx < TQ_D * TQ_D / 2; idx += ENCV_HALVES * TQ_D) {
+  for (int idx = threadIdx.x; idx < TQ_D * TQ_D / 2; idx += ENC5_PARTS * TQ_D) {
     const int ch = idx >> 6, d = (idx & 63) * 2;
     const float2 p = *(const float2*)&pi_rows[ch * TQ_D + d];
     __half h0, l0, h1, l1;
@@ -1084,8 +1118,10 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
   if (threadIdx.x < 16) s_bnd[1 + threadIdx.x] = a.tables->boundaries[threadIdx.x];
   if (threadIdx.x == 16) s_bnd[0] = -INFINITY;
   if (threadIdx.x == 17) s_bnd[17] = INFINITY;
-  if (e == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(enc_smem(&hs->bar)), "r"(1) : "memory");
+  if (e == 2) df->cnt = 0;
+  if (e < 2) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(enc_smem(&ps->st[e].bar)), "r"(1)
+                 : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (threadIdx.x < 32) {  // one warp allocates the CTA's tensor memory ...
@@ -1099,71 +1135,103 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *(volatile uint32_t*)s_tmem + (uint32_t)(half * 32);  // this half's columns
-  const uint32_t pa_addr = enc_smem(pa), ub_addr = enc_smem(&hs->ub[0][0]);
-  const uint32_t bar = enc_smem(&hs->bar);
-  unsigned phase = 0;
+  const uint32_t tmem = *(volatile uint32_t*)s_tmem + (uint32_t)(part * 64);  // this part's columns
+  const uint32_t pa_addr = enc_smem(pa);
 
-  for (int w = blockIdx.x * ENCV_HALVES + half; w < total; w += gridDim.x * ENCV_HALVES) {
-    int gq = w % groups;
-    int rr = w / groups;
-    int jb = rr % a.max_new_blocks;
-    rr /= a.max_new_blocks;
-    int head = rr % g.n_kv_heads;
-    int seq = a.seq_begin + rr / g.n_kv_heads;
-    const int n0 = a.seq_len[a.layer * g.n_seqs + seq];
-    const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
-    const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
-    const int blk = nb0 + jb;
-    if (blk >= nb1) continue;  // uniform over the half
-    const int S = g.block_tokens;
-    const TokenSource<DT> src = make_source<DT>(a, ring_base, in_base, seq, head, n0);
-    uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
+  // the groups of this part, in order; a group whose block this call does not flush is skipped
+  struct Item {
+    bool live;
+    int gq, lim, n0, pos0, ring0, cap;
+    const T* ring;
+    const T* in;
+    int64_t tok_stride;
+    uint8_t* page;
+  };
+  int w_next = blockIdx.x * ENC5_PARTS + part;
+  const int w_step = gridDim.x * ENC5_PARTS;
+  int seq_known = -1, n0_known = 0;  // (consecutive groups mostly belong to one sequence)
+  auto advance = [&](Item& it) {
+    it.live = false;
+    while (w_next < total) {
+      const int w = w_next;
+      w_next += w_step;
+      const int gq = w % groups;
+      int rr = w / groups;
+      const int jb = rr % a.max_new_blocks;
+      rr /= a.max_new_blocks;
+      const int head = rr % g.n_kv_heads;
+      const int seq = a.seq_begin + rr / g.n_kv_heads;
+      if (seq != seq_known) {
+        n0_known = a.seq_len[a.layer * g.n_seqs + seq];
+        seq_known = seq;
+      }
+      const int n0 = n0_known;
+      const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
+      const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
+      const int blk = nb0 + jb;
+      if (blk >= nb1) continue;
+      const TokenSource<DT> src = make_source<DT>(a, ring_base, in_base, seq, head, n0);
+      it.live = true;
+      it.gq = gq;
+      it.lim = S - gq * TQ_GROUP_TOK;  // tokens of the group inside the block
+      it.n0 = n0;
+      it.pos0 = blk * S + gq * TQ_GROUP_TOK;
+      it.cap = src.cap;
+      it.ring0 = it.pos0 % src.cap;
+      it.ring = (const T*)src.ring;
+      it.in = (const T*)src.in;
+      it.tok_stride = src.tok_stride;
+      it.page = a.pages + page_offset(g, a.layer, seq, head, blk);
+      return;
+    }
+  };
+  auto row_of = [&](const Item& it, int t) -> const T* {  // token t of the group (clamped)
+    const int te = min(t, it.lim - 1);
+    const int pos = it.pos0 + te;
+    int ri = it.ring0 + te;
+    ri -= ri >= it.cap ? it.cap : 0;
+    return pos < it.n0 ? it.ring + (size_t)ri * TQ_D : it.in + (size_t)(pos - it.n0) * it.tok_stride;
+  };
+  uint4 raw[NCH];
+  auto fetch = [&](const Item& it) {  // this thread's 16-byte pieces of the group's rows
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int id = e + TQ_D * i;
+      raw[i] = *(const uint4*)(row_of(it, id / CH) + (id % CH) * EPC);
+    }
+  };
+  bool gave_up = false;
 
-    if (e == 0) hs->wl_n = 0;
+  // stage `sb` <- the group `it` (rows in `raw` if the rows are aligned): rows, norms, unit
+  // vectors, and the products started
+  auto stage_in = [&](const Item& it, int sb) {
+    Enc5Stage* hs = &ps->st[sb];
+    if (rows_aligned) {
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
+        const int id = e + TQ_D * i, t = id / CH, c0 = (id % CH) * EPC;
+        const bool live = t < it.lim;
+        const T* pv = (const T*)&raw[i];
+        float f[EPC];
+#pragma unroll
+        for (int k = 0; k < EPC; ++k) f[k] = live ? Elem<DT>::ld(pv, k) : 0.0f;
+#pragma unroll
+        for (int k = 0; k < EPC; k += 4)
+          *(float4*)&hs->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
+      }
+    } else {
+      float xv[TQ_GROUP_TOK];
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) xv[t] = Elem<DT>::ld(row_of(it, t), e);
+#pragma unroll
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) hs->xs[t][e] = t < it.lim ? xv[t] : 0.0f;
+    }
+    part_sync();
+    if (e < TQ_GROUP_TOK) hs->rowp[e] = e < it.lim ? (const void*)row_of(it, e) : nullptr;
+    if (e == TQ_GROUP_TOK)
+      hs->dst = (uint32_t*)(it.page + out_off + (size_t)it.gq * v_group_bytes(vb));
     hs->img[e] = 0u;
     hs->img[e + 128] = 0u;
-    {
-      using T = typename Elem<DT>::type;
-      const int tok0 = gq * TQ_GROUP_TOK, pos0 = blk * S + tok0;
-      const int ring0 = pos0 % src.cap;
-      auto row_of = [&](int t) -> const T* {  // token t of the group (clamped)
-        const int te = min(t, S - 1 - tok0);
-        const int pos = pos0 + te;
-        int ri = ring0 + te;
-        ri -= ri >= src.cap ? src.cap : 0;
-        return pos < n0 ? (const T*)src.ring + (size_t)ri * TQ_D
-                        : (const T*)src.in + (size_t)(pos - n0) * src.tok_stride;
-      };
-      if (rows_aligned) {
-        constexpr int EPC = 16 / (int)sizeof(T), CH = TQ_D / EPC, NCH = TQ_GROUP_TOK * CH / TQ_D;
-        uint4 raw[NCH];
-#pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-          const int id = e + TQ_D * i;
-          raw[i] = *(const uint4*)(row_of(id / CH) + (id % CH) * EPC);
-        }
-#pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-          const int id = e + TQ_D * i, t = id / CH, c0 = (id % CH) * EPC;
-          const bool live = tok0 + t < S;
-          const T* pv = (const T*)&raw[i];
-          float f[EPC];
-#pragma unroll
-          for (int k = 0; k < EPC; ++k) f[k] = live ? Elem<DT>::ld(pv, k) : 0.0f;
-#pragma unroll
-          for (int k = 0; k < EPC; k += 4)
-            *(float4*)&hs->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
-        }
-      } else {
-        float xv[TQ_GROUP_TOK];
-#pragma unroll
-        for (int t = 0; t < TQ_GROUP_TOK; ++t) xv[t] = Elem<DT>::ld(row_of(t), e);
-#pragma unroll
-        for (int t = 0; t < TQ_GROUP_TOK; ++t) hs->xs[t][e] = tok0 + t < S ? xv[t] : 0.0f;
-      }
-    }
-    half_sync();
     {  // norms (numpy's 8-accumulator order) and the unit vectors as the B operand: element
        // (token t, channel d) of part p at p * 4 KB + ((d / 8) * 2 + t / 8) * 128 + (t % 8) * 16
        // + (d % 8) * 2 bytes
@@ -1180,7 +1248,7 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
       const float nrm = __fsqrt_rn(sq);
       if (j == 0) {
         hs->norm[t] = nrm;
-        ((float*)(page + nrm_off))[gq * TQ_GROUP_TOK + t] = nrm;
+        ((float*)(it.page + nrm_off))[it.gq * TQ_GROUP_TOK + t] = nrm;
       }
       const float inv = 1.0f / fmaxf(nrm, 1e-30f);
 #pragma unroll
@@ -1193,23 +1261,109 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // ... read by the tensor cores
-    half_sync();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    part_sync();
     if (e == 0) {
       // hi*hi into columns 0-15, hi*lo + lo*hi into columns 16-31; eight K steps each
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t ub_addr = enc_smem(&hs->ub[0][0]);
+      const uint32_t d_main = tmem + (uint32_t)(sb * 32);
 #pragma unroll
       for (int kb = 0; kb < 8; ++kb) {
         const uint64_t a_hi = umma_desc_k_major(pa_addr + kb * 4096, 2048, 128);
         const uint64_t a_lo = umma_desc_k_major(pa_addr + TQ_D * TQ_D * 2 + kb * 4096, 2048, 128);
         const uint64_t b_hi = umma_desc_k_major(ub_addr + kb * 512, 256, 128);
         const uint64_t b_lo = umma_desc_k_major(ub_addr + TQ_GROUP_TOK * TQ_D * 2 + kb * 512, 256, 128);
-        umma_f16_ss(tmem, a_hi, b_hi, kb > 0);
-        umma_f16_ss(tmem + 16, a_hi, b_lo, kb > 0);
-        umma_f16_ss(tmem + 16, a_lo, b_hi, 1u);
+        umma_f16_ss(d_main, a_hi, b_hi, kb > 0);
+        umma_f16_ss(d_main + 16, a_hi, b_lo, kb > 0);
+        umma_f16_ss(d_main + 16, a_lo, b_hi, 1u);
       }
-      umma_commit(bar);
+      umma_commit(enc_smem(&hs->bar));
     }
-    {  // bounded wait for the products
+  };
+
+  // tokens `bits` of channel `ch` of the stage's group go on the list; returns the ones that
+  // did not fit
+  auto list_add = [&](const Enc5Stage* hs, unsigned bits, unsigned long long packed, int ch) {
+    unsigned left = 0u;
+    while (bits) {
+      const int t = __ffs((int)bits) - 1;
+      bits &= bits - 1;
+      const void* row = hs->rowp[t];
+      if (row == nullptr) continue;  // padding: all zeros, the products are exact
+      const int i = atomicAdd(&df->cnt, 1);
+      if (i < ENC5_LIST) {
+        df->row[i] = row;
+        df->dst[i] = hs->dst;
+        df->norm[i] = hs->norm[t];
+        df->meta[i] = (uint32_t)ch | ((uint32_t)t << 8) | ((uint32_t)((packed >> (4 * t)) & 15ull) << 12);
+      } else {
+        left |= 1u << t;
+      }
+    }
+    return left;
+  };
+  // the first n entries of the list, one per thread: exact sum in the reference's order (the
+  // quotients and products rounded one by one, added up in sequence), the code it gives, and
+  // the difference to the stored code flipped in the page.  Ends with the list empty; every
+  // thread of the part calls it.
+  auto list_flush = [&](int n) {
+    for (int i = e; i < n; i += TQ_D) {
+      const T* row = (const T*)df->row[i];
+      const uint32_t meta = df->meta[i];
+      const int c2 = (int)(meta & 255u), t2 = (int)((meta >> 8) & 15u);
+      const float safe = fmaxf(df->norm[i], 1e-30f);
+      const float* pr = pi_rows + c2 * TQ_D;
+      float yy = 0.0f;
+#pragma unroll 2
+      for (int d0 = 0; d0 < TQ_D; d0 += 8) {
+        float x[8];
+        if (rows_aligned) {
+          uint4 rw[8 / EPC];
+#pragma unroll
+          for (int k = 0; k < 8 / EPC; ++k) rw[k] = *(const uint4*)(row + d0 + k * EPC);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) x[k] = Elem<DT>::ld((const T*)rw, k);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) x[k] = Elem<DT>::ld(row, d0 + k);
+        }
+        const float4 pa4 = __ldg((const float4*)(pr + d0)), pb4 = __ldg((const float4*)(pr + d0 + 4));
+        const float pv[8] = {pa4.x, pa4.y, pa4.z, pa4.w, pb4.x, pb4.y, pb4.z, pb4.w};
+        float pd[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pd[k] = __fmul_rn(__fdiv_rn(x[k], safe), pv[k]);
+        // ((p0 + p1) + p2) + ... : the first product starts the sum
+        yy = d0 == 0 ? pd[0] : __fadd_rn(yy, pd[0]);
+#pragma unroll
+        for (int k = 1; k < 8; ++k) yy = __fadd_rn(yy, pd[k]);
+      }
+      int cd = 0;
+      for (int j = 0; j < n_bnd; ++j) cd += (s_bnd[1 + j] < yy) ? 1 : 0;
+      const uint32_t delta = (uint32_t)cd ^ (meta >> 12);
+      if (delta) {
+        const int l = v_lane(t2, c2), bit = 2 * vb * v_pair(t2, c2) + vb * (t2 & 1);
+        const uint32_t v = delta << (bit & 7);
+        uint32_t* d32 = df->dst[i];
+        const int off0 = v_record_byte_off(vb, l, bit >> 3);
+        if (v & 255u) atomicXor(&d32[off0 >> 2], (v & 255u) << ((off0 & 3) * 8));
+        if (v >> 8) {
+          const int off1 = v_record_byte_off(vb, l, (bit >> 3) + 1);
+          atomicXor(&d32[off1 >> 2], (v >> 8) << ((off1 & 3) * 8));
+        }
+      }
+    }
+    part_sync();
+    if (e == 0) df->cnt = 0;
+    part_sync();
+  };
+
+  // stage `sb` -> the page: codes of the group whose products were started at the stage's
+  // previous use
+  auto stage_out = [&](int sb, unsigned parity) {
+    Enc5Stage* hs = &ps->st[sb];
+    if (!gave_up) {  // bounded wait for the products
+      const uint32_t bar = enc_smem(&hs->bar);
       int n = 0;
       unsigned done = 0;
       while (!done) {
@@ -1217,20 +1371,20 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}\n"
             : "=r"(done)
-            : "r"(bar), "r"(phase)
+            : "r"(bar), "r"(parity)
             : "memory");
         if (!done && ++n >= ENC5_WAIT) {
           atomicOr(a.status, TQ_STATUS_WAIT_TIMEOUT);
+          gave_up = true;  // (no later wait of this thread probes again)
           break;
         }
       }
-      phase ^= 1u;
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float y[TQ_GROUP_TOK];
     {
       float cx[TQ_GROUP_TOK];
-      const uint32_t taddr = tmem + ((uint32_t)(32 * wq) << 16);  // this warp's 32 lanes
+      const uint32_t taddr = tmem + (uint32_t)(sb * 32) + ((uint32_t)(32 * wq) << 16);
       tmem_ld16(taddr, y);
       tmem_ld16(taddr + 16, cx);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -1255,50 +1409,11 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
       const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
       redo |= (y[t] - below < ROT_SLACK || above - y[t] < ROT_SLACK) ? (1u << t) : 0u;
     }
-    {
-      // (every thread has seen the products complete, so the operand area is free)
-      unsigned short* wl = (unsigned short*)&hs->ub[0][0];                // (channel, token) items
-      unsigned char* fixed = (unsigned char*)(wl + TQ_D * TQ_GROUP_TOK);   // [token][channel] codes
-      float* prod = (float*)(fixed + TQ_D * TQ_GROUP_TOK) + wq * TQ_D;     // this warp's products
-      unsigned todo = redo;
-      while (todo) {
-        const int t = __ffs((int)todo) - 1;
-        todo &= todo - 1;
-        wl[atomicAdd(&hs->wl_n, 1)] = (unsigned short)(ch | (t << 8));
-      }
-      half_sync();
-      const int n_items = hs->wl_n;
-      for (int it = wq; it < n_items; it += TQ_D / 32) {
-        const int item = wl[it], c2 = item & 255, t2 = item >> 8;
-        const float safe = fmaxf(hs->norm[t2], 1e-30f);
+    unsigned long long packed = 0ull;  // the codes as computed, for the list
+    if (redo) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int dd = 32 * k + lane;
-          prod[dd] = __fmul_rn(__fdiv_rn(hs->xs[t2][dd], safe), __ldg(&pi_rows[c2 * TQ_D + dd]));
-        }
-        __syncwarp();
-        if (lane == 0) {
-          float4 p4 = *(const float4*)&prod[0];
-          float yy = __fadd_rn(__fadd_rn(__fadd_rn(p4.x, p4.y), p4.z), p4.w);
-#pragma unroll 8
-          for (int q = 1; q < TQ_D / 4; ++q) {
-            p4 = *(const float4*)&prod[4 * q];
-            yy = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(yy, p4.x), p4.y), p4.z), p4.w);
-          }
-          int cd = 0;
-          for (int j = 0; j < n_bnd; ++j) cd += (s_bnd[1 + j] < yy) ? 1 : 0;
-          fixed[t2 * TQ_D + c2] = (unsigned char)cd;
-        }
-        __syncwarp();
-      }
-      half_sync();
-      while (redo) {
-        const int t = __ffs((int)redo) - 1;
-        redo &= redo - 1;
-        const int cd = fixed[t * TQ_D + ch];
-#pragma unroll
-        for (int tt = 0; tt < TQ_GROUP_TOK; ++tt) code[tt] = tt == t ? cd : code[tt];
-      }
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) packed |= (unsigned long long)code[t] << (4 * t);
+      redo = list_add(hs, redo, packed, ch);
     }
     // pack this channel's 8 token pairs into the group image
     uint32_t* img = hs->img;
@@ -1321,12 +1436,38 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_tc5_kernel
         }
       }
     }
-    half_sync();
-    uint32_t* dst = (uint32_t*)(page + out_off + (size_t)gq * v_group_bytes(vb));
+    part_sync();
+    uint32_t* dst = hs->dst;
     const int words = v_group_bytes(vb) / 4;
     for (int i = e; i < words; i += TQ_D) dst[i] = img[i];
-    half_sync();  // the image is zeroed again at the top of the next item
+    // (the image is zeroed again after the first barrier of the stage's next use)
+    int tried = df->cnt;  // the same for every thread: nobody appends before the next group
+    while (tried > ENC5_LIST) {  // some entries did not fit: work the list off and try again
+      part_sync();               // (the group's codes are in the page)
+      list_flush(ENC5_LIST);
+      if (redo) redo = list_add(hs, redo, packed, ch);
+      part_sync();
+      tried = df->cnt;
+    }
+  };
+
+  Item nxt;
+  advance(nxt);
+  if (nxt.live && rows_aligned) fetch(nxt);
+  int n_in = 0;  // groups staged so far
+  while (nxt.live) {
+    const Item cur = nxt;
+    const int sb = n_in & 1;
+    stage_in(cur, sb);
+    advance(nxt);
+    if (nxt.live && rows_aligned) fetch(nxt);
+    if (n_in > 0) stage_out(sb ^ 1, (unsigned)(((n_in - 1) >> 1) & 1));
+    ++n_in;
   }
+  if (n_in > 0) stage_out((n_in - 1) & 1, (unsigned)(((n_in - 1) >> 1) & 1));
+  part_sync();  // the last group's codes are in the page
+  list_flush(min(df->cnt, ENC5_LIST));
+
   // ... and the same warp gives the tensor memory back
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -1432,9 +1573,10 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, ENC5_SMEM));
       attr5_set[device & 15] = true;
     }
+    const int ctas5 = (int)std::min<long>((total + ENC5_PARTS - 1) / ENC5_PARTS, (long)sm_count);
     auto values = [&](const EncodeArgs& av) {
       if (tc5)
-        encode_values_tc5_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENC5_SMEM, st>>>(av);
+        encode_values_tc5_kernel<DT><<<ctas5, ENC5_PARTS * TQ_D, ENC5_SMEM, st>>>(av);
       else
         encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(av);
     };
