@@ -314,9 +314,11 @@ int32_t tq_status(tq_ctx* ctx, int32_t* flags, void* stream);
 /* Chooses, for the whole process, the kernel that rotates and quantises values (and, in
  * TQ_KEYS_POLAR mode, keys) on tq_append — both implement PolarQuant.encode (core.py) and
  * write identical pages:
- *   0  (default) the rotation on warp-level mma.sync instructions;
- *   1  the rotation on tcgen05.mma with the accumulators in tensor memory.  Its wait for the
- *      products is bounded; if it runs out, bit 1 of the status word is set.
+ *   1  (default) the rotation on tcgen05.mma with the accumulators in tensor memory, one CTA
+ *      per SM.  Its waits for the products are bounded; if one runs out, bit 1 of the status
+ *      word is set.
+ *   0  the rotation on warp-level mma.sync instructions;
+ *  -1  back to the default.
  * Not part of the reference's interface: a switch for measurements and tests. */
 int32_t tq_set_value_encoder(int32_t kind);
 

@@ -293,9 +293,10 @@ def test_rows_off_the_16_byte_grid_encode_the_same(torch_cuda, dt):
 @pytest.mark.parametrize("aligned", [True, False])
 def test_value_encoder_on_tcgen05_writes_the_same_pages(torch_cuda, dt, vb, key_mode, aligned):
     """The value encoder whose rotation runs on tcgen05.mma (accumulators in tensor memory)
-    writes, bit for bit, the pages of the default encoder (itself checked against the oracle
-    and the golden fixtures above), for every element type, code width and row alignment, and
-    for keys in PolarQuant form."""
+    (the default; checked against the oracle and the golden fixtures by every other test of
+    this file) and the one on mma.sync write the same pages, bit for bit, for every element
+    type, code width and row alignment, and for keys in PolarQuant form; the tokens include
+    all-zero rows, whose products sit on a code boundary in every channel."""
     torch = torch_cuda
     from turboquant_pro_b200._lib import load
     from turboquant_pro_b200.synth import make_kv
@@ -334,7 +335,7 @@ def test_value_encoder_on_tcgen05_writes_the_same_pages(torch_cuda, dt, vb, key_
             assert nb >= 2
             blocks.append([ctx.export_block(0, 0, i) for i in range(nb)])
     finally:
-        lib.tq_set_value_encoder(0)
+        assert lib.tq_set_value_encoder(-1) == 0
     assert lib.tq_set_value_encoder(2) != 0
     assert len(blocks[0]) == len(blocks[1])
     if key_mode != "polar" and aligned:
@@ -350,6 +351,38 @@ def test_value_encoder_on_tcgen05_writes_the_same_pages(torch_cuda, dt, vb, key_
                 assert b[name] is None
             else:
                 assert np.array_equal(np.asarray(a[name]), np.asarray(b[name])), name
+
+
+@pytest.mark.parametrize("vb", [3, 4])
+def test_value_encoders_agree_on_many_groups_per_cta(torch_cuda, vb):
+    """A flush of 3 584 groups of 16 tokens (more than four per 128-thread part of the tcgen05
+    encoder, so that its pipeline of three groups in flight runs full and drains) gives the
+    pages of the mma.sync encoder bit for bit, in every block of every sequence and head."""
+    torch = torch_cuda
+    from turboquant_pro_b200._lib import load
+
+    lib = load()
+    b, h, n = 2, 8, 4200
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    k = torch.randn((b, n, h, 128), generator=gen, device="cuda").half()
+    v = torch.randn((b, n, h, 128), generator=gen, device="cuda").half()
+    blocks = []
+    try:
+        for kind in (0, 1):
+            assert lib.tq_set_value_encoder(kind) == 0
+            ctx = _ctx(n_layers=1, n_seqs=b, n_kv_heads=h, n_q_heads=h, value_bits=vb,
+                       hot_window=512, max_tokens_per_seq=n + 8, kv_dtype="float16", seed=6)
+            ctx.append(0, k, v)
+            assert ctx.status() == 0
+            nb = ctx.lengths(0, 0)[1] // 256
+            assert nb >= 14
+            blocks.append([ctx.export_block(0, s, i) for s in range(b) for i in range(nb)])
+    finally:
+        assert lib.tq_set_value_encoder(-1) == 0
+    for x, y in zip(*blocks):
+        for name in ("value_indices", "value_norms", "key_indices"):
+            assert np.array_equal(np.asarray(x[name]), np.asarray(y[name])), name
 
 
 def test_batched_layers_ragged(torch_cuda):

@@ -216,12 +216,25 @@ __global__ void __launch_bounds__(WARPS * 32) decode_generic_kernel(DecodeArgs a
         PageMeta pm = a.page_meta[unit_index(g, a.layer, seq, head) * g.max_blocks + pg];
         const uint32_t* ent =
             a.pool_dec + unit_index(g, a.layer, seq, head) * (size_t)g.pool_entries + pm.off;
+        // The entries are ordered by token, then channel.  The thread that holds a token's first
+        // entry adds up all of them in that order, so the sum does not depend on which thread
+        // ran first (a float atomic per entry would).
         for (uint32_t e = tid; e < pm.cnt; e += WARPS * 32) {
-          uint32_t wv = ent[e];
-          float delta = __half2float(__ushort_as_half((unsigned short)(wv & 0xffff)));
-          int col = (wv >> 16) & 255, tk = wv >> 24;
+          const int tk = (int)(ent[e] >> 24);
+          if (e > 0 && (int)(ent[e - 1] >> 24) == tk) continue;
+          float acc[GT];
 #pragma unroll
-          for (int gg = 0; gg < GT; ++gg) atomicAdd(&corr_s[gg][tk], q_s[gg][col] * delta);
+          for (int gg = 0; gg < GT; ++gg) acc[gg] = 0.0f;
+          for (uint32_t j = e; j < pm.cnt; ++j) {
+            const uint32_t wv = ent[j];
+            if ((int)(wv >> 24) != tk) break;
+            const float delta = __half2float(__ushort_as_half((unsigned short)(wv & 0xffff)));
+            const int col = (wv >> 16) & 255;
+#pragma unroll
+            for (int gg = 0; gg < GT; ++gg) acc[gg] += q_s[gg][col] * delta;
+          }
+#pragma unroll
+          for (int gg = 0; gg < GT; ++gg) corr_s[gg][tk] = acc[gg];
         }
       }
       __syncthreads();

@@ -981,18 +981,27 @@ __global__ void __launch_bounds__(ENCV_HALVES* TQ_D, 2) encode_values_kernel(Enc
 
 // ---------------------------------------------------------------------------------------
 // The same value encoder with the rotation on the fifth-generation tensor cores: both operands
-// of Y^T = Pi . U^T live in shared memory anyway, so the products are issued by one thread per
-// half as tcgen05.mma instructions (M = 128 channels, N = 16 tokens, K = 16 per instruction)
-// with the accumulators in tensor memory, and every thread reads back the 16 tokens of its own
-// channel with tcgen05.ld.  Operand split, slack and exact recomputation are those of the
-// kernel above; only the rotation and the ownership of the results (a thread owns a channel)
-// differ.
+// of Y^T = Pi . U^T live in shared memory, so the products are issued by one thread as
+// tcgen05.mma instructions (M = 128 channels, N = 16 tokens, K = 16 per instruction) with the
+// accumulators in tensor memory, and every thread reads back the 16 tokens of its own channel
+// with tcgen05.ld.  Operand split and slack are those of the kernel above.
 //
 // Shared-memory operands are K-major without swizzling: 8 x 8 core matrices of 16-bit values
 // (8 rows of 16 bytes, 128 bytes each), "stride" 128 bytes to the next eight rows and
 // "leading" offset to the core matrix of the next eight input channels.  Pi (hi and lo parts)
-// is laid out once per CTA, the unit vectors per group.  Tensor memory: 64 columns per CTA,
-// 32 per half (16 for the hi*hi sum, 16 for the cross terms).  All waits are bounded.
+// is laid out once per CTA, the unit vectors per group.
+//
+// One CTA per SM: ENC5_PARTS independent parts of 128 threads share the copy of Pi.  A part
+// has three groups in flight: while the tensor cores rotate group i + 1 (into the other half
+// of the part's 64 columns of tensor memory) and the rows of group i + 2 are on their way
+// from global memory, its threads turn the products of group i into codes.
+//
+// A product that lies within the slack of a boundary is not recomputed on the spot: the part
+// puts (row, destination, norm, channel, token, code) on a list, and the list is worked off
+// when the part has run out of groups (or the list is full): a thread per entry computes the
+// exact sum in the reference's order and, where the code differs, flips the bits of the code in
+// the page.  The main loop then has three barriers per group and no serial tail.  All waits
+// are bounded.
 // ---------------------------------------------------------------------------------------
 TQ_DEV uint32_t enc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 TQ_DEV uint64_t umma_desc_k_major(uint32_t saddr, uint32_t leading_bytes, uint32_t stride_bytes) {
@@ -1014,61 +1023,48 @@ TQ_DEV void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
-TQ_DEV void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
+TQ_DEV void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// One CTA per SM: four independent parts of 128 threads share one copy of Pi.  A part works
-// on two 16-token groups at a time: while the tensor cores rotate group i + 1 and the rows of
-// group i + 2 are on their way from global memory, its threads turn the products of group i
-// into codes.
-//
-// A product that lies within the slack of a boundary is not recomputed on the spot: the part
-// puts (row, destination, norm, channel, token, code) on a list, and the list is worked off
-// when the part has run out of groups (or the list is full): a thread per entry computes the
-// exact sum in the reference's order and, where the code differs, flips the bits of the code in
-// the page.
-// The main loop then has three barriers per group and no serial tail.
-constexpr int ENC5_PARTS = 4;
+#ifndef TQ_ENC5_PARTS
+#define TQ_ENC5_PARTS 6
+#endif
+constexpr int ENC5_PARTS = TQ_ENC5_PARTS;
 constexpr int ENC5_LIST = 160;  // entries of a part's list
-struct Enc5Stage {
-  float xs[TQ_GROUP_TOK][ENCV_XS];  // the group's rows
-  // unit vectors as tensor-core operands, hi then lo part: [K / 8][2 token groups][8][8] fp16;
-  // once the rotation is done the area holds the list, codes and products of the recomputation
-  __align__(16) __half ub[2][TQ_GROUP_TOK * TQ_D];
-  uint32_t img[256];
-  float norm[TQ_GROUP_TOK];
-  unsigned long long bar;  // "this stage's products are done"
-  const void* rowp[TQ_GROUP_TOK];  // where each token's row came from (null: padding)
+struct Enc5Info {                 // what the later phases need to know about a group
+  const void* rowp[TQ_GROUP_TOK];  // where each token's row comes from (null: padding)
   uint32_t* dst;                   // the group's codes in the page
-  int pad_[2];
+  float* nrm_dst;                  // the group's norms in the page
+  float norm[TQ_GROUP_TOK];
 };
 struct Enc5Part {
-  Enc5Stage st[2];
-};
-struct Enc5List {
-  const void* row[ENC5_LIST];
-  uint32_t* dst[ENC5_LIST];
-  float norm[ENC5_LIST];
-  uint32_t meta[ENC5_LIST];  // channel | token << 8 | code << 12
-  int cnt;                   // appends tried (may exceed the capacity)
+  float xs[TQ_GROUP_TOK][ENCV_XS];  // the rows of the group being staged
+  // its unit vectors as tensor-core operands, hi then lo part: [K / 8][2 token groups][8][8]
+  __align__(16) __half ub[2][TQ_GROUP_TOK * TQ_D];
+  uint32_t img[256];              // the codes of the group being packed
+  Enc5Info info[3];               // group m uses info[m % 3]
+  unsigned long long bar[2];      // "the products of group m are done": bar[m & 1]
+  const void* l_row[ENC5_LIST];   // the list
+  uint32_t* l_dst[ENC5_LIST];
+  float l_norm[ENC5_LIST];
+  uint32_t l_meta[ENC5_LIST];     // channel | token << 8 | code << 12
+  int l_cnt;                      // appends tried (may exceed the capacity)
   int pad_[3];
 };
-static_assert(sizeof(Enc5Stage) % 16 == 0 && sizeof(Enc5List) % 16 == 0, "16-byte operands");
-constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENC5_PARTS * (int)(sizeof(Enc5Part) + sizeof(Enc5List)) +
-                          128 + 16;
+static_assert(sizeof(Enc5Part) % 16 == 0, "16-byte operands");
+constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENC5_PARTS * (int)sizeof(Enc5Part) + 128 + 16;
 static_assert(ENC5_SMEM <= 227 * 1024, "shared memory of one CTA");
-constexpr int ENC5_TMEM_COLS = 256;  // 4 parts x 2 stages x (16 + 16) columns
-constexpr int ENC5_WAIT = 1 << 16;   // probes of the product barrier before a wait gives up
+constexpr int ENC5_TMEM_COLS = ENC5_PARTS * 64 <= 256 ? 256 : 512;  // (a power of two)
+static_assert(ENC5_PARTS * 64 <= ENC5_TMEM_COLS, "tensor memory of one SM");
+constexpr int ENC5_WAIT = 1 << 16;  // probes of a product barrier before a wait gives up
 
 template <int DT>
 __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(EncodeArgs a) {
@@ -1086,10 +1082,7 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   extern __shared__ __align__(128) uint8_t enc5_smem[];
   __half* pa = (__half*)enc5_smem;  // Pi: [hi | lo][K / 8][M / 8][8][8] fp16
   Enc5Part* ps = (Enc5Part*)(enc5_smem + ENCV_PI_BYTES) + part;
-  Enc5List* df =
-      (Enc5List*)(enc5_smem + ENCV_PI_BYTES + ENC5_PARTS * sizeof(Enc5Part)) + part;
-  float* s_bnd =
-      (float*)(enc5_smem + ENCV_PI_BYTES + ENC5_PARTS * (sizeof(Enc5Part) + sizeof(Enc5List)));
+  float* s_bnd = (float*)(enc5_smem + ENCV_PI_BYTES + ENC5_PARTS * sizeof(Enc5Part));
   uint32_t* s_tmem = (uint32_t*)(s_bnd + 32);
   auto part_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + part), "n"(TQ_D) : "memory"); };
   const float* pi_rows = a.tables->pi;  // pi[ch][d]
@@ -1118,9 +1111,9 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   if (threadIdx.x < 16) s_bnd[1 + threadIdx.x] = a.tables->boundaries[threadIdx.x];
   if (threadIdx.x == 16) s_bnd[0] = -INFINITY;
   if (threadIdx.x == 17) s_bnd[17] = INFINITY;
-  if (e == 2) df->cnt = 0;
+  if (e == 2) ps->l_cnt = 0;
   if (e < 2) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(enc_smem(&ps->st[e].bar)), "r"(1)
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(enc_smem(&ps->bar[e])), "r"(1)
                  : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1137,21 +1130,40 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *(volatile uint32_t*)s_tmem + (uint32_t)(part * 64);  // this part's columns
   const uint32_t pa_addr = enc_smem(pa);
+  const uint32_t ub_addr = enc_smem(&ps->ub[0][0]);
+
+  bool gave_up = false;
+  // bounded wait for the products of group m
+  auto wait_products = [&](int m) {
+    if (gave_up) return;
+    const uint32_t bar = enc_smem(&ps->bar[m & 1]);
+    const unsigned parity = (unsigned)((m >> 1) & 1);
+    int n = 0;
+    unsigned done = 0;
+    while (!done) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}\n"
+          : "=r"(done)
+          : "r"(bar), "r"(parity)
+          : "memory");
+      if (!done && ++n >= ENC5_WAIT) {
+        atomicOr(a.status, TQ_STATUS_WAIT_TIMEOUT);
+        gave_up = true;  // (no later wait of this thread probes again)
+        break;
+      }
+    }
+  };
 
   // the groups of this part, in order; a group whose block this call does not flush is skipped
-  struct Item {
-    bool live;
-    int gq, lim, n0, pos0, ring0, cap;
-    const T* ring;
-    const T* in;
-    int64_t tok_stride;
-    uint8_t* page;
-  };
   int w_next = blockIdx.x * ENC5_PARTS + part;
   const int w_step = gridDim.x * ENC5_PARTS;
   int seq_known = -1, n0_known = 0;  // (consecutive groups mostly belong to one sequence)
-  auto advance = [&](Item& it) {
-    it.live = false;
+  uint4 raw[NCH];                    // this thread's 16-byte pieces of the next group's rows
+  int lim_raw = 0;                   // ... and how many of its tokens lie inside the block
+  // finds group m, notes what the later phases need in info[m % 3] and starts the loads of its
+  // rows; false when the part has run out of groups
+  auto advance = [&](int m) -> bool {
     while (w_next < total) {
       const int w = w_next;
       w_next += w_step;
@@ -1171,74 +1183,73 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       const int blk = nb0 + jb;
       if (blk >= nb1) continue;
       const TokenSource<DT> src = make_source<DT>(a, ring_base, in_base, seq, head, n0);
-      it.live = true;
-      it.gq = gq;
-      it.lim = S - gq * TQ_GROUP_TOK;  // tokens of the group inside the block
-      it.n0 = n0;
-      it.pos0 = blk * S + gq * TQ_GROUP_TOK;
-      it.cap = src.cap;
-      it.ring0 = it.pos0 % src.cap;
-      it.ring = (const T*)src.ring;
-      it.in = (const T*)src.in;
-      it.tok_stride = src.tok_stride;
-      it.page = a.pages + page_offset(g, a.layer, seq, head, blk);
-      return;
-    }
-  };
-  auto row_of = [&](const Item& it, int t) -> const T* {  // token t of the group (clamped)
-    const int te = min(t, it.lim - 1);
-    const int pos = it.pos0 + te;
-    int ri = it.ring0 + te;
-    ri -= ri >= it.cap ? it.cap : 0;
-    return pos < it.n0 ? it.ring + (size_t)ri * TQ_D : it.in + (size_t)(pos - it.n0) * it.tok_stride;
-  };
-  uint4 raw[NCH];
-  auto fetch = [&](const Item& it) {  // this thread's 16-byte pieces of the group's rows
+      const int lim = S - gq * TQ_GROUP_TOK;  // tokens of the group inside the block
+      lim_raw = lim;
+      const int pos0 = blk * S + gq * TQ_GROUP_TOK, ring0 = pos0 % src.cap;
+      auto row_of = [&](int t) -> const T* {  // token t of the group (clamped)
+        const int te = min(t, lim - 1);
+        const int pos = pos0 + te;
+        int ri = ring0 + te;
+        ri -= ri >= src.cap ? src.cap : 0;
+        return pos < n0 ? (const T*)src.ring + (size_t)ri * TQ_D
+                        : (const T*)src.in + (size_t)(pos - n0) * src.tok_stride;
+      };
+      if (rows_aligned) {
 #pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-      const int id = e + TQ_D * i;
-      raw[i] = *(const uint4*)(row_of(it, id / CH) + (id % CH) * EPC);
+        for (int i = 0; i < NCH; ++i) {
+          const int id = e + TQ_D * i;
+          raw[i] = *(const uint4*)(row_of(id / CH) + (id % CH) * EPC);
+        }
+      }
+      Enc5Info* nf = &ps->info[m % 3];
+      uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
+      if (e < TQ_GROUP_TOK) nf->rowp[e] = e < lim ? (const void*)row_of(e) : nullptr;
+      if (e == TQ_GROUP_TOK) {
+        nf->dst = (uint32_t*)(page + out_off + (size_t)gq * v_group_bytes(vb));
+        nf->nrm_dst = (float*)(page + nrm_off) + gq * TQ_GROUP_TOK;
+      }
+      return true;
     }
+    return false;
   };
-  bool gave_up = false;
 
-  // stage `sb` <- the group `it` (rows in `raw` if the rows are aligned): rows, norms, unit
-  // vectors, and the products started
-  auto stage_in = [&](const Item& it, int sb) {
-    Enc5Stage* hs = &ps->st[sb];
+  // group m (rows in `raw` if the rows are aligned): rows, norms, unit vectors, and the
+  // products started
+  auto stage_in = [&](int m) {
+    Enc5Info* nf = &ps->info[m % 3];
     if (rows_aligned) {
 #pragma unroll
       for (int i = 0; i < NCH; ++i) {
         const int id = e + TQ_D * i, t = id / CH, c0 = (id % CH) * EPC;
-        const bool live = t < it.lim;
+        const bool live = t < lim_raw;
         const T* pv = (const T*)&raw[i];
         float f[EPC];
 #pragma unroll
         for (int k = 0; k < EPC; ++k) f[k] = live ? Elem<DT>::ld(pv, k) : 0.0f;
 #pragma unroll
         for (int k = 0; k < EPC; k += 4)
-          *(float4*)&hs->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
+          *(float4*)&ps->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
       }
     } else {
+      part_sync();  // (the row pointers were written by other threads)
       float xv[TQ_GROUP_TOK];
 #pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t) xv[t] = Elem<DT>::ld(row_of(it, t), e);
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) {
+        const T* row = (const T*)nf->rowp[t];
+        xv[t] = row != nullptr ? Elem<DT>::ld(row, e) : 0.0f;
+      }
 #pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t) hs->xs[t][e] = t < it.lim ? xv[t] : 0.0f;
+      for (int t = 0; t < TQ_GROUP_TOK; ++t) ps->xs[t][e] = xv[t];
     }
     part_sync();
-    if (e < TQ_GROUP_TOK) hs->rowp[e] = e < it.lim ? (const void*)row_of(it, e) : nullptr;
-    if (e == TQ_GROUP_TOK)
-      hs->dst = (uint32_t*)(it.page + out_off + (size_t)it.gq * v_group_bytes(vb));
-    hs->img[e] = 0u;
-    hs->img[e + 128] = 0u;
-    {  // norms (numpy's 8-accumulator order) and the unit vectors as the B operand: element
-       // (token t, channel d) of part p at p * 4 KB + ((d / 8) * 2 + t / 8) * 128 + (t % 8) * 16
-       // + (d % 8) * 2 bytes
-      const int t = e >> 3, j = e & 7;
-      float xr[TQ_D / 8];
+    ps->img[e] = 0u;
+    ps->img[e + 128] = 0u;
+    const int t = e >> 3, j = e & 7;
+    float xr[TQ_D / 8];
+    float inv;
+    {  // norms (numpy's 8-accumulator order)
 #pragma unroll
-      for (int i = 0; i < TQ_D / 8; ++i) xr[i] = hs->xs[t][8 * i + j];
+      for (int i = 0; i < TQ_D / 8; ++i) xr[i] = ps->xs[t][8 * i + j];
       float sq = __fmul_rn(xr[0], xr[0]);
 #pragma unroll
       for (int i = 1; i < TQ_D / 8; ++i) sq = __fadd_rn(sq, __fmul_rn(xr[i], xr[i]));
@@ -1247,18 +1258,22 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, 4));
       const float nrm = __fsqrt_rn(sq);
       if (j == 0) {
-        hs->norm[t] = nrm;
-        ((float*)(it.page + nrm_off))[it.gq * TQ_GROUP_TOK + t] = nrm;
+        nf->norm[t] = nrm;
+        nf->nrm_dst[t] = nrm;
       }
-      const float inv = 1.0f / fmaxf(nrm, 1e-30f);
+      inv = 1.0f / fmaxf(nrm, 1e-30f);
+    }
+    // the operand area is read by the products of group m - 1 until they are done
+    if (m > 0) wait_products(m - 1);
+    // the unit vectors as the B operand: element (token t, channel d) of part p at
+    // p * 4 KB + ((d / 8) * 2 + t / 8) * 128 + (t % 8) * 16 + (d % 8) * 2 bytes
 #pragma unroll
-      for (int i = 0; i < TQ_D / 8; ++i) {
-        __half h, l;
-        split_h(xr[i] * inv, h, l);
-        const int off = (i * 2 + (t >> 3)) * 64 + (t & 7) * 8 + j;  // in halves
-        hs->ub[0][off] = h;
-        hs->ub[1][off] = l;
-      }
+    for (int i = 0; i < TQ_D / 8; ++i) {
+      __half h, l;
+      split_h(xr[i] * inv, h, l);
+      const int off = (i * 2 + (t >> 3)) * 64 + (t & 7) * 8 + j;  // in halves
+      ps->ub[0][off] = h;
+      ps->ub[1][off] = l;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // ... read by the tensor cores
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1266,8 +1281,7 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
     if (e == 0) {
       // hi*hi into columns 0-15, hi*lo + lo*hi into columns 16-31; eight K steps each
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t ub_addr = enc_smem(&hs->ub[0][0]);
-      const uint32_t d_main = tmem + (uint32_t)(sb * 32);
+      const uint32_t d_main = tmem + (uint32_t)((m & 1) * 32);
 #pragma unroll
       for (int kb = 0; kb < 8; ++kb) {
         const uint64_t a_hi = umma_desc_k_major(pa_addr + kb * 4096, 2048, 128);
@@ -1278,25 +1292,26 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
         umma_f16_ss(d_main + 16, a_hi, b_lo, kb > 0);
         umma_f16_ss(d_main + 16, a_lo, b_hi, 1u);
       }
-      umma_commit(enc_smem(&hs->bar));
+      umma_commit(enc_smem(&ps->bar[m & 1]));
     }
   };
 
-  // tokens `bits` of channel `ch` of the stage's group go on the list; returns the ones that
-  // did not fit
-  auto list_add = [&](const Enc5Stage* hs, unsigned bits, unsigned long long packed, int ch) {
+  // tokens `bits` (of tokens t0 .. t0 + 7) of channel `ch` of a group go on the list; returns
+  // the ones that did not fit
+  auto list_add = [&](const Enc5Info* nf, unsigned bits, uint32_t packed, int t0, int ch) {
     unsigned left = 0u;
     while (bits) {
       const int t = __ffs((int)bits) - 1;
       bits &= bits - 1;
-      const void* row = hs->rowp[t];
+      const void* row = nf->rowp[t0 + t];
       if (row == nullptr) continue;  // padding: all zeros, the products are exact
-      const int i = atomicAdd(&df->cnt, 1);
+      const int i = atomicAdd(&ps->l_cnt, 1);
       if (i < ENC5_LIST) {
-        df->row[i] = row;
-        df->dst[i] = hs->dst;
-        df->norm[i] = hs->norm[t];
-        df->meta[i] = (uint32_t)ch | ((uint32_t)t << 8) | ((uint32_t)((packed >> (4 * t)) & 15ull) << 12);
+        ps->l_row[i] = row;
+        ps->l_dst[i] = nf->dst;
+        ps->l_norm[i] = nf->norm[t0 + t];
+        ps->l_meta[i] =
+            (uint32_t)ch | ((uint32_t)(t0 + t) << 8) | (((packed >> (4 * t)) & 15u) << 12);
       } else {
         left |= 1u << t;
       }
@@ -1309,10 +1324,10 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   // thread of the part calls it.
   auto list_flush = [&](int n) {
     for (int i = e; i < n; i += TQ_D) {
-      const T* row = (const T*)df->row[i];
-      const uint32_t meta = df->meta[i];
+      const T* row = (const T*)ps->l_row[i];
+      const uint32_t meta = ps->l_meta[i];
       const int c2 = (int)(meta & 255u), t2 = (int)((meta >> 8) & 15u);
-      const float safe = fmaxf(df->norm[i], 1e-30f);
+      const float safe = fmaxf(ps->l_norm[i], 1e-30f);
       const float* pr = pi_rows + c2 * TQ_D;
       float yy = 0.0f;
 #pragma unroll 2
@@ -1344,7 +1359,7 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       if (delta) {
         const int l = v_lane(t2, c2), bit = 2 * vb * v_pair(t2, c2) + vb * (t2 & 1);
         const uint32_t v = delta << (bit & 7);
-        uint32_t* d32 = df->dst[i];
+        uint32_t* d32 = ps->l_dst[i];
         const int off0 = v_record_byte_off(vb, l, bit >> 3);
         if (v & 255u) atomicXor(&d32[off0 >> 2], (v & 255u) << ((off0 & 3) * 8));
         if (v >> 8) {
@@ -1354,80 +1369,60 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       }
     }
     part_sync();
-    if (e == 0) df->cnt = 0;
+    if (e == 0) ps->l_cnt = 0;
     part_sync();
   };
 
-  // stage `sb` -> the page: codes of the group whose products were started at the stage's
-  // previous use
-  auto stage_out = [&](int sb, unsigned parity) {
-    Enc5Stage* hs = &ps->st[sb];
-    if (!gave_up) {  // bounded wait for the products
-      const uint32_t bar = enc_smem(&hs->bar);
-      int n = 0;
-      unsigned done = 0;
-      while (!done) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (!done && ++n >= ENC5_WAIT) {
-          atomicOr(a.status, TQ_STATUS_WAIT_TIMEOUT);
-          gave_up = true;  // (no later wait of this thread probes again)
-          break;
-        }
-      }
-    }
+  // group m: products -> codes -> the page
+  auto stage_out = [&](int m) {
+    const Enc5Info* nf = &ps->info[m % 3];
+    wait_products(m);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float y[TQ_GROUP_TOK];
-    {
-      float cx[TQ_GROUP_TOK];
-      const uint32_t taddr = tmem + (uint32_t)(sb * 32) + ((uint32_t)(32 * wq) << 16);
-      tmem_ld16(taddr, y);
-      tmem_ld16(taddr + 16, cx);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t) y[t] = fmaf(cx[t], 1.0f / 2048.0f, y[t]);
-    }
-    // thread e owns channel e: codes of its 16 tokens by bisection, exact recomputation where a
-    // boundary lies within the slack
+    // thread e owns channel e: codes of its 16 tokens, eight at a time, by bisection; a token
+    // whose product lies within the slack of a boundary goes on the list
     const int ch = 32 * wq + lane;
-    int code[TQ_GROUP_TOK];
-#pragma unroll
-    for (int t = 0; t < TQ_GROUP_TOK; ++t) code[t] = 0;
-    for (int step = (n_bnd + 1) >> 1; step > 0; step >>= 1) {
-#pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t)
-        code[t] += (s_bnd[code[t] + step] < y[t]) ? step : 0;
-    }
-    unsigned redo = 0u;
-#pragma unroll
-    for (int t = 0; t < TQ_GROUP_TOK; ++t) {
-      const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
-      redo |= (y[t] - below < ROT_SLACK || above - y[t] < ROT_SLACK) ? (1u << t) : 0u;
-    }
-    unsigned long long packed = 0ull;  // the codes as computed, for the list
-    if (redo) {
-#pragma unroll
-      for (int t = 0; t < TQ_GROUP_TOK; ++t) packed |= (unsigned long long)code[t] << (4 * t);
-      redo = list_add(hs, redo, packed, ch);
-    }
-    // pack this channel's 8 token pairs into the group image
-    uint32_t* img = hs->img;
     const int dq = ch & 7, i16 = ch >> 3;  // record lane group and slot of this thread's channel
+    uint32_t* img = ps->img;
+    unsigned redo[2];
+    uint32_t packed[2];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int h = 0; h < 2; ++h) {
+      float y[8];
+      {
+        float cx[8];
+        const uint32_t taddr =
+            tmem + (uint32_t)((m & 1) * 32 + 8 * h) + ((uint32_t)(32 * wq) << 16);
+        tmem_ld8(taddr, y);
+        tmem_ld8(taddr + 16, cx);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int ta = 2 * c + 8 * h;
+        for (int t = 0; t < 8; ++t) y[t] = fmaf(cx[t], 1.0f / 2048.0f, y[t]);
+      }
+      int code[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) code[t] = 0;
+      for (int step = (n_bnd + 1) >> 1; step > 0; step >>= 1) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) code[t] += (s_bnd[code[t] + step] < y[t]) ? step : 0;
+      }
+      unsigned rd = 0u;
+      uint32_t pk = 0u;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
+        rd |= (y[t] - below < ROT_SLACK || above - y[t] < ROT_SLACK) ? (1u << t) : 0u;
+        pk |= (uint32_t)code[t] << (4 * t);
+      }
+      packed[h] = pk;
+      redo[h] = rd ? list_add(nf, rd, pk, 8 * h, ch) : 0u;
+      // this channel's 4 token pairs into the group image
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         const int l = dq * 4 + c, p = 2 * i16 + h;
         if (vb == 4) {
-          ((uint8_t*)img)[v_record_byte_off(4, l, p)] = (uint8_t)(code[ta] | (code[ta + 1] << 4));
+          ((uint8_t*)img)[v_record_byte_off(4, l, p)] = (uint8_t)((pk >> (8 * c)) & 255u);
         } else {
-          const uint32_t f = (uint32_t)(code[ta] | (code[ta + 1] << 3));
+          const uint32_t f = (uint32_t)(code[2 * c] | (code[2 * c + 1] << 3));
           const int bit = 6 * p, wd = bit >> 5, sh = bit & 31;
           atomicOr(&img[((wd >> 1) * 256 + l * 8 + (wd & 1) * 4) >> 2], f << sh);
           if (sh > 26)
@@ -1436,37 +1431,43 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
         }
       }
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     part_sync();
-    uint32_t* dst = hs->dst;
+    uint32_t* dst = nf->dst;
     const int words = v_group_bytes(vb) / 4;
     for (int i = e; i < words; i += TQ_D) dst[i] = img[i];
-    // (the image is zeroed again after the first barrier of the stage's next use)
-    int tried = df->cnt;  // the same for every thread: nobody appends before the next group
+    // (the image is zeroed again after the first barrier of the next group's staging)
+    int tried = ps->l_cnt;  // the same for every thread: nobody appends before the next group
     while (tried > ENC5_LIST) {  // some entries did not fit: work the list off and try again
       part_sync();               // (the group's codes are in the page)
       list_flush(ENC5_LIST);
-      if (redo) redo = list_add(hs, redo, packed, ch);
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        if (redo[h]) redo[h] = list_add(nf, redo[h], packed[h], 8 * h, ch);
       part_sync();
-      tried = df->cnt;
+      tried = ps->l_cnt;
     }
   };
 
-  Item nxt;
-  advance(nxt);
-  if (nxt.live && rows_aligned) fetch(nxt);
-  int n_in = 0;  // groups staged so far
-  while (nxt.live) {
-    const Item cur = nxt;
-    const int sb = n_in & 1;
-    stage_in(cur, sb);
-    advance(nxt);
-    if (nxt.live && rows_aligned) fetch(nxt);
-    if (n_in > 0) stage_out(sb ^ 1, (unsigned)(((n_in - 1) >> 1) & 1));
-    ++n_in;
+  int m = 0;  // groups staged so far
+  bool more = advance(0);
+  while (more) {
+    stage_in(m);
+    more = advance(m + 1);
+    if (m > 0) stage_out(m - 1);
+    ++m;
   }
-  if (n_in > 0) stage_out((n_in - 1) & 1, (unsigned)(((n_in - 1) >> 1) & 1));
+  if (m > 0) {
+    if (m > 1) {  // (the image still holds the codes of group m - 2)
+      part_sync();
+      ps->img[e] = 0u;
+      ps->img[e + 128] = 0u;
+      part_sync();
+    }
+    stage_out(m - 1);
+  }
   part_sync();  // the last group's codes are in the page
-  list_flush(min(df->cnt, ENC5_LIST));
+  list_flush(min(ps->l_cnt, ENC5_LIST));
 
   // ... and the same warp gives the tensor memory back
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1535,7 +1536,8 @@ __global__ void clear_kernel(int32_t* seq_len, uint32_t* cursor, int layer, int 
     cursor[((size_t)layer * n_seqs + seq_begin) * n_heads + i] = 0u;
 }
 
-int g_value_encoder = 0;  // 0: rotation on mma.sync; 1: on tcgen05.mma (tq_set_value_encoder)
+constexpr int VALUE_ENCODER_DEFAULT = 1;
+int g_value_encoder = VALUE_ENCODER_DEFAULT;  // 0: rotation on mma.sync; 1: on tcgen05.mma
 
 template <int DT>
 int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t st, int* launches) {
@@ -1607,8 +1609,9 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
 }  // namespace
 
 extern "C" int32_t tq_set_value_encoder(int32_t kind) {
-  TQ_REQUIRE(kind == 0 || kind == 1, TQ_ERR_INVALID, "value encoder: 0 (mma.sync) or 1 (tcgen05)");
-  g_value_encoder = kind;
+  TQ_REQUIRE(kind >= -1 && kind <= 1, TQ_ERR_INVALID,
+             "value encoder: 0 (mma.sync), 1 (tcgen05) or -1 (the default)");
+  g_value_encoder = kind < 0 ? VALUE_ENCODER_DEFAULT : kind;
   return TQ_OK;
 }
 
