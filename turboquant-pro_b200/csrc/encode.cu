@@ -1060,7 +1060,7 @@ struct Enc5Part {
   int pad_[3];
 };
 static_assert(sizeof(Enc5Part) % 16 == 0, "16-byte operands");
-constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENC5_PARTS * (int)sizeof(Enc5Part) + 128 + 16;
+constexpr int ENC5_SMEM = ENCV_PI_BYTES + ENC5_PARTS * (int)sizeof(Enc5Part) + 320;
 static_assert(ENC5_SMEM <= 227 * 1024, "shared memory of one CTA");
 constexpr int ENC5_TMEM_COLS = ENC5_PARTS * 64 <= 256 ? 256 : 512;  // (a power of two)
 static_assert(ENC5_PARTS * 64 <= ENC5_TMEM_COLS, "tensor memory of one SM");
@@ -1083,7 +1083,8 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   __half* pa = (__half*)enc5_smem;  // Pi: [hi | lo][K / 8][M / 8][8][8] fp16
   Enc5Part* ps = (Enc5Part*)(enc5_smem + ENCV_PI_BYTES) + part;
   float* s_bnd = (float*)(enc5_smem + ENCV_PI_BYTES + ENC5_PARTS * sizeof(Enc5Part));
-  uint32_t* s_tmem = (uint32_t*)(s_bnd + 32);
+  float2* s_bp = (float2*)(s_bnd + 32);  // (boundary below, boundary above) of each code
+  uint32_t* s_tmem = (uint32_t*)(s_bp + 18);
   auto part_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + part), "n"(TQ_D) : "memory"); };
   const float* pi_rows = a.tables->pi;  // pi[ch][d]
   const bool keys = a.polar_keys_pass != 0;
@@ -1111,6 +1112,18 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   if (threadIdx.x < 16) s_bnd[1 + threadIdx.x] = a.tables->boundaries[threadIdx.x];
   if (threadIdx.x == 16) s_bnd[0] = -INFINITY;
   if (threadIdx.x == 17) s_bnd[17] = INFINITY;
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + 17) {
+    const int c = threadIdx.x - 32;  // code c lies between boundaries c - 1 and c
+    s_bp[c] = make_float2(c == 0 ? -INFINITY : a.tables->boundaries[c - 1],
+                          c == 16 ? INFINITY : a.tables->boundaries[c]);
+  }
+  int* s_step = (int*)(s_tmem + 1);  // the distance between a part's groups, as four indices
+  if (threadIdx.x == 18) {
+    int w = gridDim.x * ENC5_PARTS;
+    s_step[0] = w % groups, w /= groups;
+    s_step[1] = w % a.max_new_blocks, w /= a.max_new_blocks;
+    s_step[2] = w % g.n_kv_heads, s_step[3] = w / g.n_kv_heads;
+  }
   if (e == 2) ps->l_cnt = 0;
   if (e < 2) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(enc_smem(&ps->bar[e])), "r"(1)
@@ -1155,37 +1168,56 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
     }
   };
 
-  // the groups of this part, in order; a group whose block this call does not flush is skipped
-  int w_next = blockIdx.x * ENC5_PARTS + part;
-  const int w_step = gridDim.x * ENC5_PARTS;
-  int seq_known = -1, n0_known = 0;  // (consecutive groups mostly belong to one sequence)
+  // the groups of this part, in order: group number w = ((seq * heads + head) * blocks + jb) *
+  // groups + gq, w = first, first + step, ...; the four indices are kept and stepped with
+  // carries (no division per group); a group whose block this call does not flush is skipped
+  int gq_n, jb_n, head_n, seq_n;       // the next candidate (seq_n counts from seq_begin)
+  // (the step, in the same mixed radix, is s_step)
+  {
+    int w = blockIdx.x * ENC5_PARTS + part;
+    gq_n = w % groups, w /= groups;
+    jb_n = w % a.max_new_blocks, w /= a.max_new_blocks;
+    head_n = w % g.n_kv_heads, seq_n = w / g.n_kv_heads;
+  }
+  int seq_known = -1, n0_known = 0, nb0_known = 0, nb1_known = 0, r0_known = 0;  // per sequence
   uint4 raw[NCH];                    // this thread's 16-byte pieces of the next group's rows
   int lim_raw = 0;                   // ... and how many of its tokens lie inside the block
   // finds group m, notes what the later phases need in info[m % 3] and starts the loads of its
   // rows; false when the part has run out of groups
   auto advance = [&](int m) -> bool {
-    while (w_next < total) {
-      const int w = w_next;
-      w_next += w_step;
-      const int gq = w % groups;
-      int rr = w / groups;
-      const int jb = rr % a.max_new_blocks;
-      rr /= a.max_new_blocks;
-      const int head = rr % g.n_kv_heads;
-      const int seq = a.seq_begin + rr / g.n_kv_heads;
+    while (seq_n < a.seq_count) {
+      const int gq = gq_n, jb = jb_n, head = head_n, seq = a.seq_begin + seq_n;
+      {  // step to the next candidate
+        gq_n += s_step[0];
+        int c = gq_n >= groups ? 1 : 0;
+        gq_n -= c ? groups : 0;
+        jb_n += s_step[1] + c;
+        c = jb_n >= a.max_new_blocks ? 1 : 0;
+        jb_n -= c ? a.max_new_blocks : 0;
+        head_n += s_step[2] + c;
+        c = head_n >= g.n_kv_heads ? 1 : 0;
+        head_n -= c ? g.n_kv_heads : 0;
+        seq_n += s_step[3] + c;
+      }
       if (seq != seq_known) {
         n0_known = a.seq_len[a.layer * g.n_seqs + seq];
+        nb0_known = n_cold_blocks(n0_known, g.hot_window, g.block_tokens);
+        nb1_known = n_cold_blocks(n0_known + a.n_tokens, g.hot_window, g.block_tokens);
+        r0_known = n0_known % g.hot_cap;
         seq_known = seq;
       }
       const int n0 = n0_known;
-      const int nb0 = n_cold_blocks(n0, g.hot_window, g.block_tokens);
-      const int nb1 = n_cold_blocks(n0 + a.n_tokens, g.hot_window, g.block_tokens);
-      const int blk = nb0 + jb;
-      if (blk >= nb1) continue;
+      const int blk = nb0_known + jb;
+      if (blk >= nb1_known) continue;
       const TokenSource<DT> src = make_source<DT>(a, ring_base, in_base, seq, head, n0);
       const int lim = S - gq * TQ_GROUP_TOK;  // tokens of the group inside the block
       lim_raw = lim;
-      const int pos0 = blk * S + gq * TQ_GROUP_TOK, ring0 = pos0 % src.cap;
+      const int pos0 = blk * S + gq * TQ_GROUP_TOK;
+      // ring slot of position pos0 (used for positions below n0, which lie less than the
+      // ring's capacity below it)
+      int ring0 = r0_known + (pos0 - n0);
+      ring0 += ring0 < 0 ? src.cap : 0;
+      if (ring0 < 0 || ring0 >= src.cap) ring0 = pos0 % src.cap;
       auto row_of = [&](int t) -> const T* {  // token t of the group (clamped)
         const int te = min(t, lim - 1);
         const int pos = pos0 + te;
@@ -1221,11 +1253,14 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
 #pragma unroll
       for (int i = 0; i < NCH; ++i) {
         const int id = e + TQ_D * i, t = id / CH, c0 = (id % CH) * EPC;
-        const bool live = t < lim_raw;
         const T* pv = (const T*)&raw[i];
         float f[EPC];
 #pragma unroll
-        for (int k = 0; k < EPC; ++k) f[k] = live ? Elem<DT>::ld(pv, k) : 0.0f;
+        for (int k = 0; k < EPC; ++k) f[k] = Elem<DT>::ld(pv, k);
+        if (t >= lim_raw) {  // padding (only in a block's last group)
+#pragma unroll
+          for (int k = 0; k < EPC; ++k) f[k] = 0.0f;
+        }
 #pragma unroll
         for (int k = 0; k < EPC; k += 4)
           *(float4*)&ps->xs[t][c0 + k] = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
@@ -1409,8 +1444,8 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       uint32_t pk = 0u;
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        const float below = s_bnd[code[t]], above = s_bnd[code[t] + 1];
-        rd |= (y[t] - below < ROT_SLACK || above - y[t] < ROT_SLACK) ? (1u << t) : 0u;
+        const float2 ba = s_bp[code[t]];
+        rd |= (y[t] - ba.x < ROT_SLACK || ba.y - y[t] < ROT_SLACK) ? (1u << t) : 0u;
         pk |= (uint32_t)code[t] << (4 * t);
       }
       packed[h] = pk;
