@@ -1317,12 +1317,19 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       // hi*hi into columns 0-15, hi*lo + lo*hi into columns 16-31; eight K steps each
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t d_main = tmem + (uint32_t)((m & 1) * 32);
+      // the descriptors of K step kb are those of step 0 with the start address (in 16-byte
+      // units, the low 14 bits; shared memory ends below 2^18) moved on by 4 KB (Pi) or 512
+      // bytes (unit vectors)
+      const uint64_t a_hi0 = umma_desc_k_major(pa_addr, 2048, 128);
+      const uint64_t a_lo0 = umma_desc_k_major(pa_addr + TQ_D * TQ_D * 2, 2048, 128);
+      const uint64_t b_hi0 = umma_desc_k_major(ub_addr, 256, 128);
+      const uint64_t b_lo0 = umma_desc_k_major(ub_addr + TQ_GROUP_TOK * TQ_D * 2, 256, 128);
 #pragma unroll
       for (int kb = 0; kb < 8; ++kb) {
-        const uint64_t a_hi = umma_desc_k_major(pa_addr + kb * 4096, 2048, 128);
-        const uint64_t a_lo = umma_desc_k_major(pa_addr + TQ_D * TQ_D * 2 + kb * 4096, 2048, 128);
-        const uint64_t b_hi = umma_desc_k_major(ub_addr + kb * 512, 256, 128);
-        const uint64_t b_lo = umma_desc_k_major(ub_addr + TQ_GROUP_TOK * TQ_D * 2 + kb * 512, 256, 128);
+        const uint64_t a_hi = a_hi0 + (uint64_t)(kb * (4096 >> 4));
+        const uint64_t a_lo = a_lo0 + (uint64_t)(kb * (4096 >> 4));
+        const uint64_t b_hi = b_hi0 + (uint64_t)(kb * (512 >> 4));
+        const uint64_t b_lo = b_lo0 + (uint64_t)(kb * (512 >> 4));
         umma_f16_ss(d_main, a_hi, b_hi, kb > 0);
         umma_f16_ss(d_main + 16, a_hi, b_lo, kb > 0);
         umma_f16_ss(d_main + 16, a_lo, b_hi, 1u);
@@ -1441,12 +1448,15 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
         for (int t = 0; t < 8; ++t) code[t] += (s_bnd[code[t] + step] < y[t]) ? step : 0;
       }
       unsigned rd = 0u;
-      uint32_t pk = 0u;
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         const float2 ba = s_bp[code[t]];
         rd |= (y[t] - ba.x < ROT_SLACK || ba.y - y[t] < ROT_SLACK) ? (1u << t) : 0u;
-        pk |= (uint32_t)code[t] << (4 * t);
+      }
+      uint32_t pk = 0u;  // the codes as computed, a nibble each: for the list and the 4-bit image
+      if (vb == 4 || rd) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) pk |= (uint32_t)code[t] << (4 * t);
       }
       packed[h] = pk;
       redo[h] = rd ? list_add(nf, rd, pk, 8 * h, ch) : 0u;
