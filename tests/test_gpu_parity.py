@@ -353,11 +353,13 @@ def test_value_encoder_on_tcgen05_writes_the_same_pages(torch_cuda, dt, vb, key_
                 assert np.array_equal(np.asarray(a[name]), np.asarray(b[name])), name
 
 
-@pytest.mark.parametrize("vb", [3, 4])
-def test_value_encoders_agree_on_many_groups_per_cta(torch_cuda, vb):
-    """A flush of 3 584 groups of 16 tokens (more than four per 128-thread part of the tcgen05
-    encoder, so that its pipeline of three groups in flight runs full and drains) gives the
-    pages of the mma.sync encoder bit for bit, in every block of every sequence and head."""
+@pytest.mark.parametrize("vb,aligned", [(3, True), (4, True), (3, False)])
+def test_value_encoders_agree_on_many_groups_per_cta(torch_cuda, vb, aligned):
+    """Flushes of more than three thousand groups of 16 tokens (more than three per 128-thread
+    part of the tcgen05 encoder, so that its pipeline of three groups in flight runs full and
+    drains) give the pages of the mma.sync encoder bit for bit, in every block of every
+    sequence and head; the second call also takes rows from the hot ring, and one variant
+    hands the tokens over off the 16-byte grid."""
     torch = torch_cuda
     from turboquant_pro_b200._lib import load
 
@@ -367,13 +369,20 @@ def test_value_encoders_agree_on_many_groups_per_cta(torch_cuda, vb):
     gen.manual_seed(11)
     k = torch.randn((b, n, h, 128), generator=gen, device="cuda").half()
     v = torch.randn((b, n, h, 128), generator=gen, device="cuda").half()
+    if not aligned:
+        wide_k = torch.zeros((b, n, h, 129), dtype=torch.float16, device="cuda")
+        wide_v = torch.zeros((b, n, h, 129), dtype=torch.float16, device="cuda")
+        wide_k[..., 1:] = k
+        wide_v[..., 1:] = v
+        k, v = wide_k[..., 1:], wide_v[..., 1:]
     blocks = []
     try:
         for kind in (0, 1):
             assert lib.tq_set_value_encoder(kind) == 0
             ctx = _ctx(n_layers=1, n_seqs=b, n_kv_heads=h, n_q_heads=h, value_bits=vb,
                        hot_window=512, max_tokens_per_seq=n + 8, kv_dtype="float16", seed=6)
-            ctx.append(0, k, v)
+            ctx.append(0, k[:, :900], v[:, :900])
+            ctx.append(0, k[:, 900:], v[:, 900:])
             assert ctx.status() == 0
             nb = ctx.lengths(0, 0)[1] // 256
             assert nb >= 14
