@@ -1066,7 +1066,7 @@ constexpr int ENC5_TMEM_COLS = ENC5_PARTS * 64 <= 256 ? 256 : 512;  // (a power 
 static_assert(ENC5_PARTS * 64 <= ENC5_TMEM_COLS, "tensor memory of one SM");
 constexpr int ENC5_WAIT = 1 << 16;  // probes of a product barrier before a wait gives up
 
-template <int DT>
+template <int DT, int VB>
 __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(EncodeArgs a) {
   using T = typename Elem<DT>::type;
   constexpr int EPC = 16 / (int)sizeof(T), CH = TQ_D / EPC, NCH = TQ_GROUP_TOK * CH / TQ_D;
@@ -1075,8 +1075,8 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
   const int wq = e >> 5, lane = e & 31;
   const int groups = g.block_tokens_pad / TQ_GROUP_TOK;
   const int total = a.seq_count * g.n_kv_heads * a.max_new_blocks * groups;
-  const int vb = g.value_bits;
-  const int n_bnd = (1 << vb) - 1;
+  constexpr int vb = VB;  // bits of a code (the launcher picks the instance)
+  constexpr int n_bnd = (1 << vb) - 1;
   const int S = g.block_tokens;
 
   extern __shared__ __align__(128) uint8_t enc5_smem[];
@@ -1616,14 +1616,18 @@ int launch_encode_t(const EncodeArgs& a, int sm_count, int device, cudaStream_t 
     static bool attr5_set[16] = {};
     const bool tc5 = g_value_encoder == 1;
     if (tc5 && !attr5_set[device & 15]) {
-      TQ_CUDA(cudaFuncSetAttribute(encode_values_tc5_kernel<DT>,
+      TQ_CUDA(cudaFuncSetAttribute(encode_values_tc5_kernel<DT, 3>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, ENC5_SMEM));
+      TQ_CUDA(cudaFuncSetAttribute(encode_values_tc5_kernel<DT, 4>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, ENC5_SMEM));
       attr5_set[device & 15] = true;
     }
     const int ctas5 = (int)std::min<long>((total + ENC5_PARTS - 1) / ENC5_PARTS, (long)sm_count);
     auto values = [&](const EncodeArgs& av) {
-      if (tc5)
-        encode_values_tc5_kernel<DT><<<ctas5, ENC5_PARTS * TQ_D, ENC5_SMEM, st>>>(av);
+      if (tc5 && g.value_bits == 3)
+        encode_values_tc5_kernel<DT, 3><<<ctas5, ENC5_PARTS * TQ_D, ENC5_SMEM, st>>>(av);
+      else if (tc5)
+        encode_values_tc5_kernel<DT, 4><<<ctas5, ENC5_PARTS * TQ_D, ENC5_SMEM, st>>>(av);
       else
         encode_values_kernel<DT><<<ctas, ENCV_HALVES * TQ_D, ENCV_SMEM, st>>>(av);
     };
