@@ -1236,7 +1236,7 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
       Enc5Info* nf = &ps->info[m % 3];
       uint8_t* page = a.pages + page_offset(g, a.layer, seq, head, blk);
       if (e < TQ_GROUP_TOK) nf->rowp[e] = e < lim ? (const void*)row_of(e) : nullptr;
-      if (e == TQ_GROUP_TOK) {
+      if (e == 64) {
         nf->dst = (uint32_t*)(page + out_off + (size_t)gq * v_group_bytes(vb));
         nf->nrm_dst = (float*)(page + nrm_off) + gq * TQ_GROUP_TOK;
       }
@@ -1313,7 +1313,7 @@ __global__ void __launch_bounds__(ENC5_PARTS* TQ_D, 1) encode_values_tc5_kernel(
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // ... read by the tensor cores
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     part_sync();
-    if (e == 0) {
+    if (e == 32) {  // (a thread of the second warp: the first one notes the rows of the next group)
       // hi*hi into columns 0-15, hi*lo + lo*hi into columns 16-31; eight K steps each
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t d_main = tmem + (uint32_t)((m & 1) * 32);
