@@ -99,6 +99,19 @@ def test_sizes_and_null_handling(lib):
     assert lib.tq_decode(None, 0, None, 0, None, None) == -1
 
 
+def test_value_encoder_switch_checks_its_argument(lib):
+    """tq_set_value_encoder: 0 (mma.sync), 1 (tcgen05), -1 (the default); nothing else.  The
+    switch is host state, so this needs no GPU."""
+    try:
+        for kind in (0, 1, -1):
+            assert lib.tq_set_value_encoder(kind) == 0
+        for kind in (2, -2, 7):
+            assert lib.tq_set_value_encoder(kind) == -1
+            assert b"value encoder" in lib.tq_last_error()
+    finally:
+        assert lib.tq_set_value_encoder(-1) == 0
+
+
 def test_facade_refuses_cpu():
     import torch
 
